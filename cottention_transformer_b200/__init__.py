@@ -1,0 +1,6 @@
+"""cottention_transformer_b200: B200 (sm_100a) kernels for Cottention's cosine linear attention,
+behind the reference's own extension API (``FastAttention2.kernel`` / ``CustomAttention``)."""
+from . import _lib, kernel  # noqa: F401
+from .custom_kernel import CustomAttention  # noqa: F401
+
+__version__ = "0.1.0"

@@ -1,0 +1,72 @@
+"""ctypes binding of ``libcottention_b200.so`` (the C ABI declared in ``include/cottention_b200.h``).
+
+There is no fallback: if the library is missing or a call fails, a ``RuntimeError`` is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libcottention_b200.so")
+
+COTT_F32, COTT_F64, COTT_F16, COTT_BF16 = 0, 1, 2, 3
+DTYPE_CODE = {
+    torch.float32: COTT_F32,
+    torch.float64: COTT_F64,
+    torch.float16: COTT_F16,
+    torch.bfloat16: COTT_BF16,
+}
+
+_P, _I, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_long
+
+# name -> argtypes; restype is int (status) unless listed in _STR
+_SIGNATURES = {
+    "cott_scan": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "cott_scan_bwd": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+}
+_STR = {"cott_version": [], "cott_last_error": [], "cott_status_string": [_I]}
+
+_lib = None
+launch_count = 0  # kernels launched through this binding (bookkeeping for the benchmark)
+
+
+def exported_symbols() -> list[str]:
+    return sorted(list(_SIGNATURES) + list(_STR))
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} not found: build it with `python -m cottention_transformer_b200.build` "
+                "(there is no CPU or PyTorch fallback)"
+            )
+        L = ctypes.CDLL(LIB_PATH)
+        for name, args in _SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.argtypes, fn.restype = args, _I
+        for name, args in _STR.items():
+            fn = getattr(L, name)
+            fn.argtypes, fn.restype = args, ctypes.c_char_p
+        _lib = L
+    return _lib
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        L = lib()
+        raise RuntimeError(
+            f"{what}: {L.cott_status_string(status).decode()} ({status}): {L.cott_last_error().decode()}"
+        )
+
+
+def stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()

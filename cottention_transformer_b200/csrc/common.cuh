@@ -1,0 +1,64 @@
+// Shared host/device helpers for the cottention_b200 kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/cottention_b200.h"
+
+namespace cott {
+
+// ---- per-thread error text -----------------------------------------------------------------
+inline char* err_buf() {
+  static thread_local char buf[512] = {0};
+  return buf;
+}
+inline int fail(int status, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(err_buf(), 512, fmt, ap);
+  va_end(ap);
+  return status;
+}
+inline int cuda_fail(cudaError_t e, const char* what) {
+  return fail(COTT_ERR_CUDA, "%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
+}
+#define COTT_CUDA_TRY(expr)                                  \
+  do {                                                       \
+    cudaError_t _e = (expr);                                 \
+    if (_e != cudaSuccess) return ::cott::cuda_fail(_e, #expr); \
+  } while (0)
+
+inline size_t dtype_size(int dtype) {
+  switch (dtype) {
+    case COTT_F32: return 4;
+    case COTT_F64: return 8;
+    case COTT_F16: return 2;
+    case COTT_BF16: return 2;
+    default: return 0;
+  }
+}
+
+// ---- element <-> accumulator conversions ------------------------------------------------------
+template <typename T> struct AccOf { using type = float; };
+template <> struct AccOf<double> { using type = double; };
+
+__device__ __forceinline__ float to_acc(float x) { return x; }
+__device__ __forceinline__ double to_acc(double x) { return x; }
+__device__ __forceinline__ float to_acc(__half x) { return __half2float(x); }
+__device__ __forceinline__ float to_acc(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T from_acc(typename AccOf<T>::type x);
+template <> __device__ __forceinline__ float from_acc<float>(float x) { return x; }
+template <> __device__ __forceinline__ double from_acc<double>(double x) { return x; }
+template <> __device__ __forceinline__ __half from_acc<__half>(float x) { return __float2half_rn(x); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_acc<__nv_bfloat16>(float x) {
+  return __float2bfloat16_rn(x);
+}
+
+}  // namespace cott

@@ -1,0 +1,83 @@
+// C ABI of cottention_b200: argument validation and dispatch.  No torch types here;
+// the Python host (ctypes) and any other FFI bind these symbols directly.
+#include "common.cuh"
+#include "scan_simt.cuh"
+
+using namespace cott;
+
+namespace {
+
+int check_scan_args(const void* q, const void* k, const void* v, const void* out, int B, int H,
+                    int N, int Dk, int Dv, int dtype) {
+  if (dtype_size(dtype) == 0) return fail(COTT_ERR_DTYPE, "unknown dtype code %d", dtype);
+  if (B < 0 || H < 0 || N < 0) return fail(COTT_ERR_SHAPE, "negative size B=%d H=%d N=%d", B, H, N);
+  if (Dk < 16 || Dk > 256 || Dk % 16 != 0)
+    return fail(COTT_ERR_SHAPE, "D_attn must be divisible by 16 and in [16, 256] (got %d)", Dk);
+  if (Dv < 1) return fail(COTT_ERR_SHAPE, "D_value must be >= 1 (got %d)", Dv);
+  if ((long)B * H > 0x7fffffffL) return fail(COTT_ERR_SHAPE, "B*H too large");
+  if ((long)B * H * N > 0 && (!q || !k || !v || !out)) return fail(COTT_ERR_NULL, "null tensor pointer");
+  return COTT_OK;
+}
+
+int scan_dispatch(const void* q, const void* k, const void* v, void* out, int B, int H, int N,
+                  int Dk, int Dv, int dtype, int reversed, cudaStream_t stream) {
+  if ((long)B * H * N == 0) return COTT_OK;
+  switch (dtype) {
+    case COTT_F32: return launch_scan_simt<float>(q, k, v, out, B, H, N, Dk, Dv, reversed, stream);
+    case COTT_F64: return launch_scan_simt<double>(q, k, v, out, B, H, N, Dk, Dv, reversed, stream);
+    case COTT_F16: return launch_scan_simt<__half>(q, k, v, out, B, H, N, Dk, Dv, reversed, stream);
+    case COTT_BF16:
+      return launch_scan_simt<__nv_bfloat16>(q, k, v, out, B, H, N, Dk, Dv, reversed, stream);
+  }
+  return fail(COTT_ERR_DTYPE, "unknown dtype code %d", dtype);
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* cott_version(void) { return "cottention_b200 0.1.0 sm_100a"; }
+
+const char* cott_last_error(void) { return err_buf(); }
+
+const char* cott_status_string(int status) {
+  switch (status) {
+    case COTT_OK: return "ok";
+    case COTT_ERR_NULL: return "null pointer";
+    case COTT_ERR_SHAPE: return "unsupported shape";
+    case COTT_ERR_DTYPE: return "unsupported dtype";
+    case COTT_ERR_CUDA: return "CUDA error";
+    case COTT_ERR_ALIGN: return "misaligned pointer";
+    case COTT_ERR_DEVICE_WAIT: return "device-side wait gave up";
+    case COTT_ERR_UNSUPPORTED: return "unsupported request";
+    default: return "unknown status";
+  }
+}
+
+int cott_scan(const void* q, const void* k, const void* v, void* out, int B, int H, int N, int Dk,
+              int Dv, int dtype, int reversed, void* stream) {
+  int st = check_scan_args(q, k, v, out, B, H, N, Dk, Dv, dtype);
+  if (st != COTT_OK) return st;
+  return scan_dispatch(q, k, v, out, B, H, N, Dk, Dv, dtype, reversed != 0,
+                       static_cast<cudaStream_t>(stream));
+}
+
+int cott_scan_bwd(const void* q, const void* k, const void* v, const void* dout, void* dq, void* dk,
+                  void* dv, int B, int H, int N, int Dk, int Dv, int dtype, void* stream) {
+  int st = check_scan_args(q, k, v, dout, B, H, N, Dk, Dv, dtype);
+  if (st != COTT_OK) return st;
+  if (Dv < 16 || Dv > 256 || Dv % 16 != 0)
+    return fail(COTT_ERR_SHAPE, "backward needs D_value divisible by 16 and in [16, 256] (got %d)", Dv);
+  if ((long)B * H * N > 0 && (!dq || !dk || !dv)) return fail(COTT_ERR_NULL, "null gradient pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // dq = scan(dout, v, k): "Q"=dout [Dv], "K"=v [Dv], "V"=k [Dk]
+  st = scan_dispatch(dout, v, k, dq, B, H, N, Dv, Dk, dtype, 0, s);
+  if (st != COTT_OK) return st;
+  // dk = scan(v, dout, q, reversed)
+  st = scan_dispatch(v, dout, q, dk, B, H, N, Dv, Dk, dtype, 1, s);
+  if (st != COTT_OK) return st;
+  // dv = scan(k, q, dout, reversed)
+  return scan_dispatch(k, q, dout, dv, B, H, N, Dk, Dv, dtype, 1, s);
+}
+
+}  // extern "C"

@@ -1,0 +1,89 @@
+"""CPU tests of the C-ABI library: it loads and exports every symbol the header declares."""
+import ctypes
+import os
+import re
+
+import pytest
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared():
+    names = []
+    for f in sorted(os.listdir(os.path.join(REPO, "include"))):
+        if not f.endswith(".h"):
+            continue
+        src = open(os.path.join(REPO, "include", f)).read()
+        src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+        names += re.findall(r"\b(cott_[a-z0-9_]+)\s*\(", src)
+    return sorted(set(names))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from cottention_transformer_b200 import build
+    return ctypes.CDLL(build.build())
+
+
+def test_header_declares_entry_points():
+    d = _declared()
+    assert "cott_scan" in d and "cott_scan_bwd" in d and "cott_version" in d
+
+
+def test_library_exports_every_declared_symbol(lib):
+    for name in _declared():
+        assert hasattr(lib, name), f"{name} declared in include/ but not exported"
+
+
+def test_python_binding_covers_every_declared_symbol():
+    from cottention_transformer_b200 import _lib
+    assert sorted(_lib.exported_symbols()) == _declared()
+
+
+def test_version_and_status_strings(lib):
+    lib.cott_version.restype = ctypes.c_char_p
+    assert b"sm_100a" in lib.cott_version()
+    lib.cott_status_string.restype = ctypes.c_char_p
+    assert lib.cott_status_string(0) == b"ok"
+    assert lib.cott_status_string(2) == b"unsupported shape"
+
+
+def test_argument_validation_needs_no_gpu(lib):
+    """Bad arguments are rejected before any CUDA call."""
+    lib.cott_last_error.restype = ctypes.c_char_p
+    P = ctypes.c_void_p
+    lib.cott_scan.argtypes = [P, P, P, P] + [ctypes.c_int] * 7 + [P]
+    assert lib.cott_scan(None, None, None, None, 1, 1, 8, 24, 16, 0, 0, None) == 2  # Dk % 16
+    assert b"divisible by 16" in lib.cott_last_error()
+    assert lib.cott_scan(None, None, None, None, 1, 1, 8, 32, 16, 9, 0, None) == 3  # dtype
+    assert lib.cott_scan(None, None, None, None, 1, 1, 8, 32, 16, 0, 0, None) == 1  # null
+    assert lib.cott_scan(None, None, None, None, 0, 1, 8, 32, 16, 0, 0, None) == 0  # empty: nothing to do
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    from cottention_transformer_b200 import _lib
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        _lib.lib()
+
+
+def test_dropin_names_import():
+    import sys
+    sys.path.insert(0, os.path.join(REPO, "cottention_transformer_b200", "dropin"))
+    try:
+        import FastAttention2
+        from FastAttention2 import kernel
+        from Custom_Kernel import CustomAttention
+        assert all(hasattr(kernel, n) for n in ("float32", "float64", "float16", "bfloat16"))
+        assert hasattr(FastAttention2, "kernel") and hasattr(CustomAttention, "apply")
+    finally:
+        sys.path.pop(0)
+
+
+def test_kernel_rejects_cpu_tensors_like_the_reference():
+    import torch
+    from cottention_transformer_b200 import kernel
+    x = torch.zeros(1, 1, 4, 32)
+    with pytest.raises(RuntimeError, match="Q must be a CUDA tensor"):
+        kernel.float32(x, x, x, 1, False, False)

@@ -1,0 +1,182 @@
+"""GPU parity tests of the scan (FastAttention2.kernel / CustomAttention drop-in), through the C ABI."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import cott_oracle as O
+from conftest import load_reference_kernel
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+DT = {"f32": torch.float32, "f64": torch.float64, "f16": torch.float16, "bf16": torch.bfloat16}
+# max-abs tolerance against the fp64 truth on the same (rounded) inputs.  fp32: 1e-4 as specified for
+# the fp32 mode; bf16/fp16: 2e-2 relative (to the largest reference magnitude).
+ABS_TOL = {torch.float64: 1e-10, torch.float32: 1e-4}
+REL_TOL = {torch.float16: 2e-2, torch.bfloat16: 2e-2}
+
+
+@pytest.fixture(scope="module")
+def K():
+    from cottention_transformer_b200 import kernel
+    return kernel
+
+
+def _check(ours, truth, dt):
+    ours = ours.double().cpu()
+    if dt in ABS_TOL:
+        err = (ours - truth).abs().max().item()
+        assert err <= ABS_TOL[dt], f"max-abs {err} > {ABS_TOL[dt]}"
+    else:
+        err = ((ours - truth).abs().max() / truth.abs().max()).item()
+        assert err <= REL_TOL[dt], f"relative {err} > {REL_TOL[dt]}"
+
+
+SHAPES = [  # B, H, N, Dk, Dv
+    (1, 1, 1, 32, 32), (1, 2, 2, 32, 16), (1, 2, 63, 128, 128), (2, 2, 64, 64, 64), (1, 3, 65, 64, 32),
+    (1, 2, 127, 32, 32), (1, 1, 129, 64, 64), (2, 2, 1000, 64, 64), (1, 1, 200, 256, 40), (1, 2, 130, 16, 7),
+]
+
+
+@pytest.mark.parametrize("dtn", ["f32", "f64", "f16", "bf16"])
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("rev", [False, True])
+def test_scan_matches_oracle(K, dtn, shape, rev):
+    dt = DT[dtn]
+    B, H, N, Dk, Dv = shape
+    q, k, v, _, _ = O.make_inputs(B, H, N, Dk, Dv, seed=N + Dk, dtype=dt)
+    truth = O.scan_recurrent(q, k, v, rev, "f64")
+    out = K.scan(q.cuda(), k.cuda(), v.cuda(), rev)
+    assert out.dtype == dt and out.shape == (B, H, N, Dv)
+    _check(out, truth, dt)
+
+
+def test_scan_empty_sequence_and_batch(K):
+    for shape in [(0, 2, 16, 32, 32), (2, 2, 0, 32, 32)]:
+        B, H, N, Dk, Dv = shape
+        z = torch.zeros(B, H, N, Dk, device="cuda")
+        out = K.float32(z, z, torch.zeros(B, H, N, Dv, device="cuda"), 1, False, False)
+        assert out.shape == (B, H, N, Dv)
+
+
+@pytest.mark.parametrize("name", ["f64_gradcheck_shape", "f32_d64", "f32_d32_halfwarp", "f32_dv_ne_dk",
+                                  "bf16_d64", "f16_d128"])
+def test_scan_matches_recorded_reference_kernel(K, name):
+    """Against outputs recorded from the reference's compiled CUDA kernel on a B200."""
+    path = os.path.join(GOLDEN, f"kernel_ref_{name}.npz")
+    if not os.path.exists(path):
+        pytest.skip("fixture not generated yet")
+    g = np.load(path)
+    dt = DT[name.split("_")[0]]
+    q, k, v, do = (torch.from_numpy(g[n]).to(dt).cuda() for n in ("q", "k", "v", "dout"))
+    ref, ref_rev = torch.from_numpy(g["out"]), torch.from_numpy(g["out_rev"])
+    fn = {torch.float32: K.float32, torch.float64: K.float64, torch.float16: K.float16, torch.bfloat16: K.bfloat16}[dt]
+    out, out_rev = fn(q, k, v, 1, False, False), fn(q, k, v, 1, False, True)
+    if dt in ABS_TOL:
+        _check(out, ref, dt)
+        _check(out_rev, ref_rev, dt)
+        if "dq" in g.files:
+            _check(fn(do, v, k, 1, False, False), torch.from_numpy(g["dq"]), dt)
+            _check(fn(v, do, q, 1, False, True), torch.from_numpy(g["dk"]), dt)
+            _check(fn(k, q, do, 1, False, True), torch.from_numpy(g["dv"]), dt)
+    else:
+        # the reference's 16-bit modes keep the state in 16 bits; ours must be at least as close to
+        # the fp64 truth as the reference is, and within the 16-bit tolerance of it
+        truth = O.scan_recurrent(q.cpu(), k.cpu(), v.cpu(), False, "f64")
+        e_ref = (ref - truth).abs().max() / truth.abs().max()
+        e_our = (out.double().cpu() - truth).abs().max() / truth.abs().max()
+        assert e_our <= REL_TOL[dt] and e_our <= e_ref + 1e-3, (e_our, e_ref)
+
+
+def test_scan_matches_live_reference_kernel(K):
+    """Side by side with the reference extension itself, when its build is present."""
+    ref = load_reference_kernel()
+    if ref is None:
+        pytest.skip("oracle/_ref not built")
+    q, k, v, do, _ = O.make_inputs(2, 3, 333, 64, 64, seed=5)
+    q, k, v, do = (t.cuda() for t in (q, k, v, do))
+    for rev in (False, True):
+        a = K.float32(q, k, v, 1, False, rev)
+        b = ref.float32(q.clone(), k.clone(), v.clone(), 1, False, rev)
+        assert (a - b).abs().max().item() < 1e-4
+    qd, kd, vd = q.double(), k.double(), v.double()
+    a = K.float64(qd, kd, vd, 1, False, False)
+    b = ref.float64(qd.clone(), kd.clone(), vd.clone(), 1, False, False)
+    assert (a - b).abs().max().item() < 1e-11
+
+
+def test_gradcheck_fp64_like_the_reference():
+    """Cuda_Kernel/Custom_Kernel.py:157,184-188: gradcheck at N,H,S,D = 1,2,63,128 in float64."""
+    from cottention_transformer_b200 import CustomAttention
+    torch.manual_seed(0)
+    N, H, S, D = 1, 2, 63, 128
+    Q = torch.rand(N, H, S, D, device="cuda").double().requires_grad_()
+    Kk = torch.rand(N, H, S, D, device="cuda").double().requires_grad_()
+    V = torch.rand(N, H, S, D, device="cuda").double().requires_grad_()
+    assert torch.autograd.gradcheck(CustomAttention.apply, (Q, Kk, V), eps=1e-4)
+
+
+def test_custom_attention_backward_matches_autograd_of_quadratic_form():
+    from cottention_transformer_b200 import CustomAttention
+    q, k, v, do, _ = O.make_inputs(2, 2, 150, 64, 64, seed=11)
+    qc, kc, vc = (t.cuda().requires_grad_() for t in (q, k, v))
+    out = CustomAttention.apply(qc, kc, vc)
+    out.backward(do.cuda())
+    qd, kd, vd = (t.double().requires_grad_() for t in (q, k, v))
+    (O.scan_quadratic(qd, kd, vd) * do.double()).sum().backward()
+    for a, b in ((qc.grad, qd.grad), (kc.grad, kd.grad), (vc.grad, vd.grad)):
+        assert (a.double().cpu() - b).abs().max().item() < 1e-4
+
+
+def test_scan_bwd_entry_point_equals_three_scans(K):
+    from cottention_transformer_b200 import _lib
+    q, k, v, do, _ = O.make_inputs(1, 2, 90, 32, 64, seed=12)
+    q, k, v, do = (t.cuda() for t in (q, k, v, do))
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    st = _lib.lib().cott_scan_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), do.data_ptr(), dq.data_ptr(),
+                                  dk.data_ptr(), dv.data_ptr(), 1, 2, 90, 32, 64, 0, _lib.stream_ptr(q.device))
+    _lib.check(st, "cott_scan_bwd")
+    assert torch.equal(dq, K.scan(do, v, k, False))
+    assert torch.equal(dk, K.scan(v, do, q, True))
+    assert torch.equal(dv, K.scan(k, q, do, True))
+
+
+def test_autocast_dtype_rule(K):
+    """combined_kernel_general.cu:377-389: under autocast an fp32 Q runs (and returns) in the entry
+    point's autocast dtype; other dtypes are left alone."""
+    q, k, v, _, _ = O.make_inputs(1, 1, 40, 32, 32, seed=3)
+    q, k, v = q.cuda(), k.cuda(), v.cuda()
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        assert K.float32(q, k, v, 1, False, False).dtype == torch.bfloat16
+        assert K.float16(q, k, v, 1, False, False).dtype == torch.float16
+        assert K.float64(q.double(), k.double(), v.double(), 1, False, False).dtype == torch.float64
+    assert K.float32(q, k, v, 1, False, False).dtype == torch.float32
+    assert K.bfloat16(q.half(), k, v, 1, False, False).dtype == torch.float16  # follows Q, casts K and V
+
+
+def test_inplace_and_noncontiguous(K):
+    q, k, v, _, _ = O.make_inputs(1, 2, 50, 32, 32, seed=4)
+    q, k, v = q.cuda(), k.cuda(), v.cuda()
+    want = K.float32(q, k, v, 1, False, False)
+    v2 = v.clone()
+    got = K.float32(q, k, v2, 1, True, False)
+    assert got.data_ptr() == v2.data_ptr() and torch.equal(got, want)
+    qt = q.transpose(1, 2).contiguous().transpose(1, 2)  # same values, non-contiguous
+    assert not qt.is_contiguous()
+    assert torch.equal(K.float32(qt, k, v, 1, False, False), want)
+
+
+def test_reference_error_messages(K):
+    z = torch.zeros(1, 1, 8, 32, device="cuda")
+    with pytest.raises(RuntimeError, match="Q and K must have the same dimension"):
+        K.float32(z, torch.zeros(1, 1, 8, 48, device="cuda"), z, 1, False, False)
+    with pytest.raises(RuntimeError, match="D_attn must be divisible by 16"):
+        K.float32(z[..., :24], z[..., :24], z, 1, False, False)
+    with pytest.raises(RuntimeError, match="greater than or equal to 16"):
+        K.float32(z[..., :16], z[..., :16], z, 1, False, False)
+    from cottention_transformer_b200 import CustomAttention
+    zi = torch.zeros(1, 1, 8, 32, device="cuda", dtype=torch.int32)
+    with pytest.raises(ValueError, match="Only float32, float64, float16, and bfloat16"):
+        CustomAttention.apply(zi, zi, zi)
