@@ -1,0 +1,301 @@
+"""Benchmark of the hot path: causal cosine attention forward + backward (tokens/s).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" = one forward + one backward of the fused causal cosine-attention op over one batch
+of synthetic input of the headline shape (B=8 per GPU, H=16, N=4096, d=64, bfloat16).  Under
+torchrun each rank (one per GPU) processes its own batch shard; there is no data-path collective
+(weak scaling).  Rank 0 prints ONE JSON line.
+
+Keys beyond the basic contract:
+  value      whole-job tokens/s with inputs resident in HBM, device-timed (CUDA events), max over ranks
+  e2e        the same through the public Python op with pinned HOST buffers: every step copies
+             q, k, v, dO host->device and out, dq, dk, dv, dnorm device->host inside the timed region
+  roofline   the dominant kernel (reverse-direction dK/dV pass): algorithmic bytes per launch /
+             average launch duration (CUDA events on the launching stream, inside the timed region)
+             against the measured HBM copy bandwidth
+  cpu_baseline  the reference's PyTorch CPU formulation (cumsum form + autograd) restated in oracle/,
+             timed on this host on a bounded sample of the same workload
+
+``--impl reference`` times that CPU formulation alone, with all host threads, as the reference arm.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+B_PER_GPU, H, N, D = 8, 16, 4096, 64
+WORKLOAD = "causal cosine attention fwd+bwd, B=8/GPU H=16 N=4096 d=64 bf16 (Q,K L2-normalised N(0,1), norm_const=0.5)"
+ELEM = 2  # bf16
+# ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of causal_bwd_kv_kernel at the bench shape
+# (see profiles/); None until captured.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def _peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop = threading.Event()
+
+    def run(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            names = {
+                nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+                nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+                nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+                nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+            }
+            while not self._stop.is_set():
+                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+                time.sleep(0.02)
+        except Exception as e:  # NVML missing: report nothing rather than fail the bench
+            self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
+
+    def stop(self):
+        self._stop.set()
+        self.join(timeout=2)
+        return {
+            "sm_mhz": statistics.median(self.samples) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+        }
+
+
+def _host_inputs(rank):
+    """Seeded synthetic shard of this rank in pinned host memory (seed 1234 + rank)."""
+    from oracle import cott_oracle as O  # input recipe only (shared with the tests)
+    q, k, v, do, nc = O.make_inputs(B_PER_GPU, H, N, D, seed=1234 + rank, dtype=torch.bfloat16)
+    return [t.pin_memory() for t in (q, k, v, do)], nc
+
+
+def cpu_reference_sample(threads, budget_s=12.0, max_slices=64):
+    """The reference's PyTorch formulation on CPU (cumsum form, Custom_Kernel.py:63, with the module
+    math of GPTCosAttention.py:229-248 around it, gradients by autograd), fp32, on (b,h) slices of
+    the bench workload.  Returns (tokens_per_s, slices_done, seconds)."""
+    from oracle import cott_oracle as O
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(1234)
+    done, t_total = 0, 0.0
+    while done < max_slices and t_total < budget_s:
+        q = torch.nn.functional.normalize(torch.randn(1, 1, N, D, generator=g), dim=-1).requires_grad_()
+        k = torch.nn.functional.normalize(torch.randn(1, 1, N, D, generator=g), dim=-1).requires_grad_()
+        v = torch.randn(1, 1, N, D, generator=g).requires_grad_()
+        do = torch.randn(1, 1, N, D, generator=g)
+        nc = (0.5 * torch.ones(1)).requires_grad_()
+        t0 = time.perf_counter()
+        out = O.cos_attn_causal(q, k, v, nc, scan=lambda a, b, c: O.scan_cumsum(a, b, c, False))
+        out.backward(do)
+        t_total += time.perf_counter() - t0
+        done += 1
+    tokens = done * N / H  # one token = one position across all H heads
+    return tokens / t_total, done, t_total
+
+
+def run_reference_arm(args, rank, world):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    vals = []
+    for i in range(args.warmup + args.steps):
+        tps, slices, secs = cpu_reference_sample(threads, budget_s=4.0, max_slices=8)
+        if i >= args.warmup:
+            vals.append((tps, slices, secs))
+    tps = sum(v[0] for v in vals) / len(vals)
+    slices = vals[-1][1]
+    ms = 1e3 * sum(v[2] for v in vals) / len(vals)
+    line = {
+        "impl": "reference", "metric": "causal cosine-attention fwd+bwd tokens/s", "value": tps, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "global_batch": B_PER_GPU * args.gpus, "seq_len": N, "heads": H, "head_dim": D},
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": f"{slices} (batch,head) slices of N={N}, d={D} per step, fp32, PyTorch cumsum "
+                                   "formulation + autograd"},
+        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+
+    import torch.distributed as dist
+    from cottention_transformer_b200 import _lib, cos_attn_causal
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    L = _lib.lib()
+    host, nc_host = _host_inputs(rank)
+    q, k, v, do = (t.to(dev) for t in host)
+    nc = nc_host.to(dev)
+    out, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
+    dnc = torch.empty(H, dtype=torch.float32, device=dev)
+    stream = _lib.stream_ptr(dev)
+    P = lambda t: t.data_ptr()  # noqa: E731
+    code = _lib.DTYPE_CODE[torch.bfloat16]
+
+    def fwd():
+        _lib.check(L.cott_cos_attn_fwd(P(q), P(k), P(v), P(nc), P(out), B_PER_GPU, H, N, D, D, code, stream), "fwd")
+
+    def bwd_dq():
+        _lib.check(L.cott_cos_attn_bwd_dq(P(q), P(k), P(v), P(nc), P(do), P(dq), B_PER_GPU, H, N, D, D, code, stream), "dq")
+
+    def bwd_dkdv():
+        _lib.check(L.cott_cos_attn_bwd_dkdv(P(q), P(k), P(v), P(nc), P(do), P(dk), P(dv), P(dnc), B_PER_GPU, H, N, D, D,
+                                            code, stream), "dkdv")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing --------------------------------------------------------------------
+    for _ in range(args.warmup):
+        fwd(), bwd_dq(), bwd_dkdv()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    for i in range(args.steps):
+        ev[i][0].record()
+        fwd()
+        ev[i][1].record()
+        bwd_dq()
+        ev[i][2].record()
+        bwd_dkdv()
+        ev[i][3].record()
+    barrier()
+    clocks = sampler.stop()
+    _lib.check_device_status()
+    total_ms = ev[0][0].elapsed_time(ev[-1][3])
+    t_fwd = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps
+    t_dq = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps
+    t_kv = sum(e[2].elapsed_time(e[3]) for e in ev) / args.steps
+    if world > 1:
+        t = torch.tensor([total_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = t.item()
+    ms_per_step = total_ms / args.steps
+    tokens_per_step = B_PER_GPU * N * world
+    value = tokens_per_step / (ms_per_step * 1e-3)
+
+    # ---- end to end: pinned host buffers in, host buffers out ------------------------------------------
+    host_out = [torch.empty_like(t).pin_memory() for t in (out, dq, dk, dv)]
+    host_dnc = torch.empty(H, dtype=torch.float32).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in host)
+    d2h = sum(t.numel() * t.element_size() for t in host_out) + H * 4
+
+    def e2e_step():
+        qd, kd, vd, dod = (t.to(dev, non_blocking=True) for t in host)
+        qd.requires_grad_(), kd.requires_grad_(), vd.requires_grad_()
+        ncd = nc.detach().requires_grad_()
+        o = cos_attn_causal(qd, kd, vd, ncd)
+        o.backward(dod)
+        for dst, src in zip(host_out, (o.detach(), qd.grad, kd.grad, vd.grad)):
+            dst.copy_(src, non_blocking=True)
+        host_dnc.copy_(ncd.grad, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = t.item()
+    e2e_value = tokens_per_step * e2e_steps / (e2e_ms * 1e-3)
+
+    if rank == 0:
+        peak, peak_kind = _peaks()
+        per_launch = lambda passes: passes * B_PER_GPU * H * N * D * ELEM  # noqa: E731
+        kv_bytes = per_launch(6)  # read q, k, v, dO; write dk, dv
+        achieved = kv_bytes / (t_kv * 1e-3) / 1e9
+        step_bytes = per_launch(11)  # 4 (fwd) + 7 (bwd) tensor passes
+        step_gbs = step_bytes / ((t_fwd + t_dq + t_kv) * 1e-3) / 1e9
+        line = {
+            "metric": "causal cosine-attention fwd+bwd tokens/s", "value": value, "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "global_batch": B_PER_GPU * world, "seq_len": N, "heads": H,
+                       "head_dim": D, "sharding": f"batch x heads, {B_PER_GPU * H} (b,h) sequences per GPU, no collective",
+                       "l2": "inputs 268 MB + outputs 268 MB per step exceed the 126 MB L2"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": 3 * args.steps,
+            "roofline": {"bound": "hbm", "kernel": "causal_bwd_kv_kernel", "achieved": achieved, "peak": peak,
+                         "unit": "GB/s", "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                         "peak_source": peak_kind, "algorithmic_bytes_per_launch": kv_bytes,
+                         "kernel_us": {"causal_tc_kernel<fwd>": t_fwd * 1e3, "causal_tc_kernel<dq>": t_dq * 1e3,
+                                       "causal_bwd_kv_kernel": t_kv * 1e3},
+                         "step": {"algorithmic_bytes": step_bytes, "achieved": step_gbs, "frac": step_gbs / peak}},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            tps, slices, secs = cpu_reference_sample(threads, budget_s=12.0)
+            line["cpu_baseline"] = {
+                "value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
+                "sample": f"{slices} of {B_PER_GPU * H} (batch,head) slices at N={N}, d={D}, fp32, PyTorch cumsum "
+                          f"formulation + autograd, {secs:.1f} s"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -26,6 +26,11 @@ _P, _I, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_long
 _SIGNATURES = {
     "cott_scan": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "cott_scan_bwd": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "cott_cos_attn_fwd": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "cott_cos_attn_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "cott_cos_attn_bwd_dq": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "cott_cos_attn_bwd_dkdv": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "cott_check_status": [ctypes.POINTER(ctypes.c_int)],
 }
 _STR = {"cott_version": [], "cott_last_error": [], "cott_status_string": [_I]}
 
@@ -62,6 +67,12 @@ def check(status: int, what: str) -> None:
         raise RuntimeError(
             f"{what}: {L.cott_status_string(status).decode()} ({status}): {L.cott_last_error().decode()}"
         )
+
+
+def check_device_status() -> None:
+    """Synchronise and raise if a tensor-core kernel recorded a bounded wait that gave up."""
+    detail = ctypes.c_int(0)
+    check(lib().cott_check_status(ctypes.byref(detail)), "cott_check_status")
 
 
 def stream_ptr(device: torch.device) -> int:

@@ -1,0 +1,95 @@
+"""Fused cosine attention operators (the module-level math of the reference, in one op).
+
+``cos_attn_causal(q, k, v, norm_const)`` computes what the training branch of
+``GPTCosAttention._cos_attn`` (``GPT_Trainer/GPTCosAttention.py:229-248,282``) computes:
+L2-normalise q and k, divide v by ``max(n_s ** sigmoid(norm_const_h), 1)`` where ``n_s`` counts
+the un-masked keys up to position s, zero the masked rows, and run the causal scan -- and it is
+differentiable w.r.t. q, k, v and ``norm_const``.
+
+Two modes, chosen by dtype (not a fallback chain -- each mode is a CUDA path of this library):
+
+* float16 / bfloat16, head dim 64, no padding mask: ONE fused tensor-core kernel for the forward
+  (``cott_cos_attn_fwd``) and two for the backward (``cott_cos_attn_bwd``), fp32 accumulation;
+* float32 / float64 (and any other shape or a padding mask): the reference's own structure --
+  elementwise torch ops around ``CustomAttention`` (the exact-mode scan kernel), gradients of
+  ``norm_const`` by autograd exactly as in the reference.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from .custom_kernel import CustomAttention
+
+FUSED_DTYPES = (torch.float16, torch.bfloat16)
+
+
+def fused_supported(q, k, v, keep=None) -> bool:
+    return (
+        q.is_cuda and q.dtype in FUSED_DTYPES and k.dtype == q.dtype and v.dtype == q.dtype
+        and q.shape[-1] == 64 and v.shape[-1] == 64 and keep is None
+    )
+
+
+class _FusedCausal(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, norm_const):
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        B, H, N, D = q.shape
+        nc = norm_const.detach().reshape(-1).to(device=q.device, dtype=torch.float32).contiguous()
+        if nc.numel() != H:
+            raise RuntimeError(f"norm_const must have one entry per head ({H}), got {nc.numel()}")
+        out = torch.empty_like(v)
+        with torch.cuda.device(q.device):
+            st = _lib.lib().cott_cos_attn_fwd(
+                _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(nc), _lib.ptr(out), B, H, N, D, D,
+                _lib.DTYPE_CODE[q.dtype], _lib.stream_ptr(q.device))
+        _lib.check(st, "cott_cos_attn_fwd")
+        ctx.save_for_backward(q, k, v, nc)
+        ctx.nc_shape, ctx.nc_dtype = norm_const.shape, norm_const.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, nc = ctx.saved_tensors
+        dout = dout.contiguous().to(q.dtype)
+        B, H, N, D = q.shape
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        dnc = torch.empty(H, dtype=torch.float32, device=q.device)
+        with torch.cuda.device(q.device):
+            st = _lib.lib().cott_cos_attn_bwd(
+                _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(nc), _lib.ptr(dout), _lib.ptr(dq), _lib.ptr(dk),
+                _lib.ptr(dv), _lib.ptr(dnc), B, H, N, D, D, _lib.DTYPE_CODE[q.dtype], _lib.stream_ptr(q.device))
+        _lib.check(st, "cott_cos_attn_bwd")
+        return dq, dk, dv, dnc.reshape(ctx.nc_shape).to(ctx.nc_dtype)
+
+
+def _exact_causal(q, k, v, norm_const, keep):
+    """The reference's structure (GPTCosAttention.py:229-248,282) around the exact-mode scan."""
+    B, H, N, _ = q.shape
+    qh = torch.nn.functional.normalize(q, dim=-1, p=2)
+    kh = torch.nn.functional.normalize(k, dim=-1, p=2)
+    if keep is None:
+        n = torch.arange(1, N + 1, device=q.device, dtype=q.dtype).view(1, 1, N, 1)
+    else:
+        n = keep.to(torch.int64).cumsum(-1).to(q.dtype).view(B, 1, N, 1)
+    sig = torch.sigmoid(norm_const).reshape(1, H, 1, 1).to(q.dtype)
+    vp = v / (n ** sig).clamp(min=1)
+    if keep is not None:
+        m = keep.view(B, 1, N, 1).to(q.dtype)
+        qh, kh, vp = qh * m, kh * m, vp * m
+    return CustomAttention.apply(qh, kh, vp)
+
+
+def cos_attn_causal(q, k, v, norm_const, keep=None):
+    """Causal cosine attention with the learned length-norm.
+
+    q, k, v: ``[B, H, N, d]`` CUDA tensors; ``norm_const``: H values (any shape, e.g. the module's
+    ``[1, H, 1, 1]`` parameter); ``keep``: optional ``[B, N]`` bool, True = un-masked
+    (``attention_mask == 0`` in the reference, ``GPTCosAttention.py:232``).
+    """
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        raise RuntimeError("cos_attn_causal needs CUDA tensors (there is no CPU path)")
+    if fused_supported(q, k, v, keep):
+        return _FusedCausal.apply(q, k, v, norm_const)
+    return _exact_causal(q, k, v, norm_const, keep)

@@ -34,6 +34,34 @@ inline int cuda_fail(cudaError_t e, const char* what) {
     if (_e != cudaSuccess) return ::cott::cuda_fail(_e, #expr); \
   } while (0)
 
+// Makes the device that owns `ptr` current on the calling thread for the lifetime of the object
+// (like the reference's at::cuda::CUDAGuard, combined_kernel_general.cu:412) and thereby binds
+// that device's primary context to the thread -- needed before any driver-API call on threads
+// that have made no CUDA call yet, e.g. autograd worker threads.
+class DeviceScope {
+ public:
+  explicit DeviceScope(const void* ptr) {
+    cudaPointerAttributes attr;
+    if (ptr && cudaPointerGetAttributes(&attr, ptr) == cudaSuccess && attr.type == cudaMemoryTypeDevice) {
+      dev_ = attr.device;
+    } else {
+      cudaGetLastError();
+      if (cudaGetDevice(&dev_) != cudaSuccess) dev_ = 0;
+    }
+    if (cudaGetDevice(&prev_) != cudaSuccess) prev_ = dev_;
+    status_ = cudaSetDevice(dev_);
+  }
+  ~DeviceScope() {
+    if (prev_ != dev_) cudaSetDevice(prev_);
+  }
+  cudaError_t status() const { return status_; }
+  int device() const { return dev_; }
+
+ private:
+  int dev_ = 0, prev_ = 0;
+  cudaError_t status_ = cudaSuccess;
+};
+
 inline size_t dtype_size(int dtype) {
   switch (dtype) {
     case COTT_F32: return 4;

@@ -1,0 +1,173 @@
+// C ABI of the fused cosine-attention operators (tensor-core path).
+#include "causal_tc.cuh"
+#include "common.cuh"
+
+#include <initializer_list>
+#include <utility>
+
+using namespace cott;
+
+namespace {
+
+int check_fused_args(int B, int H, int N, int Dk, int Dv, int dtype) {
+  if (dtype != COTT_BF16 && dtype != COTT_F16)
+    return fail(COTT_ERR_DTYPE,
+                "the fused tensor-core path takes float16/bfloat16 (dtype code %d given); float32/float64 go "
+                "through cott_scan", dtype);
+  if (B < 0 || H < 0 || N < 0) return fail(COTT_ERR_SHAPE, "negative size B=%d H=%d N=%d", B, H, N);
+  if (Dk != kTcD || Dv != kTcD)
+    return fail(COTT_ERR_UNSUPPORTED, "the fused tensor-core path is built for head dim 64 (got Dk=%d Dv=%d)", Dk, Dv);
+  if ((long)B * H > 0x7fffffffL) return fail(COTT_ERR_SHAPE, "B*H too large");
+  return COTT_OK;
+}
+
+int aligned16(const void* p, const char* name) {
+  if (reinterpret_cast<uintptr_t>(p) & 15) return fail(COTT_ERR_ALIGN, "%s must be 16-byte aligned", name);
+  return COTT_OK;
+}
+
+int tmap(CUtensorMap* m, const void* p, int dtype, long BH, long N) {
+  int r = make_tmap_rows64(m, p, dtype == COTT_BF16, BH, N, kTcD, kTcChunk);
+  if (r == 1) return fail(COTT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  if (r) return fail(COTT_ERR_CUDA, "cuTensorMapEncodeTiled failed: CUresult %d (ptr %p, BH %ld, N %ld)", r - 100, p, BH, N);
+  return COTT_OK;
+}
+
+template <typename T>
+int launch_fwd(const void* q, const void* k, const void* v, const float* nc, void* out, int B, int H, int N,
+               int dtype, cudaStream_t stream) {
+  const long BH = (long)B * H;
+  CUtensorMap mq, mk, mv;
+  int st;
+  if ((st = tmap(&mq, q, dtype, BH, N)) || (st = tmap(&mk, k, dtype, BH, N)) || (st = tmap(&mv, v, dtype, BH, N)))
+    return st;
+  auto kern = causal_tc_kernel<T, kModeFwd>;
+  const size_t smem = causal_tc_smem_bytes(kModeFwd);
+  COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<(unsigned)BH, 128, smem, stream>>>(mq, mk, mv, mq, static_cast<T*>(out), nc, H, N);
+  COTT_CUDA_TRY(cudaGetLastError());
+  return COTT_OK;
+}
+
+template <typename T>
+int launch_bwd_dq(const void* q, const void* k, const void* v, const float* nc, const void* dout, void* dq, int B,
+                  int H, int N, int dtype, cudaStream_t stream) {
+  const long BH = (long)B * H;
+  CUtensorMap mq, mk, mv, md;
+  int st;
+  if ((st = tmap(&mq, q, dtype, BH, N)) || (st = tmap(&mk, k, dtype, BH, N)) ||
+      (st = tmap(&mv, v, dtype, BH, N)) || (st = tmap(&md, dout, dtype, BH, N)))
+    return st;
+  auto kern = causal_tc_kernel<T, kModeDq>;
+  const size_t smem = causal_tc_smem_bytes(kModeDq);
+  COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<(unsigned)BH, 128, smem, stream>>>(md, mv, mk, mq, static_cast<T*>(dq), nc, H, N);
+  COTT_CUDA_TRY(cudaGetLastError());
+  return COTT_OK;
+}
+
+template <typename T>
+int launch_bwd_dkdv(const void* q, const void* k, const void* v, const float* nc, const void* dout, void* dk,
+                    void* dv, float* dnorm, int B, int H, int N, int dtype, cudaStream_t stream) {
+  const long BH = (long)B * H;
+  CUtensorMap mq, mk, mv, md;
+  int st;
+  if ((st = tmap(&mq, q, dtype, BH, N)) || (st = tmap(&mk, k, dtype, BH, N)) ||
+      (st = tmap(&mv, v, dtype, BH, N)) || (st = tmap(&md, dout, dtype, BH, N)))
+    return st;
+  COTT_CUDA_TRY(cudaMemsetAsync(dnorm, 0, sizeof(float) * H, stream));
+  auto kern = causal_bwd_kv_kernel<T>;
+  const size_t smem = causal_bwd_kv_smem_bytes();
+  COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<(unsigned)BH, 128, smem, stream>>>(mq, mk, mv, md, static_cast<T*>(dk), static_cast<T*>(dv), dnorm, nc, H,
+                                            N);
+  COTT_CUDA_TRY(cudaGetLastError());
+  return COTT_OK;
+}
+
+int check_ptrs16(std::initializer_list<std::pair<const void*, const char*>> ps) {
+  for (auto& p : ps) {
+    if (!p.first) return fail(COTT_ERR_NULL, "null pointer: %s", p.second);
+    int st = aligned16(p.first, p.second);
+    if (st) return st;
+  }
+  return COTT_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int cott_cos_attn_fwd(const void* q, const void* k, const void* v, const float* norm_const, void* out, int B,
+                      int H, int N, int Dk, int Dv, int dtype, void* stream) {
+  int st = check_fused_args(B, H, N, Dk, Dv, dtype);
+  if (st) return st;
+  if ((long)B * H * N == 0) return COTT_OK;
+  if (!q || !k || !v || !out || !norm_const) return fail(COTT_ERR_NULL, "null tensor pointer");
+  if ((st = aligned16(q, "q")) || (st = aligned16(k, "k")) || (st = aligned16(v, "v")) || (st = aligned16(out, "out")))
+    return st;
+  DeviceScope scope(q);
+  COTT_CUDA_TRY(scope.status());
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return dtype == COTT_BF16 ? launch_fwd<__nv_bfloat16>(q, k, v, norm_const, out, B, H, N, dtype, s)
+                            : launch_fwd<__half>(q, k, v, norm_const, out, B, H, N, dtype, s);
+}
+
+int cott_cos_attn_bwd_dq(const void* q, const void* k, const void* v, const float* norm_const, const void* dout,
+                         void* dq, int B, int H, int N, int Dk, int Dv, int dtype, void* stream) {
+  int st = check_fused_args(B, H, N, Dk, Dv, dtype);
+  if (st) return st;
+  if ((long)B * H * N == 0) return COTT_OK;
+  if ((st = check_ptrs16({{q, "q"}, {k, "k"}, {v, "v"}, {dout, "dout"}, {dq, "dq"}}))) return st;
+  if (!norm_const) return fail(COTT_ERR_NULL, "null pointer: norm_const");
+  DeviceScope scope(q);
+  COTT_CUDA_TRY(scope.status());
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return dtype == COTT_BF16 ? launch_bwd_dq<__nv_bfloat16>(q, k, v, norm_const, dout, dq, B, H, N, dtype, s)
+                            : launch_bwd_dq<__half>(q, k, v, norm_const, dout, dq, B, H, N, dtype, s);
+}
+
+int cott_cos_attn_bwd_dkdv(const void* q, const void* k, const void* v, const float* norm_const, const void* dout,
+                           void* dk, void* dv, float* dnorm_const, int B, int H, int N, int Dk, int Dv, int dtype,
+                           void* stream) {
+  int st = check_fused_args(B, H, N, Dk, Dv, dtype);
+  if (st) return st;
+  if (!dnorm_const && H > 0) return fail(COTT_ERR_NULL, "null pointer: dnorm_const");
+  if (H == 0) return COTT_OK;
+  DeviceScope scope(dnorm_const);
+  COTT_CUDA_TRY(scope.status());
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if ((long)B * H * N == 0) {
+    COTT_CUDA_TRY(cudaMemsetAsync(dnorm_const, 0, sizeof(float) * H, s));
+    return COTT_OK;
+  }
+  if ((st = check_ptrs16({{q, "q"}, {k, "k"}, {v, "v"}, {dout, "dout"}, {dk, "dk"}, {dv, "dv"}}))) return st;
+  if (!norm_const) return fail(COTT_ERR_NULL, "null pointer: norm_const");
+  return dtype == COTT_BF16
+             ? launch_bwd_dkdv<__nv_bfloat16>(q, k, v, norm_const, dout, dk, dv, dnorm_const, B, H, N, dtype, s)
+             : launch_bwd_dkdv<__half>(q, k, v, norm_const, dout, dk, dv, dnorm_const, B, H, N, dtype, s);
+}
+
+int cott_cos_attn_bwd(const void* q, const void* k, const void* v, const float* norm_const, const void* dout,
+                      void* dq, void* dk, void* dv, float* dnorm_const, int B, int H, int N, int Dk, int Dv,
+                      int dtype, void* stream) {
+  int st = cott_cos_attn_bwd_dq(q, k, v, norm_const, dout, dq, B, H, N, Dk, Dv, dtype, stream);
+  if (st) return st;
+  return cott_cos_attn_bwd_dkdv(q, k, v, norm_const, dout, dk, dv, dnorm_const, B, H, N, Dk, Dv, dtype, stream);
+}
+
+int cott_check_status(int* detail) {
+  int v = 0;
+  COTT_CUDA_TRY(cudaDeviceSynchronize());
+  COTT_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_cott_status, sizeof(int)));
+  if (detail) *detail = v;
+  if (v != 0) {
+    int zero = 0;
+    COTT_CUDA_TRY(cudaMemcpyToSymbol(g_cott_status, &zero, sizeof(int)));
+    return fail(COTT_ERR_DEVICE_WAIT, "a device-side wait gave up: stage %d (1=TMA, 2=score MMA, 3=accumulator MMA) at chunk %d",
+                v >> 16, v & 0xffff);
+  }
+  return COTT_OK;
+}
+
+}  // extern "C"

@@ -58,6 +58,9 @@ int cott_scan(const void* q, const void* k, const void* v, void* out, int B, int
               int Dv, int dtype, int reversed, void* stream) {
   int st = check_scan_args(q, k, v, out, B, H, N, Dk, Dv, dtype);
   if (st != COTT_OK) return st;
+  if ((long)B * H * N == 0) return COTT_OK;
+  DeviceScope scope(q);
+  COTT_CUDA_TRY(scope.status());
   return scan_dispatch(q, k, v, out, B, H, N, Dk, Dv, dtype, reversed != 0,
                        static_cast<cudaStream_t>(stream));
 }
@@ -69,6 +72,9 @@ int cott_scan_bwd(const void* q, const void* k, const void* v, const void* dout,
   if (Dv < 16 || Dv > 256 || Dv % 16 != 0)
     return fail(COTT_ERR_SHAPE, "backward needs D_value divisible by 16 and in [16, 256] (got %d)", Dv);
   if ((long)B * H * N > 0 && (!dq || !dk || !dv)) return fail(COTT_ERR_NULL, "null gradient pointer");
+  if ((long)B * H * N == 0) return COTT_OK;
+  DeviceScope scope(q);
+  COTT_CUDA_TRY(scope.status());
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // dq = scan(dout, v, k): "Q"=dout [Dv], "K"=v [Dv], "V"=k [Dk]
   st = scan_dispatch(dout, v, k, dq, B, H, N, Dv, Dk, dtype, 0, s);

@@ -252,7 +252,7 @@ inline int make_tmap_rows64(CUtensorMap* map, const void* base, int is_bf16, lon
                    const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : 2;
+  return r == CUDA_SUCCESS ? 0 : 100 + static_cast<int>(r);
 }
 
 }  // namespace cott

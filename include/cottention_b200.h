@@ -55,7 +55,7 @@ const char* cott_status_string(int status);
  * Unlike the reference (which accumulates in the storage type, :121,133) sums are
  * kept in fp32 (fp64 for COTT_F64).  Constraints: Dk % 16 == 0, 16 <= Dk <= 256
  * (the reference: D_attn % 16 == 0, D_attn >= 32, :372-374), Dv >= 1, N >= 0.
- * `out` may alias `v` (the reference's inplace=true, :403-404) only if Dv <= 16.
+ * `out` may be the same buffer as `v` (the reference's inplace=true, :403-404).
  */
 int cott_scan(const void* q, const void* k, const void* v, void* out, int B, int H, int N, int Dk,
               int Dv, int dtype, int reversed, void* stream);
@@ -69,6 +69,58 @@ int cott_scan(const void* q, const void* k, const void* v, void* out, int B, int
  */
 int cott_scan_bwd(const void* q, const void* k, const void* v, const void* dout, void* dq, void* dk,
                   void* dv, int B, int H, int N, int Dk, int Dv, int dtype, void* stream);
+
+/*
+ * Fused causal cosine attention, forward (tensor-core path: tcgen05 / TMEM / TMA).
+ *
+ *   q^ = q/max(|q|,1e-12)   k^ = k/max(|k|,1e-12)   v'_s = v_s / max((s+1)^sigmoid(norm_const[h]), 1)
+ *   out[b,h,t,:] = sum_{s<=t} (q^_t . k^_s) v'_s
+ *
+ * Replaces, in one launch, the non-decode branch of GPTCosAttention._cos_attn,
+ * GPT_Trainer/GPTCosAttention.py:229-248 (normalize, length-norm of V by key position) followed by
+ * CustomAttention.apply (:282 -> Cuda_Kernel/Custom_Kernel.py:9-30 -> combined_kernel_general.cu),
+ * for an all-keep attention mask.  `norm_const` is H floats in device memory (the module's
+ * [1,H,1,1] parameter, :89).  dtype: COTT_BF16 or COTT_F16; Dk = Dv = 64; pointers 16-byte aligned.
+ * fp32 accumulation throughout.
+ */
+int cott_cos_attn_fwd(const void* q, const void* k, const void* v, const float* norm_const, void* out,
+                      int B, int H, int N, int Dk, int Dv, int dtype, void* stream);
+
+/*
+ * Fused backward of cott_cos_attn_fwd: dq, dk, dv (same layout and dtype as the inputs) and
+ * dnorm_const (H floats, overwritten).  Two launches: a forward-direction pass for dq and a
+ * reverse-direction pass for dk, dv and dnorm_const.
+ *
+ * Replaces CustomAttention.backward (Cuda_Kernel/Custom_Kernel.py:35-141, three kernel calls) plus
+ * the autograd of GPTCosAttention.py:229-230 (normalize) and :241 (length-norm; this is where the
+ * gradient of norm_const comes from in the reference).
+ */
+int cott_cos_attn_bwd(const void* q, const void* k, const void* v, const float* norm_const,
+                      const void* dout, void* dq, void* dk, void* dv, float* dnorm_const, int B, int H,
+                      int N, int Dk, int Dv, int dtype, void* stream);
+
+/*
+ * The two launches of cott_cos_attn_bwd as separate calls (same arguments, same results), so
+ * that a caller can time or schedule them individually:
+ *   _dq    forward-direction pass: dq     (role of Custom_Kernel.py:106 + autograd of the q normalize)
+ *   _dkdv  reverse-direction pass: dk, dv, dnorm_const   (Custom_Kernel.py:107-108 + autograd of the
+ *          k normalize and of the length-norm, GPTCosAttention.py:230,241)
+ */
+int cott_cos_attn_bwd_dq(const void* q, const void* k, const void* v, const float* norm_const,
+                         const void* dout, void* dq, int B, int H, int N, int Dk, int Dv, int dtype,
+                         void* stream);
+int cott_cos_attn_bwd_dkdv(const void* q, const void* k, const void* v, const float* norm_const,
+                           const void* dout, void* dk, void* dv, float* dnorm_const, int B, int H, int N,
+                           int Dk, int Dv, int dtype, void* stream);
+
+/*
+ * Device-side health check.  The tensor-core kernels bound every wait (TMA arrival, MMA
+ * completion); a wait that gives up records a code and the kernel returns without hanging.
+ * This call synchronises the current device, returns COTT_ERR_DEVICE_WAIT if a code was
+ * recorded since the last check (clearing it), else COTT_OK.  `detail` (may be NULL) receives
+ * the raw code: (stage << 16) | chunk.  No counterpart in the reference, which checks no errors.
+ */
+int cott_check_status(int* detail);
 
 #ifdef __cplusplus
 }
