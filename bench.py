@@ -57,7 +57,7 @@ class ClockSampler(threading.Thread):
     def __init__(self, index):
         super().__init__(daemon=True)
         self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
-        self._stop = threading.Event()
+        self._halt = threading.Event()
 
     def run(self):
         try:
@@ -71,7 +71,7 @@ class ClockSampler(threading.Thread):
                 nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
                 nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
             }
-            while not self._stop.is_set():
+            while not self._halt.is_set():
                 self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
                 r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
                 for bit, name in names.items():
@@ -82,7 +82,7 @@ class ClockSampler(threading.Thread):
             self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
 
     def stop(self):
-        self._stop.set()
+        self._halt.set()
         self.join(timeout=2)
         return {
             "sm_mhz": statistics.median(self.samples) if self.samples else None,
@@ -153,7 +153,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -229,7 +230,7 @@ def main():
     value = tokens_per_step / (ms_per_step * 1e-3)
 
     # ---- end to end: pinned host buffers in, host buffers out ------------------------------------------
-    host_out = [torch.empty_like(t).pin_memory() for t in (out, dq, dk, dv)]
+    host_out = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in (out, dq, dk, dv)]
     host_dnc = torch.empty(H, dtype=torch.float32).pin_memory()
     h2d = sum(t.numel() * t.element_size() for t in host)
     d2h = sum(t.numel() * t.element_size() for t in host_out) + H * 4
@@ -245,21 +246,23 @@ def main():
         host_dnc.copy_(ncd.grad, non_blocking=True)
 
     e2e_steps = max(3, min(args.steps, 10))
-    for _ in range(2):
-        e2e_step()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    e1.record()
-    barrier()
-    e2e_ms = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([e2e_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = t.item()
-    e2e_value = tokens_per_step * e2e_steps / (e2e_ms * 1e-3)
+    e2e_value = None
+    if not args.no_e2e:
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        e1.record()
+        barrier()
+        e2e_ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([e2e_ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_ms = t.item()
+        e2e_value = tokens_per_step * e2e_steps / (e2e_ms * 1e-3)
 
     if rank == 0:
         peak, peak_kind = _peaks()
