@@ -31,6 +31,21 @@ namespace cott {
 
 __device__ int g_cott_status;  // 0 = ok; else (code << 16 | chunk) of the first wait that gave up
 
+// Optional timeline tracing (debug builds only, -DCOTT_TRACE): CTA 0 records clock64() at role events.
+#ifdef COTT_TRACE
+constexpr int kTraceWarps = 10, kTraceChunks = 40, kTraceEvents = 8;
+__device__ long long g_cott_trace[kTraceWarps * kTraceChunks * kTraceEvents];
+#define COTT_TRACE_EV(ev, c)                                                                     \
+  do {                                                                                           \
+    if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (c) < kTraceChunks)                        \
+      g_cott_trace[((threadIdx.x >> 5) * kTraceChunks + (c)) * kTraceEvents + (ev)] = clock64(); \
+  } while (0)
+#else
+#define COTT_TRACE_EV(ev, c) \
+  do {                       \
+  } while (0)
+#endif
+
 constexpr int kTcChunk = 128;
 constexpr int kTcD = 64;
 constexpr int kTileBytes = kTcChunk * kTcD * 2;  // 16 KB: one [128 x 64] 16-bit tile
@@ -119,16 +134,26 @@ __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatil
                                          int chunk) {
   for (uint32_t i = 0; i < ptx::kMaxPolls; ++i) {
     if (ptx::mbar_try_wait(bar, parity)) return true;
+#ifdef COTT_POLL_SLEEP
+    __nanosleep(COTT_POLL_SLEEP);
+#endif
     if ((i & 255u) == 255u && *abort_flag) return false;
   }
   *abort_flag = 1;
   atomicCAS(&g_cott_status, 0, (code << 16) | (chunk & 0xffff));
   return false;
 }
-// Same, agreed on by the whole warp.
+// Whole-warp wait: only lane 0 polls (32 lanes polling an mbarrier flood the shared-memory
+// instruction queue and starve the LDS/STS/STG of the warps that have work); once lane 0 has seen
+// the phase complete, every lane tests the barrier once so that each thread itself observes the
+// completion (needed for the visibility of TMA-written data).
 __device__ __forceinline__ bool wait_bar_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code,
                                               int chunk) {
-  return __all_sync(0xffffffffu, wait_bar(bar, parity, abort_flag, code, chunk));
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = wait_bar(bar, parity, abort_flag, code, chunk) ? 1 : 0;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  if (ok) ptx::mbar_try_wait(bar, parity);
+  return ok != 0;
 }
 __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
   __syncwarp();
@@ -208,6 +233,11 @@ __device__ __forceinline__ void state_to_smem(uint32_t tS_lane, unsigned char* s
   }
 }
 
+// Descriptors of a [rows x 64] 16-bit tile with the 128-byte swizzle (see sm100_ptx.cuh).
+// K-major: advance K by 16 elements = +32 B = +2 in descriptor units; MN-major: +2048 B = +128.
+__device__ __forceinline__ uint64_t kdesc(uint32_t saddr) { return ptx::make_smem_desc(saddr, 16, 1024); }
+__device__ __forceinline__ uint64_t mdesc(uint32_t saddr) { return ptx::make_smem_desc(saddr, 8192, 1024); }
+
 enum { kModeFwd = 0, kModeDq = 1 };
 
 // which wait gave up (recorded in g_cott_status)
@@ -234,14 +264,15 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   // 1024-byte alignment is required by the 128-byte swizzle atoms
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                          ~static_cast<uintptr_t>(1023));
-  unsigned char* sS = smem + NS * STAGE;  // [64 x 64] 16-bit state operand, 8 KB
+  unsigned char* sS = smem + NS * STAGE;  // 2 x [64 x 64] 16-bit state operand (double-buffered), 2 x 8 KB
   __shared__ uint64_t bar_full[NS], bar_free[NS], bar_prep[NS], bar_p_full[2], bar_p_ready[2], bar_acc_full[2],
-      bar_acc_free[2], bar_state;
+      bar_acc_free[2], bar_s_full, bar_state;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag_s;
   volatile int* abort_flag = &abort_flag_s;
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // broadcast: provably warp-uniform
   const int bh = blockIdx.x;
   const int h = bh % H;
   const int nchunks = (N + kTcChunk - 1) / kTcChunk;
@@ -258,6 +289,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       mbar_init(&bar_acc_full[b], 1);
       mbar_init(&bar_acc_free[b], 4);
     }
+    mbar_init(&bar_s_full, 1);
     mbar_init(&bar_state, 4);
     mbar_fence_init();
     abort_flag_s = 0;
@@ -289,53 +321,89 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         tma_load_3d(st + kTileBytes, &mapY, &bar_full[s], 0, c * kTcChunk, bh);
         tma_load_3d(st + 2 * kTileBytes, &mapZ, &bar_full[s], 0, c * kTcChunk, bh);
         if (MODE == kModeDq) tma_load_3d(st + 3 * kTileBytes, &mapQ, &bar_full[s], 0, c * kTcChunk, bh);
+        COTT_TRACE_EV(0, c);
       }
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // The whole warp runs this loop with warp-uniform values; one elected lane issues.
+    {
+      // Lane 0 issues (it is also the lane that polls the barriers).  A leader picked by elect.sync
+      // faulted with an illegal address under back-to-back launches at the full problem size
+      // while a fixed lane 0 never did, so the leader is fixed.
+      const uint32_t el = lane == 0 ? 1u : 0u;
       constexpr uint32_t kIdescP = make_idesc(128, 128, BF, false, false);
       constexpr uint32_t kIdescAcc = make_idesc(128, 64, BF, false, true);
       constexpr uint32_t kIdescS = make_idesc(64, 64, BF, true, true);
-      const uint32_t s0 = smem_u32(sS);
+      const uint64_t dS0 = mdesc(smem_u32(sS));
       auto issue_scores = [&](int c) -> bool {
         const int s = c % NS;
-        if (!wait_bar(&bar_full[s], (c / NS) & 1, abort_flag, kWaitTma, c)) return false;
+        if (!wait_bar_warp(&bar_full[s], (c / NS) & 1, abort_flag, kWaitTma, c)) return false;
         tc_fence_after_sync();
-        const uint32_t x0 = smem_u32(smem + s * STAGE), y0 = x0 + kTileBytes;
+        COTT_TRACE_EV(6, c);
+        const uint32_t x0 = smem_u32(smem + s * STAGE);
+        const uint64_t dX = kdesc(x0), dY = kdesc(x0 + kTileBytes);
         const uint32_t tP = tP0 + 128 * (c & 1);
+        if (el) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          mma_ss(tP, make_smem_desc(x0 + 32 * k, 16, 1024), make_smem_desc(y0 + 32 * k, 16, 1024), kIdescP, k > 0);
-        mma_commit(&bar_p_full[c & 1]);
+          for (int k = 0; k < 4; ++k) mma_ss(tP, dX + 2 * k, dY + 2 * k, kIdescP, k > 0);
+          mma_commit(&bar_p_full[c & 1]);
+        }
+        __syncwarp();
+        COTT_TRACE_EV(7, c);
         return true;
       };
+      // Issue order per chunk c -- chosen so that nothing this warp waits for was requested
+      // less than about one chunk period earlier:
+      //   S += Y^T Zw (c)      needs Zw(c) and the conversion of S after chunk c-1
+      //   scores (c+1)         needs the TMA of chunk c+1
+      //   Acc = X S (c)        needs the 16-bit S converted after chunk c-1 (buffer c&1)
+      //   Acc += P Zw (c)      needs the masked scores of chunk c (issued one chunk earlier)
       bool ok = issue_scores(0);
       for (int c = 0; ok && c < nchunks; ++c) {
         const int s = c % NS, b = c & 1;
-        const uint32_t x0 = smem_u32(smem + s * STAGE), y0 = x0 + kTileBytes, z0 = x0 + 2 * kTileBytes;
+        const uint32_t x0 = smem_u32(smem + s * STAGE);
+        const uint64_t dX = kdesc(x0), dYm = mdesc(x0 + kTileBytes), dZm = mdesc(x0 + 2 * kTileBytes);
         const uint32_t tP = tP0 + 128 * b, tAcc = tAcc0 + 64 * b;
-        if (c >= 2 && !(ok = wait_bar(&bar_acc_free[b], ((c >> 1) - 1) & 1, abort_flag, kWaitAccFree, c))) break;
-        if (c > 0) {
-          if (!(ok = wait_bar(&bar_state, (c - 1) & 1, abort_flag, kWaitState, c))) break;
-          tc_fence_after_sync();
-#pragma unroll
-          for (int k = 0; k < 4; ++k)  // Acc = X S   (S as MN-major B operand)
-            mma_ss(tAcc, make_smem_desc(x0 + 32 * k, 16, 1024), make_smem_desc(s0 + 2048 * k, 8192, 1024), kIdescAcc,
-                   k > 0);
-        }
-        if (c + 1 < nchunks && !(ok = issue_scores(c + 1))) break;
-        if (!(ok = wait_bar(&bar_prep[s], (c / NS) & 1, abort_flag, kWaitPrepped, c))) break;
-        if (!(ok = wait_bar(&bar_p_ready[b], (c >> 1) & 1, abort_flag, kWaitScoreReady, c))) break;
+        const uint32_t acc_s = c > 0 ? 1u : 0u;
+        if (!(ok = wait_bar_warp(&bar_prep[s], (c / NS) & 1, abort_flag, kWaitPrepped, c))) break;
+        if (c > 0 && !(ok = wait_bar_warp(&bar_state, (c - 1) & 1, abort_flag, kWaitState, c))) break;
         tc_fence_after_sync();
+        COTT_TRACE_EV(0, c);
+        if (c + 1 < nchunks) {
+          if (el) {
+            mma_ss(tS, dYm, dZm, kIdescS, acc_s);  // S += Y^T Zw
 #pragma unroll
-        for (int k = 0; k < 8; ++k)  // Acc += P Zw   (P from TMEM, Zw MN-major)
-          mma_ts(tAcc, tP + 8 * k, make_smem_desc(z0 + 2048 * k, 8192, 1024), kIdescAcc, (c > 0 || k > 0));
+            for (int k = 1; k < 8; ++k) mma_ss(tS, dYm + 128 * k, dZm + 128 * k, kIdescS, 1u);
+            mma_commit(&bar_s_full);
+          }
+          __syncwarp();
+          COTT_TRACE_EV(5, c);
+          if (!(ok = issue_scores(c + 1))) break;
+        }
+        COTT_TRACE_EV(1, c);
+        if (c >= 2 && !(ok = wait_bar_warp(&bar_acc_free[b], ((c >> 1) - 1) & 1, abort_flag, kWaitAccFree, c))) break;
+        if (c > 0) {
+          tc_fence_after_sync();
+          const uint64_t dS = dS0 + static_cast<uint64_t>(b * ((kTcD * 128) >> 4));
+          if (el) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k)  // S += Y^T Zw
-          mma_ss(tS, make_smem_desc(y0 + 2048 * k, 8192, 1024), make_smem_desc(z0 + 2048 * k, 8192, 1024), kIdescS,
-                 (c > 0 || k > 0));
-        mma_commit(&bar_acc_full[b]);
+            for (int k = 0; k < 4; ++k)  // Acc = X S   (S as MN-major B operand)
+              mma_ss(tAcc, dX + 2 * k, dS + 128 * k, kIdescAcc, k > 0);
+          }
+          __syncwarp();
+        }
+        if (!(ok = wait_bar_warp(&bar_p_ready[b], (c >> 1) & 1, abort_flag, kWaitScoreReady, c))) break;
+        tc_fence_after_sync();
+        COTT_TRACE_EV(2, c);
+        if (el) {
+          mma_ts(tAcc, tP, dZm, kIdescAcc, acc_s);  // Acc += P Zw   (P from TMEM, Zw MN-major)
+#pragma unroll
+          for (int k = 1; k < 8; ++k) mma_ts(tAcc, tP + 8 * k, dZm + 128 * k, kIdescAcc, 1u);
+          mma_commit(&bar_acc_full[b]);
+        }
+        __syncwarp();
+        COTT_TRACE_EV(3, c);
       }
     }
   } else if (warp < 6) {
@@ -346,13 +414,18 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
     auto prepare = [&](int c) -> bool {  // Zw = diag(a_s / |k_s|) Z, in place
       const int s = c % NS;
       if (!wait_bar_warp(&bar_full[s], (c / NS) & 1, abort_flag, kWaitTma, c)) return false;
+      COTT_TRACE_EV(3, c);
       unsigned char* sZ = smem + s * STAGE + 2 * kTileBytes;
       unsigned char* sK = (MODE == kModeDq) ? sZ : smem + s * STAGE + kTileBytes;
       const float rk = inv_norm(row_sumsq<T>(sK, row));
+      COTT_TRACE_EV(4, c);
       const float a = length_factor(static_cast<float>(c * kTcChunk + row + 1), sigma);
+      COTT_TRACE_EV(5, c);
       scale_row<T>(sZ, row, rk * a);
+      COTT_TRACE_EV(6, c);
       fence_proxy_async_smem();
       warp_arrive(&bar_prep[s], lane);
+      COTT_TRACE_EV(7, c);
       return true;
     };
     bool ok = prepare(0);
@@ -360,10 +433,13 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       const int b = c & 1;
       if (!(ok = wait_bar_warp(&bar_p_full[b], (c >> 1) & 1, abort_flag, kWaitScore, c))) break;
       tc_fence_after_sync();
+      COTT_TRACE_EV(0, c);
       mask_pack_inplace<T>(tP0 + 128 * b + lane_base, 0, row, 0, wq);
       tc_fence_before_sync();
       warp_arrive(&bar_p_ready[b], lane);
+      COTT_TRACE_EV(1, c);
       if (c + 1 < nchunks) ok = prepare(c + 1);
+      COTT_TRACE_EV(2, c);
     }
   } else {
     // ---------------------------------------------------------------- output group
@@ -375,18 +451,24 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       // the row norm of q only needs the TMA data: do it while the MMAs run
       if (!wait_bar_warp(&bar_full[s], (c / NS) & 1, abort_flag, kWaitTma, c)) break;
       const float rq = inv_norm(row_sumsq<T>(sQ, row));
-      if (!wait_bar_warp(&bar_acc_full[b], (c >> 1) & 1, abort_flag, kWaitAcc, c)) break;
-      tc_fence_after_sync();
-      if (c + 1 < nchunks) {
-        state_to_smem<T>(tS + lane_base, sS, wq, lane);
+      COTT_TRACE_EV(0, c);
+      if (c + 1 < nchunks) {  // S after chunk c -> 16-bit operand for chunk c+1 (buffer (c+1)&1)
+        if (!wait_bar_warp(&bar_s_full, c & 1, abort_flag, kWaitState, c)) break;
+        tc_fence_after_sync();
+        state_to_smem<T>(tS + lane_base, sS + ((c + 1) & 1) * (kTcD * 128), wq, lane);
         fence_proxy_async_smem();
         tc_fence_before_sync();
         warp_arrive(&bar_state, lane);
       }
+      COTT_TRACE_EV(1, c);
+      if (!wait_bar_warp(&bar_acc_full[b], (c >> 1) & 1, abort_flag, kWaitAcc, c)) break;
+      tc_fence_after_sync();
+      COTT_TRACE_EV(2, c);
       float acc[64];
       tmem_row64(tAcc0 + 64 * b + lane_base, acc);
       tc_fence_before_sync();
       warp_arrive(&bar_acc_free[b], lane);
+      COTT_TRACE_EV(3, c);
       if (MODE == kModeFwd) {
 #pragma unroll
         for (int j = 0; j < 64; ++j) acc[j] *= rq;
@@ -400,7 +482,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
           delta += p0.x * acc[8 * j] + p0.y * acc[8 * j + 1] + p1.x * acc[8 * j + 2] + p1.y * acc[8 * j + 3] +
                    p2.x * acc[8 * j + 4] + p2.y * acc[8 * j + 5] + p3.x * acc[8 * j + 6] + p3.y * acc[8 * j + 7];
         }
-        delta *= rq * rq;  // q^ . dq^ times 1/|q|
+        delta *= rq * rq * rq;  // (q^ . dq^) / |q|^2, with dq^ = acc and q^ = rq q
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           uint4 u = *tile_piece(sQ, row, j);
@@ -416,9 +498,12 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
           acc[8 * j + 7] = rq * acc[8 * j + 7] - p3.y * delta;
         }
       }
+      COTT_TRACE_EV(5, c);
       warp_arrive(&bar_free[s], lane);  // last read of this stage by this warp
+      COTT_TRACE_EV(6, c);
       const int pos = c * kTcChunk + row;
       if (pos < N) store_row64<T>(out + (static_cast<size_t>(bh) * N + pos) * kTcD, acc);
+      COTT_TRACE_EV(4, c);
     }
   }
 
@@ -434,10 +519,271 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
-/*KV_KERNEL*/
+// -------------------------------------------------------------------------------------------------
+// dK, dV and the gradient of the length-norm parameter: one reverse-direction pass.
+//
+// With q^ = q/|q| (written back to smem as the 16-bit operand Qw), R = sum_{t > chunk} q^_t (x) dO_t:
+//   E = mask_{t>=s}(V dO^T)        F = mask_{t>=s}(K Qw^T)            tcgen05 128x128x64 each
+//   AccK = E Qw + V R^T            AccV = F dO + K R                  tcgen05 128x64x128 + 128x64x64
+//   R   += Qw^T dO                                                    tcgen05 64x64x128 (M=64)
+//   dv'_s = AccV_s / |k_s|         (gradient w.r.t. v' = a_s v)       dv_s = a_s dv'_s
+//   eps_s = v'_s . dv'_s           (= k^_s . dk^_s)
+//   dk^_s = a_s AccK_s             dk_s = (dk^_s - k^_s eps_s) / |k_s|
+//   d norm_const[h] += -sigma (1 - sigma) sum_s ln(n_s) eps_s         (GPTCosAttention.py:241 by the chain rule)
+// Same warp roles as causal_tc_kernel; the two score tiles fill TMEM, so they are single-buffered:
+// the score MMAs of chunk c+1 are queued right behind the accumulator MMAs of chunk c.
+template <typename T>
+__global__ void __launch_bounds__(kTcThreads, 1)
+causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                     const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
+                     T* __restrict__ dk, T* __restrict__ dv, float* __restrict__ dnorm,
+                     const float* __restrict__ norm_const, int H, int N) {
+  using namespace ptx;
+  constexpr int STAGE = 4 * kTileBytes;
+  constexpr int NS = kTcStages;
+  constexpr bool BF = Pack2<T>::kBf16;
+
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                                         ~static_cast<uintptr_t>(1023));
+  unsigned char* sR = smem + NS * STAGE;  // [64 x 64] 16-bit state operand (rows = d_k, cols = d_v)
+  __shared__ uint64_t bar_full[NS], bar_free[NS], bar_prep[NS], bar_p_full, bar_p_ready, bar_acc_full, bar_acc_free,
+      bar_state;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag_s;
+  volatile int* abort_flag = &abort_flag_s;
+
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // broadcast: provably warp-uniform
+  const int bh = blockIdx.x;
+  const int h = bh % H;
+  const int nchunks = (N + kTcChunk - 1) / kTcChunk;
+
+  if (tid == 0) {
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(&bar_full[s], 1);
+      mbar_init(&bar_free[s], 4);
+      mbar_init(&bar_prep[s], 4);
+    }
+    mbar_init(&bar_p_full, 1);
+    mbar_init(&bar_p_ready, 4);
+    mbar_init(&bar_acc_full, 1);
+    mbar_init(&bar_acc_free, 4);
+    mbar_init(&bar_state, 4);
+    mbar_fence_init();
+    abort_flag_s = 0;
+    tma_prefetch_desc(&mapQ);
+    tma_prefetch_desc(&mapK);
+    tma_prefetch_desc(&mapV);
+    tma_prefetch_desc(&mapDO);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t tE = tmem, tF = tmem + 128, tK = tmem + 256, tV = tmem + 320, tR = tmem + 384;
+
+  // iteration ci handles chunk nchunks-1-ci (the sequence is walked backwards)
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int ci = 0; ci < nchunks; ++ci) {
+        const int s = ci % NS;
+        if (ci >= NS && !wait_bar(&bar_free[s], ((ci / NS) - 1) & 1, abort_flag, kWaitStageFree, ci)) break;
+        const int y = (nchunks - 1 - ci) * kTcChunk;
+        unsigned char* st = smem + s * STAGE;
+        mbar_expect_tx(&bar_full[s], STAGE);
+        tma_load_3d(st, &mapQ, &bar_full[s], 0, y, bh);
+        tma_load_3d(st + kTileBytes, &mapK, &bar_full[s], 0, y, bh);
+        tma_load_3d(st + 2 * kTileBytes, &mapV, &bar_full[s], 0, y, bh);
+        tma_load_3d(st + 3 * kTileBytes, &mapDO, &bar_full[s], 0, y, bh);
+      }
+    }
+  } else if (warp == 1) {
+    // MMA issuer: the whole warp runs the loop with warp-uniform values; lane 0 issues
+    {
+      const uint32_t el = lane == 0 ? 1u : 0u;
+      constexpr uint32_t kIdescP = make_idesc(128, 128, BF, false, false);
+      constexpr uint32_t kIdescAccKK = make_idesc(128, 64, BF, false, false);  // B K-major (V R^T)
+      constexpr uint32_t kIdescAccMN = make_idesc(128, 64, BF, false, true);   // B MN-major
+      constexpr uint32_t kIdescR = make_idesc(64, 64, BF, true, true);
+      const uint64_t dRk = kdesc(smem_u32(sR)), dRm = mdesc(smem_u32(sR));
+      auto issue_scores = [&](int ci) -> bool {
+        const int s = ci % NS;
+        if (!wait_bar_warp(&bar_full[s], (ci / NS) & 1, abort_flag, kWaitTma, ci)) return false;
+        if (!wait_bar_warp(&bar_prep[s], (ci / NS) & 1, abort_flag, kWaitPrepped, ci)) return false;
+        tc_fence_after_sync();
+        const uint32_t q0 = smem_u32(smem + s * STAGE);
+        const uint64_t dQ = kdesc(q0), dK = kdesc(q0 + kTileBytes), dV = kdesc(q0 + 2 * kTileBytes),
+                       dD = kdesc(q0 + 3 * kTileBytes);
+        if (el) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) mma_ss(tE, dV + 2 * k, dD + 2 * k, kIdescP, k > 0);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) mma_ss(tF, dK + 2 * k, dQ + 2 * k, kIdescP, k > 0);
+          mma_commit(&bar_p_full);
+        }
+        __syncwarp();
+        return true;
+      };
+      bool ok = issue_scores(0);
+      for (int ci = 0; ok && ci < nchunks; ++ci) {
+        const int s = ci % NS;
+        const uint32_t q0 = smem_u32(smem + s * STAGE);
+        const uint64_t dK = kdesc(q0 + kTileBytes), dV = kdesc(q0 + 2 * kTileBytes), dQm = mdesc(q0),
+                       dDm = mdesc(q0 + 3 * kTileBytes);
+        const uint32_t acc0 = ci > 0 ? 1u : 0u;
+        if (ci > 0) {
+          if (!(ok = wait_bar_warp(&bar_acc_free, (ci - 1) & 1, abort_flag, kWaitAccFree, ci))) break;
+          if (!(ok = wait_bar_warp(&bar_state, (ci - 1) & 1, abort_flag, kWaitState, ci))) break;
+          tc_fence_after_sync();
+          if (el) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k)  // AccK = V R^T : B[n = d_k][k = d_v] = R, K-major
+              mma_ss(tK, dV + 2 * k, dRk + 2 * k, kIdescAccKK, k > 0);
+#pragma unroll
+            for (int k = 0; k < 4; ++k)  // AccV = K R : B[n = d_v][k = d_k] = R, MN-major
+              mma_ss(tV, dK + 2 * k, dRm + 128 * k, kIdescAccMN, k > 0);
+          }
+          __syncwarp();
+        }
+        if (!(ok = wait_bar_warp(&bar_p_ready, ci & 1, abort_flag, kWaitScoreReady, ci))) break;
+        tc_fence_after_sync();
+        if (el) {
+          mma_ts(tK, tE, dQm, kIdescAccMN, acc0);
+#pragma unroll
+          for (int k = 1; k < 8; ++k) mma_ts(tK, tE + 8 * k, dQm + 128 * k, kIdescAccMN, 1u);
+          mma_ts(tV, tF, dDm, kIdescAccMN, acc0);
+#pragma unroll
+          for (int k = 1; k < 8; ++k) mma_ts(tV, tF + 8 * k, dDm + 128 * k, kIdescAccMN, 1u);
+          mma_ss(tR, dQm, dDm, kIdescR, acc0);
+#pragma unroll
+          for (int k = 1; k < 8; ++k) mma_ss(tR, dQm + 128 * k, dDm + 128 * k, kIdescR, 1u);
+          mma_commit(&bar_acc_full);
+        }
+        __syncwarp();
+        if (ci + 1 < nchunks) ok = issue_scores(ci + 1);
+      }
+    }
+  } else if (warp < 6) {
+    // score group: Qw = q^ in place, then mask + convert E and F
+    const int wq = warp & 3, row = 32 * wq + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(32 * wq) << 16;
+    auto prepare = [&](int ci) -> bool {
+      const int s = ci % NS;
+      if (!wait_bar_warp(&bar_full[s], (ci / NS) & 1, abort_flag, kWaitTma, ci)) return false;
+      unsigned char* sQ = smem + s * STAGE;
+      scale_row<T>(sQ, row, inv_norm(row_sumsq<T>(sQ, row)));
+      fence_proxy_async_smem();
+      warp_arrive(&bar_prep[s], lane);
+      return true;
+    };
+    bool ok = prepare(0);
+    for (int ci = 0; ok && ci < nchunks; ++ci) {
+      if (ci + 1 < nchunks && !(ok = prepare(ci + 1))) break;
+      if (!(ok = wait_bar_warp(&bar_p_full, ci & 1, abort_flag, kWaitScore, ci))) break;
+      tc_fence_after_sync();
+      mask_pack_inplace<T>(tE + lane_base, row, 127, wq, 3);
+      mask_pack_inplace<T>(tF + lane_base, row, 127, wq, 3);
+      tc_fence_before_sync();
+      warp_arrive(&bar_p_ready, lane);
+    }
+  } else {
+    // output group
+    const int wq = warp & 3, row = 32 * wq + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(32 * wq) << 16;
+    const float sigma = 1.0f / (1.0f + __expf(-norm_const[h]));
+    float gsum = 0.f;  // sum_s ln(n_s) eps_s over this thread's rows
+    for (int ci = 0; ci < nchunks; ++ci) {
+      const int s = ci % NS;
+      unsigned char* sK = smem + s * STAGE + kTileBytes;
+      unsigned char* sV = smem + s * STAGE + 2 * kTileBytes;
+      const int pos = (nchunks - 1 - ci) * kTcChunk + row;
+      if (!wait_bar_warp(&bar_full[s], (ci / NS) & 1, abort_flag, kWaitTma, ci)) break;
+      const float rk = inv_norm(row_sumsq<T>(sK, row));
+      const float a = length_factor(static_cast<float>(pos + 1), sigma);
+      if (!wait_bar_warp(&bar_acc_full, ci & 1, abort_flag, kWaitAcc, ci)) break;
+      tc_fence_after_sync();
+      if (ci + 1 < nchunks) {
+        state_to_smem<T>(tR + lane_base, sR, wq, lane);
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        warp_arrive(&bar_state, lane);
+      }
+      float accv[64], acck[64];
+      {
+        uint32_t r0[64], r1[64];
+        tmem_ld_x64(tV + lane_base, r0);
+        tmem_ld_x64(tK + lane_base, r1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          accv[j] = __uint_as_float(r0[j]) * rk;  // dv'
+          acck[j] = __uint_as_float(r1[j]) * a;   // dk^
+        }
+      }
+      tc_fence_before_sync();
+      warp_arrive(&bar_acc_free, lane);
+      float eps = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        uint4 u = *tile_piece(sV, row, j);
+        float2 p0 = Pack2<T>::unpack(u.x), p1 = Pack2<T>::unpack(u.y), p2 = Pack2<T>::unpack(u.z),
+               p3 = Pack2<T>::unpack(u.w);
+        eps += p0.x * accv[8 * j] + p0.y * accv[8 * j + 1] + p1.x * accv[8 * j + 2] + p1.y * accv[8 * j + 3] +
+               p2.x * accv[8 * j + 4] + p2.y * accv[8 * j + 5] + p3.x * accv[8 * j + 6] + p3.y * accv[8 * j + 7];
+      }
+      eps *= a;  // v' . dv'
+      const float ke = rk * eps;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        uint4 u = *tile_piece(sK, row, j);
+        float2 p0 = Pack2<T>::unpack(u.x), p1 = Pack2<T>::unpack(u.y), p2 = Pack2<T>::unpack(u.z),
+               p3 = Pack2<T>::unpack(u.w);
+        acck[8 * j + 0] = rk * (acck[8 * j + 0] - p0.x * ke);
+        acck[8 * j + 1] = rk * (acck[8 * j + 1] - p0.y * ke);
+        acck[8 * j + 2] = rk * (acck[8 * j + 2] - p1.x * ke);
+        acck[8 * j + 3] = rk * (acck[8 * j + 3] - p1.y * ke);
+        acck[8 * j + 4] = rk * (acck[8 * j + 4] - p2.x * ke);
+        acck[8 * j + 5] = rk * (acck[8 * j + 5] - p2.y * ke);
+        acck[8 * j + 6] = rk * (acck[8 * j + 6] - p3.x * ke);
+        acck[8 * j + 7] = rk * (acck[8 * j + 7] - p3.y * ke);
+      }
+      warp_arrive(&bar_free[s], lane);  // last read of this stage by this warp
+      if (pos < N) {
+#pragma unroll
+        for (int j = 0; j < 64; ++j) accv[j] *= a;
+        store_row64<T>(dv + (static_cast<size_t>(bh) * N + pos) * kTcD, accv);
+        store_row64<T>(dk + (static_cast<size_t>(bh) * N + pos) * kTcD, acck);
+        if (pos > 0) gsum += logf(static_cast<float>(pos + 1)) * eps;
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) gsum += __shfl_down_sync(0xffffffffu, gsum, off);
+    if (lane == 0) atomicAdd(dnorm + h, -sigma * (1.0f - sigma) * gsum);
+  }
+
+  __syncwarp();
+  tc_fence_before_sync();
+  __syncthreads();
+  if (tid == 0 && *abort_flag) {
+    for (int ci = (nchunks > NS ? nchunks - NS : 0); ci < nchunks; ++ci)
+      mbar_wait(&bar_full[ci % NS], (ci / NS) & 1, 1u << 16);
+  }
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+inline size_t causal_bwd_kv_smem_bytes() {
+  return static_cast<size_t>(kTcStages * 4 * kTileBytes + kTcD * 128 + 1024);
+}
+
 inline size_t causal_tc_smem_bytes(int mode) {
   const int nt = mode == kModeFwd ? 3 : 4;
-  return static_cast<size_t>(kTcStages * nt * kTileBytes + kTcD * 128 + 1024);
+  return static_cast<size_t>(kTcStages * nt * kTileBytes + 2 * kTcD * 128 + 1024);
 }
 
 }  // namespace cott

@@ -44,7 +44,7 @@ int launch_fwd(const void* q, const void* k, const void* v, const float* nc, voi
   auto kern = causal_tc_kernel<T, kModeFwd>;
   const size_t smem = causal_tc_smem_bytes(kModeFwd);
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<(unsigned)BH, 128, smem, stream>>>(mq, mk, mv, mq, static_cast<T*>(out), nc, H, N);
+  kern<<<(unsigned)BH, kTcThreads, smem, stream>>>(mq, mk, mv, mq, static_cast<T*>(out), nc, H, N);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
@@ -61,7 +61,7 @@ int launch_bwd_dq(const void* q, const void* k, const void* v, const float* nc, 
   auto kern = causal_tc_kernel<T, kModeDq>;
   const size_t smem = causal_tc_smem_bytes(kModeDq);
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<(unsigned)BH, 128, smem, stream>>>(md, mv, mk, mq, static_cast<T*>(dq), nc, H, N);
+  kern<<<(unsigned)BH, kTcThreads, smem, stream>>>(md, mv, mk, mq, static_cast<T*>(dq), nc, H, N);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
@@ -79,7 +79,7 @@ int launch_bwd_dkdv(const void* q, const void* k, const void* v, const float* nc
   auto kern = causal_bwd_kv_kernel<T>;
   const size_t smem = causal_bwd_kv_smem_bytes();
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<(unsigned)BH, 128, smem, stream>>>(mq, mk, mv, md, static_cast<T*>(dk), static_cast<T*>(dv), dnorm, nc, H,
+  kern<<<(unsigned)BH, kTcThreads, smem, stream>>>(mq, mk, mv, md, static_cast<T*>(dk), static_cast<T*>(dv), dnorm, nc, H,
                                             N);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
