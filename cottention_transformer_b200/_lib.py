@@ -30,6 +30,8 @@ _SIGNATURES = {
     "cott_cos_attn_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "cott_cos_attn_bwd_dq": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "cott_cos_attn_bwd_dkdv": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "cott_decode_step": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, ctypes.c_longlong, _P, _P],
+    "cott_decode_steps": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, ctypes.c_longlong, _P, _P],
     "cott_check_status": [ctypes.POINTER(ctypes.c_int)],
 }
 _STR = {"cott_version": [], "cott_last_error": [], "cott_status_string": [_I]}

@@ -1,6 +1,7 @@
 // C ABI of cottention_b200: argument validation and dispatch.  No torch types here;
 // the Python host (ctypes) and any other FFI bind these symbols directly.
 #include "common.cuh"
+#include "decode.cuh"
 #include "scan_simt.cuh"
 
 using namespace cott;
@@ -84,6 +85,36 @@ int cott_scan_bwd(const void* q, const void* k, const void* v, const void* dout,
   if (st != COTT_OK) return st;
   // dv = scan(k, q, dout, reversed)
   return scan_dispatch(k, q, dout, dv, B, H, N, Dk, Dv, dtype, 1, s);
+}
+
+
+int cott_decode_steps(float* state, const void* q, const void* k, const void* v, const float* norm_const, void* out,
+                      int B, int H, int T, int Dk, int Dv, int dtype, long long pos, const long long* positions,
+                      void* stream) {
+  if (dtype != COTT_F32 && dtype != COTT_F16 && dtype != COTT_BF16)
+    return fail(COTT_ERR_DTYPE, "decode takes float32/float16/bfloat16 tokens and a float32 state (dtype code %d)", dtype);
+  if (B < 0 || H < 0 || T < 0) return fail(COTT_ERR_SHAPE, "negative size B=%d H=%d T=%d", B, H, T);
+  if (Dk != 16 && Dk != 32 && Dk != 64 && Dk != 128)
+    return fail(COTT_ERR_SHAPE, "decode supports D_attn in {16, 32, 64, 128} (got %d)", Dk);
+  if (Dv < 1 || Dv > 128) return fail(COTT_ERR_SHAPE, "decode supports D_value in [1, 128] (got %d)", Dv);
+  if (!positions && pos < 1) return fail(COTT_ERR_SHAPE, "positions are 1-based (got %lld)", pos);
+  if ((long)B * H * T == 0) return COTT_OK;
+  if (!state || !q || !k || !v || !norm_const || !out) return fail(COTT_ERR_NULL, "null pointer");
+  if (reinterpret_cast<uintptr_t>(state) & 15) return fail(COTT_ERR_ALIGN, "state must be 16-byte aligned");
+  DeviceScope scope(state);
+  COTT_CUDA_TRY(scope.status());
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case COTT_F32: return launch_decode<float>(state, q, k, v, norm_const, out, B, H, Dk, Dv, T, pos, positions, s);
+    case COTT_F16: return launch_decode<__half>(state, q, k, v, norm_const, out, B, H, Dk, Dv, T, pos, positions, s);
+    default: return launch_decode<__nv_bfloat16>(state, q, k, v, norm_const, out, B, H, Dk, Dv, T, pos, positions, s);
+  }
+}
+
+int cott_decode_step(float* state, const void* q, const void* k, const void* v, const float* norm_const, void* out,
+                     int B, int H, int Dk, int Dv, int dtype, long long pos, const long long* positions,
+                     void* stream) {
+  return cott_decode_steps(state, q, k, v, norm_const, out, B, H, 1, Dk, Dv, dtype, pos, positions, stream);
 }
 
 }  // extern "C"

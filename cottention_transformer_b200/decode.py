@@ -1,0 +1,44 @@
+"""Recurrent decode state for cosine attention: the B200 replacement of the reference's
+``fast_inference`` branch (``GPT_Trainer/GPTCosAttention.py:76-85,235-272``).
+
+The reference keeps, per attention module, ``past_KV`` (float64 ``[1, H, d, d]``, V index first)
+and ``cur_s`` (1-based position) as module attributes and loops over tokens in Python on the CPU.
+``CosAttnDecodeState`` holds the same two things on the GPU -- float32 ``[B, H, d_v, d_k]`` plus a
+position counter -- and advances them with ``cott_decode_step`` / ``cott_decode_steps``.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+
+class CosAttnDecodeState:
+    def __init__(self, batch: int, heads: int, d_k: int, d_v: int | None = None, device="cuda"):
+        d_v = d_k if d_v is None else d_v
+        self.state = torch.zeros(batch, heads, d_v, d_k, dtype=torch.float32, device=device)
+        self.cur_s = 1  # GPTCosAttention.py:82
+
+    def reset(self):
+        self.state.zero_()
+        self.cur_s = 1
+
+    def step(self, q, k, v, norm_const):
+        """q, k: ``[B, H, T, d_k]``; v: ``[B, H, T, d_v]`` (T >= 1 tokens, e.g. a prompt or one new
+        token).  Returns ``[B, H, T, d_v]`` and advances the state and the position by T."""
+        if not q.is_cuda:
+            raise RuntimeError("decode needs CUDA tensors (there is no CPU path)")
+        B, H, T, Dk = q.shape
+        Dv = v.shape[-1]
+        if q.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+            raise RuntimeError("decode takes float32, float16 or bfloat16 tokens")
+        q, k, v = q.contiguous(), k.to(q.dtype).contiguous(), v.to(q.dtype).contiguous()
+        nc = norm_const.detach().reshape(-1).to(device=q.device, dtype=torch.float32).contiguous()
+        out = torch.empty(B, H, T, Dv, dtype=q.dtype, device=q.device)
+        with torch.cuda.device(q.device):
+            st = _lib.lib().cott_decode_steps(
+                _lib.ptr(self.state), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(nc), _lib.ptr(out),
+                B, H, T, Dk, Dv, _lib.DTYPE_CODE[q.dtype], self.cur_s, None, _lib.stream_ptr(q.device))
+        _lib.check(st, "cott_decode_steps")
+        self.cur_s += T  # GPTCosAttention.py:269
+        return out

@@ -114,6 +114,34 @@ int cott_cos_attn_bwd_dkdv(const void* q, const void* k, const void* v, const fl
                            int Dk, int Dv, int dtype, void* stream);
 
 /*
+ * Recurrent decode.  Per (batch, head) a float32 state[b,h,j,i] ([B,H,Dv,Dk], updated in place) is
+ * advanced by one token:
+ *   q^ = q/|q|, k^ = k/|k|, v' = v / max(pos^sigmoid(norm_const[h]), 1)
+ *   state[j][i] += v'[j] k^[i]        out[j] = sum_i q^[i] state[j][i]
+ * q, k are [B,H,Dk], v and out [B,H,Dv] of `dtype` (COTT_F32, COTT_F16 or COTT_BF16).  `pos` is the
+ * 1-based position of the token (the reference's cur_s); if `positions` is not NULL it is an array
+ * of B int64 positions in device memory, one per batch entry, and `pos` is ignored.
+ *
+ * Replaces the fast_inference branch of GPTCosAttention._cos_attn for one token,
+ * GPT_Trainer/GPTCosAttention.py:229-230,236,253-272 (state init :76-85; driven token by token by
+ * GPT_Trainer/fast_infer.py:111-139).  The reference keeps a float64 [1,H,d,d] state on the CPU;
+ * this one is float32, batched, in HBM.  Dk in {16,32,64,128}, 1 <= Dv <= 128.
+ */
+int cott_decode_step(float* state, const void* q, const void* k, const void* v, const float* norm_const,
+                     void* out, int B, int H, int Dk, int Dv, int dtype, long long pos,
+                     const long long* positions, void* stream);
+
+/*
+ * T consecutive decode steps in one launch: q, k [B,H,T,Dk], v, out [B,H,T,Dv]; token t of batch
+ * entry b sits at position (positions ? positions[b] : pos) + t.  The state is read once, kept in
+ * registers for the T steps and written back once.  This is the reference's loop over the tokens
+ * of a prompt in the same branch (GPTCosAttention.py:262-269).
+ */
+int cott_decode_steps(float* state, const void* q, const void* k, const void* v, const float* norm_const,
+                      void* out, int B, int H, int T, int Dk, int Dv, int dtype, long long pos,
+                      const long long* positions, void* stream);
+
+/*
  * Device-side health check.  The tensor-core kernels bound every wait (TMA arrival, MMA
  * completion); a wait that gives up records a code and the kernel returns without hanging.
  * This call synchronises the current device, returns COTT_ERR_DEVICE_WAIT if a code was
