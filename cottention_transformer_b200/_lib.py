@@ -32,16 +32,19 @@ _SIGNATURES = {
     "cott_cos_attn_bwd_dkdv": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "cott_decode_step": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, ctypes.c_longlong, _P, _P],
     "cott_decode_steps": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, ctypes.c_longlong, _P, _P],
+    "cott_bidir_fwd": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "cott_bidir_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "cott_check_status": [ctypes.POINTER(ctypes.c_int)],
 }
 _STR = {"cott_version": [], "cott_last_error": [], "cott_status_string": [_I]}
+_SIZE = {"cott_bidir_scratch_bytes": [_I, _I, _I, _I, _I, _I]}
 
 _lib = None
 launch_count = 0  # kernels launched through this binding (bookkeeping for the benchmark)
 
 
 def exported_symbols() -> list[str]:
-    return sorted(list(_SIGNATURES) + list(_STR))
+    return sorted(list(_SIGNATURES) + list(_STR) + list(_SIZE))
 
 
 def lib() -> ctypes.CDLL:
@@ -59,6 +62,9 @@ def lib() -> ctypes.CDLL:
         for name, args in _STR.items():
             fn = getattr(L, name)
             fn.argtypes, fn.restype = args, ctypes.c_char_p
+        for name, args in _SIZE.items():
+            fn = getattr(L, name)
+            fn.argtypes, fn.restype = args, ctypes.c_size_t
         _lib = L
     return _lib
 

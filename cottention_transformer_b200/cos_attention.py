@@ -93,3 +93,58 @@ def cos_attn_causal(q, k, v, norm_const, keep=None):
     if fused_supported(q, k, v, keep):
         return _FusedCausal.apply(q, k, v, norm_const)
     return _exact_causal(q, k, v, norm_const, keep)
+
+
+class _Bidirectional(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, norm_const, keep):
+        q, k, v = q.contiguous(), k.to(q.dtype).contiguous(), v.to(q.dtype).contiguous()
+        B, H, N, Dk = q.shape
+        Dv = v.shape[-1]
+        L = _lib.lib()
+        code = _lib.DTYPE_CODE[q.dtype]
+        nc = norm_const.detach().reshape(-1).to(device=q.device, dtype=torch.float32).contiguous()
+        kp = None if keep is None else keep.to(device=q.device, dtype=torch.uint8).contiguous()
+        nbytes = L.cott_bidir_scratch_bytes(B, H, N, Dk, Dv, code)
+        scratch = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=q.device)
+        out = torch.empty(B, H, N, Dv, dtype=q.dtype, device=q.device)
+        with torch.cuda.device(q.device):
+            st = L.cott_bidir_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(kp), _lib.ptr(nc), _lib.ptr(out),
+                                  _lib.ptr(scratch), B, H, N, Dk, Dv, code, _lib.stream_ptr(q.device))
+        _lib.check(st, "cott_bidir_fwd")
+        ctx.save_for_backward(q, k, v, nc, scratch)
+        ctx.kp = kp
+        ctx.nc_shape, ctx.nc_dtype = norm_const.shape, norm_const.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, nc, scratch = ctx.saved_tensors
+        kp = ctx.kp
+        B, H, N, Dk = q.shape
+        Dv = v.shape[-1]
+        dout = dout.contiguous().to(q.dtype)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        dnc = torch.empty(H, dtype=torch.float32, device=q.device)
+        scratch2 = torch.empty_like(scratch)
+        with torch.cuda.device(q.device):
+            st = _lib.lib().cott_bidir_bwd(
+                _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(kp), _lib.ptr(nc), _lib.ptr(dout), _lib.ptr(scratch),
+                _lib.ptr(scratch2), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(dnc), B, H, N, Dk, Dv,
+                _lib.DTYPE_CODE[q.dtype], _lib.stream_ptr(q.device))
+        _lib.check(st, "cott_bidir_bwd")
+        return dq, dk, dv, dnc.reshape(ctx.nc_shape).to(ctx.nc_dtype), None
+
+
+def cos_attn_bidirectional(q, k, v, norm_const, keep=None):
+    """Bidirectional cosine attention with the learned length-norm, the cosine section of the
+    reference's ``BertCosAttention.forward`` (``BERT_Trainer/BertCosAttention.py:162-178,249``).
+
+    q, k: ``[B, H, N, d_k]``; v: ``[B, H, N, d_v]``; ``norm_const``: H values (e.g. the module's
+    ``[1, H, 1, 1]`` parameter, ``:81``); ``keep``: optional ``[B, N]`` bool, True = un-masked
+    (``attention_mask == 0``, ``:163``).  Differentiable w.r.t. q, k, v and ``norm_const``."""
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        raise RuntimeError("cos_attn_bidirectional needs CUDA tensors (there is no CPU path)")
+    if q.dtype not in _lib.DTYPE_CODE:
+        raise ValueError("Only float32, float64, float16, and bfloat16 are supported")
+    return _Bidirectional.apply(q, k, v, norm_const, keep)

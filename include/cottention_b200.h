@@ -142,6 +142,34 @@ int cott_decode_steps(float* state, const void* q, const void* k, const void* v,
                       const long long* positions, void* stream);
 
 /*
+ * Bidirectional (encoder) cosine attention, forward:
+ *   keep_s: un-masked positions ([B,N] bytes, non-zero = keep; NULL = keep all), L_b = their count
+ *   q^ = keep q/|q|, k^ = keep k/|k|, v' = keep v / max(L_b^sigmoid(norm_const[h]), 1)
+ *   out[b,h,t,:] = q^_t (sum_s k^_s (x) v'_s)
+ * Replaces the cosine section of BertCosAttention.forward, BERT_Trainer/BertCosAttention.py:162-178
+ * (mask, normalize, length-norm) and :197-249 (the two einsum orders, which are the same function).
+ * All four dtypes; Dk, Dv divisible by 16 and <= 128; fp32 accumulation (fp64 for COTT_F64).
+ *
+ * `scratch` is caller-provided device memory of cott_bidir_scratch_bytes(...) bytes that receives
+ * the per-(b,h) state partials; pass the same buffer, untouched, to cott_bidir_bwd as `scratch_state`.
+ */
+size_t cott_bidir_scratch_bytes(int B, int H, int N, int Dk, int Dv, int dtype);
+int cott_bidir_fwd(const void* q, const void* k, const void* v, const unsigned char* keep,
+                   const float* norm_const, void* out, void* scratch, int B, int H, int N, int Dk, int Dv,
+                   int dtype, void* stream);
+
+/*
+ * Backward of cott_bidir_fwd: dq, dk, dv and dnorm_const (H floats, overwritten).  The reference
+ * obtains these by autograd through the einsums (its hand-written non-causal Function `Multiply`,
+ * GPT_Trainer/GPTCosAttention.py:22-37, is unused and its grad_V line is wrong).
+ * `scratch_state` is the forward's scratch; `scratch_dstate` is a second buffer of the same size.
+ */
+int cott_bidir_bwd(const void* q, const void* k, const void* v, const unsigned char* keep,
+                   const float* norm_const, const void* dout, const void* scratch_state, void* scratch_dstate,
+                   void* dq, void* dk, void* dv, float* dnorm_const, int B, int H, int N, int Dk, int Dv,
+                   int dtype, void* stream);
+
+/*
  * Device-side health check.  The tensor-core kernels bound every wait (TMA arrival, MMA
  * completion); a wait that gives up records a code and the kernel returns without hanging.
  * This call synchronises the current device, returns COTT_ERR_DEVICE_WAIT if a code was

@@ -1,0 +1,79 @@
+"""GPU parity tests of the bidirectional (encoder) cosine attention through the C ABI."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import cott_oracle as O
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+@pytest.mark.parametrize("name", ["bert_cos_attn_s40.npz", "bert_cos_attn_s12.npz"])
+@pytest.mark.parametrize("dt", [torch.float64, torch.float32])
+def test_matches_reference_module_fixture(name, dt):
+    """Against BertCosAttention.forward executed unmodified (both einsum orders), including the
+    gradients w.r.t. the hidden states and norm_const."""
+    from cottention_transformer_b200 import cos_attn_bidirectional
+    g = np.load(os.path.join(GOLDEN, name))
+    H = int(g["num_heads"])
+    hs = torch.from_numpy(g["hidden"]).to(dt).cuda().requires_grad_()
+    nc = torch.from_numpy(g["norm_const"]).to(dt).cuda().requires_grad_()
+    keep = torch.from_numpy(g["keep"]).cuda()
+    B, S, E = hs.shape
+    d = E // H
+
+    def proj(w, b):
+        W, bb = torch.from_numpy(g[w]).to(dt).cuda(), torch.from_numpy(g[b]).to(dt).cuda()
+        return (hs @ W.t() + bb).view(B, S, H, d).permute(0, 2, 1, 3)
+
+    out = cos_attn_bidirectional(proj("wq", "bq"), proj("wk", "bk"), proj("wv", "bv"), nc.view(1, H, 1, 1), keep)
+    ctx = out.permute(0, 2, 1, 3).reshape(B, S, E)
+    (ctx * torch.from_numpy(g["dctx"]).to(dt).cuda()).sum().backward()
+    # norm_const crosses the C ABI as float32, which bounds the fp64 agreement at about 1e-7
+    tol = 1e-6 if dt == torch.float64 else 1e-4
+    e_ctx = (ctx.detach().double().cpu() - torch.from_numpy(g["ctx"])).abs().max().item()
+    e_hid = (hs.grad.double().cpu() - torch.from_numpy(g["dhidden"])).abs().max().item()
+    e_nc = (nc.grad.double().cpu() - torch.from_numpy(g["dnorm_const"])).abs().max().item()
+    assert e_ctx <= tol and e_hid <= tol * 10 and e_nc <= tol * 10, (e_ctx, e_hid, e_nc)
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(2, 3, 512, 64, 64), (1, 2, 77, 32, 48), (2, 2, 1, 16, 16), (1, 1, 300, 128, 128)])
+@pytest.mark.parametrize("masked", [False, True])
+def test_matches_oracle(dt, shape, masked):
+    from cottention_transformer_b200 import cos_attn_bidirectional
+    B, H, N, Dk, Dv = shape
+    q, k, v, do, _ = O.make_inputs(B, H, N, Dk, Dv, seed=N + Dk, normalize=False, dtype=dt)
+    nc = torch.linspace(-1.0, 1.2, H)
+    keep = None
+    if masked:
+        keep = torch.ones(B, N, dtype=torch.bool)
+        keep[0, N // 2:] = False
+        keep[-1, : N // 3] = False
+    qd, kd, vd = (t.double().requires_grad_() for t in (q, k, v))
+    ncd = nc.double().requires_grad_()
+    ref = O.cos_attn_bidirectional(qd, kd, vd, ncd, keep)
+    (ref * do.double()).sum().backward()
+    qc, kc, vc = (t.cuda().requires_grad_() for t in (q, k, v))
+    ncc = nc.cuda().requires_grad_()
+    out = cos_attn_bidirectional(qc, kc, vc, ncc, None if keep is None else keep.cuda())
+    out.backward(do.cuda())
+
+    def err(a, b):
+        scale = max(b.abs().max().item(), 1e-6)
+        return (a.double().cpu() - b).abs().max().item() / (1.0 if dt == torch.float32 else scale)
+
+    tol = 2e-4 if dt == torch.float32 else 2e-2
+    for name, a, b in (("out", out, ref.detach()), ("dq", qc.grad, qd.grad), ("dk", kc.grad, kd.grad),
+                       ("dv", vc.grad, vd.grad), ("dnorm", ncc.grad, ncd.grad)):
+        assert err(a, b) <= tol * (5 if name == "dnorm" else 1), (name, err(a, b))
+
+
+def test_rejects_unsupported_head_dim():
+    from cottention_transformer_b200 import cos_attn_bidirectional
+    x = torch.zeros(1, 1, 8, 24, device="cuda")
+    with pytest.raises(RuntimeError, match="divisible by 16"):
+        cos_attn_bidirectional(x, x, x, torch.zeros(1, device="cuda"))
