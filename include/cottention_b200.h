@@ -170,6 +170,36 @@ int cott_bidir_bwd(const void* q, const void* k, const void* v, const unsigned c
                    int dtype, void* stream);
 
 /*
+ * cott_bidir_fwd for callers that cannot allocate.  (No counterpart in the reference, whose
+ * bidirectional path lets PyTorch allocate its einsum intermediates.)
+ *
+ * Same inputs, outputs and results as cott_bidir_fwd, but there is no `scratch` argument: the state
+ * partials go to a fixed array of COTT_BIDIR_STATIC_SCRATCH_BYTES that is linked into the library
+ * and therefore sits on every GPU that loads it until the process exits.  Meant for hosts that
+ * give away all device memory at start-up and must never enter the CUDA allocator afterwards (a
+ * serving process with a frozen pool, a loop that cannot afford cudaMalloc's device-wide
+ * synchronisation).  The call makes no cudaMalloc/cudaFree and uses no allocating library routine.
+ *
+ * Limits and rules:
+ *  - B*H*nsplit*Dk*Dv accumulator elements (4 bytes, 8 for COTT_F64; nsplit <= 8 is chosen from
+ *    B*H and N) must fit in COTT_BIDIR_STATIC_SCRATCH_BYTES; larger problems are rejected with
+ *    COTT_ERR_SHAPE and a message that names both sizes.  BERT-base at batch 32 (B*H = 384,
+ *    N = 512, d = 64) needs 6 MiB.
+ *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *    that device current) and caches it; make that first call before any stream capture begins.
+ *  - All calls on a device share the one array, and it keeps whatever the last call left in it.
+ *    Nothing needs clearing (every slot that is read is first written in full by the same call),
+ *    but two calls that overlap on the GPU -- different streams, or the same array reached from two
+ *    host threads -- race on it.  Serialise them.
+ *  - There is no matching backward: the backward needs the forward's scratch kept alive, which a
+ *    shared array cannot promise.
+ */
+#define COTT_BIDIR_STATIC_SCRATCH_BYTES (8u << 20)
+int cott_bidir_fwd_static(const void* q, const void* k, const void* v, const unsigned char* keep,
+                          const float* norm_const, void* out, int B, int H, int N, int Dk, int Dv,
+                          int dtype, void* stream);
+
+/*
  * Device-side health check.  The tensor-core kernels bound every wait (TMA arrival, MMA
  * completion); a wait that gives up records a code and the kernel returns without hanging.
  * This call synchronises the current device, returns COTT_ERR_DEVICE_WAIT if a code was
