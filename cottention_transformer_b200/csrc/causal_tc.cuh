@@ -103,29 +103,61 @@ __device__ __forceinline__ float row_sumsq(unsigned char* tile, int row) {
   return s;
 }
 
-// tile[row] *= w (in place)
+// tile[row] *= w (in place), in packed 16-bit arithmetic.  w is split into a 16-bit head and a
+// 16-bit tail, and x*w = fma(x, w_hi, x*w_lo): the tail product is tiny, so the result carries one
+// 16-bit rounding, the same as converting the fp32 product -- at 2 instructions per element pair.
+template <typename T> struct Vec2;
+template <> struct Vec2<__nv_bfloat16> {
+  using type = __nv_bfloat162;
+  static __device__ __forceinline__ type bcast(float x) { return __float2bfloat162_rn(x); }
+  static __device__ __forceinline__ float head(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+};
+template <> struct Vec2<__half> {
+  using type = __half2;
+  static __device__ __forceinline__ type bcast(float x) { return __float2half2_rn(x); }
+  static __device__ __forceinline__ float head(float x) { return __half2float(__float2half_rn(x)); }
+};
 template <typename T>
 __device__ __forceinline__ void scale_row(unsigned char* tile, int row, float w) {
+  if constexpr (Pack2<T>::kBf16) {
+    using V = typename Vec2<T>::type;
+    const float wh = Vec2<T>::head(w);
+    const V whi = Vec2<T>::bcast(wh), wlo = Vec2<T>::bcast(w - wh);
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    uint4* p = tile_piece(tile, row, j);
-    uint4 u = *p;
-    float2 a = Pack2<T>::unpack(u.x), b = Pack2<T>::unpack(u.y), c = Pack2<T>::unpack(u.z),
-           d = Pack2<T>::unpack(u.w);
-    u.x = Pack2<T>::pack(a.x * w, a.y * w);
-    u.y = Pack2<T>::pack(b.x * w, b.y * w);
-    u.z = Pack2<T>::pack(c.x * w, c.y * w);
-    u.w = Pack2<T>::pack(d.x * w, d.y * w);
-    *p = u;
+    for (int j = 0; j < 8; ++j) {
+      uint4* p = tile_piece(tile, row, j);
+      uint4 u = *p;
+      V* x = reinterpret_cast<V*>(&u);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) x[e] = __hfma2(x[e], whi, __hmul2(x[e], wlo));
+      *p = u;
+    }
+  } else {
+    // float16 has too little range to hold the factor itself (1/|k| of a small row): multiply in fp32
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      uint4* p = tile_piece(tile, row, j);
+      uint4 u = *p;
+      float2 a = Pack2<T>::unpack(u.x), b = Pack2<T>::unpack(u.y), c = Pack2<T>::unpack(u.z),
+             d = Pack2<T>::unpack(u.w);
+      u.x = Pack2<T>::pack(a.x * w, a.y * w);
+      u.y = Pack2<T>::pack(b.x * w, b.y * w);
+      u.z = Pack2<T>::pack(c.x * w, c.y * w);
+      u.w = Pack2<T>::pack(d.x * w, d.y * w);
+      *p = u;
+    }
   }
 }
 
-// 1 / max(|x|, 1e-12): torch.nn.functional.normalize's denominator (GPTCosAttention.py:229-230)
-__device__ __forceinline__ float inv_norm(float sumsq) { return 1.0f / fmaxf(sqrtf(sumsq), 1e-12f); }
+// One MUFU.RSQ.  A non-zero 16-bit row has |x| >= 6e-8 > 1e-12, so the epsilon only ever matters for
+// an all-zero row, whose normalised value is zero whatever the factor: return 0 there (a huge factor
+// would overflow the 16-bit operand it is folded into).
+__device__ __forceinline__ float inv_norm(float sumsq) { return sumsq > 0.f ? rsqrtf(sumsq) : 0.f; }
 
 // a = 1 / max(n ** sigma, 1)  (GPTCosAttention.py:241), n >= 1
 __device__ __forceinline__ float length_factor(float n, float sigma) {
-  return 1.0f / fmaxf(exp2f(sigma * log2f(n)), 1.0f);
+  // 1 / max(n^sigma, 1) = min(2^(-sigma log2 n), 1); lg2.approx / ex2.approx, relative error ~1e-6
+  return fminf(exp2f(-sigma * __log2f(n)), 1.0f);
 }
 
 // Bounded wait that also gives up when another role of the CTA has raised `abort_flag`.
@@ -262,8 +294,9 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
 
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // 1024-byte alignment is required by the 128-byte swizzle atoms
-  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                                         ~static_cast<uintptr_t>(1023));
+  // (offset arithmetic on the __shared__ array keeps the pointer's address space known to the
+  // compiler, so tile accesses compile to LDS/STS rather than generic loads and stores)
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char* sS = smem + NS * STAGE;  // 2 x [64 x 64] 16-bit state operand (double-buffered), 2 x 8 KB
   __shared__ uint64_t bar_full[NS], bar_free[NS], bar_prep[NS], bar_p_full[2], bar_p_ready[2], bar_acc_full[2],
       bar_acc_free[2], bar_s_full, bar_state;
@@ -544,8 +577,9 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   constexpr bool BF = Pack2<T>::kBf16;
 
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                                         ~static_cast<uintptr_t>(1023));
+  // (offset arithmetic on the __shared__ array keeps the pointer's address space known to the
+  // compiler, so tile accesses compile to LDS/STS rather than generic loads and stores)
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char* sR = smem + NS * STAGE;  // [64 x 64] 16-bit state operand (rows = d_k, cols = d_v)
   __shared__ uint64_t bar_full[NS], bar_free[NS], bar_prep[NS], bar_p_full, bar_p_ready, bar_acc_full, bar_acc_free,
       bar_state;
