@@ -58,6 +58,8 @@ class ClockSampler(threading.Thread):
         super().__init__(daemon=True)
         self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
         self._halt = threading.Event()
+        self.ready = threading.Event()   # set once NVML is initialised (or has failed)
+        self.armed = False               # samples are recorded only while armed (the timed region)
 
     def run(self):
         try:
@@ -71,15 +73,18 @@ class ClockSampler(threading.Thread):
                 nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
                 nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
             }
+            self.ready.set()
             while not self._halt.is_set():
-                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
-                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
-                for bit, name in names.items():
-                    if r & bit:
-                        self.reasons.add(name)
-                time.sleep(0.02)
+                if self.armed:
+                    self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                    for bit, name in names.items():
+                        if r & bit:
+                            self.reasons.add(name)
+                time.sleep(0.001)
         except Exception as e:  # NVML missing: report nothing rather than fail the bench
             self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
+            self.ready.set()
 
     def stop(self):
         self._halt.set()
@@ -204,8 +209,10 @@ def main():
         fwd(), bwd_dq(), bwd_dkdv()
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
     sampler = ClockSampler(local_rank)
-    barrier()
     sampler.start()
+    sampler.ready.wait(timeout=10)
+    barrier()
+    sampler.armed = True
     for i in range(args.steps):
         ev[i][0].record()
         fwd()
@@ -215,6 +222,7 @@ def main():
         bwd_dkdv()
         ev[i][3].record()
     barrier()
+    sampler.armed = False
     clocks = sampler.stop()
     _lib.check_device_status()
     total_ms = ev[0][0].elapsed_time(ev[-1][3])

@@ -1,0 +1,140 @@
+"""Secondary measurements of the hot path (not the headline bench line): recurrent decode and the
+bidirectional (encoder) form, each against the HBM roofline.
+
+    python -m cottention_transformer_b200.bench_extra [--decode-steps 256] [--json out.json]
+
+Decode: batch 64, H=16, d in {64, 128}, bf16 tokens, fp32 state in HBM, one launch per token
+(``cott_decode_step``), plus the multi-token launch (``cott_decode_steps``) that keeps the state in
+registers.  Algorithmic bytes per (b,h) per step: 2*d*d*4 (state read + write) + 4*d*2 (q, k, v, out).
+Bidirectional: B=32, H=12, N=512, d=64, bf16 (BERT-base attention shapes), forward + backward.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from . import _lib
+
+
+def _peak_gbs():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def _time(fn, iters, warmup=5):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e-3  # seconds per call
+
+
+def bench_decode(d, steps, B=64, H=16, use_graph=True):
+    L = _lib.lib()
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(1234)
+    nstates = 8  # rotate over several state buffers so that the state does not sit in L2 (8 x 16.8/67 MB)
+    states = [torch.zeros(B, H, d, d, device=dev) for _ in range(nstates)]
+    q = torch.randn(B, H, 1, d, device=dev, generator=g).bfloat16()
+    k = torch.randn(B, H, 1, d, device=dev, generator=g).bfloat16()
+    v = torch.randn(B, H, 1, d, device=dev, generator=g).bfloat16()
+    out = torch.empty_like(v)
+    nc = 0.5 * torch.ones(H, device=dev)
+    stream = _lib.stream_ptr(dev)
+    it = [0]
+
+    def one():
+        s = states[it[0] % nstates]
+        it[0] += 1
+        _lib.check(L.cott_decode_step(s.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), nc.data_ptr(), out.data_ptr(),
+                                      B, H, d, d, 3, it[0], None, stream), "cott_decode_step")
+
+    t_eager = _time(one, steps)
+    # the per-token launch is host-bound when driven from Python: replay the same launches from a CUDA graph
+    t = t_eager
+    graphed = False
+    try:
+        if not use_graph:
+            raise RuntimeError("disabled by --no-graph")
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            stream_side = _lib.stream_ptr(dev)
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=side):
+                for i in range(64):
+                    s_ = states[i % nstates]
+                    _lib.check(L.cott_decode_step(s_.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), nc.data_ptr(),
+                                                  out.data_ptr(), B, H, d, d, 3, i + 1, None, _lib.stream_ptr(dev)),
+                               "cott_decode_step")
+        torch.cuda.current_stream().wait_stream(side)
+        t = _time(gr.replay, max(4, steps // 64), warmup=2) / 64
+        graphed = True
+    except Exception as e:  # report the eager figure and say why
+        graphed = f"graph capture failed: {type(e).__name__}: {str(e)[:80]}"
+    bytes_step = B * H * (2 * d * d * 4 + 4 * d * 2)
+    # multi-token launch: state resident in registers
+    T = 512
+    qs = torch.randn(B, H, T, d, device=dev, generator=g).bfloat16()
+    ks = torch.randn(B, H, T, d, device=dev, generator=g).bfloat16()
+    vs = torch.randn(B, H, T, d, device=dev, generator=g).bfloat16()
+    outs = torch.empty_like(vs)
+
+    def many():
+        _lib.check(L.cott_decode_steps(states[0].data_ptr(), qs.data_ptr(), ks.data_ptr(), vs.data_ptr(), nc.data_ptr(),
+                                       outs.data_ptr(), B, H, T, d, d, 3, 1, None, stream), "cott_decode_steps")
+
+    tm = _time(many, 5, warmup=2)
+    peak, kind = _peak_gbs()
+    return {
+        "what": f"decode step, batch {B}, H={H}, d={d}, bf16 tokens, fp32 state",
+        "us_per_step": t * 1e6, "us_per_step_python_launch": t_eager * 1e6, "cuda_graph": graphed,
+        "tokens_per_s": B / t, "algorithmic_bytes_per_step": bytes_step,
+        "achieved_gbs": bytes_step / t / 1e9, "peak_gbs": peak, "peak_source": kind, "frac": bytes_step / t / 1e9 / peak,
+        "multi_token_launch": {"T": T, "us_per_token": tm / T * 1e6, "tokens_per_s": B * T / tm},
+    }
+
+
+def bench_bidir(B=32, H=12, N=512, d=64):
+    from .cos_attention import cos_attn_bidirectional
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(1234)
+    q, k, v, do = (torch.randn(B, H, N, d, device=dev, generator=g).bfloat16() for _ in range(4))
+    nc = (0.5 * torch.ones(H, device=dev)).requires_grad_()
+    q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
+
+    def step():
+        out = cos_attn_bidirectional(q, k, v, nc)
+        out.backward(do)
+        q.grad = k.grad = v.grad = nc.grad = None
+
+    t = _time(step, 20)
+    nbytes = 11 * B * H * N * d * 2
+    peak, kind = _peak_gbs()
+    return {"what": f"bidirectional fwd+bwd, B={B} H={H} N={N} d={d} bf16", "us_per_step": t * 1e6,
+            "tokens_per_s": B * N / t, "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / t / 1e9,
+            "peak_gbs": peak, "peak_source": kind, "frac": nbytes / t / 1e9 / peak}
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--decode-steps", type=int, default=256)
+    ap.add_argument("--json", default=None)
+    ap.add_argument("--no-graph", action="store_true", help="do not replay decode from a CUDA graph (profiler runs)")
+    a = ap.parse_args()
+    res = [bench_decode(64, a.decode_steps, use_graph=not a.no_graph), bench_decode(128, a.decode_steps, use_graph=not a.no_graph),
+           bench_bidir()]
+    for r in res:
+        print(json.dumps(r))
+    if a.json:
+        json.dump(res, open(a.json, "w"), indent=1)

@@ -33,17 +33,35 @@ __device__ int g_cott_status;  // 0 = ok; else (code << 16 | chunk) of the first
 
 // Optional timeline tracing (debug builds only, -DCOTT_TRACE): CTA 0 records clock64() at role events.
 #ifdef COTT_TRACE
-constexpr int kTraceWarps = 10, kTraceChunks = 40, kTraceEvents = 8;
-__device__ long long g_cott_trace[kTraceWarps * kTraceChunks * kTraceEvents];
-#define COTT_TRACE_EV(ev, c)                                                                     \
-  do {                                                                                           \
-    if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (c) < kTraceChunks)                        \
-      g_cott_trace[((threadIdx.x >> 5) * kTraceChunks + (c)) * kTraceEvents + (ev)] = clock64(); \
+constexpr int kTraceWarps = 16, kTraceChunks = 40, kTraceEvents = 8;
+__device__ unsigned int g_cott_trace[kTraceWarps * kTraceChunks * kTraceEvents];
+// timestamps go to shared memory (a global store in the middle of a role would itself disturb the
+// fences and waits being timed) and are copied out when the kernel ends
+#define COTT_TRACE_DECL __shared__ unsigned int s_cott_trace[kTraceWarps * kTraceChunks * kTraceEvents];
+#define COTT_TRACE_EV(ev, c)                                                                      \
+  do {                                                                                            \
+    if ((threadIdx.x & 31) == 0 && (c) < kTraceChunks)                                            \
+      s_cott_trace[((threadIdx.x >> 5) * kTraceChunks + (c)) * kTraceEvents + (ev)] = (unsigned int)clock64(); \
+  } while (0)
+#define COTT_TRACE_FLUSH()                                                                        \
+  do {                                                                                            \
+    __syncthreads();                                                                              \
+    if (blockIdx.x == 0)                                                                          \
+      for (int i_ = threadIdx.x; i_ < kTraceWarps * kTraceChunks * kTraceEvents; i_ += blockDim.x) \
+        g_cott_trace[i_] = s_cott_trace[i_];                                                      \
   } while (0)
 #else
+#define COTT_TRACE_DECL
 #define COTT_TRACE_EV(ev, c) \
   do {                       \
   } while (0)
+#define COTT_TRACE_FLUSH() \
+  do {                     \
+  } while (0)
+#endif
+
+#ifndef COTT_SKEL
+#define COTT_SKEL 0  // debug only: bit mask of role work to skip when timing the pipeline skeleton
 #endif
 
 constexpr int kTcChunk = 128;
@@ -169,7 +187,7 @@ __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatil
 #ifdef COTT_POLL_SLEEP
     __nanosleep(COTT_POLL_SLEEP);
 #endif
-    if ((i & 255u) == 255u && *abort_flag) return false;
+    if (*abort_flag) return false;
   }
   *abort_flag = 1;
   atomicCAS(&g_cott_status, 0, (code << 16) | (chunk & 0xffff));
@@ -301,6 +319,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   __shared__ uint64_t bar_full[NS], bar_free[NS], bar_prep[NS], bar_p_full[2], bar_p_ready[2], bar_acc_full[2],
       bar_acc_free[2], bar_s_full, bar_state;
   __shared__ uint32_t tmem_slot;
+  COTT_TRACE_DECL
   __shared__ int abort_flag_s;
   volatile int* abort_flag = &abort_flag_s;
 
@@ -450,12 +469,14 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       COTT_TRACE_EV(3, c);
       unsigned char* sZ = smem + s * STAGE + 2 * kTileBytes;
       unsigned char* sK = (MODE == kModeDq) ? sZ : smem + s * STAGE + kTileBytes;
+#if !(COTT_SKEL & 2)
       const float rk = inv_norm(row_sumsq<T>(sK, row));
       COTT_TRACE_EV(4, c);
       const float a = length_factor(static_cast<float>(c * kTcChunk + row + 1), sigma);
       COTT_TRACE_EV(5, c);
       scale_row<T>(sZ, row, rk * a);
       COTT_TRACE_EV(6, c);
+#endif
       fence_proxy_async_smem();
       warp_arrive(&bar_prep[s], lane);
       COTT_TRACE_EV(7, c);
@@ -467,7 +488,9 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       if (!(ok = wait_bar_warp(&bar_p_full[b], (c >> 1) & 1, abort_flag, kWaitScore, c))) break;
       tc_fence_after_sync();
       COTT_TRACE_EV(0, c);
+#if !(COTT_SKEL & 1)
       mask_pack_inplace<T>(tP0 + 128 * b + lane_base, 0, row, 0, wq);
+#endif
       tc_fence_before_sync();
       warp_arrive(&bar_p_ready[b], lane);
       COTT_TRACE_EV(1, c);
@@ -483,12 +506,18 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       unsigned char* sQ = smem + s * STAGE + ((MODE == kModeDq) ? 3 * kTileBytes : 0);
       // the row norm of q only needs the TMA data: do it while the MMAs run
       if (!wait_bar_warp(&bar_full[s], (c / NS) & 1, abort_flag, kWaitTma, c)) break;
+#if !(COTT_SKEL & 4)
       const float rq = inv_norm(row_sumsq<T>(sQ, row));
+#else
+      const float rq = 1.f;
+#endif
       COTT_TRACE_EV(0, c);
       if (c + 1 < nchunks) {  // S after chunk c -> 16-bit operand for chunk c+1 (buffer (c+1)&1)
         if (!wait_bar_warp(&bar_s_full, c & 1, abort_flag, kWaitState, c)) break;
         tc_fence_after_sync();
+#if !(COTT_SKEL & 4)
         state_to_smem<T>(tS + lane_base, sS + ((c + 1) & 1) * (kTcD * 128), wq, lane);
+#endif
         fence_proxy_async_smem();
         tc_fence_before_sync();
         warp_arrive(&bar_state, lane);
@@ -498,7 +527,11 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       tc_fence_after_sync();
       COTT_TRACE_EV(2, c);
       float acc[64];
+#if !(COTT_SKEL & 4)
       tmem_row64(tAcc0 + 64 * b + lane_base, acc);
+#else
+      for (int j = 0; j < 64; ++j) acc[j] = 0.f;
+#endif
       tc_fence_before_sync();
       warp_arrive(&bar_acc_free[b], lane);
       COTT_TRACE_EV(3, c);
@@ -535,7 +568,11 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       warp_arrive(&bar_free[s], lane);  // last read of this stage by this warp
       COTT_TRACE_EV(6, c);
       const int pos = c * kTcChunk + row;
+#if !(COTT_SKEL & 4)
       if (pos < N) store_row64<T>(out + (static_cast<size_t>(bh) * N + pos) * kTcD, acc);
+#else
+      if (pos < N && acc[5] == 123.f) out[0] = T(0);
+#endif
       COTT_TRACE_EV(4, c);
     }
   }
@@ -546,10 +583,11 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   __syncthreads();
   if (tid == 0 && *abort_flag) {
     for (int c = (nchunks > NS ? nchunks - NS : 0); c < nchunks; ++c)
-      mbar_wait(&bar_full[c % NS], (c / NS) & 1, 1u << 16);
+      mbar_wait(&bar_full[c % NS], (c / NS) & 1, 64);
   }
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, 512);
+  COTT_TRACE_FLUSH();
 }
 
 // -------------------------------------------------------------------------------------------------
@@ -805,7 +843,7 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   __syncthreads();
   if (tid == 0 && *abort_flag) {
     for (int ci = (nchunks > NS ? nchunks - NS : 0); ci < nchunks; ++ci)
-      mbar_wait(&bar_full[ci % NS], (ci / NS) & 1, 1u << 16);
+      mbar_wait(&bar_full[ci % NS], (ci / NS) & 1, 64);
   }
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, 512);

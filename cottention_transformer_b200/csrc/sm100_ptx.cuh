@@ -42,21 +42,24 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One try_wait with a suspend-time hint: the thread sleeps in hardware until the phase completes
+// or about `kSuspendNs` have passed, instead of spinning through the issue slots of its scheduler.
+constexpr uint32_t kSuspendNs = 200000;  // 0.2 ms per try
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
       "selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendNs)
       : "memory");
   return ok != 0;
 }
 // Bounded wait.  Returns false if the phase did not complete within `max_polls` polls.
-constexpr uint32_t kMaxPolls = 1u << 22;
+constexpr uint32_t kMaxPolls = 1u << 14;  // x 0.2 ms suspend per try: gives up after about 3 s
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t max_polls = kMaxPolls) {
   for (uint32_t i = 0; i < max_polls; ++i)
     if (mbar_try_wait(bar, parity)) return true;
