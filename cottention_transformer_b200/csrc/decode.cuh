@@ -26,8 +26,10 @@ __device__ __forceinline__ float ld_as_float(const T* p) { return to_acc(*p); }
 // q, k: [B,H,T,Dk]  v, out: [B,H,T,Dv] (T = 1 for a single step); state: [B,H,Dv,Dk] fp32.
 // positions: optional [B] int64 array of the 1-based position of the FIRST token of this call for
 // each batch entry; if null, `pos0` is used for all.  LPR = lanes per state row = Dk/4.
+// (the register cap keeps 4 CTAs per SM resident for d <= 64, 2 for d = 128: the kernel is latency-bound
+// on its state loads, so resident CTAs are what hides the HBM latency)
 template <typename T, int DK>
-__global__ void __launch_bounds__(kDecodeThreads)
+__global__ void __launch_bounds__(kDecodeThreads, (DK <= 64 ? 4 : 2))
 decode_kernel(float* __restrict__ state, const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
               const float* __restrict__ norm_const, T* __restrict__ out, int H, int Dv, int Tsteps, long long pos0,
               const long long* __restrict__ positions) {
