@@ -193,17 +193,29 @@ __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatil
   atomicCAS(&g_cott_status, 0, (code << 16) | (chunk & 0xffff));
   return false;
 }
-// Whole-warp wait: only lane 0 polls (32 lanes polling an mbarrier flood the shared-memory
-// instruction queue and starve the LDS/STS/STG of the warps that have work); once lane 0 has seen
-// the phase complete, every lane tests the barrier once so that each thread itself observes the
-// completion (needed for the visibility of TMA-written data).
+// Two barriers at once: both try_waits are in flight together, so the pair costs one mbarrier
+// round trip (about 200 cycles even for a completed phase) instead of two.
+__device__ __forceinline__ bool wait_bar2(uint64_t* bar_a, uint32_t parity_a, uint64_t* bar_b, uint32_t parity_b,
+                                          volatile int* abort_flag, int code, int chunk) {
+  bool a = false, b = false;
+  for (uint32_t i = 0; i < ptx::kMaxPolls; ++i) {
+    const bool ta = a || ptx::mbar_try_wait(bar_a, parity_a);
+    const bool tb = b || ptx::mbar_try_wait(bar_b, parity_b);
+    a = ta;
+    b = tb;
+    if (a && b) return true;
+    if (*abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicCAS(&g_cott_status, 0, (code << 16) | (chunk & 0xffff));
+  return false;
+}
+// Whole-warp wait: every lane waits on the barrier itself (each thread must observe the completion
+// to see TMA-written data) -- one warp-wide try_wait with a suspend hint, so a waiting warp sleeps in
+// hardware instead of spinning; the outcome is made warp-uniform.
 __device__ __forceinline__ bool wait_bar_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code,
                                               int chunk) {
-  int ok = 1;
-  if ((threadIdx.x & 31) == 0) ok = wait_bar(bar, parity, abort_flag, code, chunk) ? 1 : 0;
-  ok = __shfl_sync(0xffffffffu, ok, 0);
-  if (ok) ptx::mbar_try_wait(bar, parity);
-  return ok != 0;
+  return __all_sync(0xffffffffu, wait_bar(bar, parity, abort_flag, code, chunk) ? 1 : 0) != 0;
 }
 __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
   __syncwarp();
@@ -377,84 +389,75 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       }
     }
   } else if (warp == 1) {
-    // ---------------------------------------------------------------- MMA issuer
-    // The whole warp runs this loop with warp-uniform values; one elected lane issues.
-    {
-      // Lane 0 issues (it is also the lane that polls the barriers).  A leader picked by elect.sync
-      // faulted with an illegal address under back-to-back launches at the full problem size
-      // while a fixed lane 0 never did, so the leader is fixed.
-      const uint32_t el = lane == 0 ? 1u : 0u;
+    // ---------------------------------------------------------------- MMA issuer (one thread)
+    // An mbarrier wait costs about 200 cycles even when the phase is already complete, so the waits
+    // are paired (both try_waits in flight together) and only this one thread takes part.
+    if (lane == 0) {
       constexpr uint32_t kIdescP = make_idesc(128, 128, BF, false, false);
       constexpr uint32_t kIdescAcc = make_idesc(128, 64, BF, false, true);
       constexpr uint32_t kIdescS = make_idesc(64, 64, BF, true, true);
       const uint64_t dS0 = mdesc(smem_u32(sS));
-      auto issue_scores = [&](int c) -> bool {
-        const int s = c % NS;
-        if (!wait_bar_warp(&bar_full[s], (c / NS) & 1, abort_flag, kWaitTma, c)) return false;
-        tc_fence_after_sync();
-        COTT_TRACE_EV(6, c);
-        const uint32_t x0 = smem_u32(smem + s * STAGE);
+      auto issue_scores = [&](int c) {  // caller has waited for the TMA of chunk c
+        const uint32_t x0 = smem_u32(smem + (c % NS) * STAGE);
         const uint64_t dX = kdesc(x0), dY = kdesc(x0 + kTileBytes);
         const uint32_t tP = tP0 + 128 * (c & 1);
-        if (el) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k) mma_ss(tP, dX + 2 * k, dY + 2 * k, kIdescP, k > 0);
-          mma_commit(&bar_p_full[c & 1]);
-        }
-        __syncwarp();
+        for (int k = 0; k < 4; ++k) mma_ss(tP, dX + 2 * k, dY + 2 * k, kIdescP, k > 0);
+        mma_commit(&bar_p_full[c & 1]);
         COTT_TRACE_EV(7, c);
-        return true;
       };
-      // Issue order per chunk c -- chosen so that nothing this warp waits for was requested
-      // less than about one chunk period earlier:
+      // Issue order per chunk c -- chosen so that nothing this thread waits for was requested less
+      // than about one chunk period earlier:
       //   S += Y^T Zw (c)      needs Zw(c) and the conversion of S after chunk c-1
       //   scores (c+1)         needs the TMA of chunk c+1
-      //   Acc = X S (c)        needs the 16-bit S converted after chunk c-1 (buffer c&1)
+      //   Acc = X S (c)        needs the 16-bit S converted after chunk c-1 (buffer c&1), Acc buffer free
       //   Acc += P Zw (c)      needs the masked scores of chunk c (issued one chunk earlier)
-      bool ok = issue_scores(0);
+      bool ok = wait_bar(&bar_full[0], 0, abort_flag, kWaitTma, 0);
+      if (ok) {
+        tc_fence_after_sync();
+        issue_scores(0);
+      }
       for (int c = 0; ok && c < nchunks; ++c) {
         const int s = c % NS, b = c & 1;
         const uint32_t x0 = smem_u32(smem + s * STAGE);
         const uint64_t dX = kdesc(x0), dYm = mdesc(x0 + kTileBytes), dZm = mdesc(x0 + 2 * kTileBytes);
         const uint32_t tP = tP0 + 128 * b, tAcc = tAcc0 + 64 * b;
         const uint32_t acc_s = c > 0 ? 1u : 0u;
-        if (!(ok = wait_bar_warp(&bar_prep[s], (c / NS) & 1, abort_flag, kWaitPrepped, c))) break;
-        if (c > 0 && !(ok = wait_bar_warp(&bar_state, (c - 1) & 1, abort_flag, kWaitState, c))) break;
+        if (c > 0) ok = wait_bar2(&bar_prep[s], (c / NS) & 1, &bar_state, (c - 1) & 1, abort_flag, kWaitPrepped, c);
+        else ok = wait_bar(&bar_prep[s], (c / NS) & 1, abort_flag, kWaitPrepped, c);
+        if (!ok) break;
         tc_fence_after_sync();
         COTT_TRACE_EV(0, c);
         if (c + 1 < nchunks) {
-          if (el) {
-            mma_ss(tS, dYm, dZm, kIdescS, acc_s);  // S += Y^T Zw
+          mma_ss(tS, dYm, dZm, kIdescS, acc_s);  // S += Y^T Zw
 #pragma unroll
-            for (int k = 1; k < 8; ++k) mma_ss(tS, dYm + 128 * k, dZm + 128 * k, kIdescS, 1u);
-            mma_commit(&bar_s_full);
-          }
-          __syncwarp();
+          for (int k = 1; k < 8; ++k) mma_ss(tS, dYm + 128 * k, dZm + 128 * k, kIdescS, 1u);
+          mma_commit(&bar_s_full);
           COTT_TRACE_EV(5, c);
-          if (!(ok = issue_scores(c + 1))) break;
+          const int s1 = (c + 1) % NS;
+          if (c >= 2) ok = wait_bar2(&bar_full[s1], ((c + 1) / NS) & 1, &bar_acc_free[b], ((c >> 1) - 1) & 1, abort_flag, kWaitTma, c);
+          else ok = wait_bar(&bar_full[s1], ((c + 1) / NS) & 1, abort_flag, kWaitTma, c);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_scores(c + 1);
+        } else if (c >= 2) {
+          if (!(ok = wait_bar(&bar_acc_free[b], ((c >> 1) - 1) & 1, abort_flag, kWaitAccFree, c))) break;
+          tc_fence_after_sync();
         }
         COTT_TRACE_EV(1, c);
-        if (c >= 2 && !(ok = wait_bar_warp(&bar_acc_free[b], ((c >> 1) - 1) & 1, abort_flag, kWaitAccFree, c))) break;
         if (c > 0) {
-          tc_fence_after_sync();
           const uint64_t dS = dS0 + static_cast<uint64_t>(b * ((kTcD * 128) >> 4));
-          if (el) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k)  // Acc = X S   (S as MN-major B operand)
-              mma_ss(tAcc, dX + 2 * k, dS + 128 * k, kIdescAcc, k > 0);
-          }
-          __syncwarp();
+          for (int k = 0; k < 4; ++k)  // Acc = X S   (S as MN-major B operand)
+            mma_ss(tAcc, dX + 2 * k, dS + 128 * k, kIdescAcc, k > 0);
         }
-        if (!(ok = wait_bar_warp(&bar_p_ready[b], (c >> 1) & 1, abort_flag, kWaitScoreReady, c))) break;
+        if (!(ok = wait_bar(&bar_p_ready[b], (c >> 1) & 1, abort_flag, kWaitScoreReady, c))) break;
         tc_fence_after_sync();
         COTT_TRACE_EV(2, c);
-        if (el) {
-          mma_ts(tAcc, tP, dZm, kIdescAcc, acc_s);  // Acc += P Zw   (P from TMEM, Zw MN-major)
+        mma_ts(tAcc, tP, dZm, kIdescAcc, acc_s);  // Acc += P Zw   (P from TMEM, Zw MN-major)
 #pragma unroll
-          for (int k = 1; k < 8; ++k) mma_ts(tAcc, tP + 8 * k, dZm + 128 * k, kIdescAcc, 1u);
-          mma_commit(&bar_acc_full[b]);
-        }
-        __syncwarp();
+        for (int k = 1; k < 8; ++k) mma_ts(tAcc, tP + 8 * k, dZm + 128 * k, kIdescAcc, 1u);
+        mma_commit(&bar_acc_full[b]);
         COTT_TRACE_EV(3, c);
       }
     }
@@ -675,9 +678,8 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       }
     }
   } else if (warp == 1) {
-    // MMA issuer: the whole warp runs the loop with warp-uniform values; lane 0 issues
-    {
-      const uint32_t el = lane == 0 ? 1u : 0u;
+    // MMA issuer (one thread; waits paired, see causal_tc_kernel)
+    if (lane == 0) {
       constexpr uint32_t kIdescP = make_idesc(128, 128, BF, false, false);
       constexpr uint32_t kIdescAccKK = make_idesc(128, 64, BF, false, false);  // B K-major (V R^T)
       constexpr uint32_t kIdescAccMN = make_idesc(128, 64, BF, false, true);   // B MN-major
@@ -685,20 +687,16 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       const uint64_t dRk = kdesc(smem_u32(sR)), dRm = mdesc(smem_u32(sR));
       auto issue_scores = [&](int ci) -> bool {
         const int s = ci % NS;
-        if (!wait_bar_warp(&bar_full[s], (ci / NS) & 1, abort_flag, kWaitTma, ci)) return false;
-        if (!wait_bar_warp(&bar_prep[s], (ci / NS) & 1, abort_flag, kWaitPrepped, ci)) return false;
+        if (!wait_bar2(&bar_full[s], (ci / NS) & 1, &bar_prep[s], (ci / NS) & 1, abort_flag, kWaitTma, ci)) return false;
         tc_fence_after_sync();
         const uint32_t q0 = smem_u32(smem + s * STAGE);
         const uint64_t dQ = kdesc(q0), dK = kdesc(q0 + kTileBytes), dV = kdesc(q0 + 2 * kTileBytes),
                        dD = kdesc(q0 + 3 * kTileBytes);
-        if (el) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k) mma_ss(tE, dV + 2 * k, dD + 2 * k, kIdescP, k > 0);
+        for (int k = 0; k < 4; ++k) mma_ss(tE, dV + 2 * k, dD + 2 * k, kIdescP, k > 0);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) mma_ss(tF, dK + 2 * k, dQ + 2 * k, kIdescP, k > 0);
-          mma_commit(&bar_p_full);
-        }
-        __syncwarp();
+        for (int k = 0; k < 4; ++k) mma_ss(tF, dK + 2 * k, dQ + 2 * k, kIdescP, k > 0);
+        mma_commit(&bar_p_full);
         return true;
       };
       bool ok = issue_scores(0);
@@ -709,34 +707,27 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                        dDm = mdesc(q0 + 3 * kTileBytes);
         const uint32_t acc0 = ci > 0 ? 1u : 0u;
         if (ci > 0) {
-          if (!(ok = wait_bar_warp(&bar_acc_free, (ci - 1) & 1, abort_flag, kWaitAccFree, ci))) break;
-          if (!(ok = wait_bar_warp(&bar_state, (ci - 1) & 1, abort_flag, kWaitState, ci))) break;
+          if (!(ok = wait_bar2(&bar_acc_free, (ci - 1) & 1, &bar_state, (ci - 1) & 1, abort_flag, kWaitAccFree, ci))) break;
           tc_fence_after_sync();
-          if (el) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k)  // AccK = V R^T : B[n = d_k][k = d_v] = R, K-major
-              mma_ss(tK, dV + 2 * k, dRk + 2 * k, kIdescAccKK, k > 0);
+          for (int k = 0; k < 4; ++k)  // AccK = V R^T : B[n = d_k][k = d_v] = R, K-major
+            mma_ss(tK, dV + 2 * k, dRk + 2 * k, kIdescAccKK, k > 0);
 #pragma unroll
-            for (int k = 0; k < 4; ++k)  // AccV = K R : B[n = d_v][k = d_k] = R, MN-major
-              mma_ss(tV, dK + 2 * k, dRm + 128 * k, kIdescAccMN, k > 0);
-          }
-          __syncwarp();
+          for (int k = 0; k < 4; ++k)  // AccV = K R : B[n = d_v][k = d_k] = R, MN-major
+            mma_ss(tV, dK + 2 * k, dRm + 128 * k, kIdescAccMN, k > 0);
         }
-        if (!(ok = wait_bar_warp(&bar_p_ready, ci & 1, abort_flag, kWaitScoreReady, ci))) break;
+        if (!(ok = wait_bar(&bar_p_ready, ci & 1, abort_flag, kWaitScoreReady, ci))) break;
         tc_fence_after_sync();
-        if (el) {
-          mma_ts(tK, tE, dQm, kIdescAccMN, acc0);
+        mma_ts(tK, tE, dQm, kIdescAccMN, acc0);
 #pragma unroll
-          for (int k = 1; k < 8; ++k) mma_ts(tK, tE + 8 * k, dQm + 128 * k, kIdescAccMN, 1u);
-          mma_ts(tV, tF, dDm, kIdescAccMN, acc0);
+        for (int k = 1; k < 8; ++k) mma_ts(tK, tE + 8 * k, dQm + 128 * k, kIdescAccMN, 1u);
+        mma_ts(tV, tF, dDm, kIdescAccMN, acc0);
 #pragma unroll
-          for (int k = 1; k < 8; ++k) mma_ts(tV, tF + 8 * k, dDm + 128 * k, kIdescAccMN, 1u);
-          mma_ss(tR, dQm, dDm, kIdescR, acc0);
+        for (int k = 1; k < 8; ++k) mma_ts(tV, tF + 8 * k, dDm + 128 * k, kIdescAccMN, 1u);
+        mma_ss(tR, dQm, dDm, kIdescR, acc0);
 #pragma unroll
-          for (int k = 1; k < 8; ++k) mma_ss(tR, dQm + 128 * k, dDm + 128 * k, kIdescR, 1u);
-          mma_commit(&bar_acc_full);
-        }
-        __syncwarp();
+        for (int k = 1; k < 8; ++k) mma_ss(tR, dQm + 128 * k, dDm + 128 * k, kIdescR, 1u);
+        mma_commit(&bar_acc_full);
         if (ci + 1 < nchunks) ok = issue_scores(ci + 1);
       }
     }
