@@ -210,6 +210,23 @@ __device__ __forceinline__ bool wait_bar2(uint64_t* bar_a, uint32_t parity_a, ui
   atomicCAS(&g_cott_status, 0, (code << 16) | (chunk & 0xffff));
   return false;
 }
+// Up to four barriers at once (null entries are skipped).
+__device__ __forceinline__ bool wait_bar4(uint64_t* b0, uint32_t p0, uint64_t* b1, uint32_t p1, uint64_t* b2, uint32_t p2,
+                                          uint64_t* b3, uint32_t p3, volatile int* abort_flag, int code, int chunk) {
+  bool d0 = b0 == nullptr, d1 = b1 == nullptr, d2 = b2 == nullptr, d3 = b3 == nullptr;
+  for (uint32_t i = 0; i < ptx::kMaxPolls; ++i) {
+    const bool t0 = d0 || ptx::mbar_try_wait(b0, p0);
+    const bool t1 = d1 || ptx::mbar_try_wait(b1, p1);
+    const bool t2 = d2 || ptx::mbar_try_wait(b2, p2);
+    const bool t3 = d3 || ptx::mbar_try_wait(b3, p3);
+    d0 = t0; d1 = t1; d2 = t2; d3 = t3;
+    if (d0 && d1 && d2 && d3) return true;
+    if (*abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicCAS(&g_cott_status, 0, (code << 16) | (chunk & 0xffff));
+  return false;
+}
 // Whole-warp wait: every lane waits on the barrier itself (each thread must observe the completion
 // to see TMA-written data) -- one warp-wide try_wait with a suspend hint, so a waiting warp sleeps in
 // hardware instead of spinning; the outcome is made warp-uniform.
@@ -406,12 +423,14 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         mma_commit(&bar_p_full[c & 1]);
         COTT_TRACE_EV(7, c);
       };
-      // Issue order per chunk c -- chosen so that nothing this thread waits for was requested less
-      // than about one chunk period earlier:
-      //   S += Y^T Zw (c)      needs Zw(c) and the conversion of S after chunk c-1
-      //   scores (c+1)         needs the TMA of chunk c+1
-      //   Acc = X S (c)        needs the 16-bit S converted after chunk c-1 (buffer c&1), Acc buffer free
-      //   Acc += P Zw (c)      needs the masked scores of chunk c (issued one chunk earlier)
+      // ONE wait point per chunk c, with all its barriers polled together (an mbarrier wait costs a few
+      // hundred cycles in this kernel even when the phase is already complete):
+      //   masked scores of chunk c ready   (implies Zw(c): the score group prepares Zw(c) before it masks chunk c)
+      //   state converted after chunk c-1  (16-bit S in buffer c&1, and the TMEM state free to accumulate)
+      //   accumulator buffer c&1 read out  (chunk c-2)
+      //   TMA of chunk c+1 landed
+      // then everything for the chunk is issued in the order that gets the dependants started soonest:
+      //   scores(c+1) -> mask pass;  S += Y^T Zw (c) -> state conversion;  Acc(c) = X S + P Zw -> output pass.
       bool ok = wait_bar(&bar_full[0], 0, abort_flag, kWaitTma, 0);
       if (ok) {
         tc_fence_after_sync();
@@ -423,37 +442,27 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         const uint64_t dX = kdesc(x0), dYm = mdesc(x0 + kTileBytes), dZm = mdesc(x0 + 2 * kTileBytes);
         const uint32_t tP = tP0 + 128 * b, tAcc = tAcc0 + 64 * b;
         const uint32_t acc_s = c > 0 ? 1u : 0u;
-        if (c > 0) ok = wait_bar2(&bar_prep[s], (c / NS) & 1, &bar_state, (c - 1) & 1, abort_flag, kWaitPrepped, c);
-        else ok = wait_bar(&bar_prep[s], (c / NS) & 1, abort_flag, kWaitPrepped, c);
+        const bool more = c + 1 < nchunks;
+        ok = wait_bar4(&bar_p_ready[b], (c >> 1) & 1, c > 0 ? &bar_state : nullptr, (c - 1) & 1,
+                       c >= 2 ? &bar_acc_free[b] : nullptr, ((c >> 1) - 1) & 1,
+                       more ? &bar_full[(c + 1) % NS] : nullptr, ((c + 1) / NS) & 1, abort_flag, kWaitScoreReady, c);
         if (!ok) break;
         tc_fence_after_sync();
         COTT_TRACE_EV(0, c);
-        if (c + 1 < nchunks) {
+        if (more) {
+          issue_scores(c + 1);
           mma_ss(tS, dYm, dZm, kIdescS, acc_s);  // S += Y^T Zw
 #pragma unroll
           for (int k = 1; k < 8; ++k) mma_ss(tS, dYm + 128 * k, dZm + 128 * k, kIdescS, 1u);
           mma_commit(&bar_s_full);
-          COTT_TRACE_EV(5, c);
-          const int s1 = (c + 1) % NS;
-          if (c >= 2) ok = wait_bar2(&bar_full[s1], ((c + 1) / NS) & 1, &bar_acc_free[b], ((c >> 1) - 1) & 1, abort_flag, kWaitTma, c);
-          else ok = wait_bar(&bar_full[s1], ((c + 1) / NS) & 1, abort_flag, kWaitTma, c);
-          if (!ok) break;
-          tc_fence_after_sync();
-          issue_scores(c + 1);
-        } else if (c >= 2) {
-          if (!(ok = wait_bar(&bar_acc_free[b], ((c >> 1) - 1) & 1, abort_flag, kWaitAccFree, c))) break;
-          tc_fence_after_sync();
+          COTT_TRACE_EV(1, c);
         }
-        COTT_TRACE_EV(1, c);
         if (c > 0) {
           const uint64_t dS = dS0 + static_cast<uint64_t>(b * ((kTcD * 128) >> 4));
 #pragma unroll
           for (int k = 0; k < 4; ++k)  // Acc = X S   (S as MN-major B operand)
             mma_ss(tAcc, dX + 2 * k, dS + 128 * k, kIdescAcc, k > 0);
         }
-        if (!(ok = wait_bar(&bar_p_ready[b], (c >> 1) & 1, abort_flag, kWaitScoreReady, c))) break;
-        tc_fence_after_sync();
-        COTT_TRACE_EV(2, c);
         mma_ts(tAcc, tP, dZm, kIdescAcc, acc_s);  // Acc += P Zw   (P from TMEM, Zw MN-major)
 #pragma unroll
         for (int k = 1; k < 8; ++k) mma_ts(tAcc, tP + 8 * k, dZm + 128 * k, kIdescAcc, 1u);
