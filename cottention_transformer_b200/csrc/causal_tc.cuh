@@ -346,7 +346,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char* sS = smem + NS * STAGE;  // 2 x [64 x 64] 16-bit state operand (double-buffered), 2 x 8 KB
   __shared__ uint64_t bar_full[NS], bar_free[NS], bar_prep[NS], bar_p_full[2], bar_p_ready[2], bar_acc_full[2],
-      bar_acc_free[2], bar_s_full, bar_state;
+      bar_acc_free[2], bar_s_full, bar_state, bar_state2;
   __shared__ uint32_t tmem_slot;
   COTT_TRACE_DECL
   __shared__ int abort_flag_s;
@@ -372,6 +372,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
     }
     mbar_init(&bar_s_full, 1);
     mbar_init(&bar_state, 4);
+    mbar_init(&bar_state2, 4);
     mbar_fence_init();
     abort_flag_s = 0;
     tma_prefetch_desc(&mapX);
@@ -390,12 +391,20 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   // TMEM columns: scores 2 x 128 | accumulators 2 x 64 | state 64
   const uint32_t tP0 = tmem, tAcc0 = tmem + 256, tS = tmem + 384;
 
+  // Two issuing threads on two different schedulers share the tensor-core and TMA issue work: with a
+  // single issuing thread that thread was busy for the whole chunk period (each of its instructions
+  // competes with the two epilogue warps of its scheduler), i.e. it was the critical path.
+  //   warp 0, lane 0:  TMA loads, scores P(c+1) = X Y^T, state S += Y^T Zw (c)
+  //   warp 1, lane 0:  accumulators Acc(c) = X S + P Zw
+  // MMAs of the two threads are ordered only through the mbarriers.
+  constexpr uint32_t kIdescP = make_idesc(128, 128, BF, false, false);
+  constexpr uint32_t kIdescAcc = make_idesc(128, 64, BF, false, true);
+  constexpr uint32_t kIdescS = make_idesc(64, 64, BF, true, true);
   if (warp == 0) {
-    // ---------------------------------------------------------------- TMA producer
+    // ---------------------------------------------------------------- TMA + scores + state
     if (lane == 0) {
-      for (int c = 0; c < nchunks; ++c) {
+      auto issue_loads = [&](int c) {
         const int s = c % NS;
-        if (c >= NS && !wait_bar(&bar_free[s], ((c / NS) - 1) & 1, abort_flag, kWaitStageFree, c)) break;
         unsigned char* st = smem + s * STAGE;
         mbar_expect_tx(&bar_full[s], STAGE);
         tma_load_3d(st, &mapX, &bar_full[s], 0, c * kTcChunk, bh);
@@ -403,67 +412,74 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         tma_load_3d(st + 2 * kTileBytes, &mapZ, &bar_full[s], 0, c * kTcChunk, bh);
         if (MODE == kModeDq) tma_load_3d(st + 3 * kTileBytes, &mapQ, &bar_full[s], 0, c * kTcChunk, bh);
         COTT_TRACE_EV(0, c);
-      }
-    }
-  } else if (warp == 1) {
-    // ---------------------------------------------------------------- MMA issuer (one thread)
-    // An mbarrier wait costs about 200 cycles even when the phase is already complete, so the waits
-    // are paired (both try_waits in flight together) and only this one thread takes part.
-    if (lane == 0) {
-      constexpr uint32_t kIdescP = make_idesc(128, 128, BF, false, false);
-      constexpr uint32_t kIdescAcc = make_idesc(128, 64, BF, false, true);
-      constexpr uint32_t kIdescS = make_idesc(64, 64, BF, true, true);
-      const uint64_t dS0 = mdesc(smem_u32(sS));
-      auto issue_scores = [&](int c) {  // caller has waited for the TMA of chunk c
+      };
+      auto issue_scores = [&](int c) {  // caller has waited for the TMA of chunk c and for the buffer
         const uint32_t x0 = smem_u32(smem + (c % NS) * STAGE);
         const uint64_t dX = kdesc(x0), dY = kdesc(x0 + kTileBytes);
         const uint32_t tP = tP0 + 128 * (c & 1);
 #pragma unroll
         for (int k = 0; k < 4; ++k) mma_ss(tP, dX + 2 * k, dY + 2 * k, kIdescP, k > 0);
         mma_commit(&bar_p_full[c & 1]);
-        COTT_TRACE_EV(7, c);
+        COTT_TRACE_EV(1, c);
       };
-      // ONE wait point per chunk c, with all its barriers polled together (an mbarrier wait costs a few
-      // hundred cycles in this kernel even when the phase is already complete):
-      //   masked scores of chunk c ready   (implies Zw(c): the score group prepares Zw(c) before it masks chunk c)
-      //   state converted after chunk c-1  (16-bit S in buffer c&1, and the TMEM state free to accumulate)
-      //   accumulator buffer c&1 read out  (chunk c-2)
-      //   TMA of chunk c+1 landed
-      // then everything for the chunk is issued in the order that gets the dependants started soonest:
-      //   scores(c+1) -> mask pass;  S += Y^T Zw (c) -> state conversion;  Acc(c) = X S + P Zw -> output pass.
+      for (int c = 0; c < NS && c < nchunks; ++c) issue_loads(c);
       bool ok = wait_bar(&bar_full[0], 0, abort_flag, kWaitTma, 0);
       if (ok) {
         tc_fence_after_sync();
         issue_scores(0);
       }
       for (int c = 0; ok && c < nchunks; ++c) {
-        const int s = c % NS, b = c & 1;
-        const uint32_t x0 = smem_u32(smem + s * STAGE);
-        const uint64_t dX = kdesc(x0), dYm = mdesc(x0 + kTileBytes), dZm = mdesc(x0 + 2 * kTileBytes);
-        const uint32_t tP = tP0 + 128 * b, tAcc = tAcc0 + 64 * b;
-        const uint32_t acc_s = c > 0 ? 1u : 0u;
-        const bool more = c + 1 < nchunks;
-        ok = wait_bar4(&bar_p_ready[b], (c >> 1) & 1, c > 0 ? &bar_state : nullptr, (c - 1) & 1,
-                       c >= 2 ? &bar_acc_free[b] : nullptr, ((c >> 1) - 1) & 1,
-                       more ? &bar_full[(c + 1) % NS] : nullptr, ((c + 1) / NS) & 1, abort_flag, kWaitScoreReady, c);
-        if (!ok) break;
-        tc_fence_after_sync();
-        COTT_TRACE_EV(0, c);
-        if (more) {
+        if (c + 1 < nchunks) {
+          // scores of chunk c+1: its TMA, and (buffer reuse) the accumulator MMAs of chunk c-1 done
+          const int s1 = (c + 1) % NS;
+          ok = wait_bar4(&bar_full[s1], ((c + 1) / NS) & 1, c >= 1 ? &bar_acc_full[(c + 1) & 1] : nullptr,
+                         ((c - 1) >> 1) & 1, nullptr, 0, nullptr, 0, abort_flag, kWaitTma, c);
+          if (!ok) break;
+          tc_fence_after_sync();
           issue_scores(c + 1);
-          mma_ss(tS, dYm, dZm, kIdescS, acc_s);  // S += Y^T Zw
+          // state update of chunk c: Zw(c), and the conversion of S after chunk c-1
+          ok = wait_bar4(&bar_prep[c % NS], (c / NS) & 1, c > 0 ? &bar_state2 : nullptr, (c - 1) & 1, nullptr, 0,
+                         nullptr, 0, abort_flag, kWaitPrepped, c);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t x0 = smem_u32(smem + (c % NS) * STAGE);
+          const uint64_t dYm = mdesc(x0 + kTileBytes), dZm = mdesc(x0 + 2 * kTileBytes);
+          mma_ss(tS, dYm, dZm, kIdescS, c > 0 ? 1u : 0u);
 #pragma unroll
           for (int k = 1; k < 8; ++k) mma_ss(tS, dYm + 128 * k, dZm + 128 * k, kIdescS, 1u);
           mma_commit(&bar_s_full);
-          COTT_TRACE_EV(1, c);
+          COTT_TRACE_EV(2, c);
         }
+        if (c + NS < nchunks) {
+          if (!(ok = wait_bar(&bar_free[c % NS], (c / NS) & 1, abort_flag, kWaitStageFree, c))) break;
+          issue_loads(c + NS);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- accumulators
+    if (lane == 0) {
+      const uint64_t dS0 = mdesc(smem_u32(sS));
+      for (int c = 0; c < nchunks; ++c) {
+        const int s = c % NS, b = c & 1;
+        const uint32_t x0 = smem_u32(smem + s * STAGE);
+        const uint64_t dX = kdesc(x0), dZm = mdesc(x0 + 2 * kTileBytes);
+        const uint32_t tP = tP0 + 128 * b, tAcc = tAcc0 + 64 * b;
+        // masked scores of chunk c (this also implies Zw(c): the score group prepares Zw(c) before it
+        // masks chunk c), the 16-bit state after chunk c-1, and the accumulator buffer read out
+        if (!wait_bar4(&bar_p_ready[b], (c >> 1) & 1, c > 0 ? &bar_state : nullptr, (c - 1) & 1,
+                       c >= 2 ? &bar_acc_free[b] : nullptr, ((c >> 1) - 1) & 1, nullptr, 0, abort_flag,
+                       kWaitScoreReady, c))
+          break;
+        tc_fence_after_sync();
+        COTT_TRACE_EV(0, c);
         if (c > 0) {
           const uint64_t dS = dS0 + static_cast<uint64_t>(b * ((kTcD * 128) >> 4));
 #pragma unroll
           for (int k = 0; k < 4; ++k)  // Acc = X S   (S as MN-major B operand)
             mma_ss(tAcc, dX + 2 * k, dS + 128 * k, kIdescAcc, k > 0);
         }
-        mma_ts(tAcc, tP, dZm, kIdescAcc, acc_s);  // Acc += P Zw   (P from TMEM, Zw MN-major)
+        mma_ts(tAcc, tP, dZm, kIdescAcc, c > 0 ? 1u : 0u);  // Acc += P Zw   (P from TMEM, Zw MN-major)
 #pragma unroll
         for (int k = 1; k < 8; ++k) mma_ts(tAcc, tP + 8 * k, dZm + 128 * k, kIdescAcc, 1u);
         mma_commit(&bar_acc_full[b]);
@@ -533,6 +549,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         fence_proxy_async_smem();
         tc_fence_before_sync();
         warp_arrive(&bar_state, lane);
+        if (lane == 0) mbar_arrive(&bar_state2);
       }
       COTT_TRACE_EV(1, c);
       if (!wait_bar_warp(&bar_acc_full[b], (c >> 1) & 1, abort_flag, kWaitAcc, c)) break;
