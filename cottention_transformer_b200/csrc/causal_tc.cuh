@@ -33,7 +33,7 @@ __device__ int g_cott_status;  // 0 = ok; else (code << 16 | chunk) of the first
 
 // Optional timeline tracing (debug builds only, -DCOTT_TRACE): CTA 0 records clock64() at role events.
 #ifdef COTT_TRACE
-constexpr int kTraceWarps = 16, kTraceChunks = 40, kTraceEvents = 8;
+constexpr int kTraceWarps = 11, kTraceChunks = 40, kTraceEvents = 8;
 __device__ unsigned int g_cott_trace[kTraceWarps * kTraceChunks * kTraceEvents];
 // timestamps go to shared memory (a global store in the middle of a role would itself disturb the
 // fences and waits being timed) and are copied out when the kernel ends
@@ -277,6 +277,38 @@ __device__ __forceinline__ void tmem_row64(uint32_t taddr_lane, float* x) {
   for (int j = 0; j < 64; ++j) x[j] = __uint_as_float(r[j]);
 }
 
+// Row `row` of a swizzled [128 x 64] 16-bit tile <- 64 floats (the layout a TMA store with the same
+// 128-byte swizzle reads).
+template <typename T>
+__device__ __forceinline__ void write_row64(unsigned char* tile, int row, const float* x) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    uint4 u;
+    u.x = Pack2<T>::pack(x[8 * j + 0], x[8 * j + 1]);
+    u.y = Pack2<T>::pack(x[8 * j + 2], x[8 * j + 3]);
+    u.z = Pack2<T>::pack(x[8 * j + 4], x[8 * j + 5]);
+    u.w = Pack2<T>::pack(x[8 * j + 6], x[8 * j + 7]);
+    *tile_piece(tile, row, j) = u;
+  }
+}
+
+// The warp's 32 rows (rows 32*wq .. 32*wq+31 of a swizzled tile, written by its own lanes) go to global
+// memory rows y0 + 32*wq.. as one TMA store; rows past the end of the sequence are clipped by the
+// tensor map.  The store is left in flight: stores_read() must come before the tile is handed back.
+__device__ __forceinline__ void warp_store_rows32(const CUtensorMap* map, unsigned char* tile, int wq, int lane, int y0,
+                                                  int n_rows, int bh) {
+  ptx::fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0 && y0 + 32 * wq < n_rows) {
+    ptx::tma_store_3d(map, tile + wq * (32 * 128), 0, y0 + 32 * wq, bh);
+    ptx::tma_store_commit();
+  }
+}
+// Lane 0 waits until the TMA engine has read the shared memory of every store it has issued.
+__device__ __forceinline__ void stores_read(int lane) {
+  if (lane == 0) ptx::tma_store_wait_read<0>();
+}
+
 template <typename T>
 __device__ __forceinline__ void store_row64(T* dst_row, const float* x) {
   uint4* dst = reinterpret_cast<uint4*>(dst_row);
@@ -325,14 +357,14 @@ enum {
   kWaitAccFree = 7, kWaitState = 8
 };
 
-constexpr int kTcThreads = 320;
+constexpr int kTcThreads = 352;
 constexpr int kTcStages = 3;
 
 template <typename T, int MODE>
 __global__ void __launch_bounds__(kTcThreads, 1)
 causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapY,
                  const __grid_constant__ CUtensorMap mapZ, const __grid_constant__ CUtensorMap mapQ,
-                 T* __restrict__ out, const float* __restrict__ norm_const, int H, int N) {
+                 const __grid_constant__ CUtensorMap mapOut, const float* __restrict__ norm_const, int H, int N) {
   using namespace ptx;
   constexpr int NT = (MODE == kModeFwd) ? 3 : 4;  // tiles per stage
   constexpr int STAGE = NT * kTileBytes;
@@ -401,18 +433,8 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   constexpr uint32_t kIdescAcc = make_idesc(128, 64, BF, false, true);
   constexpr uint32_t kIdescS = make_idesc(64, 64, BF, true, true);
   if (warp == 0) {
-    // ---------------------------------------------------------------- TMA + scores + state
+    // ---------------------------------------------------------------- scores + state
     if (lane == 0) {
-      auto issue_loads = [&](int c) {
-        const int s = c % NS;
-        unsigned char* st = smem + s * STAGE;
-        mbar_expect_tx(&bar_full[s], STAGE);
-        tma_load_3d(st, &mapX, &bar_full[s], 0, c * kTcChunk, bh);
-        tma_load_3d(st + kTileBytes, &mapY, &bar_full[s], 0, c * kTcChunk, bh);
-        tma_load_3d(st + 2 * kTileBytes, &mapZ, &bar_full[s], 0, c * kTcChunk, bh);
-        if (MODE == kModeDq) tma_load_3d(st + 3 * kTileBytes, &mapQ, &bar_full[s], 0, c * kTcChunk, bh);
-        COTT_TRACE_EV(0, c);
-      };
       auto issue_scores = [&](int c) {  // caller has waited for the TMA of chunk c and for the buffer
         const uint32_t x0 = smem_u32(smem + (c % NS) * STAGE);
         const uint64_t dX = kdesc(x0), dY = kdesc(x0 + kTileBytes);
@@ -422,14 +444,13 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         mma_commit(&bar_p_full[c & 1]);
         COTT_TRACE_EV(1, c);
       };
-      for (int c = 0; c < NS && c < nchunks; ++c) issue_loads(c);
       bool ok = wait_bar(&bar_full[0], 0, abort_flag, kWaitTma, 0);
       if (ok) {
         tc_fence_after_sync();
         issue_scores(0);
       }
-      for (int c = 0; ok && c < nchunks; ++c) {
-        if (c + 1 < nchunks) {
+      for (int c = 0; ok && c + 1 < nchunks; ++c) {
+        {
           // scores of chunk c+1: its TMA, and (buffer reuse) the accumulator MMAs of chunk c-1 done
           const int s1 = (c + 1) % NS;
           ok = wait_bar4(&bar_full[s1], ((c + 1) / NS) & 1, c >= 1 ? &bar_acc_full[(c + 1) & 1] : nullptr,
@@ -450,10 +471,27 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
           mma_commit(&bar_s_full);
           COTT_TRACE_EV(2, c);
         }
-        if (c + NS < nchunks) {
-          if (!(ok = wait_bar(&bar_free[c % NS], (c / NS) & 1, abort_flag, kWaitStageFree, c))) break;
-          issue_loads(c + NS);
-        }
+      }
+    }
+  } else if (warp == kTcThreads / 32 - 1) {
+    // ---------------------------------------------------------------- TMA loads
+    // A thread of its own: the wait for a free stage ends late in a chunk's life (after its output
+    // store has left shared memory) and must not hold up the MMA issue of the following chunks.
+    if (lane == 0) {
+      auto issue_loads = [&](int c) {
+        const int s = c % NS;
+        unsigned char* st = smem + s * STAGE;
+        mbar_expect_tx(&bar_full[s], STAGE);
+        tma_load_3d(st, &mapX, &bar_full[s], 0, c * kTcChunk, bh);
+        tma_load_3d(st + kTileBytes, &mapY, &bar_full[s], 0, c * kTcChunk, bh);
+        tma_load_3d(st + 2 * kTileBytes, &mapZ, &bar_full[s], 0, c * kTcChunk, bh);
+        if (MODE == kModeDq) tma_load_3d(st + 3 * kTileBytes, &mapQ, &bar_full[s], 0, c * kTcChunk, bh);
+        COTT_TRACE_EV(0, c);
+      };
+      for (int c = 0; c < NS && c < nchunks; ++c) issue_loads(c);
+      for (int c = 0; c + NS < nchunks; ++c) {
+        if (!wait_bar(&bar_free[c % NS], (c / NS) & 1, abort_flag, kWaitStageFree, c)) break;
+        issue_loads(c + NS);
       }
     }
   } else if (warp == 1) {
@@ -529,6 +567,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
     // ---------------------------------------------------------------- output group
     const int wq = warp & 3, row = 32 * wq + lane;
     const uint32_t lane_base = static_cast<uint32_t>(32 * wq) << 16;
+    int pending = -1;  // stage whose output store may still be reading shared memory
     for (int c = 0; c < nchunks; ++c) {
       const int s = c % NS, b = c & 1;
       unsigned char* sQ = smem + s * STAGE + ((MODE == kModeDq) ? 3 * kTileBytes : 0);
@@ -540,6 +579,12 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       const float rq = 1.f;
 #endif
       COTT_TRACE_EV(0, c);
+      // Release the previous chunk's stage once its output store has read it.  This must come before
+      // any wait on the issuing thread that also refills stages, or the two would wait on each other.
+      if (pending >= 0) {
+        stores_read(lane);
+        warp_arrive(&bar_free[pending], lane);
+      }
       if (c + 1 < nchunks) {  // S after chunk c -> 16-bit operand for chunk c+1 (buffer (c+1)&1)
         if (!wait_bar_warp(&bar_s_full, c & 1, abort_flag, kWaitState, c)) break;
         tc_fence_after_sync();
@@ -594,16 +639,18 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         }
       }
       COTT_TRACE_EV(5, c);
-      warp_arrive(&bar_free[s], lane);  // last read of this stage by this warp
+      // The X tile of this stage has no reader left (its MMAs completed before acc_full, and in forward
+      // mode this thread has taken the norm of its own row): the output rows are staged in it, in the
+      // swizzled layout, and leave by TMA.  The stage is released (next iteration) once the TMA engine
+      // has read them.
+      unsigned char* sO = smem + s * STAGE;
+      write_row64<T>(sO, row, acc);
       COTT_TRACE_EV(6, c);
-      const int pos = c * kTcChunk + row;
-#if !(COTT_SKEL & 4)
-      if (pos < N) store_row64<T>(out + (static_cast<size_t>(bh) * N + pos) * kTcD, acc);
-#else
-      if (pos < N && acc[5] == 123.f) out[0] = T(0);
-#endif
+      warp_store_rows32(&mapOut, sO, wq, lane, c * kTcChunk, N, bh);
+      pending = s;
       COTT_TRACE_EV(4, c);
     }
+    if (lane == 0) tma_store_wait<0>();
   }
 
   // ---- leave: make sure no TMA of this CTA is still in flight (bounded), release TMEM ------------
@@ -636,7 +683,7 @@ template <typename T>
 __global__ void __launch_bounds__(kTcThreads, 1)
 causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                      const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
-                     T* __restrict__ dk, T* __restrict__ dv, float* __restrict__ dnorm,
+                     const __grid_constant__ CUtensorMap mapDK, const __grid_constant__ CUtensorMap mapDV, float* __restrict__ dnorm,
                      const float* __restrict__ norm_const, int H, int N) {
   using namespace ptx;
   constexpr int STAGE = 4 * kTileBytes;
@@ -647,10 +694,11 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   // (offset arithmetic on the __shared__ array keeps the pointer's address space known to the
   // compiler, so tile accesses compile to LDS/STS rather than generic loads and stores)
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  unsigned char* sR = smem + NS * STAGE;  // [64 x 64] 16-bit state operand (rows = d_k, cols = d_v)
+  unsigned char* sR = smem + NS * STAGE;  // 2 x [64 x 64] 16-bit state operand (rows = d_k, cols = d_v), double-buffered
   __shared__ uint64_t bar_full[NS], bar_free[NS], bar_prep[NS], bar_p_full, bar_p_ready, bar_acc_full, bar_acc_free,
-      bar_state;
+      bar_state, bar_state2, bar_r_full;
   __shared__ uint32_t tmem_slot;
+  COTT_TRACE_DECL
   __shared__ int abort_flag_s;
   volatile int* abort_flag = &abort_flag_s;
 
@@ -671,6 +719,8 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     mbar_init(&bar_acc_full, 1);
     mbar_init(&bar_acc_free, 4);
     mbar_init(&bar_state, 4);
+    mbar_init(&bar_state2, 4);
+    mbar_init(&bar_r_full, 1);
     mbar_fence_init();
     abort_flag_s = 0;
     tma_prefetch_desc(&mapQ);
@@ -689,11 +739,17 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   const uint32_t tE = tmem, tF = tmem + 128, tK = tmem + 256, tV = tmem + 320, tR = tmem + 384;
 
   // iteration ci handles chunk nchunks-1-ci (the sequence is walked backwards)
-  if (warp == 0) {
-    if (lane == 0) {
-      for (int ci = 0; ci < nchunks; ++ci) {
+  // Two issuing threads (see causal_tc_kernel):
+  //   warp 0, lane 0:  TMA loads, score tiles E, F of chunk ci+1, state R += Qw^T dO (ci)
+  //   warp 1, lane 0:  accumulators AccK, AccV of chunk ci
+  constexpr uint32_t kIdescP = make_idesc(128, 128, BF, false, false);
+  constexpr uint32_t kIdescAccKK = make_idesc(128, 64, BF, false, false);  // B K-major (V R^T)
+  constexpr uint32_t kIdescAccMN = make_idesc(128, 64, BF, false, true);   // B MN-major
+  constexpr uint32_t kIdescR = make_idesc(64, 64, BF, true, true);
+  if (warp == kTcThreads / 32 - 1) {
+    if (lane == 0) {  // TMA loads (a thread of its own, see causal_tc_kernel)
+      auto issue_loads = [&](int ci) {
         const int s = ci % NS;
-        if (ci >= NS && !wait_bar(&bar_free[s], ((ci / NS) - 1) & 1, abort_flag, kWaitStageFree, ci)) break;
         const int y = (nchunks - 1 - ci) * kTcChunk;
         unsigned char* st = smem + s * STAGE;
         mbar_expect_tx(&bar_full[s], STAGE);
@@ -701,21 +757,18 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         tma_load_3d(st + kTileBytes, &mapK, &bar_full[s], 0, y, bh);
         tma_load_3d(st + 2 * kTileBytes, &mapV, &bar_full[s], 0, y, bh);
         tma_load_3d(st + 3 * kTileBytes, &mapDO, &bar_full[s], 0, y, bh);
+      };
+      for (int ci = 0; ci < NS && ci < nchunks; ++ci) issue_loads(ci);
+      for (int ci = 0; ci + NS < nchunks; ++ci) {
+        if (!wait_bar(&bar_free[ci % NS], (ci / NS) & 1, abort_flag, kWaitStageFree, ci)) break;
+        COTT_TRACE_EV(4, ci);
+        issue_loads(ci + NS);
       }
     }
-  } else if (warp == 1) {
-    // MMA issuer (one thread; waits paired, see causal_tc_kernel)
+  } else if (warp == 0) {
     if (lane == 0) {
-      constexpr uint32_t kIdescP = make_idesc(128, 128, BF, false, false);
-      constexpr uint32_t kIdescAccKK = make_idesc(128, 64, BF, false, false);  // B K-major (V R^T)
-      constexpr uint32_t kIdescAccMN = make_idesc(128, 64, BF, false, true);   // B MN-major
-      constexpr uint32_t kIdescR = make_idesc(64, 64, BF, true, true);
-      const uint64_t dRk = kdesc(smem_u32(sR)), dRm = mdesc(smem_u32(sR));
-      auto issue_scores = [&](int ci) -> bool {
-        const int s = ci % NS;
-        if (!wait_bar2(&bar_full[s], (ci / NS) & 1, &bar_prep[s], (ci / NS) & 1, abort_flag, kWaitTma, ci)) return false;
-        tc_fence_after_sync();
-        const uint32_t q0 = smem_u32(smem + s * STAGE);
+      auto issue_scores = [&](int ci) {  // caller has waited for TMA(ci), Qw(ci) and for the tiles to be free
+        const uint32_t q0 = smem_u32(smem + (ci % NS) * STAGE);
         const uint64_t dQ = kdesc(q0), dK = kdesc(q0 + kTileBytes), dV = kdesc(q0 + 2 * kTileBytes),
                        dD = kdesc(q0 + 3 * kTileBytes);
 #pragma unroll
@@ -723,18 +776,57 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
 #pragma unroll
         for (int k = 0; k < 4; ++k) mma_ss(tF, dK + 2 * k, dQ + 2 * k, kIdescP, k > 0);
         mma_commit(&bar_p_full);
-        return true;
       };
-      bool ok = issue_scores(0);
-      for (int ci = 0; ok && ci < nchunks; ++ci) {
+      bool ok = wait_bar2(&bar_full[0], 0, &bar_prep[0], 0, abort_flag, kWaitTma, 0);
+      if (ok) {
+        tc_fence_after_sync();
+        issue_scores(0);
+      }
+      for (int ci = 0; ok && ci + 1 < nchunks; ++ci) {
+        {
+          // state of chunk ci (Qw(ci) was waited for before its score tiles were issued); the 16-bit
+          // conversion after chunk ci-1 must have finished reading the TMEM state
+          if (ci > 0 && !(ok = wait_bar(&bar_state2, (ci - 1) & 1, abort_flag, kWaitState, ci))) break;
+          tc_fence_after_sync();
+          COTT_TRACE_EV(0, ci);
+          const uint32_t q0 = smem_u32(smem + (ci % NS) * STAGE);
+          const uint64_t dQm = mdesc(q0), dDm = mdesc(q0 + 3 * kTileBytes);
+          mma_ss(tR, dQm, dDm, kIdescR, ci > 0 ? 1u : 0u);
+#pragma unroll
+          for (int k = 1; k < 8; ++k) mma_ss(tR, dQm + 128 * k, dDm + 128 * k, kIdescR, 1u);
+          mma_commit(&bar_r_full);
+          COTT_TRACE_EV(1, ci);
+          // score tiles of chunk ci+1: single-buffered, so the accumulator MMAs of chunk ci (which read the
+          // 16-bit scores from TMEM) must be complete
+          const int s1 = (ci + 1) % NS;
+          ok = wait_bar4(&bar_full[s1], ((ci + 1) / NS) & 1, &bar_prep[s1], ((ci + 1) / NS) & 1, &bar_acc_full, ci & 1,
+                         nullptr, 0, abort_flag, kWaitTma, ci);
+          if (!ok) break;
+          tc_fence_after_sync();
+          COTT_TRACE_EV(2, ci);
+          issue_scores(ci + 1);
+          COTT_TRACE_EV(3, ci);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t r0 = smem_u32(sR);
+      for (int ci = 0; ci < nchunks; ++ci) {
         const int s = ci % NS;
         const uint32_t q0 = smem_u32(smem + s * STAGE);
         const uint64_t dK = kdesc(q0 + kTileBytes), dV = kdesc(q0 + 2 * kTileBytes), dQm = mdesc(q0),
                        dDm = mdesc(q0 + 3 * kTileBytes);
         const uint32_t acc0 = ci > 0 ? 1u : 0u;
+        // masked scores of chunk ci (which implies Qw(ci)), 16-bit state after chunk ci-1, accumulators read out
+        if (!wait_bar4(&bar_p_ready, ci & 1, ci > 0 ? &bar_state : nullptr, (ci - 1) & 1,
+                       ci > 0 ? &bar_acc_free : nullptr, (ci - 1) & 1, nullptr, 0, abort_flag, kWaitScoreReady, ci))
+          break;
+        tc_fence_after_sync();
+        COTT_TRACE_EV(0, ci);
         if (ci > 0) {
-          if (!(ok = wait_bar2(&bar_acc_free, (ci - 1) & 1, &bar_state, (ci - 1) & 1, abort_flag, kWaitAccFree, ci))) break;
-          tc_fence_after_sync();
+          const uint32_t rb = r0 + (ci & 1) * (kTcD * 128);
+          const uint64_t dRk = kdesc(rb), dRm = mdesc(rb);
 #pragma unroll
           for (int k = 0; k < 4; ++k)  // AccK = V R^T : B[n = d_k][k = d_v] = R, K-major
             mma_ss(tK, dV + 2 * k, dRk + 2 * k, kIdescAccKK, k > 0);
@@ -742,19 +834,14 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
           for (int k = 0; k < 4; ++k)  // AccV = K R : B[n = d_v][k = d_k] = R, MN-major
             mma_ss(tV, dK + 2 * k, dRm + 128 * k, kIdescAccMN, k > 0);
         }
-        if (!(ok = wait_bar(&bar_p_ready, ci & 1, abort_flag, kWaitScoreReady, ci))) break;
-        tc_fence_after_sync();
         mma_ts(tK, tE, dQm, kIdescAccMN, acc0);
 #pragma unroll
         for (int k = 1; k < 8; ++k) mma_ts(tK, tE + 8 * k, dQm + 128 * k, kIdescAccMN, 1u);
         mma_ts(tV, tF, dDm, kIdescAccMN, acc0);
 #pragma unroll
         for (int k = 1; k < 8; ++k) mma_ts(tV, tF + 8 * k, dDm + 128 * k, kIdescAccMN, 1u);
-        mma_ss(tR, dQm, dDm, kIdescR, acc0);
-#pragma unroll
-        for (int k = 1; k < 8; ++k) mma_ss(tR, dQm + 128 * k, dDm + 128 * k, kIdescR, 1u);
         mma_commit(&bar_acc_full);
-        if (ci + 1 < nchunks) ok = issue_scores(ci + 1);
+        COTT_TRACE_EV(1, ci);
       }
     }
   } else if (warp < 6) {
@@ -772,13 +859,18 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     };
     bool ok = prepare(0);
     for (int ci = 0; ok && ci < nchunks; ++ci) {
-      if (ci + 1 < nchunks && !(ok = prepare(ci + 1))) break;
       if (!(ok = wait_bar_warp(&bar_p_full, ci & 1, abort_flag, kWaitScore, ci))) break;
       tc_fence_after_sync();
+      COTT_TRACE_EV(1, ci);
       mask_pack_inplace<T>(tE + lane_base, row, 127, wq, 3);
+      COTT_TRACE_EV(2, ci);
       mask_pack_inplace<T>(tF + lane_base, row, 127, wq, 3);
       tc_fence_before_sync();
       warp_arrive(&bar_p_ready, lane);
+      COTT_TRACE_EV(3, ci);
+      // Qw of the next chunk, while the accumulator MMAs of this one run
+      if (ci + 1 < nchunks && !(ok = prepare(ci + 1))) break;
+      COTT_TRACE_EV(0, ci);
     }
   } else {
     // output group
@@ -786,6 +878,7 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     const uint32_t lane_base = static_cast<uint32_t>(32 * wq) << 16;
     const float sigma = 1.0f / (1.0f + __expf(-norm_const[h]));
     float gsum = 0.f;  // sum_s ln(n_s) eps_s over this thread's rows
+    int pending = -1;  // stage whose output stores may still be reading shared memory
     for (int ci = 0; ci < nchunks; ++ci) {
       const int s = ci % NS;
       unsigned char* sK = smem + s * STAGE + kTileBytes;
@@ -794,14 +887,27 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       if (!wait_bar_warp(&bar_full[s], (ci / NS) & 1, abort_flag, kWaitTma, ci)) break;
       const float rk = inv_norm(row_sumsq<T>(sK, row));
       const float a = length_factor(static_cast<float>(pos + 1), sigma);
-      if (!wait_bar_warp(&bar_acc_full, ci & 1, abort_flag, kWaitAcc, ci)) break;
-      tc_fence_after_sync();
-      if (ci + 1 < nchunks) {
-        state_to_smem<T>(tR + lane_base, sR, wq, lane);
+      COTT_TRACE_EV(0, ci);
+      // Release the previous chunk's stage once its output store has read it.  This must come before
+      // any wait on the issuing thread that also refills stages, or the two would wait on each other.
+      if (pending >= 0) {
+        stores_read(lane);
+        warp_arrive(&bar_free[pending], lane);
+      }
+      if (ci + 1 < nchunks) {  // R after chunk ci -> 16-bit operand of chunk ci+1 (buffer (ci+1)&1)
+        if (!wait_bar_warp(&bar_r_full, ci & 1, abort_flag, kWaitState, ci)) break;
+        tc_fence_after_sync();
+        COTT_TRACE_EV(1, ci);
+        state_to_smem<T>(tR + lane_base, sR + ((ci + 1) & 1) * (kTcD * 128), wq, lane);
         fence_proxy_async_smem();
         tc_fence_before_sync();
         warp_arrive(&bar_state, lane);
+        if (lane == 0) mbar_arrive(&bar_state2);
+        COTT_TRACE_EV(2, ci);
       }
+      if (!wait_bar_warp(&bar_acc_full, ci & 1, abort_flag, kWaitAcc, ci)) break;
+      tc_fence_after_sync();
+      COTT_TRACE_EV(3, ci);
       float accv[64], acck[64];
       {
         uint32_t r0[64], r1[64];
@@ -816,6 +922,7 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       }
       tc_fence_before_sync();
       warp_arrive(&bar_acc_free, lane);
+      COTT_TRACE_EV(4, ci);
       float eps = 0.f;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -841,15 +948,28 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         acck[8 * j + 6] = rk * (acck[8 * j + 6] - p3.x * ke);
         acck[8 * j + 7] = rk * (acck[8 * j + 7] - p3.y * ke);
       }
-      warp_arrive(&bar_free[s], lane);  // last read of this stage by this warp
-      if (pos < N) {
+      COTT_TRACE_EV(5, ci);
+      // The K and V tiles of this stage have no reader left (every MMA that reads them completed before
+      // acc_full, and this thread is done with its own rows): dK and dV rows are staged in them, in the
+      // swizzled layout, and leave by TMA.  The stage is released (next iteration) once the TMA engine
+      // has read them.
 #pragma unroll
-        for (int j = 0; j < 64; ++j) accv[j] *= a;
-        store_row64<T>(dv + (static_cast<size_t>(bh) * N + pos) * kTcD, accv);
-        store_row64<T>(dk + (static_cast<size_t>(bh) * N + pos) * kTcD, acck);
-        if (pos > 0) gsum += logf(static_cast<float>(pos + 1)) * eps;
+      for (int j = 0; j < 64; ++j) accv[j] *= a;
+      write_row64<T>(sV, row, accv);
+      write_row64<T>(sK, row, acck);
+      const int y0 = (nchunks - 1 - ci) * kTcChunk;
+      ptx::fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0 && y0 + 32 * wq < N) {
+        ptx::tma_store_3d(&mapDV, sV + wq * (32 * 128), 0, y0 + 32 * wq, bh);
+        ptx::tma_store_3d(&mapDK, sK + wq * (32 * 128), 0, y0 + 32 * wq, bh);
+        ptx::tma_store_commit();
       }
+      pending = s;
+      if (pos > 0 && pos < N) gsum += logf(static_cast<float>(pos + 1)) * eps;
+      COTT_TRACE_EV(6, ci);
     }
+    if (lane == 0) ptx::tma_store_wait<0>();
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) gsum += __shfl_down_sync(0xffffffffu, gsum, off);
     if (lane == 0) atomicAdd(dnorm + h, -sigma * (1.0f - sigma) * gsum);
@@ -864,10 +984,11 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   }
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, 512);
+  COTT_TRACE_FLUSH();
 }
 
 inline size_t causal_bwd_kv_smem_bytes() {
-  return static_cast<size_t>(kTcStages * 4 * kTileBytes + kTcD * 128 + 1024);
+  return static_cast<size_t>(kTcStages * 4 * kTileBytes + 2 * kTcD * 128 + 1024);
 }
 
 inline size_t causal_tc_smem_bytes(int mode) {

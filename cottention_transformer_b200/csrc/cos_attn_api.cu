@@ -26,8 +26,9 @@ int aligned16(const void* p, const char* name) {
   return COTT_OK;
 }
 
-int tmap(CUtensorMap* m, const void* p, int dtype, long BH, long N) {
-  int r = make_tmap_rows64(m, p, dtype == COTT_BF16, BH, N, kTcD, kTcChunk);
+// box_rows: 128 for the chunk loads, 32 for the per-warp output stores
+int tmap(CUtensorMap* m, const void* p, int dtype, long BH, long N, int box_rows = kTcChunk) {
+  int r = make_tmap_rows64(m, p, dtype == COTT_BF16, BH, N, kTcD, box_rows);
   if (r == 1) return fail(COTT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   if (r) return fail(COTT_ERR_CUDA, "cuTensorMapEncodeTiled failed: CUresult %d (ptr %p, BH %ld, N %ld)", r - 100, p, BH, N);
   return COTT_OK;
@@ -37,14 +38,15 @@ template <typename T>
 int launch_fwd(const void* q, const void* k, const void* v, const float* nc, void* out, int B, int H, int N,
                int dtype, cudaStream_t stream) {
   const long BH = (long)B * H;
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq, mk, mv, mo;
   int st;
-  if ((st = tmap(&mq, q, dtype, BH, N)) || (st = tmap(&mk, k, dtype, BH, N)) || (st = tmap(&mv, v, dtype, BH, N)))
+  if ((st = tmap(&mq, q, dtype, BH, N)) || (st = tmap(&mk, k, dtype, BH, N)) || (st = tmap(&mv, v, dtype, BH, N)) ||
+      (st = tmap(&mo, out, dtype, BH, N, 32)))
     return st;
   auto kern = causal_tc_kernel<T, kModeFwd>;
   const size_t smem = causal_tc_smem_bytes(kModeFwd);
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<(unsigned)BH, kTcThreads, smem, stream>>>(mq, mk, mv, mq, static_cast<T*>(out), nc, H, N);
+  kern<<<(unsigned)BH, kTcThreads, smem, stream>>>(mq, mk, mv, mq, mo, nc, H, N);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
@@ -53,15 +55,16 @@ template <typename T>
 int launch_bwd_dq(const void* q, const void* k, const void* v, const float* nc, const void* dout, void* dq, int B,
                   int H, int N, int dtype, cudaStream_t stream) {
   const long BH = (long)B * H;
-  CUtensorMap mq, mk, mv, md;
+  CUtensorMap mq, mk, mv, md, mo;
   int st;
   if ((st = tmap(&mq, q, dtype, BH, N)) || (st = tmap(&mk, k, dtype, BH, N)) ||
-      (st = tmap(&mv, v, dtype, BH, N)) || (st = tmap(&md, dout, dtype, BH, N)))
+      (st = tmap(&mv, v, dtype, BH, N)) || (st = tmap(&md, dout, dtype, BH, N)) ||
+      (st = tmap(&mo, dq, dtype, BH, N, 32)))
     return st;
   auto kern = causal_tc_kernel<T, kModeDq>;
   const size_t smem = causal_tc_smem_bytes(kModeDq);
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<(unsigned)BH, kTcThreads, smem, stream>>>(md, mv, mk, mq, static_cast<T*>(dq), nc, H, N);
+  kern<<<(unsigned)BH, kTcThreads, smem, stream>>>(md, mv, mk, mq, mo, nc, H, N);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
@@ -70,17 +73,17 @@ template <typename T>
 int launch_bwd_dkdv(const void* q, const void* k, const void* v, const float* nc, const void* dout, void* dk,
                     void* dv, float* dnorm, int B, int H, int N, int dtype, cudaStream_t stream) {
   const long BH = (long)B * H;
-  CUtensorMap mq, mk, mv, md;
+  CUtensorMap mq, mk, mv, md, mdk, mdv;
   int st;
   if ((st = tmap(&mq, q, dtype, BH, N)) || (st = tmap(&mk, k, dtype, BH, N)) ||
-      (st = tmap(&mv, v, dtype, BH, N)) || (st = tmap(&md, dout, dtype, BH, N)))
+      (st = tmap(&mv, v, dtype, BH, N)) || (st = tmap(&md, dout, dtype, BH, N)) ||
+      (st = tmap(&mdk, dk, dtype, BH, N, 32)) || (st = tmap(&mdv, dv, dtype, BH, N, 32)))
     return st;
   COTT_CUDA_TRY(cudaMemsetAsync(dnorm, 0, sizeof(float) * H, stream));
   auto kern = causal_bwd_kv_kernel<T>;
   const size_t smem = causal_bwd_kv_smem_bytes();
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<(unsigned)BH, kTcThreads, smem, stream>>>(mq, mk, mv, md, static_cast<T*>(dk), static_cast<T*>(dv), dnorm, nc, H,
-                                            N);
+  kern<<<(unsigned)BH, kTcThreads, smem, stream>>>(mq, mk, mv, md, mdk, mdv, dnorm, nc, H, N);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
