@@ -33,7 +33,7 @@ __device__ int g_cott_status;  // 0 = ok; else (code << 16 | chunk) of the first
 
 // Optional timeline tracing (debug builds only, -DCOTT_TRACE): CTA 0 records clock64() at role events.
 #ifdef COTT_TRACE
-constexpr int kTraceWarps = 11, kTraceChunks = 40, kTraceEvents = 8;
+constexpr int kTraceWarps = 15, kTraceChunks = 32, kTraceEvents = 8;
 __device__ unsigned int g_cott_trace[kTraceWarps * kTraceChunks * kTraceEvents];
 // timestamps go to shared memory (a global store in the middle of a role would itself disturb the
 // fences and waits being timed) and are copied out when the kernel ends
@@ -108,17 +108,50 @@ __device__ __forceinline__ void load_row(unsigned char* tile, int row, float* x 
   }
 }
 
+// (packed 16-bit row u) . y : 8 independent chains of 8, then a tree
 template <typename T>
-__device__ __forceinline__ float row_sumsq(unsigned char* tile, int row) {
-  float s = 0.f;
+__device__ __forceinline__ float packed_dot64(const uint4* u, const float* y) {
+  float s[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    uint4 u = *tile_piece(tile, row, j);
-    float2 a = Pack2<T>::unpack(u.x), b = Pack2<T>::unpack(u.y), c = Pack2<T>::unpack(u.z),
-           d = Pack2<T>::unpack(u.w);
-    s += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y + c.x * c.x + c.y * c.y + d.x * d.x + d.y * d.y;
+    float2 a = Pack2<T>::unpack(u[j].x), b = Pack2<T>::unpack(u[j].y), c = Pack2<T>::unpack(u[j].z),
+           d = Pack2<T>::unpack(u[j].w);
+    const float* yy = y + 8 * j;
+    s[j] = fmaf(a.x, yy[0], fmaf(b.x, yy[2], fmaf(c.x, yy[4], d.x * yy[6]))) +
+           fmaf(a.y, yy[1], fmaf(b.y, yy[3], fmaf(c.y, yy[5], d.y * yy[7])));
   }
-  return s;
+  return ((s[0] + s[1]) + (s[2] + s[3])) + ((s[4] + s[5]) + (s[6] + s[7]));
+}
+// y = beta y + alpha (packed 16-bit row u)
+template <typename T>
+__device__ __forceinline__ void packed_axpby64(const uint4* u, float alpha, float beta, float* y) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float2 a = Pack2<T>::unpack(u[j].x), b = Pack2<T>::unpack(u[j].y), c = Pack2<T>::unpack(u[j].z),
+           d = Pack2<T>::unpack(u[j].w);
+    float* yy = y + 8 * j;
+    yy[0] = fmaf(beta, yy[0], alpha * a.x); yy[1] = fmaf(beta, yy[1], alpha * a.y);
+    yy[2] = fmaf(beta, yy[2], alpha * b.x); yy[3] = fmaf(beta, yy[3], alpha * b.y);
+    yy[4] = fmaf(beta, yy[4], alpha * c.x); yy[5] = fmaf(beta, yy[5], alpha * c.y);
+    yy[6] = fmaf(beta, yy[6], alpha * d.x); yy[7] = fmaf(beta, yy[7], alpha * d.y);
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ float row_sumsq(unsigned char* tile, int row) {
+  // all loads first, then 16 independent chains of 4: the row is on the critical path of its role
+  uint4 u[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) u[j] = *tile_piece(tile, row, j);
+  float s[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float2 a = Pack2<T>::unpack(u[j].x), b = Pack2<T>::unpack(u[j].y), c = Pack2<T>::unpack(u[j].z),
+           d = Pack2<T>::unpack(u[j].w);
+    s[j] = fmaf(a.x, a.x, fmaf(b.x, b.x, fmaf(c.x, c.x, d.x * d.x))) +
+           fmaf(a.y, a.y, fmaf(b.y, b.y, fmaf(c.y, c.y, d.y * d.y)));
+  }
+  return ((s[0] + s[1]) + (s[2] + s[3])) + ((s[4] + s[5]) + (s[6] + s[7]));
 }
 
 // tile[row] *= w (in place), in packed 16-bit arithmetic.  w is split into a 16-bit head and a
@@ -141,29 +174,35 @@ __device__ __forceinline__ void scale_row(unsigned char* tile, int row, float w)
     using V = typename Vec2<T>::type;
     const float wh = Vec2<T>::head(w);
     const V whi = Vec2<T>::bcast(wh), wlo = Vec2<T>::bcast(w - wh);
+    // loads, arithmetic and stores in three separate sweeps: the compiler cannot tell that the eight
+    // pieces do not alias, and would otherwise chain load -> store -> load
+    uint4 u[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) u[j] = *tile_piece(tile, row, j);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      uint4* p = tile_piece(tile, row, j);
-      uint4 u = *p;
-      V* x = reinterpret_cast<V*>(&u);
+      V* x = reinterpret_cast<V*>(&u[j]);
 #pragma unroll
       for (int e = 0; e < 4; ++e) x[e] = __hfma2(x[e], whi, __hmul2(x[e], wlo));
-      *p = u;
     }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) *tile_piece(tile, row, j) = u[j];
   } else {
     // float16 has too little range to hold the factor itself (1/|k| of a small row): multiply in fp32
+    uint4 u[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) u[j] = *tile_piece(tile, row, j);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      uint4* p = tile_piece(tile, row, j);
-      uint4 u = *p;
-      float2 a = Pack2<T>::unpack(u.x), b = Pack2<T>::unpack(u.y), c = Pack2<T>::unpack(u.z),
-             d = Pack2<T>::unpack(u.w);
-      u.x = Pack2<T>::pack(a.x * w, a.y * w);
-      u.y = Pack2<T>::pack(b.x * w, b.y * w);
-      u.z = Pack2<T>::pack(c.x * w, c.y * w);
-      u.w = Pack2<T>::pack(d.x * w, d.y * w);
-      *p = u;
+      float2 a = Pack2<T>::unpack(u[j].x), b = Pack2<T>::unpack(u[j].y), c = Pack2<T>::unpack(u[j].z),
+             d = Pack2<T>::unpack(u[j].w);
+      u[j].x = Pack2<T>::pack(a.x * w, a.y * w);
+      u[j].y = Pack2<T>::pack(b.x * w, b.y * w);
+      u[j].z = Pack2<T>::pack(c.x * w, c.y * w);
+      u[j].w = Pack2<T>::pack(d.x * w, d.y * w);
     }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) *tile_piece(tile, row, j) = u[j];
   }
 }
 
@@ -193,14 +232,25 @@ __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatil
   atomicCAS(&g_cott_status, 0, (code << 16) | (chunk & 0xffff));
   return false;
 }
+// The same for a role that is a single thread: plain polling (no suspend hint), bounded by kMaxSpins.
+__device__ __forceinline__ bool wait_bar1(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code,
+                                          int chunk) {
+  for (uint32_t i = 0; i < ptx::kMaxSpins; ++i) {
+    if (ptx::mbar_test_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicCAS(&g_cott_status, 0, (code << 16) | (chunk & 0xffff));
+  return false;
+}
 // Two barriers at once: both try_waits are in flight together, so the pair costs one mbarrier
 // round trip (about 200 cycles even for a completed phase) instead of two.
 __device__ __forceinline__ bool wait_bar2(uint64_t* bar_a, uint32_t parity_a, uint64_t* bar_b, uint32_t parity_b,
                                           volatile int* abort_flag, int code, int chunk) {
   bool a = false, b = false;
-  for (uint32_t i = 0; i < ptx::kMaxPolls; ++i) {
-    const bool ta = a || ptx::mbar_try_wait(bar_a, parity_a);
-    const bool tb = b || ptx::mbar_try_wait(bar_b, parity_b);
+  for (uint32_t i = 0; i < ptx::kMaxSpins; ++i) {
+    const bool ta = a || ptx::mbar_test_wait(bar_a, parity_a);
+    const bool tb = b || ptx::mbar_test_wait(bar_b, parity_b);
     a = ta;
     b = tb;
     if (a && b) return true;
@@ -214,11 +264,11 @@ __device__ __forceinline__ bool wait_bar2(uint64_t* bar_a, uint32_t parity_a, ui
 __device__ __forceinline__ bool wait_bar4(uint64_t* b0, uint32_t p0, uint64_t* b1, uint32_t p1, uint64_t* b2, uint32_t p2,
                                           uint64_t* b3, uint32_t p3, volatile int* abort_flag, int code, int chunk) {
   bool d0 = b0 == nullptr, d1 = b1 == nullptr, d2 = b2 == nullptr, d3 = b3 == nullptr;
-  for (uint32_t i = 0; i < ptx::kMaxPolls; ++i) {
-    const bool t0 = d0 || ptx::mbar_try_wait(b0, p0);
-    const bool t1 = d1 || ptx::mbar_try_wait(b1, p1);
-    const bool t2 = d2 || ptx::mbar_try_wait(b2, p2);
-    const bool t3 = d3 || ptx::mbar_try_wait(b3, p3);
+  for (uint32_t i = 0; i < ptx::kMaxSpins; ++i) {
+    const bool t0 = d0 || ptx::mbar_test_wait(b0, p0);
+    const bool t1 = d1 || ptx::mbar_test_wait(b1, p1);
+    const bool t2 = d2 || ptx::mbar_test_wait(b2, p2);
+    const bool t3 = d3 || ptx::mbar_test_wait(b3, p3);
     d0 = t0; d1 = t1; d2 = t2; d3 = t3;
     if (d0 && d1 && d2 && d3) return true;
     if (*abort_flag) return false;
@@ -245,6 +295,33 @@ __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
 // 32-column blocks that hold at least one surviving element for ANY row of the warp (warp-uniform).
 template <typename T>
 __device__ __forceinline__ void mask_pack_inplace(uint32_t taddr_lane, int lo, int hi, int blk_lo, int blk_hi) {
+#ifndef COTT_MASK_UNROLLED
+  // One 32-column block per iteration of a loop that is NOT unrolled: the fully unrolled form is four
+  // times the code, and the roles of this kernel already overflow the instruction cache.  Packed block
+  // b lands on fp32 columns 16b .. 16b+15, which belong to block b/2 <= b: already read.
+#pragma unroll 1
+  for (int blk = 0; blk < 4; ++blk) {
+    uint32_t packed[16];
+    if (blk < blk_lo || blk > blk_hi) {  // warp-uniform: nothing of this block survives for any row
+#pragma unroll
+      for (int j = 0; j < 16; ++j) packed[j] = 0u;
+    } else {
+      uint32_t r[32];
+      ptx::tmem_ld_x32(taddr_lane + 32 * blk, r);
+      ptx::tmem_ld_wait();
+      const int s0 = 32 * blk;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float x0 = (s0 + 2 * j >= lo && s0 + 2 * j <= hi) ? __uint_as_float(r[2 * j]) : 0.f;
+        const float x1 = (s0 + 2 * j + 1 >= lo && s0 + 2 * j + 1 <= hi) ? __uint_as_float(r[2 * j + 1]) : 0.f;
+        packed[j] = Pack2<T>::pack(x0, x1);
+      }
+    }
+    ptx::tmem_st_x16(taddr_lane + 16 * blk, packed);
+  }
+  ptx::tmem_st_wait();
+  return;
+#endif
 #pragma unroll
   for (int p = 0; p < 2; ++p) {
     uint32_t packed[32];
@@ -290,23 +367,6 @@ __device__ __forceinline__ void write_row64(unsigned char* tile, int row, const 
     u.w = Pack2<T>::pack(x[8 * j + 6], x[8 * j + 7]);
     *tile_piece(tile, row, j) = u;
   }
-}
-
-// The warp's 32 rows (rows 32*wq .. 32*wq+31 of a swizzled tile, written by its own lanes) go to global
-// memory rows y0 + 32*wq.. as one TMA store; rows past the end of the sequence are clipped by the
-// tensor map.  The store is left in flight: stores_read() must come before the tile is handed back.
-__device__ __forceinline__ void warp_store_rows32(const CUtensorMap* map, unsigned char* tile, int wq, int lane, int y0,
-                                                  int n_rows, int bh) {
-  ptx::fence_proxy_async_smem();
-  __syncwarp();
-  if (lane == 0 && y0 + 32 * wq < n_rows) {
-    ptx::tma_store_3d(map, tile + wq * (32 * 128), 0, y0 + 32 * wq, bh);
-    ptx::tma_store_commit();
-  }
-}
-// Lane 0 waits until the TMA engine has read the shared memory of every store it has issued.
-__device__ __forceinline__ void stores_read(int lane) {
-  if (lane == 0) ptx::tma_store_wait_read<0>();
 }
 
 template <typename T>
@@ -357,7 +417,7 @@ enum {
   kWaitAccFree = 7, kWaitState = 8
 };
 
-constexpr int kTcThreads = 352;
+constexpr int kTcThreads = 480;  // 2 issuing warps, 3 groups of 4 warps, 1 TMA warp
 constexpr int kTcStages = 3;
 
 template <typename T, int MODE>
@@ -377,7 +437,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   // compiler, so tile accesses compile to LDS/STS rather than generic loads and stores)
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char* sS = smem + NS * STAGE;  // 2 x [64 x 64] 16-bit state operand (double-buffered), 2 x 8 KB
-  __shared__ uint64_t bar_full[NS], bar_free[NS], bar_prep[NS], bar_p_full[2], bar_p_ready[2], bar_acc_full[2],
+  __shared__ uint64_t bar_full[NS], bar_free_in[NS], bar_out[NS], bar_prep[NS], bar_p_full[2], bar_p_ready[2], bar_acc_full[2],
       bar_acc_free[2], bar_s_full, bar_state, bar_state2;
   __shared__ uint32_t tmem_slot;
   COTT_TRACE_DECL
@@ -393,7 +453,8 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
       mbar_init(&bar_full[s], 1);
-      mbar_init(&bar_free[s], 4);
+      mbar_init(&bar_free_in[s], 8);  // output group (accumulator MMAs done) + operand group (state MMAs done)
+      mbar_init(&bar_out[s], 4);
       mbar_init(&bar_prep[s], 4);
     }
     for (int b = 0; b < 2; ++b) {
@@ -423,12 +484,17 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   // TMEM columns: scores 2 x 128 | accumulators 2 x 64 | state 64
   const uint32_t tP0 = tmem, tAcc0 = tmem + 256, tS = tmem + 384;
 
-  // Two issuing threads on two different schedulers share the tensor-core and TMA issue work: with a
-  // single issuing thread that thread was busy for the whole chunk period (each of its instructions
-  // competes with the two epilogue warps of its scheduler), i.e. it was the critical path.
-  //   warp 0, lane 0:  TMA loads, scores P(c+1) = X Y^T, state S += Y^T Zw (c)
-  //   warp 1, lane 0:  accumulators Acc(c) = X S + P Zw
-  // MMAs of the two threads are ordered only through the mbarriers.
+  // Roles.  Two issuing threads on two different schedulers share the tensor-core issue work (a single
+  // one was busy for the whole chunk period and so was the critical path); their MMAs are ordered only
+  // through the mbarriers.  The per-row work is spread over three groups of four warps (warp w of a group
+  // owns TMEM lanes / tile rows 32 (w % 4) ..): each group's work per chunk is serial and latency-bound,
+  // so the chunk period is set by the busiest group.
+  //   warp 0, lane 0:   scores P(c+1) = X Y^T, state S += Y^T Zw (c)
+  //   warp 1, lane 0:   accumulators Acc(c) = X S + P Zw
+  //   warps 2-5:        score group: mask + convert P
+  //   warps 6-9:        output group: row norm of q, accumulator -> output rows
+  //   warps 10-13:      operand group: Zw in place, fp32 state -> 16-bit operand
+  //   warp 14, lane 0:  TMA loads and stores
   constexpr uint32_t kIdescP = make_idesc(128, 128, BF, false, false);
   constexpr uint32_t kIdescAcc = make_idesc(128, 64, BF, false, true);
   constexpr uint32_t kIdescS = make_idesc(64, 64, BF, true, true);
@@ -444,7 +510,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         mma_commit(&bar_p_full[c & 1]);
         COTT_TRACE_EV(1, c);
       };
-      bool ok = wait_bar(&bar_full[0], 0, abort_flag, kWaitTma, 0);
+      bool ok = wait_bar1(&bar_full[0], 0, abort_flag, kWaitTma, 0);
       if (ok) {
         tc_fence_after_sync();
         issue_scores(0);
@@ -473,26 +539,59 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         }
       }
     }
-  } else if (warp == kTcThreads / 32 - 1) {
-    // ---------------------------------------------------------------- TMA loads
-    // A thread of its own: the wait for a free stage ends late in a chunk's life (after its output
-    // store has left shared memory) and must not hold up the MMA issue of the following chunks.
+  } else if (warp == 14) {
+    // ---------------------------------------------------------------- TMA loads and stores
+    // A thread of its own.  The output rows of a chunk are staged in one tile of the chunk's own stage
+    // (forward: the X tile, dQ: the q tile -- the tile whose rows the output group reads last), so a stage
+    // is refilled in two steps: the other tiles as soon as every MMA of the chunk has completed, the
+    // staging tile once the output store has read it.  Both steps count on the same `full` barrier.
     if (lane == 0) {
-      auto issue_loads = [&](int c) {
+      constexpr int kOutTile = (MODE == kModeDq) ? 3 : 0;
+      auto load_inputs = [&](int c) {  // all tiles but the staging one
         const int s = c % NS;
         unsigned char* st = smem + s * STAGE;
+#if COTT_SKEL & 8
+        if (c >= NS) return;
+#endif
         mbar_expect_tx(&bar_full[s], STAGE);
-        tma_load_3d(st, &mapX, &bar_full[s], 0, c * kTcChunk, bh);
+        if (MODE == kModeDq) tma_load_3d(st, &mapX, &bar_full[s], 0, c * kTcChunk, bh);
         tma_load_3d(st + kTileBytes, &mapY, &bar_full[s], 0, c * kTcChunk, bh);
         tma_load_3d(st + 2 * kTileBytes, &mapZ, &bar_full[s], 0, c * kTcChunk, bh);
-        if (MODE == kModeDq) tma_load_3d(st + 3 * kTileBytes, &mapQ, &bar_full[s], 0, c * kTcChunk, bh);
         COTT_TRACE_EV(0, c);
       };
-      for (int c = 0; c < NS && c < nchunks; ++c) issue_loads(c);
-      for (int c = 0; c + NS < nchunks; ++c) {
-        if (!wait_bar(&bar_free[c % NS], (c / NS) & 1, abort_flag, kWaitStageFree, c)) break;
-        issue_loads(c + NS);
+      auto load_staging = [&](int c) {
+        const int s = c % NS;
+        unsigned char* st = smem + s * STAGE + kOutTile * kTileBytes;
+#if COTT_SKEL & 8
+        if (c >= NS) {
+          mbar_arrive(&bar_full[s]);
+          return;
+        }
+#endif
+        tma_load_3d(st, MODE == kModeDq ? &mapQ : &mapX, &bar_full[s], 0, c * kTcChunk, bh);
+      };
+      for (int c = 0; c < NS && c < nchunks; ++c) {
+        load_inputs(c);
+        load_staging(c);
       }
+      for (int c = 0; c < nchunks; ++c) {
+        const int s = c % NS;
+        const bool refill = c + NS < nchunks;
+        if (refill) {
+          if (!wait_bar(&bar_free_in[s], (c / NS) & 1, abort_flag, kWaitStageFree, c)) break;
+          load_inputs(c + NS);
+        }
+        if (!wait_bar(&bar_out[s], (c / NS) & 1, abort_flag, kWaitStageFree, c)) break;
+#if !(COTT_SKEL & 16)
+        tma_store_3d(&mapOut, smem + s * STAGE + kOutTile * kTileBytes, 0, c * kTcChunk, bh);
+        tma_store_commit();
+#endif
+        if (refill) {
+          tma_store_wait_read<0>();
+          load_staging(c + NS);
+        }
+      }
+      tma_store_wait<0>();
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- accumulators
@@ -528,6 +627,22 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
     // ---------------------------------------------------------------- score group
     const int wq = warp & 3, row = 32 * wq + lane;
     const uint32_t lane_base = static_cast<uint32_t>(32 * wq) << 16;
+    for (int c = 0; c < nchunks; ++c) {
+      const int b = c & 1;
+      if (!wait_bar_warp(&bar_p_full[b], (c >> 1) & 1, abort_flag, kWaitScore, c)) break;
+      tc_fence_after_sync();
+      COTT_TRACE_EV(0, c);
+#if !(COTT_SKEL & 1)
+      mask_pack_inplace<T>(tP0 + 128 * b + lane_base, 0, row, 0, wq);
+#endif
+      tc_fence_before_sync();
+      warp_arrive(&bar_p_ready[b], lane);
+      COTT_TRACE_EV(1, c);
+    }
+  } else if (warp >= 10) {
+    // ---------------------------------------------------------------- operand group
+    const int wq = warp & 3, row = 32 * wq + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(32 * wq) << 16;
     const float sigma = 1.0f / (1.0f + __expf(-norm_const[h]));
     auto prepare = [&](int c) -> bool {  // Zw = diag(a_s / |k_s|) Z, in place
       const int s = c % NS;
@@ -537,11 +652,8 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       unsigned char* sK = (MODE == kModeDq) ? sZ : smem + s * STAGE + kTileBytes;
 #if !(COTT_SKEL & 2)
       const float rk = inv_norm(row_sumsq<T>(sK, row));
-      COTT_TRACE_EV(4, c);
       const float a = length_factor(static_cast<float>(c * kTcChunk + row + 1), sigma);
-      COTT_TRACE_EV(5, c);
       scale_row<T>(sZ, row, rk * a);
-      COTT_TRACE_EV(6, c);
 #endif
       fence_proxy_async_smem();
       warp_arrive(&bar_prep[s], lane);
@@ -549,54 +661,39 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       return true;
     };
     bool ok = prepare(0);
-    for (int c = 0; ok && c < nchunks; ++c) {
-      const int b = c & 1;
-      if (!(ok = wait_bar_warp(&bar_p_full[b], (c >> 1) & 1, abort_flag, kWaitScore, c))) break;
+    for (int c = 0; ok && c + 1 < nchunks; ++c) {
+      // Zw of the next chunk first: the state MMAs of chunk c are still running
+      if (!(ok = prepare(c + 1))) break;
+      // S after chunk c -> 16-bit operand for chunk c+1 (buffer (c+1)&1)
+      if (!(ok = wait_bar_warp(&bar_s_full, c & 1, abort_flag, kWaitState, c))) break;
       tc_fence_after_sync();
+      if (lane == 0) mbar_arrive(&bar_free_in[c % NS]);  // the state MMAs of chunk c have read its tiles
       COTT_TRACE_EV(0, c);
-#if !(COTT_SKEL & 1)
-      mask_pack_inplace<T>(tP0 + 128 * b + lane_base, 0, row, 0, wq);
+#if !(COTT_SKEL & 4)
+      state_to_smem<T>(tS + lane_base, sS + ((c + 1) & 1) * (kTcD * 128), wq, lane);
 #endif
+      fence_proxy_async_smem();
       tc_fence_before_sync();
-      warp_arrive(&bar_p_ready[b], lane);
+      warp_arrive(&bar_state, lane);
+      if (lane == 0) mbar_arrive(&bar_state2);
       COTT_TRACE_EV(1, c);
-      if (c + 1 < nchunks) ok = prepare(c + 1);
-      COTT_TRACE_EV(2, c);
     }
   } else {
     // ---------------------------------------------------------------- output group
     const int wq = warp & 3, row = 32 * wq + lane;
     const uint32_t lane_base = static_cast<uint32_t>(32 * wq) << 16;
-    int pending = -1;  // stage whose output store may still be reading shared memory
     for (int c = 0; c < nchunks; ++c) {
       const int s = c % NS, b = c & 1;
       unsigned char* sQ = smem + s * STAGE + ((MODE == kModeDq) ? 3 * kTileBytes : 0);
       // the row norm of q only needs the TMA data: do it while the MMAs run
       if (!wait_bar_warp(&bar_full[s], (c / NS) & 1, abort_flag, kWaitTma, c)) break;
+      COTT_TRACE_EV(7, c);
 #if !(COTT_SKEL & 4)
       const float rq = inv_norm(row_sumsq<T>(sQ, row));
 #else
       const float rq = 1.f;
 #endif
       COTT_TRACE_EV(0, c);
-      // Release the previous chunk's stage once its output store has read it.  This must come before
-      // any wait on the issuing thread that also refills stages, or the two would wait on each other.
-      if (pending >= 0) {
-        stores_read(lane);
-        warp_arrive(&bar_free[pending], lane);
-      }
-      if (c + 1 < nchunks) {  // S after chunk c -> 16-bit operand for chunk c+1 (buffer (c+1)&1)
-        if (!wait_bar_warp(&bar_s_full, c & 1, abort_flag, kWaitState, c)) break;
-        tc_fence_after_sync();
-#if !(COTT_SKEL & 4)
-        state_to_smem<T>(tS + lane_base, sS + ((c + 1) & 1) * (kTcD * 128), wq, lane);
-#endif
-        fence_proxy_async_smem();
-        tc_fence_before_sync();
-        warp_arrive(&bar_state, lane);
-        if (lane == 0) mbar_arrive(&bar_state2);
-      }
-      COTT_TRACE_EV(1, c);
       if (!wait_bar_warp(&bar_acc_full[b], (c >> 1) & 1, abort_flag, kWaitAcc, c)) break;
       tc_fence_after_sync();
       COTT_TRACE_EV(2, c);
@@ -608,49 +705,31 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
 #endif
       tc_fence_before_sync();
       warp_arrive(&bar_acc_free[b], lane);
+      // the score and accumulator MMAs of this chunk have completed (the operand group reports the state
+      // MMAs): all tiles but the staging one can be refilled
+      if (lane == 0) mbar_arrive(&bar_free_in[s]);
       COTT_TRACE_EV(3, c);
       if (MODE == kModeFwd) {
 #pragma unroll
         for (int j = 0; j < 64; ++j) acc[j] *= rq;
       } else {
-        float delta = 0.f;
+        uint4 uq[8];  // the q row, kept packed (32 registers) and unpacked twice
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          uint4 u = *tile_piece(sQ, row, j);
-          float2 p0 = Pack2<T>::unpack(u.x), p1 = Pack2<T>::unpack(u.y), p2 = Pack2<T>::unpack(u.z),
-                 p3 = Pack2<T>::unpack(u.w);
-          delta += p0.x * acc[8 * j] + p0.y * acc[8 * j + 1] + p1.x * acc[8 * j + 2] + p1.y * acc[8 * j + 3] +
-                   p2.x * acc[8 * j + 4] + p2.y * acc[8 * j + 5] + p3.x * acc[8 * j + 6] + p3.y * acc[8 * j + 7];
-        }
+        for (int j = 0; j < 8; ++j) uq[j] = *tile_piece(sQ, row, j);
+        float delta = packed_dot64<T>(uq, acc);
         delta *= rq * rq * rq;  // (q^ . dq^) / |q|^2, with dq^ = acc and q^ = rq q
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          uint4 u = *tile_piece(sQ, row, j);
-          float2 p0 = Pack2<T>::unpack(u.x), p1 = Pack2<T>::unpack(u.y), p2 = Pack2<T>::unpack(u.z),
-                 p3 = Pack2<T>::unpack(u.w);
-          acc[8 * j + 0] = rq * acc[8 * j + 0] - p0.x * delta;
-          acc[8 * j + 1] = rq * acc[8 * j + 1] - p0.y * delta;
-          acc[8 * j + 2] = rq * acc[8 * j + 2] - p1.x * delta;
-          acc[8 * j + 3] = rq * acc[8 * j + 3] - p1.y * delta;
-          acc[8 * j + 4] = rq * acc[8 * j + 4] - p2.x * delta;
-          acc[8 * j + 5] = rq * acc[8 * j + 5] - p2.y * delta;
-          acc[8 * j + 6] = rq * acc[8 * j + 6] - p3.x * delta;
-          acc[8 * j + 7] = rq * acc[8 * j + 7] - p3.y * delta;
-        }
+        packed_axpby64<T>(uq, -delta, rq, acc);  // acc = rq acc - delta q
       }
       COTT_TRACE_EV(5, c);
-      // The X tile of this stage has no reader left (its MMAs completed before acc_full, and in forward
-      // mode this thread has taken the norm of its own row): the output rows are staged in it, in the
-      // swizzled layout, and leave by TMA.  The stage is released (next iteration) once the TMA engine
-      // has read them.
-      unsigned char* sO = smem + s * STAGE;
-      write_row64<T>(sO, row, acc);
-      COTT_TRACE_EV(6, c);
-      warp_store_rows32(&mapOut, sO, wq, lane, c * kTcChunk, N, bh);
-      pending = s;
+      // The staging tile has no reader left: its MMAs completed before acc_full (forward: X, and this
+      // thread has taken the norm of its own row; dQ: the q tile, which no MMA reads and whose row this
+      // thread has just used).  The output rows go there in the swizzled layout; the TMA thread stores
+      // the tile and refills it.
+      write_row64<T>(sQ, row, acc);
+      fence_proxy_async_smem();
+      warp_arrive(&bar_out[s], lane);
       COTT_TRACE_EV(4, c);
     }
-    if (lane == 0) tma_store_wait<0>();
   }
 
   // ---- leave: make sure no TMA of this CTA is still in flight (bounded), release TMEM ------------
@@ -695,7 +774,7 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   // compiler, so tile accesses compile to LDS/STS rather than generic loads and stores)
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char* sR = smem + NS * STAGE;  // 2 x [64 x 64] 16-bit state operand (rows = d_k, cols = d_v), double-buffered
-  __shared__ uint64_t bar_full[NS], bar_free[NS], bar_prep[NS], bar_p_full, bar_p_ready, bar_acc_full, bar_acc_free,
+  __shared__ uint64_t bar_full[NS], bar_free_in[NS], bar_out[NS], bar_prep[NS], bar_p_full, bar_p_ready, bar_acc_full, bar_acc_free,
       bar_state, bar_state2, bar_r_full;
   __shared__ uint32_t tmem_slot;
   COTT_TRACE_DECL
@@ -711,11 +790,12 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
       mbar_init(&bar_full[s], 1);
-      mbar_init(&bar_free[s], 4);
+      mbar_init(&bar_free_in[s], 8);  // output group (accumulator MMAs done) + operand group (state MMAs done)
+      mbar_init(&bar_out[s], 4);
       mbar_init(&bar_prep[s], 4);
     }
     mbar_init(&bar_p_full, 1);
-    mbar_init(&bar_p_ready, 4);
+    mbar_init(&bar_p_ready, 8);  // score group (E) + operand group (F)
     mbar_init(&bar_acc_full, 1);
     mbar_init(&bar_acc_free, 4);
     mbar_init(&bar_state, 4);
@@ -747,23 +827,48 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   constexpr uint32_t kIdescAccMN = make_idesc(128, 64, BF, false, true);   // B MN-major
   constexpr uint32_t kIdescR = make_idesc(64, 64, BF, true, true);
   if (warp == kTcThreads / 32 - 1) {
-    if (lane == 0) {  // TMA loads (a thread of its own, see causal_tc_kernel)
-      auto issue_loads = [&](int ci) {
+    // TMA loads and stores (a thread of its own, see causal_tc_kernel).  dK and dV are staged in the K and
+    // V tiles of the chunk's own stage: q and dO are refilled as soon as every MMA of the chunk has
+    // completed, K and V once the output stores have read them.
+    if (lane == 0) {
+      auto load_inputs = [&](int ci) {
         const int s = ci % NS;
         const int y = (nchunks - 1 - ci) * kTcChunk;
         unsigned char* st = smem + s * STAGE;
         mbar_expect_tx(&bar_full[s], STAGE);
         tma_load_3d(st, &mapQ, &bar_full[s], 0, y, bh);
-        tma_load_3d(st + kTileBytes, &mapK, &bar_full[s], 0, y, bh);
-        tma_load_3d(st + 2 * kTileBytes, &mapV, &bar_full[s], 0, y, bh);
         tma_load_3d(st + 3 * kTileBytes, &mapDO, &bar_full[s], 0, y, bh);
       };
-      for (int ci = 0; ci < NS && ci < nchunks; ++ci) issue_loads(ci);
-      for (int ci = 0; ci + NS < nchunks; ++ci) {
-        if (!wait_bar(&bar_free[ci % NS], (ci / NS) & 1, abort_flag, kWaitStageFree, ci)) break;
-        COTT_TRACE_EV(4, ci);
-        issue_loads(ci + NS);
+      auto load_staging = [&](int ci) {
+        const int s = ci % NS;
+        const int y = (nchunks - 1 - ci) * kTcChunk;
+        unsigned char* st = smem + s * STAGE;
+        tma_load_3d(st + kTileBytes, &mapK, &bar_full[s], 0, y, bh);
+        tma_load_3d(st + 2 * kTileBytes, &mapV, &bar_full[s], 0, y, bh);
+      };
+      for (int ci = 0; ci < NS && ci < nchunks; ++ci) {
+        load_inputs(ci);
+        load_staging(ci);
       }
+      for (int ci = 0; ci < nchunks; ++ci) {
+        const int s = ci % NS;
+        const int y = (nchunks - 1 - ci) * kTcChunk;
+        const bool refill = ci + NS < nchunks;
+        if (refill) {
+          if (!wait_bar(&bar_free_in[s], (ci / NS) & 1, abort_flag, kWaitStageFree, ci)) break;
+          COTT_TRACE_EV(4, ci);
+          load_inputs(ci + NS);
+        }
+        if (!wait_bar(&bar_out[s], (ci / NS) & 1, abort_flag, kWaitStageFree, ci)) break;
+        tma_store_3d(&mapDV, smem + s * STAGE + 2 * kTileBytes, 0, y, bh);
+        tma_store_3d(&mapDK, smem + s * STAGE + kTileBytes, 0, y, bh);
+        tma_store_commit();
+        if (refill) {
+          tma_store_wait_read<0>();
+          load_staging(ci + NS);
+        }
+      }
+      tma_store_wait<0>();
     }
   } else if (warp == 0) {
     if (lane == 0) {
@@ -786,7 +891,7 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         {
           // state of chunk ci (Qw(ci) was waited for before its score tiles were issued); the 16-bit
           // conversion after chunk ci-1 must have finished reading the TMEM state
-          if (ci > 0 && !(ok = wait_bar(&bar_state2, (ci - 1) & 1, abort_flag, kWaitState, ci))) break;
+          if (ci > 0 && !(ok = wait_bar1(&bar_state2, (ci - 1) & 1, abort_flag, kWaitState, ci))) break;
           tc_fence_after_sync();
           COTT_TRACE_EV(0, ci);
           const uint32_t q0 = smem_u32(smem + (ci % NS) * STAGE);
@@ -818,13 +923,11 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         const uint64_t dK = kdesc(q0 + kTileBytes), dV = kdesc(q0 + 2 * kTileBytes), dQm = mdesc(q0),
                        dDm = mdesc(q0 + 3 * kTileBytes);
         const uint32_t acc0 = ci > 0 ? 1u : 0u;
-        // masked scores of chunk ci (which implies Qw(ci)), 16-bit state after chunk ci-1, accumulators read out
-        if (!wait_bar4(&bar_p_ready, ci & 1, ci > 0 ? &bar_state : nullptr, (ci - 1) & 1,
-                       ci > 0 ? &bar_acc_free : nullptr, (ci - 1) & 1, nullptr, 0, abort_flag, kWaitScoreReady, ci))
-          break;
-        tc_fence_after_sync();
-        COTT_TRACE_EV(0, ci);
         if (ci > 0) {
+          // the state terms need the 16-bit state after chunk ci-1 and the accumulators read out, not the
+          // masked scores: they are issued while the score tiles are still being masked
+          if (!wait_bar2(&bar_state, (ci - 1) & 1, &bar_acc_free, (ci - 1) & 1, abort_flag, kWaitState, ci)) break;
+          tc_fence_after_sync();
           const uint32_t rb = r0 + (ci & 1) * (kTcD * 128);
           const uint64_t dRk = kdesc(rb), dRm = mdesc(rb);
 #pragma unroll
@@ -834,6 +937,10 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
           for (int k = 0; k < 4; ++k)  // AccV = K R : B[n = d_v][k = d_k] = R, MN-major
             mma_ss(tV, dK + 2 * k, dRm + 128 * k, kIdescAccMN, k > 0);
         }
+        // masked scores of chunk ci (which implies Qw(ci))
+        if (!wait_bar1(&bar_p_ready, ci & 1, abort_flag, kWaitScoreReady, ci)) break;
+        tc_fence_after_sync();
+        COTT_TRACE_EV(0, ci);
         mma_ts(tK, tE, dQm, kIdescAccMN, acc0);
 #pragma unroll
         for (int k = 1; k < 8; ++k) mma_ts(tK, tE + 8 * k, dQm + 128 * k, kIdescAccMN, 1u);
@@ -845,7 +952,7 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       }
     }
   } else if (warp < 6) {
-    // score group: Qw = q^ in place, then mask + convert E and F
+    // score group: mask + convert E, then Qw = q^ of the next chunk in place
     const int wq = warp & 3, row = 32 * wq + lane;
     const uint32_t lane_base = static_cast<uint32_t>(32 * wq) << 16;
     auto prepare = [&](int ci) -> bool {
@@ -864,7 +971,6 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       COTT_TRACE_EV(1, ci);
       mask_pack_inplace<T>(tE + lane_base, row, 127, wq, 3);
       COTT_TRACE_EV(2, ci);
-      mask_pack_inplace<T>(tF + lane_base, row, 127, wq, 3);
       tc_fence_before_sync();
       warp_arrive(&bar_p_ready, lane);
       COTT_TRACE_EV(3, ci);
@@ -872,13 +978,33 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       if (ci + 1 < nchunks && !(ok = prepare(ci + 1))) break;
       COTT_TRACE_EV(0, ci);
     }
+  } else if (warp >= 10) {
+    // operand group: mask + convert F, then the fp32 state after this chunk -> 16-bit operand
+    const int wq = warp & 3, row = 32 * wq + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(32 * wq) << 16;
+    for (int ci = 0; ci < nchunks; ++ci) {
+      if (!wait_bar_warp(&bar_p_full, ci & 1, abort_flag, kWaitScore, ci)) break;
+      tc_fence_after_sync();
+      mask_pack_inplace<T>(tF + lane_base, row, 127, wq, 3);
+      tc_fence_before_sync();
+      warp_arrive(&bar_p_ready, lane);
+      if (ci + 1 < nchunks) {  // R after chunk ci -> 16-bit operand of chunk ci+1 (buffer (ci+1)&1)
+        if (!wait_bar_warp(&bar_r_full, ci & 1, abort_flag, kWaitState, ci)) break;
+        tc_fence_after_sync();
+        if (lane == 0) mbar_arrive(&bar_free_in[ci % NS]);  // the state MMAs of chunk ci have read its tiles
+        state_to_smem<T>(tR + lane_base, sR + ((ci + 1) & 1) * (kTcD * 128), wq, lane);
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        warp_arrive(&bar_state, lane);
+        if (lane == 0) mbar_arrive(&bar_state2);
+      }
+    }
   } else {
     // output group
     const int wq = warp & 3, row = 32 * wq + lane;
     const uint32_t lane_base = static_cast<uint32_t>(32 * wq) << 16;
     const float sigma = 1.0f / (1.0f + __expf(-norm_const[h]));
     float gsum = 0.f;  // sum_s ln(n_s) eps_s over this thread's rows
-    int pending = -1;  // stage whose output stores may still be reading shared memory
     for (int ci = 0; ci < nchunks; ++ci) {
       const int s = ci % NS;
       unsigned char* sK = smem + s * STAGE + kTileBytes;
@@ -888,88 +1014,44 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       const float rk = inv_norm(row_sumsq<T>(sK, row));
       const float a = length_factor(static_cast<float>(pos + 1), sigma);
       COTT_TRACE_EV(0, ci);
-      // Release the previous chunk's stage once its output store has read it.  This must come before
-      // any wait on the issuing thread that also refills stages, or the two would wait on each other.
-      if (pending >= 0) {
-        stores_read(lane);
-        warp_arrive(&bar_free[pending], lane);
-      }
-      if (ci + 1 < nchunks) {  // R after chunk ci -> 16-bit operand of chunk ci+1 (buffer (ci+1)&1)
-        if (!wait_bar_warp(&bar_r_full, ci & 1, abort_flag, kWaitState, ci)) break;
-        tc_fence_after_sync();
-        COTT_TRACE_EV(1, ci);
-        state_to_smem<T>(tR + lane_base, sR + ((ci + 1) & 1) * (kTcD * 128), wq, lane);
-        fence_proxy_async_smem();
-        tc_fence_before_sync();
-        warp_arrive(&bar_state, lane);
-        if (lane == 0) mbar_arrive(&bar_state2);
-        COTT_TRACE_EV(2, ci);
-      }
       if (!wait_bar_warp(&bar_acc_full, ci & 1, abort_flag, kWaitAcc, ci)) break;
       tc_fence_after_sync();
       COTT_TRACE_EV(3, ci);
-      float accv[64], acck[64];
+      // dV first (its row product with v gives eps), then dK; each is staged as soon as it is ready, in
+      // the V / K tile of this stage: every MMA that reads them completed before acc_full and this thread
+      // is done with its own rows, so they have no reader left.  The TMA thread stores and refills them.
+      if (lane == 0) mbar_arrive(&bar_free_in[s]);  // (warp-converged: follows wait_bar_warp) q, dO tiles are free
+      const float c1 = rk * a;
+      float acc[64];
+      float eps;
       {
-        uint32_t r0[64], r1[64];
-        tmem_ld_x64(tV + lane_base, r0);
-        tmem_ld_x64(tK + lane_base, r1);
-        tmem_ld_wait();
+        tmem_row64(tV + lane_base, acc);  // raw: dv' = rk * raw
+        uint4 uv[8];
 #pragma unroll
-        for (int j = 0; j < 64; ++j) {
-          accv[j] = __uint_as_float(r0[j]) * rk;  // dv'
-          acck[j] = __uint_as_float(r1[j]) * a;   // dk^
-        }
+        for (int j = 0; j < 8; ++j) uv[j] = *tile_piece(sV, row, j);
+        eps = c1 * packed_dot64<T>(uv, acc);  // v' . dv' with v' = a v
+#pragma unroll
+        for (int j = 0; j < 64; ++j) acc[j] *= c1;  // dv = a dv'
+        write_row64<T>(sV, row, acc);
       }
-      tc_fence_before_sync();
-      warp_arrive(&bar_acc_free, lane);
-      COTT_TRACE_EV(4, ci);
-      float eps = 0.f;
+      {
+        tmem_row64(tK + lane_base, acc);  // raw: dk^ = a * raw
+        tc_fence_before_sync();
+        warp_arrive(&bar_acc_free, lane);
+        COTT_TRACE_EV(4, ci);
+        uint4 uk[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        uint4 u = *tile_piece(sV, row, j);
-        float2 p0 = Pack2<T>::unpack(u.x), p1 = Pack2<T>::unpack(u.y), p2 = Pack2<T>::unpack(u.z),
-               p3 = Pack2<T>::unpack(u.w);
-        eps += p0.x * accv[8 * j] + p0.y * accv[8 * j + 1] + p1.x * accv[8 * j + 2] + p1.y * accv[8 * j + 3] +
-               p2.x * accv[8 * j + 4] + p2.y * accv[8 * j + 5] + p3.x * accv[8 * j + 6] + p3.y * accv[8 * j + 7];
-      }
-      eps *= a;  // v' . dv'
-      const float ke = rk * eps;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        uint4 u = *tile_piece(sK, row, j);
-        float2 p0 = Pack2<T>::unpack(u.x), p1 = Pack2<T>::unpack(u.y), p2 = Pack2<T>::unpack(u.z),
-               p3 = Pack2<T>::unpack(u.w);
-        acck[8 * j + 0] = rk * (acck[8 * j + 0] - p0.x * ke);
-        acck[8 * j + 1] = rk * (acck[8 * j + 1] - p0.y * ke);
-        acck[8 * j + 2] = rk * (acck[8 * j + 2] - p1.x * ke);
-        acck[8 * j + 3] = rk * (acck[8 * j + 3] - p1.y * ke);
-        acck[8 * j + 4] = rk * (acck[8 * j + 4] - p2.x * ke);
-        acck[8 * j + 5] = rk * (acck[8 * j + 5] - p2.y * ke);
-        acck[8 * j + 6] = rk * (acck[8 * j + 6] - p3.x * ke);
-        acck[8 * j + 7] = rk * (acck[8 * j + 7] - p3.y * ke);
+        for (int j = 0; j < 8; ++j) uk[j] = *tile_piece(sK, row, j);
+        // dk = rk (dk^ - k^ (k^ . dk^)) with k^ . dk^ = v' . dv' = eps and k^ = rk k
+        packed_axpby64<T>(uk, -rk * rk * eps, c1, acc);
+        write_row64<T>(sK, row, acc);
       }
       COTT_TRACE_EV(5, ci);
-      // The K and V tiles of this stage have no reader left (every MMA that reads them completed before
-      // acc_full, and this thread is done with its own rows): dK and dV rows are staged in them, in the
-      // swizzled layout, and leave by TMA.  The stage is released (next iteration) once the TMA engine
-      // has read them.
-#pragma unroll
-      for (int j = 0; j < 64; ++j) accv[j] *= a;
-      write_row64<T>(sV, row, accv);
-      write_row64<T>(sK, row, acck);
-      const int y0 = (nchunks - 1 - ci) * kTcChunk;
       ptx::fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0 && y0 + 32 * wq < N) {
-        ptx::tma_store_3d(&mapDV, sV + wq * (32 * 128), 0, y0 + 32 * wq, bh);
-        ptx::tma_store_3d(&mapDK, sK + wq * (32 * 128), 0, y0 + 32 * wq, bh);
-        ptx::tma_store_commit();
-      }
-      pending = s;
+      warp_arrive(&bar_out[s], lane);
       if (pos > 0 && pos < N) gsum += logf(static_cast<float>(pos + 1)) * eps;
       COTT_TRACE_EV(6, ci);
     }
-    if (lane == 0) ptx::tma_store_wait<0>();
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) gsum += __shfl_down_sync(0xffffffffu, gsum, off);
     if (lane == 0) atomicAdd(dnorm + h, -sigma * (1.0f - sigma) * gsum);

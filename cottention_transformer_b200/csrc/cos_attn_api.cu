@@ -26,9 +26,8 @@ int aligned16(const void* p, const char* name) {
   return COTT_OK;
 }
 
-// box_rows: 128 for the chunk loads, 32 for the per-warp output stores
-int tmap(CUtensorMap* m, const void* p, int dtype, long BH, long N, int box_rows = kTcChunk) {
-  int r = make_tmap_rows64(m, p, dtype == COTT_BF16, BH, N, kTcD, box_rows);
+int tmap(CUtensorMap* m, const void* p, int dtype, long BH, long N) {
+  int r = make_tmap_rows64(m, p, dtype == COTT_BF16, BH, N, kTcD, kTcChunk);
   if (r == 1) return fail(COTT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   if (r) return fail(COTT_ERR_CUDA, "cuTensorMapEncodeTiled failed: CUresult %d (ptr %p, BH %ld, N %ld)", r - 100, p, BH, N);
   return COTT_OK;
@@ -41,7 +40,7 @@ int launch_fwd(const void* q, const void* k, const void* v, const float* nc, voi
   CUtensorMap mq, mk, mv, mo;
   int st;
   if ((st = tmap(&mq, q, dtype, BH, N)) || (st = tmap(&mk, k, dtype, BH, N)) || (st = tmap(&mv, v, dtype, BH, N)) ||
-      (st = tmap(&mo, out, dtype, BH, N, 32)))
+      (st = tmap(&mo, out, dtype, BH, N)))
     return st;
   auto kern = causal_tc_kernel<T, kModeFwd>;
   const size_t smem = causal_tc_smem_bytes(kModeFwd);
@@ -59,7 +58,7 @@ int launch_bwd_dq(const void* q, const void* k, const void* v, const float* nc, 
   int st;
   if ((st = tmap(&mq, q, dtype, BH, N)) || (st = tmap(&mk, k, dtype, BH, N)) ||
       (st = tmap(&mv, v, dtype, BH, N)) || (st = tmap(&md, dout, dtype, BH, N)) ||
-      (st = tmap(&mo, dq, dtype, BH, N, 32)))
+      (st = tmap(&mo, dq, dtype, BH, N)))
     return st;
   auto kern = causal_tc_kernel<T, kModeDq>;
   const size_t smem = causal_tc_smem_bytes(kModeDq);
@@ -77,7 +76,7 @@ int launch_bwd_dkdv(const void* q, const void* k, const void* v, const float* nc
   int st;
   if ((st = tmap(&mq, q, dtype, BH, N)) || (st = tmap(&mk, k, dtype, BH, N)) ||
       (st = tmap(&mv, v, dtype, BH, N)) || (st = tmap(&md, dout, dtype, BH, N)) ||
-      (st = tmap(&mdk, dk, dtype, BH, N, 32)) || (st = tmap(&mdv, dv, dtype, BH, N, 32)))
+      (st = tmap(&mdk, dk, dtype, BH, N)) || (st = tmap(&mdv, dv, dtype, BH, N)))
     return st;
   COTT_CUDA_TRY(cudaMemsetAsync(dnorm, 0, sizeof(float) * H, stream));
   auto kern = causal_bwd_kv_kernel<T>;

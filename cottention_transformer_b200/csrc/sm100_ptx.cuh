@@ -58,6 +58,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// The same test without the suspend hint: for a single polling thread, whose wake-up latency matters
+// more than the issue slots it takes.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+constexpr uint32_t kMaxSpins = 1u << 22;
 // Bounded wait.  Returns false if the phase did not complete within `max_polls` polls.
 constexpr uint32_t kMaxPolls = 1u << 14;  // x 0.2 ms suspend per try: gives up after about 3 s
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t max_polls = kMaxPolls) {
