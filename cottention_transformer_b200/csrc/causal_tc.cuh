@@ -404,6 +404,152 @@ __device__ __forceinline__ void state_to_smem(uint32_t tS_lane, unsigned char* s
   }
 }
 
+// ---- rolled row routines ---------------------------------------------------------------------------
+// The per-row work below is written as loops that are NOT unrolled (16 columns = two 16-byte pieces per
+// trip).  Every role of these kernels runs on every scheduler, so the roles' code competes for one
+// instruction cache; straight-line versions of these routines (4-8 times the code) measurably slowed
+// all roles down.
+
+// sum of squares of a tile row
+template <typename T>
+__device__ __forceinline__ float row_sumsq_rolled(unsigned char* tile, int row) {
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll 1
+  for (int j = 0; j < 8; j += 2) {
+    const uint4 u = *tile_piece(tile, row, j), w = *tile_piece(tile, row, j + 1);
+    float2 a = Pack2<T>::unpack(u.x), b = Pack2<T>::unpack(u.y), c = Pack2<T>::unpack(u.z), d = Pack2<T>::unpack(u.w);
+    s0 = fmaf(a.x, a.x, fmaf(b.x, b.x, fmaf(c.x, c.x, fmaf(d.x, d.x, s0))));
+    s1 = fmaf(a.y, a.y, fmaf(b.y, b.y, fmaf(c.y, c.y, fmaf(d.y, d.y, s1))));
+    a = Pack2<T>::unpack(w.x), b = Pack2<T>::unpack(w.y), c = Pack2<T>::unpack(w.z), d = Pack2<T>::unpack(w.w);
+    s2 = fmaf(a.x, a.x, fmaf(b.x, b.x, fmaf(c.x, c.x, fmaf(d.x, d.x, s2))));
+    s3 = fmaf(a.y, a.y, fmaf(b.y, b.y, fmaf(c.y, c.y, fmaf(d.y, d.y, s3))));
+  }
+  return (s0 + s1) + (s2 + s3);
+}
+
+// 16 fp32 accumulator columns (this thread's TMEM lane, columns 16 blk ..) times the matching two pieces
+// of a packed 16-bit row
+template <typename T>
+__device__ __forceinline__ float dot16(const uint32_t* r, const uint4& u, const uint4& w) {
+  float2 a = Pack2<T>::unpack(u.x), b = Pack2<T>::unpack(u.y), c = Pack2<T>::unpack(u.z), d = Pack2<T>::unpack(u.w);
+  float s0 = fmaf(a.x, __uint_as_float(r[0]), fmaf(b.x, __uint_as_float(r[2]),
+                  fmaf(c.x, __uint_as_float(r[4]), d.x * __uint_as_float(r[6]))));
+  float s1 = fmaf(a.y, __uint_as_float(r[1]), fmaf(b.y, __uint_as_float(r[3]),
+                  fmaf(c.y, __uint_as_float(r[5]), d.y * __uint_as_float(r[7]))));
+  a = Pack2<T>::unpack(w.x), b = Pack2<T>::unpack(w.y), c = Pack2<T>::unpack(w.z), d = Pack2<T>::unpack(w.w);
+  s0 = fmaf(a.x, __uint_as_float(r[8]), fmaf(b.x, __uint_as_float(r[10]),
+            fmaf(c.x, __uint_as_float(r[12]), fmaf(d.x, __uint_as_float(r[14]), s0))));
+  s1 = fmaf(a.y, __uint_as_float(r[9]), fmaf(b.y, __uint_as_float(r[11]),
+            fmaf(c.y, __uint_as_float(r[13]), fmaf(d.y, __uint_as_float(r[15]), s1))));
+  return s0 + s1;
+}
+// (tile row) . (64 fp32 accumulator columns at taddr_lane)
+template <typename T>
+__device__ __forceinline__ float row_dot_acc(unsigned char* tile, int row, uint32_t taddr_lane) {
+  float s = 0.f;
+#pragma unroll 1
+  for (int blk = 0; blk < 4; ++blk) {
+    uint32_t r[16];
+    ptx::tmem_ld_x16(taddr_lane + 16 * blk, r);
+    const uint4 u = *tile_piece(tile, row, 2 * blk), w = *tile_piece(tile, row, 2 * blk + 1);
+    ptx::tmem_ld_wait();
+    s += dot16<T>(r, u, w);
+  }
+  return s;
+}
+// tile row <- beta * (64 fp32 accumulator columns) + alpha * (tile row), in place (16-bit, swizzled)
+template <typename T, bool kWithRow>
+__device__ __forceinline__ void row_from_acc(unsigned char* tile, int row, uint32_t taddr_lane, float beta, float alpha) {
+#pragma unroll 1
+  for (int blk = 0; blk < 4; ++blk) {
+    uint32_t r[16];
+    ptx::tmem_ld_x16(taddr_lane + 16 * blk, r);
+    uint4* p0 = tile_piece(tile, row, 2 * blk);
+    uint4* p1 = tile_piece(tile, row, 2 * blk + 1);
+    uint4 u = make_uint4(0, 0, 0, 0), w = make_uint4(0, 0, 0, 0);
+    if (kWithRow) {
+      u = *p0;
+      w = *p1;
+    }
+    ptx::tmem_ld_wait();
+    float x[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) x[j] = beta * __uint_as_float(r[j]);
+    if (kWithRow) {
+      const uint32_t q[8] = {u.x, u.y, u.z, u.w, w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float2 f = Pack2<T>::unpack(q[j]);
+        x[2 * j] = fmaf(alpha, f.x, x[2 * j]);
+        x[2 * j + 1] = fmaf(alpha, f.y, x[2 * j + 1]);
+      }
+    }
+    u.x = Pack2<T>::pack(x[0], x[1]);   u.y = Pack2<T>::pack(x[2], x[3]);
+    u.z = Pack2<T>::pack(x[4], x[5]);   u.w = Pack2<T>::pack(x[6], x[7]);
+    w.x = Pack2<T>::pack(x[8], x[9]);   w.y = Pack2<T>::pack(x[10], x[11]);
+    w.z = Pack2<T>::pack(x[12], x[13]); w.w = Pack2<T>::pack(x[14], x[15]);
+    *p0 = u;
+    *p1 = w;
+  }
+}
+// tile row *= w, in place (see scale_row for the arithmetic)
+template <typename T>
+__device__ __forceinline__ void scale_row_rolled(unsigned char* tile, int row, float w) {
+  using V = typename Vec2<T>::type;
+  const float wh = Vec2<T>::head(w);
+  const V whi = Vec2<T>::bcast(wh), wlo = Vec2<T>::bcast(w - wh);
+#pragma unroll 1
+  for (int j = 0; j < 8; j += 2) {
+    uint4* p0 = tile_piece(tile, row, j);
+    uint4* p1 = tile_piece(tile, row, j + 1);
+    uint4 u = *p0, v = *p1;
+    if constexpr (Pack2<T>::kBf16) {
+      V* x = reinterpret_cast<V*>(&u);
+      V* y = reinterpret_cast<V*>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        x[e] = __hfma2(x[e], whi, __hmul2(x[e], wlo));
+        y[e] = __hfma2(y[e], whi, __hmul2(y[e], wlo));
+      }
+    } else {  // float16 has too little range to hold the factor itself: multiply in fp32
+      uint32_t* x = reinterpret_cast<uint32_t*>(&u);
+      uint32_t* y = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float2 f = Pack2<T>::unpack(x[e]), g = Pack2<T>::unpack(y[e]);
+        x[e] = Pack2<T>::pack(f.x * w, f.y * w);
+        y[e] = Pack2<T>::pack(g.x * w, g.y * w);
+      }
+    }
+    *p0 = u;
+    *p1 = v;
+  }
+}
+// fp32 state (M=64 accumulator layout, see state_to_smem) -> 16-bit swizzled smem operand
+template <typename T>
+__device__ __forceinline__ void state_to_smem_rolled(uint32_t tS_lane, unsigned char* sS, int wq, int lane) {
+  const int i = 16 * wq + (lane & 15);
+#pragma unroll 1
+  for (int blk = 0; blk < 4; ++blk) {
+    uint32_t r[16];
+    ptx::tmem_ld_x16(tS_lane + 16 * blk, r);
+    ptx::tmem_ld_wait();
+    if (lane < 16) {
+      uint4 u, w;
+      u.x = Pack2<T>::pack(__uint_as_float(r[0]), __uint_as_float(r[1]));
+      u.y = Pack2<T>::pack(__uint_as_float(r[2]), __uint_as_float(r[3]));
+      u.z = Pack2<T>::pack(__uint_as_float(r[4]), __uint_as_float(r[5]));
+      u.w = Pack2<T>::pack(__uint_as_float(r[6]), __uint_as_float(r[7]));
+      w.x = Pack2<T>::pack(__uint_as_float(r[8]), __uint_as_float(r[9]));
+      w.y = Pack2<T>::pack(__uint_as_float(r[10]), __uint_as_float(r[11]));
+      w.z = Pack2<T>::pack(__uint_as_float(r[12]), __uint_as_float(r[13]));
+      w.w = Pack2<T>::pack(__uint_as_float(r[14]), __uint_as_float(r[15]));
+      *tile_piece(sS, i, 2 * blk) = u;
+      *tile_piece(sS, i, 2 * blk + 1) = w;
+    }
+  }
+}
+
 // Descriptors of a [rows x 64] 16-bit tile with the 128-byte swizzle (see sm100_ptx.cuh).
 // K-major: advance K by 16 elements = +32 B = +2 in descriptor units; MN-major: +2048 B = +128.
 __device__ __forceinline__ uint64_t kdesc(uint32_t saddr) { return ptx::make_smem_desc(saddr, 16, 1024); }
@@ -651,9 +797,9 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       unsigned char* sZ = smem + s * STAGE + 2 * kTileBytes;
       unsigned char* sK = (MODE == kModeDq) ? sZ : smem + s * STAGE + kTileBytes;
 #if !(COTT_SKEL & 2)
-      const float rk = inv_norm(row_sumsq<T>(sK, row));
+      const float rk = inv_norm(row_sumsq_rolled<T>(sK, row));
       const float a = length_factor(static_cast<float>(c * kTcChunk + row + 1), sigma);
-      scale_row<T>(sZ, row, rk * a);
+      scale_row_rolled<T>(sZ, row, rk * a);
 #endif
       fence_proxy_async_smem();
       warp_arrive(&bar_prep[s], lane);
@@ -670,7 +816,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       if (lane == 0) mbar_arrive(&bar_free_in[c % NS]);  // the state MMAs of chunk c have read its tiles
       COTT_TRACE_EV(0, c);
 #if !(COTT_SKEL & 4)
-      state_to_smem<T>(tS + lane_base, sS + ((c + 1) & 1) * (kTcD * 128), wq, lane);
+      state_to_smem_rolled<T>(tS + lane_base, sS + ((c + 1) & 1) * (kTcD * 128), wq, lane);
 #endif
       fence_proxy_async_smem();
       tc_fence_before_sync();
@@ -689,7 +835,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       if (!wait_bar_warp(&bar_full[s], (c / NS) & 1, abort_flag, kWaitTma, c)) break;
       COTT_TRACE_EV(7, c);
 #if !(COTT_SKEL & 4)
-      const float rq = inv_norm(row_sumsq<T>(sQ, row));
+      const float rq = inv_norm(row_sumsq_rolled<T>(sQ, row));
 #else
       const float rq = 1.f;
 #endif
@@ -697,35 +843,25 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       if (!wait_bar_warp(&bar_acc_full[b], (c >> 1) & 1, abort_flag, kWaitAcc, c)) break;
       tc_fence_after_sync();
       COTT_TRACE_EV(2, c);
-      float acc[64];
+      // The score and accumulator MMAs of this chunk have completed (the operand group reports the state
+      // MMAs): all tiles but the staging one can be refilled.
+      if (lane == 0) mbar_arrive(&bar_free_in[s]);
+      // The staging tile has no MMA reader left (forward: X, whose row norm this thread has taken; dQ: the
+      // q tile, which no MMA reads).  Its rows are replaced in place, in the swizzled layout, by the
+      // output rows; the TMA thread stores the tile and refills it.
+      const uint32_t tAcc = tAcc0 + 64 * b + lane_base;
 #if !(COTT_SKEL & 4)
-      tmem_row64(tAcc0 + 64 * b + lane_base, acc);
-#else
-      for (int j = 0; j < 64; ++j) acc[j] = 0.f;
+      if (MODE == kModeFwd) {
+        row_from_acc<T, false>(sQ, row, tAcc, rq, 0.f);  // o = acc / |q|
+      } else {
+        // dq = (dq^ - q^ (q^ . dq^)) / |q| with dq^ = acc and q^ = rq q
+        const float delta = row_dot_acc<T>(sQ, row, tAcc) * (rq * rq * rq);
+        row_from_acc<T, true>(sQ, row, tAcc, rq, -delta);
+      }
 #endif
       tc_fence_before_sync();
       warp_arrive(&bar_acc_free[b], lane);
-      // the score and accumulator MMAs of this chunk have completed (the operand group reports the state
-      // MMAs): all tiles but the staging one can be refilled
-      if (lane == 0) mbar_arrive(&bar_free_in[s]);
       COTT_TRACE_EV(3, c);
-      if (MODE == kModeFwd) {
-#pragma unroll
-        for (int j = 0; j < 64; ++j) acc[j] *= rq;
-      } else {
-        uint4 uq[8];  // the q row, kept packed (32 registers) and unpacked twice
-#pragma unroll
-        for (int j = 0; j < 8; ++j) uq[j] = *tile_piece(sQ, row, j);
-        float delta = packed_dot64<T>(uq, acc);
-        delta *= rq * rq * rq;  // (q^ . dq^) / |q|^2, with dq^ = acc and q^ = rq q
-        packed_axpby64<T>(uq, -delta, rq, acc);  // acc = rq acc - delta q
-      }
-      COTT_TRACE_EV(5, c);
-      // The staging tile has no reader left: its MMAs completed before acc_full (forward: X, and this
-      // thread has taken the norm of its own row; dQ: the q tile, which no MMA reads and whose row this
-      // thread has just used).  The output rows go there in the swizzled layout; the TMA thread stores
-      // the tile and refills it.
-      write_row64<T>(sQ, row, acc);
       fence_proxy_async_smem();
       warp_arrive(&bar_out[s], lane);
       COTT_TRACE_EV(4, c);
@@ -959,7 +1095,7 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       const int s = ci % NS;
       if (!wait_bar_warp(&bar_full[s], (ci / NS) & 1, abort_flag, kWaitTma, ci)) return false;
       unsigned char* sQ = smem + s * STAGE;
-      scale_row<T>(sQ, row, inv_norm(row_sumsq<T>(sQ, row)));
+      scale_row_rolled<T>(sQ, row, inv_norm(row_sumsq_rolled<T>(sQ, row)));
       fence_proxy_async_smem();
       warp_arrive(&bar_prep[s], lane);
       return true;
@@ -992,7 +1128,7 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         if (!wait_bar_warp(&bar_r_full, ci & 1, abort_flag, kWaitState, ci)) break;
         tc_fence_after_sync();
         if (lane == 0) mbar_arrive(&bar_free_in[ci % NS]);  // the state MMAs of chunk ci have read its tiles
-        state_to_smem<T>(tR + lane_base, sR + ((ci + 1) & 1) * (kTcD * 128), wq, lane);
+        state_to_smem_rolled<T>(tR + lane_base, sR + ((ci + 1) & 1) * (kTcD * 128), wq, lane);
         fence_proxy_async_smem();
         tc_fence_before_sync();
         warp_arrive(&bar_state, lane);
@@ -1011,7 +1147,7 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       unsigned char* sV = smem + s * STAGE + 2 * kTileBytes;
       const int pos = (nchunks - 1 - ci) * kTcChunk + row;
       if (!wait_bar_warp(&bar_full[s], (ci / NS) & 1, abort_flag, kWaitTma, ci)) break;
-      const float rk = inv_norm(row_sumsq<T>(sK, row));
+      const float rk = inv_norm(row_sumsq_rolled<T>(sK, row));
       const float a = length_factor(static_cast<float>(pos + 1), sigma);
       COTT_TRACE_EV(0, ci);
       if (!wait_bar_warp(&bar_acc_full, ci & 1, abort_flag, kWaitAcc, ci)) break;
@@ -1022,30 +1158,14 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       // is done with its own rows, so they have no reader left.  The TMA thread stores and refills them.
       if (lane == 0) mbar_arrive(&bar_free_in[s]);  // (warp-converged: follows wait_bar_warp) q, dO tiles are free
       const float c1 = rk * a;
-      float acc[64];
-      float eps;
-      {
-        tmem_row64(tV + lane_base, acc);  // raw: dv' = rk * raw
-        uint4 uv[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) uv[j] = *tile_piece(sV, row, j);
-        eps = c1 * packed_dot64<T>(uv, acc);  // v' . dv' with v' = a v
-#pragma unroll
-        for (int j = 0; j < 64; ++j) acc[j] *= c1;  // dv = a dv'
-        write_row64<T>(sV, row, acc);
-      }
-      {
-        tmem_row64(tK + lane_base, acc);  // raw: dk^ = a * raw
-        tc_fence_before_sync();
-        warp_arrive(&bar_acc_free, lane);
-        COTT_TRACE_EV(4, ci);
-        uint4 uk[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) uk[j] = *tile_piece(sK, row, j);
-        // dk = rk (dk^ - k^ (k^ . dk^)) with k^ . dk^ = v' . dv' = eps and k^ = rk k
-        packed_axpby64<T>(uk, -rk * rk * eps, c1, acc);
-        write_row64<T>(sK, row, acc);
-      }
+      // dv = a dv' = c1 raw;  eps = v' . dv' = c1 (v . raw)
+      const float eps = c1 * row_dot_acc<T>(sV, row, tV + lane_base);
+      row_from_acc<T, false>(sV, row, tV + lane_base, c1, 0.f);
+      // dk = rk (dk^ - k^ (k^ . dk^)) with dk^ = a raw, k^ . dk^ = v' . dv' = eps and k^ = rk k
+      row_from_acc<T, true>(sK, row, tK + lane_base, c1, -rk * rk * eps);
+      tc_fence_before_sync();
+      warp_arrive(&bar_acc_free, lane);
+      COTT_TRACE_EV(4, ci);
       COTT_TRACE_EV(5, ci);
       ptx::fence_proxy_async_smem();
       warp_arrive(&bar_out[s], lane);
