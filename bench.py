@@ -39,8 +39,8 @@ B_PER_GPU, H, N, D = 8, 16, 4096, 64
 WORKLOAD = "causal cosine attention fwd+bwd, B=8/GPU H=16 N=4096 d=64 bf16 (Q,K L2-normalised N(0,1), norm_const=0.5)"
 ELEM = 2  # bf16
 # ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of causal_bwd_kv_kernel at the bench shape
-# (profiles/causal_fwd_bwd_B8_H16_N4096_d64_bf16_warp_specialised.md: 269.3 MB read + 96.8 MB write).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 366_035_712
+# (profiles/causal_fwd_bwd_B8_H16_N4096_d64_bf16_three_groups.md: 268.5 MB read + 95.1 MB write).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 363_582_208
 
 
 def _peaks():
