@@ -126,12 +126,40 @@ def bench_bidir(B=32, H=12, N=512, d=64):
             "peak_gbs": peak, "peak_source": kind, "frac": nbytes / t / 1e9 / peak}
 
 
+def bench_causal_kernels(B, H=16, N=4096, d=64, iters=20):
+    """Each of the three fused kernels on its own, through the C ABI (small-batch profiler runs)."""
+    L = _lib.lib()
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(1234)
+    q, k, v, do = (torch.randn(B, H, N, d, device=dev, generator=g).bfloat16() for _ in range(4))
+    out, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
+    nc, dnc = 0.5 * torch.ones(H, device=dev), torch.empty(H, device=dev)
+    st = _lib.stream_ptr(dev)
+    P = lambda t: t.data_ptr()  # noqa: E731
+    fns = {
+        "fwd": lambda: _lib.check(L.cott_cos_attn_fwd(P(q), P(k), P(v), P(nc), P(out), B, H, N, d, d, 3, st), "fwd"),
+        "dq": lambda: _lib.check(L.cott_cos_attn_bwd_dq(P(q), P(k), P(v), P(nc), P(do), P(dq), B, H, N, d, d, 3, st), "dq"),
+        "dkdv": lambda: _lib.check(L.cott_cos_attn_bwd_dkdv(P(q), P(k), P(v), P(nc), P(do), P(dk), P(dv), P(dnc), B, H, N,
+                                                            d, d, 3, st), "dkdv"),
+    }
+    res = {"what": f"fused causal kernels one by one, B={B} H={H} N={N} d={d} bf16"}
+    for name, fn in fns.items():
+        res[name + "_us"] = _time(fn, iters, warmup=3) * 1e6
+    _lib.check_device_status()
+    return res
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
+    ap.add_argument("--causal", type=int, default=0, metavar="B",
+                    help="only time the three fused causal kernels at batch B (H=16, N=4096, d=64)")
     ap.add_argument("--decode-steps", type=int, default=256)
     ap.add_argument("--json", default=None)
     ap.add_argument("--no-graph", action="store_true", help="do not replay decode from a CUDA graph (profiler runs)")
     a = ap.parse_args()
+    if a.causal:
+        print(json.dumps(bench_causal_kernels(a.causal)))
+        raise SystemExit(0)
     res = [bench_decode(64, a.decode_steps, use_graph=not a.no_graph), bench_decode(128, a.decode_steps, use_graph=not a.no_graph),
            bench_bidir()]
     for r in res:
