@@ -33,7 +33,7 @@ __device__ int g_cott_status;  // 0 = ok; else (code << 16 | chunk) of the first
 
 // Optional timeline tracing (debug builds only, -DCOTT_TRACE): CTA 0 records clock64() at role events.
 #ifdef COTT_TRACE
-constexpr int kTraceWarps = 15, kTraceChunks = 32, kTraceEvents = 8;
+constexpr int kTraceWarps = 28, kTraceChunks = 32, kTraceEvents = 8;
 __device__ unsigned int g_cott_trace[kTraceWarps * kTraceChunks * kTraceEvents];
 // timestamps go to shared memory (a global store in the middle of a role would itself disturb the
 // fences and waits being timed) and are copied out when the kernel ends
@@ -563,8 +563,10 @@ enum {
   kWaitAccFree = 7, kWaitState = 8
 };
 
-constexpr int kTcThreads = 480;  // 2 issuing warps, 3 groups of 4 warps, 1 TMA warp
+constexpr int kTcThreads = 896;  // forward / dQ: 3 issuing warps, 6 groups of 4 warps, 1 TMA warp
+constexpr int kKvThreads = 480;  // dK/dV: 2 issuing warps, 3 groups of 4 warps, 1 TMA warp
 constexpr int kTcStages = 3;
+constexpr int kTcRing = kTcStages + 1;  // slots of the tile that doubles as output staging buffer (forward / dQ)
 
 template <typename T, int MODE>
 __global__ void __launch_bounds__(kTcThreads, 1)
@@ -572,9 +574,14 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
                  const __grid_constant__ CUtensorMap mapZ, const __grid_constant__ CUtensorMap mapQ,
                  const __grid_constant__ CUtensorMap mapOut, const float* __restrict__ norm_const, int H, int N) {
   using namespace ptx;
-  constexpr int NT = (MODE == kModeFwd) ? 3 : 4;  // tiles per stage
-  constexpr int STAGE = NT * kTileBytes;
+  // Shared memory: NS stages of the tiles that are only read (forward: Y, Z; dQ: X, Y, Z), a ring of
+  // kTcRing tiles for the tile that doubles as the output staging buffer (forward: X; dQ: q), the 16-bit
+  // state operand (2 x 8 KB).  The ring is one slot longer than the stage count, so the tile of chunk c+NS
+  // is loaded into the slot chunk c-1 left, while chunk c's output is still being written and stored.
+  constexpr int NIN = (MODE == kModeFwd) ? 2 : 3;  // read-only tiles per stage
+  constexpr int STAGE = NIN * kTileBytes;
   constexpr int NS = kTcStages;
+  constexpr int kIdxY = (MODE == kModeFwd) ? 0 : 1, kIdxZ = kIdxY + 1;  // tile index inside a stage (dQ: X = 0)
   constexpr bool BF = Pack2<T>::kBf16;
 
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -582,9 +589,13 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   // (offset arithmetic on the __shared__ array keeps the pointer's address space known to the
   // compiler, so tile accesses compile to LDS/STS rather than generic loads and stores)
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  unsigned char* sS = smem + NS * STAGE;  // 2 x [64 x 64] 16-bit state operand (double-buffered), 2 x 8 KB
+  unsigned char* ring = smem + NS * STAGE;
+  unsigned char* sS = ring + kTcRing * kTileBytes;  // 2 x [64 x 64] 16-bit state operand (double-buffered)
+  auto stage_of = [&](int c) { return smem + (c % NS) * STAGE; };
+  auto ring_of = [&](int c) { return ring + (c % kTcRing) * kTileBytes; };
+  auto tile_x = [&](int c) { return MODE == kModeFwd ? ring_of(c) : stage_of(c); };
   __shared__ uint64_t bar_full[NS], bar_free_in[NS], bar_out[NS], bar_prep[NS], bar_p_full[2], bar_p_ready[2], bar_acc_full[2],
-      bar_acc_free[2], bar_s_full, bar_state, bar_state2;
+      bar_acc_free[2], bar_s_full, bar_state[2], bar_state2;
   __shared__ uint32_t tmem_slot;
   COTT_TRACE_DECL
   __shared__ int abort_flag_s;
@@ -610,7 +621,8 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       mbar_init(&bar_acc_free[b], 4);
     }
     mbar_init(&bar_s_full, 1);
-    mbar_init(&bar_state, 4);
+    mbar_init(&bar_state[0], 4);
+    mbar_init(&bar_state[1], 4);
     mbar_init(&bar_state2, 4);
     mbar_fence_init();
     abort_flag_s = 0;
@@ -632,24 +644,25 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
 
   // Roles.  Two issuing threads on two different schedulers share the tensor-core issue work (a single
   // one was busy for the whole chunk period and so was the critical path); their MMAs are ordered only
-  // through the mbarriers.  The per-row work is spread over three groups of four warps (warp w of a group
+  // through the mbarriers.  The per-row work is spread over six groups of four warps (warp w of a group
   // owns TMEM lanes / tile rows 32 (w % 4) ..): each group's work per chunk is serial and latency-bound,
   // so the chunk period is set by the busiest group.
-  //   warp 0, lane 0:   scores P(c+1) = X Y^T, state S += Y^T Zw (c)
+  //   warp 0, lane 0:   scores P(c+1) = X Y^T
+  //   warp 19, lane 0:  state S += Y^T Zw (c)
   //   warp 1, lane 0:   accumulators Acc(c) = X S + P Zw
   //   warps 2-5:        score group: mask + convert P
-  //   warps 6-9:        output group: row norm of q, accumulator -> output rows
-  //   warps 10-13:      operand group: Zw in place, fp32 state -> 16-bit operand
+  //   warps 6-9, 20-23: output groups (even / odd chunks): row norm of q, accumulator -> output rows
+  //   warps 10-13:      state group: fp32 state -> 16-bit operand
   //   warp 14, lane 0:  TMA loads and stores
+  //   warps 15-18, 24-27: operand groups (even / odd chunks): Zw in place
   constexpr uint32_t kIdescP = make_idesc(128, 128, BF, false, false);
   constexpr uint32_t kIdescAcc = make_idesc(128, 64, BF, false, true);
   constexpr uint32_t kIdescS = make_idesc(64, 64, BF, true, true);
   if (warp == 0) {
-    // ---------------------------------------------------------------- scores + state
+    // ---------------------------------------------------------------- scores
     if (lane == 0) {
       auto issue_scores = [&](int c) {  // caller has waited for the TMA of chunk c and for the buffer
-        const uint32_t x0 = smem_u32(smem + (c % NS) * STAGE);
-        const uint64_t dX = kdesc(x0), dY = kdesc(x0 + kTileBytes);
+        const uint64_t dX = kdesc(smem_u32(tile_x(c))), dY = kdesc(smem_u32(stage_of(c) + kIdxY * kTileBytes));
         const uint32_t tP = tP0 + 128 * (c & 1);
 #pragma unroll
         for (int k = 0; k < 4; ++k) mma_ss(tP, dX + 2 * k, dY + 2 * k, kIdescP, k > 0);
@@ -670,13 +683,23 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
           if (!ok) break;
           tc_fence_after_sync();
           issue_scores(c + 1);
+        }
+      }
+    }
+  } else if (warp == 19) {
+    // ---------------------------------------------------------------- state
+    // state MMA -> conversion -> next state MMA is the loop that sets the chunk period: its issuing thread
+    // does nothing else
+    if (lane == 0) {
+      for (int c = 0; c + 1 < nchunks; ++c) {
+        {
           // state update of chunk c: Zw(c), and the conversion of S after chunk c-1
-          ok = wait_bar4(&bar_prep[c % NS], (c / NS) & 1, c > 0 ? &bar_state2 : nullptr, (c - 1) & 1, nullptr, 0,
-                         nullptr, 0, abort_flag, kWaitPrepped, c);
-          if (!ok) break;
+          if (!wait_bar4(&bar_prep[c % NS], (c / NS) & 1, c > 0 ? &bar_state2 : nullptr, (c - 1) & 1, nullptr, 0,
+                         nullptr, 0, abort_flag, kWaitPrepped, c))
+            break;
           tc_fence_after_sync();
-          const uint32_t x0 = smem_u32(smem + (c % NS) * STAGE);
-          const uint64_t dYm = mdesc(x0 + kTileBytes), dZm = mdesc(x0 + 2 * kTileBytes);
+          const uint32_t y0 = smem_u32(stage_of(c) + kIdxY * kTileBytes);
+          const uint64_t dYm = mdesc(y0), dZm = mdesc(y0 + kTileBytes);
           mma_ss(tS, dYm, dZm, kIdescS, c > 0 ? 1u : 0u);
 #pragma unroll
           for (int k = 1; k < 8; ++k) mma_ss(tS, dYm + 128 * k, dZm + 128 * k, kIdescS, 1u);
@@ -687,55 +710,40 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
     }
   } else if (warp == 14) {
     // ---------------------------------------------------------------- TMA loads and stores
-    // A thread of its own.  The output rows of a chunk are staged in one tile of the chunk's own stage
-    // (forward: the X tile, dQ: the q tile -- the tile whose rows the output group reads last), so a stage
-    // is refilled in two steps: the other tiles as soon as every MMA of the chunk has completed, the
-    // staging tile once the output store has read it.  Both steps count on the same `full` barrier.
+    // A thread of its own.  The output rows of a chunk are staged over the ring tile of the chunk (forward:
+    // the X tile, dQ: the q tile -- the tile whose rows the output group reads last) and stored from there.
     if (lane == 0) {
-      constexpr int kOutTile = (MODE == kModeDq) ? 3 : 0;
-      auto load_inputs = [&](int c) {  // all tiles but the staging one
+      auto issue_loads = [&](int c) {
         const int s = c % NS;
-        unsigned char* st = smem + s * STAGE;
-#if COTT_SKEL & 8
-        if (c >= NS) return;
-#endif
-        mbar_expect_tx(&bar_full[s], STAGE);
-        if (MODE == kModeDq) tma_load_3d(st, &mapX, &bar_full[s], 0, c * kTcChunk, bh);
-        tma_load_3d(st + kTileBytes, &mapY, &bar_full[s], 0, c * kTcChunk, bh);
-        tma_load_3d(st + 2 * kTileBytes, &mapZ, &bar_full[s], 0, c * kTcChunk, bh);
-        COTT_TRACE_EV(0, c);
-      };
-      auto load_staging = [&](int c) {
-        const int s = c % NS;
-        unsigned char* st = smem + s * STAGE + kOutTile * kTileBytes;
+        unsigned char* st = stage_of(c);
 #if COTT_SKEL & 8
         if (c >= NS) {
           mbar_arrive(&bar_full[s]);
           return;
         }
 #endif
-        tma_load_3d(st, MODE == kModeDq ? &mapQ : &mapX, &bar_full[s], 0, c * kTcChunk, bh);
+        mbar_expect_tx(&bar_full[s], STAGE + kTileBytes);
+        if (MODE == kModeDq) tma_load_3d(st, &mapX, &bar_full[s], 0, c * kTcChunk, bh);
+        tma_load_3d(st + kIdxY * kTileBytes, &mapY, &bar_full[s], 0, c * kTcChunk, bh);
+        tma_load_3d(st + kIdxZ * kTileBytes, &mapZ, &bar_full[s], 0, c * kTcChunk, bh);
+        tma_load_3d(ring_of(c), MODE == kModeDq ? &mapQ : &mapX, &bar_full[s], 0, c * kTcChunk, bh);
+        COTT_TRACE_EV(0, c);
       };
-      for (int c = 0; c < NS && c < nchunks; ++c) {
-        load_inputs(c);
-        load_staging(c);
-      }
+      for (int c = 0; c < NS && c < nchunks; ++c) issue_loads(c);
       for (int c = 0; c < nchunks; ++c) {
         const int s = c % NS;
-        const bool refill = c + NS < nchunks;
-        if (refill) {
+        if (c + NS < nchunks) {
+          // every MMA of chunk c has completed; the ring slot of chunk c+NS is the one chunk c-1 was stored
+          // from (group committed one iteration ago): make sure the TMA engine has read it
           if (!wait_bar(&bar_free_in[s], (c / NS) & 1, abort_flag, kWaitStageFree, c)) break;
-          load_inputs(c + NS);
+          tma_store_wait_read<0>();
+          issue_loads(c + NS);
         }
         if (!wait_bar(&bar_out[s], (c / NS) & 1, abort_flag, kWaitStageFree, c)) break;
 #if !(COTT_SKEL & 16)
-        tma_store_3d(&mapOut, smem + s * STAGE + kOutTile * kTileBytes, 0, c * kTcChunk, bh);
+        tma_store_3d(&mapOut, ring_of(c), 0, c * kTcChunk, bh);
         tma_store_commit();
 #endif
-        if (refill) {
-          tma_store_wait_read<0>();
-          load_staging(c + NS);
-        }
       }
       tma_store_wait<0>();
     }
@@ -745,13 +753,11 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       const uint64_t dS0 = mdesc(smem_u32(sS));
       for (int c = 0; c < nchunks; ++c) {
         const int s = c % NS, b = c & 1;
-        const uint32_t x0 = smem_u32(smem + s * STAGE);
-        const uint64_t dX = kdesc(x0), dZm = mdesc(x0 + 2 * kTileBytes);
+        const uint64_t dX = kdesc(smem_u32(tile_x(c))), dZm = mdesc(smem_u32(stage_of(c) + kIdxZ * kTileBytes));
         const uint32_t tP = tP0 + 128 * b, tAcc = tAcc0 + 64 * b;
-        // masked scores of chunk c (this also implies Zw(c): the score group prepares Zw(c) before it
-        // masks chunk c), the 16-bit state after chunk c-1, and the accumulator buffer read out
-        if (!wait_bar4(&bar_p_ready[b], (c >> 1) & 1, c > 0 ? &bar_state : nullptr, (c - 1) & 1,
-                       c >= 2 ? &bar_acc_free[b] : nullptr, ((c >> 1) - 1) & 1, nullptr, 0, abort_flag,
+        // masked scores of chunk c, the 16-bit state after chunk c-1, the accumulator buffer read out, Zw(c)
+        if (!wait_bar4(&bar_p_ready[b], (c >> 1) & 1, c > 0 ? &bar_state[(c - 1) & 1] : nullptr, ((c - 1) >> 1) & 1,
+                       c >= 2 ? &bar_acc_free[b] : nullptr, ((c >> 1) - 1) & 1, &bar_prep[s], (c / NS) & 1, abort_flag,
                        kWaitScoreReady, c))
           break;
         tc_fence_after_sync();
@@ -785,17 +791,62 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       warp_arrive(&bar_p_ready[b], lane);
       COTT_TRACE_EV(1, c);
     }
-  } else if (warp >= 10) {
-    // ---------------------------------------------------------------- operand group
-    const int wq = warp & 3, row = 32 * wq + lane;
+  } else if (warp >= 10 && warp < 14) {
+    // ---------------------------------------------------------------- state group
+    const int wq = warp & 3;
     const uint32_t lane_base = static_cast<uint32_t>(32 * wq) << 16;
+    for (int c = 0; c + 1 < nchunks; ++c) {
+      // S after chunk c -> 16-bit operand for chunk c+1 (buffer (c+1)&1)
+      if (!wait_bar_warp(&bar_s_full, c & 1, abort_flag, kWaitState, c)) break;
+      tc_fence_after_sync();
+      if (lane == 0) mbar_arrive(&bar_free_in[c % NS]);  // the state MMAs of chunk c have read its tiles
+      COTT_TRACE_EV(0, c);
+      // The state MMA of chunk c+1 waits for this read of the fp32 state (and the accumulator MMAs of
+      // chunk c+1 for the 16-bit copy): that loop sets the chunk period.  So the read is reported as soon
+      // as the second half of the row has arrived, before its conversion and the shared-memory writes.
+      {
+        uint32_t r[32], pk[32];
+        tmem_ld_x32(tS + lane_base, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) pk[j] = Pack2<T>::pack(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+        tmem_ld_x32(tS + lane_base + 32, r);
+        tmem_ld_wait();
+        tc_fence_before_sync();
+        warp_arrive(&bar_state2, lane);
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          pk[16 + j] = Pack2<T>::pack(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+        // The 16-bit buffer written now was last read by the accumulator MMAs of chunk c-1.  (The state
+        // thread runs ahead of the accumulator thread, so nothing else orders the two.)
+        if (c > 0 && !wait_bar_warp(&bar_acc_full[(c - 1) & 1], ((c - 1) >> 1) & 1, abort_flag, kWaitAccFree, c)) break;
+        if (lane < 16) {
+          unsigned char* dst = sS + ((c + 1) & 1) * (kTcD * 128);
+          const int i = 16 * wq + lane;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *tile_piece(dst, i, j) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+        }
+      }
+      fence_proxy_async_smem();
+      warp_arrive(&bar_state[c & 1], lane);
+      COTT_TRACE_EV(1, c);
+    }
+  } else if ((warp >= 15 && warp < 19) || warp >= 24) {
+    // ---------------------------------------------------------------- operand groups (even / odd chunks)
+    const int row = 32 * (warp & 3) + lane;
     const float sigma = 1.0f / (1.0f + __expf(-norm_const[h]));
-    auto prepare = [&](int c) -> bool {  // Zw = diag(a_s / |k_s|) Z, in place
+    const int mine = (warp >= 24) ? 1 : 0;
+    for (int c = 0; c < nchunks; ++c) {  // Zw = diag(a_s / |k_s|) Z, in place
       const int s = c % NS;
-      if (!wait_bar_warp(&bar_full[s], (c / NS) & 1, abort_flag, kWaitTma, c)) return false;
+      // Every phase of a barrier has to be observed, also for the chunks of the other group: a parity
+      // wait cannot tell phase n from phase n+2, and with 3 stages a group that only looked at its own
+      // chunks would skip every other phase of each `full` barrier.
+      if (!wait_bar_warp(&bar_full[s], (c / NS) & 1, abort_flag, kWaitTma, c)) break;
+      if ((c & 1) != mine) continue;
       COTT_TRACE_EV(3, c);
-      unsigned char* sZ = smem + s * STAGE + 2 * kTileBytes;
-      unsigned char* sK = (MODE == kModeDq) ? sZ : smem + s * STAGE + kTileBytes;
+      unsigned char* sZ = stage_of(c) + kIdxZ * kTileBytes;
+      unsigned char* sK = (MODE == kModeDq) ? sZ : stage_of(c) + kIdxY * kTileBytes;
 #if !(COTT_SKEL & 2)
       const float rk = inv_norm(row_sumsq_rolled<T>(sK, row));
       const float a = length_factor(static_cast<float>(c * kTcChunk + row + 1), sigma);
@@ -804,35 +855,19 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       fence_proxy_async_smem();
       warp_arrive(&bar_prep[s], lane);
       COTT_TRACE_EV(7, c);
-      return true;
-    };
-    bool ok = prepare(0);
-    for (int c = 0; ok && c + 1 < nchunks; ++c) {
-      // Zw of the next chunk first: the state MMAs of chunk c are still running
-      if (!(ok = prepare(c + 1))) break;
-      // S after chunk c -> 16-bit operand for chunk c+1 (buffer (c+1)&1)
-      if (!(ok = wait_bar_warp(&bar_s_full, c & 1, abort_flag, kWaitState, c))) break;
-      tc_fence_after_sync();
-      if (lane == 0) mbar_arrive(&bar_free_in[c % NS]);  // the state MMAs of chunk c have read its tiles
-      COTT_TRACE_EV(0, c);
-#if !(COTT_SKEL & 4)
-      state_to_smem_rolled<T>(tS + lane_base, sS + ((c + 1) & 1) * (kTcD * 128), wq, lane);
-#endif
-      fence_proxy_async_smem();
-      tc_fence_before_sync();
-      warp_arrive(&bar_state, lane);
-      if (lane == 0) mbar_arrive(&bar_state2);
-      COTT_TRACE_EV(1, c);
     }
   } else {
-    // ---------------------------------------------------------------- output group
+    // ---------------------------------------------------------------- output groups (even / odd chunks)
     const int wq = warp & 3, row = 32 * wq + lane;
     const uint32_t lane_base = static_cast<uint32_t>(32 * wq) << 16;
+    const int mine = (warp >= 20) ? 1 : 0;
     for (int c = 0; c < nchunks; ++c) {
       const int s = c % NS, b = c & 1;
-      unsigned char* sQ = smem + s * STAGE + ((MODE == kModeDq) ? 3 * kTileBytes : 0);
+      unsigned char* sQ = ring_of(c);  // forward: X; dQ: q
       // the row norm of q only needs the TMA data: do it while the MMAs run
+      // (every phase of `full` is observed, also for the other group's chunks: see the operand groups)
       if (!wait_bar_warp(&bar_full[s], (c / NS) & 1, abort_flag, kWaitTma, c)) break;
+      if ((c & 1) != mine) continue;
       COTT_TRACE_EV(7, c);
 #if !(COTT_SKEL & 4)
       const float rq = inv_norm(row_sumsq_rolled<T>(sQ, row));
@@ -844,7 +879,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       tc_fence_after_sync();
       COTT_TRACE_EV(2, c);
       // The score and accumulator MMAs of this chunk have completed (the operand group reports the state
-      // MMAs): all tiles but the staging one can be refilled.
+      // MMAs): the stage can be refilled.
       if (lane == 0) mbar_arrive(&bar_free_in[s]);
       // The staging tile has no MMA reader left (forward: X, whose row norm this thread has taken; dQ: the
       // q tile, which no MMA reads).  Its rows are replaced in place, in the swizzled layout, by the
@@ -895,7 +930,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
 // Same warp roles as causal_tc_kernel; the two score tiles fill TMEM, so they are single-buffered:
 // the score MMAs of chunk c+1 are queued right behind the accumulator MMAs of chunk c.
 template <typename T>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(kKvThreads, 1)
 causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                      const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
                      const __grid_constant__ CUtensorMap mapDK, const __grid_constant__ CUtensorMap mapDV, float* __restrict__ dnorm,
@@ -962,7 +997,7 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   constexpr uint32_t kIdescAccKK = make_idesc(128, 64, BF, false, false);  // B K-major (V R^T)
   constexpr uint32_t kIdescAccMN = make_idesc(128, 64, BF, false, true);   // B MN-major
   constexpr uint32_t kIdescR = make_idesc(64, 64, BF, true, true);
-  if (warp == kTcThreads / 32 - 1) {
+  if (warp == 14) {
     // TMA loads and stores (a thread of its own, see causal_tc_kernel).  dK and dV are staged in the K and
     // V tiles of the chunk's own stage: q and dO are refilled as soon as every MMA of the chunk has
     // completed, K and V once the output stores have read them.
@@ -1194,8 +1229,8 @@ inline size_t causal_bwd_kv_smem_bytes() {
 }
 
 inline size_t causal_tc_smem_bytes(int mode) {
-  const int nt = mode == kModeFwd ? 3 : 4;
-  return static_cast<size_t>(kTcStages * nt * kTileBytes + 2 * kTcD * 128 + 1024);
+  const int nin = mode == kModeFwd ? 2 : 3;
+  return static_cast<size_t>((kTcStages * nin + kTcRing) * kTileBytes + 2 * kTcD * 128 + 1024);
 }
 
 }  // namespace cott

@@ -82,7 +82,7 @@ int launch_bwd_dkdv(const void* q, const void* k, const void* v, const float* nc
   auto kern = causal_bwd_kv_kernel<T>;
   const size_t smem = causal_bwd_kv_smem_bytes();
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<(unsigned)BH, kTcThreads, smem, stream>>>(mq, mk, mv, md, mdk, mdv, dnorm, nc, H, N);
+  kern<<<(unsigned)BH, kKvThreads, smem, stream>>>(mq, mk, mv, md, mdk, mdv, dnorm, nc, H, N);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
