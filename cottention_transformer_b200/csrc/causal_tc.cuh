@@ -492,6 +492,33 @@ __device__ __forceinline__ void row_from_acc(unsigned char* tile, int row, uint3
     *p1 = w;
   }
 }
+// One pass that does both: returns (tile row) . (64 fp32 accumulator columns) and replaces the tile row by
+// beta * (those columns).  The accumulator is read once, so it can be handed back sooner.
+template <typename T>
+__device__ __forceinline__ float row_from_acc_dot(unsigned char* tile, int row, uint32_t taddr_lane, float beta) {
+  float s = 0.f;
+#pragma unroll 1
+  for (int blk = 0; blk < 4; ++blk) {
+    uint32_t r[16];
+    ptx::tmem_ld_x16(taddr_lane + 16 * blk, r);
+    uint4* p0 = tile_piece(tile, row, 2 * blk);
+    uint4* p1 = tile_piece(tile, row, 2 * blk + 1);
+    uint4 u = *p0, w = *p1;
+    ptx::tmem_ld_wait();
+    s += dot16<T>(r, u, w);
+    u.x = Pack2<T>::pack(beta * __uint_as_float(r[0]), beta * __uint_as_float(r[1]));
+    u.y = Pack2<T>::pack(beta * __uint_as_float(r[2]), beta * __uint_as_float(r[3]));
+    u.z = Pack2<T>::pack(beta * __uint_as_float(r[4]), beta * __uint_as_float(r[5]));
+    u.w = Pack2<T>::pack(beta * __uint_as_float(r[6]), beta * __uint_as_float(r[7]));
+    w.x = Pack2<T>::pack(beta * __uint_as_float(r[8]), beta * __uint_as_float(r[9]));
+    w.y = Pack2<T>::pack(beta * __uint_as_float(r[10]), beta * __uint_as_float(r[11]));
+    w.z = Pack2<T>::pack(beta * __uint_as_float(r[12]), beta * __uint_as_float(r[13]));
+    w.w = Pack2<T>::pack(beta * __uint_as_float(r[14]), beta * __uint_as_float(r[15]));
+    *p0 = u;
+    *p1 = w;
+  }
+  return s;
+}
 // tile row *= w, in place (see scale_row for the arithmetic)
 template <typename T>
 __device__ __forceinline__ void scale_row_rolled(unsigned char* tile, int row, float w) {
@@ -1194,8 +1221,7 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       if (lane == 0) mbar_arrive(&bar_free_in[s]);  // (warp-converged: follows wait_bar_warp) q, dO tiles are free
       const float c1 = rk * a;
       // dv = a dv' = c1 raw;  eps = v' . dv' = c1 (v . raw)
-      const float eps = c1 * row_dot_acc<T>(sV, row, tV + lane_base);
-      row_from_acc<T, false>(sV, row, tV + lane_base, c1, 0.f);
+      const float eps = c1 * row_from_acc_dot<T>(sV, row, tV + lane_base, c1);
       // dk = rk (dk^ - k^ (k^ . dk^)) with dk^ = a raw, k^ . dk^ = v' . dv' = eps and k^ = rk k
       row_from_acc<T, true>(sK, row, tK + lane_base, c1, -rk * rk * eps);
       tc_fence_before_sync();
