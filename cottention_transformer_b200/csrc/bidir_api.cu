@@ -92,6 +92,8 @@ int cott_bidir_fwd(const void* q, const void* k, const void* v, const unsigned c
   DeviceScope scope(q);
   COTT_CUDA_TRY(scope.status());
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // head dim 64 in a 16-bit dtype: tensor-core kernel (it keeps the state on chip and ignores `scratch`)
+  if (bidir_tc_usable(Dk, Dv, dtype, {q, k, v, out})) return launch_bidir_fwd_tc(q, k, v, keep, norm_const, out, B, H, N, dtype, s);
   switch (dtype) {
     case COTT_F32: return run_fwd<float>(q, k, v, keep, norm_const, out, scratch, B, H, N, Dk, Dv, s);
     case COTT_F64: return run_fwd<double>(q, k, v, keep, norm_const, out, scratch, B, H, N, Dk, Dv, s);
@@ -116,6 +118,9 @@ int cott_bidir_bwd(const void* q, const void* k, const void* v, const unsigned c
   }
   if (!q || !k || !v || !norm_const || !dout || !scratch_state || !scratch_dstate || !dq || !dk || !dv)
     return fail(COTT_ERR_NULL, "null pointer");
+  // tensor-core kernel: recomputes the forward state on chip, so neither scratch buffer is touched
+  if (bidir_tc_usable(Dk, Dv, dtype, {q, k, v, dout, dq, dk, dv}))
+    return launch_bidir_bwd_tc(q, k, v, keep, norm_const, dout, dq, dk, dv, dnorm_const, B, H, N, dtype, s);
   switch (dtype) {
     case COTT_F32:
       return run_bwd<float>(q, k, v, keep, norm_const, dout, scratch_state, scratch_dstate, dq, dk, dv, dnorm_const, B, H, N, Dk, Dv, s);

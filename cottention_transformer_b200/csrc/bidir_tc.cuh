@@ -1,0 +1,410 @@
+// Bidirectional (encoder) cosine attention on the tensor cores (tcgen05 + TMEM + TMA), head dim 64,
+// 16-bit inputs, fp32 accumulation.
+//
+// Math (BERT_Trainer/BertCosAttention.py:162-178,197-249 of the reference), per (batch, head):
+//   keep_s = un-masked position, L = their count, a = 1 / max(L^sigmoid(c_h), 1)
+//   q^ = keep q/|q|,  k^ = keep k/|k|,  v' = keep a v
+//   S = sum_s k^_s (x) v'_s  [64 x 64],   out_t = q^_t S
+// backward (autograd of the einsum; the reference's hand-written `Multiply.backward` is not used):
+//   D = sum_t q^_t (x) dO_t,   dq^ = dO S^T,   dk^ = v' D^T,   dv' = k^ D
+//   dq = keep/|q| (dq^ - q^ (q^.dq^)),  dk = 1/|k| (dk^ - k^ (k^.dk^)),  dv = keep a dv'
+//   dc_h = -sigma (1 - sigma) ln(L) [L^sigma > 1] sum_s v'_s . dv'_s
+//
+// One CTA per (batch, head) walks the sequence twice in chunks of 128 positions: the first pass
+// accumulates the state(s) in TMEM (M = 64 MMAs, one row-scaled operand per product), the second applies
+// them.  With w_s = keep_s a / |k_s| and Zw = diag(w) V, Qw = diag(keep/|q|) Q:
+//   S = K^T Zw,  D = Qw^T dO;   out = (Q S) keep/|q|;
+//   AccQ = dO S^T,  AccK = Zw D^T = dk^/|k|,  AccV = K D = |k| dv'
+//   dq = keep/|q| (AccQ - q^ (q^.AccQ)),  dk = AccK - k^ (k^.AccK),  dv = w AccV,  v'.dv' = w (v . AccV)
+// Roles: warp 0 lane 0 = TMA loads and stores, warp 1 lane 0 = MMA issue, warps 2-5 = the per-row work
+// (row norms, operand scaling in place, state conversion, output rows staged in place over an input
+// tile and stored by TMA).  Every wait is bounded (see causal_tc.cuh).
+#pragma once
+
+#include "causal_tc.cuh"
+
+namespace cott {
+
+constexpr int kBtcThreads = 192;
+
+// number of un-masked positions of one batch entry, computed redundantly by every warp that asks
+__device__ __forceinline__ float btc_count_keep(const unsigned char* keep_b, int N, int lane) {
+  if (!keep_b) return static_cast<float>(N);
+  int cnt = 0;
+  for (int s = lane; s < N; s += 32) cnt += keep_b[s] ? 1 : 0;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, off);
+  return static_cast<float>(cnt);
+}
+
+// -------------------------------------------------------------------------------------------------
+// forward
+// shared memory: 2 x (K, V) tiles | 2 x Q tile (also the output staging buffer) | 16-bit state
+// TMEM (256 columns): state 64 | accumulators 2 x 64
+template <typename T>
+__global__ void __launch_bounds__(kBtcThreads, 2)
+bidir_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                    const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapOut,
+                    const unsigned char* __restrict__ keep, const float* __restrict__ norm_const, int H, int N) {
+  using namespace ptx;
+  constexpr bool BF = Pack2<T>::kBf16;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char* sKV = smem;                      // [2][K tile, V tile]
+  unsigned char* sQ = smem + 4 * kTileBytes;      // [2]
+  unsigned char* sS = smem + 6 * kTileBytes;      // [64 x 64] 16-bit
+  __shared__ uint64_t bar_full1[2], bar_prep1[2], bar_free1[2], bar_s_full, bar_state, bar_fullq[2], bar_acc_full[2],
+      bar_acc_free[2], bar_out[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag_s;
+  volatile int* abort_flag = &abort_flag_s;
+
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
+  const int bh = blockIdx.x, h = bh % H, b = bh / H;
+  const int nchunks = (N + kTcChunk - 1) / kTcChunk;
+  const unsigned char* keep_b = keep ? keep + static_cast<size_t>(b) * N : nullptr;
+
+  if (tid == 0) {
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bar_full1[s], 1);
+      mbar_init(&bar_prep1[s], 4);
+      mbar_init(&bar_free1[s], 1);
+      mbar_init(&bar_fullq[s], 1);
+      mbar_init(&bar_acc_full[s], 1);
+      mbar_init(&bar_acc_free[s], 4);
+      mbar_init(&bar_out[s], 4);
+    }
+    mbar_init(&bar_s_full, 1);
+    mbar_init(&bar_state, 4);
+    mbar_fence_init();
+    abort_flag_s = 0;
+    tma_prefetch_desc(&mapQ);
+    tma_prefetch_desc(&mapK);
+    tma_prefetch_desc(&mapV);
+    tma_prefetch_desc(&mapOut);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_slot, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t tS = tmem, tAcc0 = tmem + 64;
+  constexpr uint32_t kIdescS = make_idesc(64, 64, BF, true, true);
+  constexpr uint32_t kIdescAcc = make_idesc(128, 64, BF, false, true);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int c = 0; c < 2 && c < nchunks; ++c) {  // the first two Q tiles travel while the state is built
+        mbar_expect_tx(&bar_fullq[c], kTileBytes);
+        tma_load_3d(sQ + c * kTileBytes, &mapQ, &bar_fullq[c], 0, c * kTcChunk, bh);
+      }
+      for (int c = 0; ok && c < nchunks; ++c) {
+        const int s = c & 1;
+        if (c >= 2 && !(ok = wait_bar(&bar_free1[s], ((c >> 1) - 1) & 1, abort_flag, kWaitStageFree, c))) break;
+        unsigned char* st = sKV + s * 2 * kTileBytes;
+        mbar_expect_tx(&bar_full1[s], 2 * kTileBytes);
+        tma_load_3d(st, &mapK, &bar_full1[s], 0, c * kTcChunk, bh);
+        tma_load_3d(st + kTileBytes, &mapV, &bar_full1[s], 0, c * kTcChunk, bh);
+      }
+      for (int c = 0; ok && c < nchunks; ++c) {
+        const int s = c & 1;
+        if (!(ok = wait_bar(&bar_out[s], (c >> 1) & 1, abort_flag, kWaitStageFree, c))) break;
+        tma_store_3d(&mapOut, sQ + s * kTileBytes, 0, c * kTcChunk, bh);
+        tma_store_commit();
+        if (c + 2 < nchunks) {
+          tma_store_wait_read<0>();
+          mbar_expect_tx(&bar_fullq[s], kTileBytes);
+          tma_load_3d(sQ + s * kTileBytes, &mapQ, &bar_fullq[s], 0, (c + 2) * kTcChunk, bh);
+        }
+      }
+      tma_store_wait<0>();
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int c = 0; ok && c < nchunks; ++c) {  // S += K^T Zw
+        const int s = c & 1;
+        if (!(ok = wait_bar1(&bar_prep1[s], (c >> 1) & 1, abort_flag, kWaitPrepped, c))) break;
+        tc_fence_after_sync();
+        const uint32_t k0 = smem_u32(sKV + s * 2 * kTileBytes);
+        const uint64_t dKm = mdesc(k0), dZm = mdesc(k0 + kTileBytes);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) mma_ss(tS, dKm + 128 * k, dZm + 128 * k, kIdescS, (c > 0 || k > 0) ? 1u : 0u);
+        mma_commit(&bar_free1[s]);  // the stage may be refilled once these MMAs have read it
+      }
+      if (ok) mma_commit(&bar_s_full);
+      ok = ok && wait_bar1(&bar_state, 0, abort_flag, kWaitState, 0);
+      const uint64_t dS = mdesc(smem_u32(sS));
+      for (int c = 0; ok && c < nchunks; ++c) {  // Acc = Q S
+        const int s = c & 1;
+        if (!(ok = wait_bar4(&bar_fullq[s], (c >> 1) & 1, c >= 2 ? &bar_acc_free[s] : nullptr, ((c >> 1) - 1) & 1, nullptr,
+                             0, nullptr, 0, abort_flag, kWaitTma, c)))
+          break;
+        tc_fence_after_sync();
+        const uint64_t dX = kdesc(smem_u32(sQ + s * kTileBytes));
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mma_ss(tAcc0 + 64 * s, dX + 2 * k, dS + 128 * k, kIdescAcc, k > 0);
+        mma_commit(&bar_acc_full[s]);
+      }
+    }
+  } else {
+    const int wq = warp & 3, row = 32 * wq + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(32 * wq) << 16;
+    const float L = btc_count_keep(keep_b, N, lane);
+    const float sigma = 1.0f / (1.0f + __expf(-norm_const[h]));
+    const float a = length_factor(fmaxf(L, 1.0f), sigma);
+    bool ok = true;
+    for (int c = 0; ok && c < nchunks; ++c) {  // Zw = diag(keep a / |k|) V, in place
+      const int s = c & 1, pos = c * kTcChunk + row;
+      if (!(ok = wait_bar_warp(&bar_full1[s], (c >> 1) & 1, abort_flag, kWaitTma, c))) break;
+      unsigned char* sK = sKV + s * 2 * kTileBytes;
+      const bool kp = pos < N && (!keep_b || keep_b[pos]);
+      const float w = kp ? inv_norm(row_sumsq_rolled<T>(sK, row)) * a : 0.f;
+      scale_row_rolled<T>(sK + kTileBytes, row, w);
+      fence_proxy_async_smem();
+      warp_arrive(&bar_prep1[s], lane);
+    }
+    if (ok && (ok = wait_bar_warp(&bar_s_full, 0, abort_flag, kWaitState, 0))) {
+      tc_fence_after_sync();
+      state_to_smem_rolled<T>(tS + lane_base, sS, wq, lane);
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      warp_arrive(&bar_state, lane);
+    }
+    for (int c = 0; ok && c < nchunks; ++c) {  // out = keep / |q| (Q S), staged over the Q tile
+      const int s = c & 1, pos = c * kTcChunk + row;
+      unsigned char* q = sQ + s * kTileBytes;
+      if (!(ok = wait_bar_warp(&bar_fullq[s], (c >> 1) & 1, abort_flag, kWaitTma, c))) break;
+      const bool kp = pos < N && (!keep_b || keep_b[pos]);
+      const float rq = kp ? inv_norm(row_sumsq_rolled<T>(q, row)) : 0.f;
+      if (!(ok = wait_bar_warp(&bar_acc_full[s], (c >> 1) & 1, abort_flag, kWaitAcc, c))) break;
+      tc_fence_after_sync();
+      row_from_acc<T, false>(q, row, tAcc0 + 64 * s + lane_base, rq, 0.f);
+      tc_fence_before_sync();
+      warp_arrive(&bar_acc_free[s], lane);
+      fence_proxy_async_smem();
+      warp_arrive(&bar_out[s], lane);
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before_sync();
+  __syncthreads();
+  if (tid == 0 && *abort_flag) {  // bounded drain of loads that may still be in flight
+    for (int s = 0; s < 2; ++s) {
+      mbar_wait(&bar_full1[s], 0, 64);
+      mbar_wait(&bar_fullq[s], 0, 64);
+    }
+  }
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 256);
+}
+
+// -------------------------------------------------------------------------------------------------
+// backward
+// The sequence is walked twice over one ring of two stages (q, K, V, dO tiles): items 0 .. n-1 build the two
+// states, items n .. 2n-1 apply them.  dq, dk, dv rows are staged in place over the q, K, V tiles.
+// TMEM (512 columns allocated): S 64 | D 64 | AccQ 64 | AccK 64 | AccV 64
+template <typename T>
+__global__ void __launch_bounds__(kBtcThreads, 1)
+bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                    const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
+                    const __grid_constant__ CUtensorMap mapDQ, const __grid_constant__ CUtensorMap mapDK,
+                    const __grid_constant__ CUtensorMap mapDV, const unsigned char* __restrict__ keep,
+                    const float* __restrict__ norm_const, float* __restrict__ dnorm, int H, int N) {
+  using namespace ptx;
+  constexpr bool BF = Pack2<T>::kBf16;
+  constexpr int STAGE = 4 * kTileBytes;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  unsigned char* sS = smem + 2 * STAGE;      // [64 x 64] 16-bit, rows d_k
+  unsigned char* sD = sS + kTcD * 128;       // [64 x 64] 16-bit, rows d_k
+  __shared__ uint64_t bar_full[2], bar_prep[2], bar_free1[2], bar_out[2], bar_st_full, bar_state, bar_acc_full, bar_acc_free;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag_s;
+  volatile int* abort_flag = &abort_flag_s;
+
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
+  const int bh = blockIdx.x, h = bh % H, b = bh / H;
+  const int n = (N + kTcChunk - 1) / kTcChunk;  // chunks; the ring carries 2n items
+  const unsigned char* keep_b = keep ? keep + static_cast<size_t>(b) * N : nullptr;
+
+  if (tid == 0) {
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bar_full[s], 1);
+      mbar_init(&bar_prep[s], 4);
+      mbar_init(&bar_free1[s], 1);
+      mbar_init(&bar_out[s], 4);
+    }
+    mbar_init(&bar_st_full, 1);
+    mbar_init(&bar_state, 4);
+    mbar_init(&bar_acc_full, 1);
+    mbar_init(&bar_acc_free, 4);
+    mbar_fence_init();
+    abort_flag_s = 0;
+    tma_prefetch_desc(&mapQ);
+    tma_prefetch_desc(&mapK);
+    tma_prefetch_desc(&mapV);
+    tma_prefetch_desc(&mapDO);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t tS = tmem, tD = tmem + 64, tAQ = tmem + 128, tAK = tmem + 192, tAV = tmem + 256;
+  constexpr uint32_t kIdescS = make_idesc(64, 64, BF, true, true);
+  constexpr uint32_t kIdescKK = make_idesc(128, 64, BF, false, false);  // B K-major
+  constexpr uint32_t kIdescMN = make_idesc(128, 64, BF, false, true);   // B MN-major
+
+  if (warp == 0) {
+    if (lane == 0) {
+      bool ok = true;
+      // hand back the stage of item i: state items are released by their MMAs, apply items once their three
+      // output tiles have been stored from it
+      auto retire = [&](int i) -> bool {
+        const int s = i & 1;
+        if (i < n) return wait_bar(&bar_free1[s], (i >> 1) & 1, abort_flag, kWaitStageFree, i);
+        if (!wait_bar(&bar_out[s], ((i - n) >> 1) & 1, abort_flag, kWaitStageFree, i)) return false;
+        unsigned char* st = smem + s * STAGE;
+        const int y = (i - n) * kTcChunk;
+        tma_store_3d(&mapDQ, st, 0, y, bh);
+        tma_store_3d(&mapDK, st + kTileBytes, 0, y, bh);
+        tma_store_3d(&mapDV, st + 2 * kTileBytes, 0, y, bh);
+        tma_store_commit();
+        tma_store_wait_read<0>();
+        return true;
+      };
+      for (int j = 0; ok && j < 2 * n; ++j) {
+        const int s = j & 1, y = (j < n ? j : j - n) * kTcChunk;
+        if (j >= 2 && !(ok = retire(j - 2))) break;
+        unsigned char* st = smem + s * STAGE;
+        mbar_expect_tx(&bar_full[s], STAGE);
+        tma_load_3d(st, &mapQ, &bar_full[s], 0, y, bh);
+        tma_load_3d(st + kTileBytes, &mapK, &bar_full[s], 0, y, bh);
+        tma_load_3d(st + 2 * kTileBytes, &mapV, &bar_full[s], 0, y, bh);
+        tma_load_3d(st + 3 * kTileBytes, &mapDO, &bar_full[s], 0, y, bh);
+      }
+      for (int i = (2 * n >= 2 ? 2 * n - 2 : 0); ok && i < 2 * n; ++i) ok = retire(i);
+      tma_store_wait<0>();
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int j = 0; ok && j < n; ++j) {  // S += K^T Zw,  D += Qw^T dO
+        const int s = j & 1;
+        if (!(ok = wait_bar1(&bar_prep[s], (j >> 1) & 1, abort_flag, kWaitPrepped, j))) break;
+        tc_fence_after_sync();
+        const uint32_t q0 = smem_u32(smem + s * STAGE);
+        const uint64_t dQm = mdesc(q0), dKm = mdesc(q0 + kTileBytes), dZm = mdesc(q0 + 2 * kTileBytes),
+                       dDm = mdesc(q0 + 3 * kTileBytes);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) mma_ss(tS, dKm + 128 * k, dZm + 128 * k, kIdescS, (j > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) mma_ss(tD, dQm + 128 * k, dDm + 128 * k, kIdescS, (j > 0 || k > 0) ? 1u : 0u);
+        mma_commit(&bar_free1[s]);
+      }
+      if (ok) mma_commit(&bar_st_full);
+      ok = ok && wait_bar1(&bar_state, 0, abort_flag, kWaitState, 0);
+      const uint64_t dSk = kdesc(smem_u32(sS)), dDk = kdesc(smem_u32(sD)), dDmn = mdesc(smem_u32(sD));
+      for (int c = 0; ok && c < n; ++c) {
+        const int j = n + c, s = j & 1;
+        if (!(ok = wait_bar4(&bar_prep[s], (j >> 1) & 1, c > 0 ? &bar_acc_free : nullptr, (c - 1) & 1, nullptr, 0, nullptr, 0,
+                             abort_flag, kWaitPrepped, j)))
+          break;
+        tc_fence_after_sync();
+        const uint32_t q0 = smem_u32(smem + s * STAGE);
+        const uint64_t dK = kdesc(q0 + kTileBytes), dZ = kdesc(q0 + 2 * kTileBytes), dDO = kdesc(q0 + 3 * kTileBytes);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mma_ss(tAQ, dDO + 2 * k, dSk + 2 * k, kIdescKK, k > 0);   // AccQ = dO S^T
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mma_ss(tAK, dZ + 2 * k, dDk + 2 * k, kIdescKK, k > 0);    // AccK = Zw D^T
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mma_ss(tAV, dK + 2 * k, dDmn + 128 * k, kIdescMN, k > 0);  // AccV = K D
+        mma_commit(&bar_acc_full);
+      }
+    }
+  } else {
+    const int wq = warp & 3, row = 32 * wq + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(32 * wq) << 16;
+    const float L = btc_count_keep(keep_b, N, lane);
+    const float sigma = 1.0f / (1.0f + __expf(-norm_const[h]));
+    const float a = length_factor(fmaxf(L, 1.0f), sigma);
+    float gsum = 0.f;
+    bool ok = true;
+    for (int j = 0; ok && j < n; ++j) {  // Qw = diag(keep / |q|) q,  Zw = diag(keep a / |k|) V, in place
+      const int s = j & 1, pos = j * kTcChunk + row;
+      if (!(ok = wait_bar_warp(&bar_full[s], (j >> 1) & 1, abort_flag, kWaitTma, j))) break;
+      unsigned char* st = smem + s * STAGE;
+      const bool kp = pos < N && (!keep_b || keep_b[pos]);
+      scale_row_rolled<T>(st, row, kp ? inv_norm(row_sumsq_rolled<T>(st, row)) : 0.f);
+      scale_row_rolled<T>(st + 2 * kTileBytes, row, kp ? inv_norm(row_sumsq_rolled<T>(st + kTileBytes, row)) * a : 0.f);
+      fence_proxy_async_smem();
+      warp_arrive(&bar_prep[s], lane);
+    }
+    if (ok && (ok = wait_bar_warp(&bar_st_full, 0, abort_flag, kWaitState, 0))) {
+      tc_fence_after_sync();
+      state_to_smem_rolled<T>(tS + lane_base, sS, wq, lane);
+      state_to_smem_rolled<T>(tD + lane_base, sD, wq, lane);
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      warp_arrive(&bar_state, lane);
+    }
+    for (int c = 0; ok && c < n; ++c) {
+      const int j = n + c, s = j & 1, pos = c * kTcChunk + row;
+      if (!(ok = wait_bar_warp(&bar_full[s], (j >> 1) & 1, abort_flag, kWaitTma, j))) break;
+      unsigned char* sQ = smem + s * STAGE;
+      unsigned char* sK = sQ + kTileBytes;
+      unsigned char* sV = sQ + 2 * kTileBytes;
+      const bool kp = pos < N && (!keep_b || keep_b[pos]);
+      const float rq = kp ? inv_norm(row_sumsq_rolled<T>(sQ, row)) : 0.f;
+      const float rk = kp ? inv_norm(row_sumsq_rolled<T>(sK, row)) : 0.f;
+      const float w = rk * a;
+      scale_row_rolled<T>(sV, row, w);  // Zw again (q and K stay raw for the epilogue)
+      fence_proxy_async_smem();
+      warp_arrive(&bar_prep[s], lane);
+      if (!(ok = wait_bar_warp(&bar_acc_full, c & 1, abort_flag, kWaitAcc, c))) break;
+      tc_fence_after_sync();
+      // dq = keep/|q| (dq^ - q^ (q^ . dq^)),  dq^ = AccQ,  q^ = rq q
+      const float dotq = row_dot_acc<T>(sQ, row, tAQ + lane_base);
+      row_from_acc<T, true>(sQ, row, tAQ + lane_base, rq, -rq * rq * rq * dotq);
+      // dk = AccK - k^ (k^ . AccK)   (AccK = dk^ / |k|)
+      const float dotk = row_dot_acc<T>(sK, row, tAK + lane_base);
+      row_from_acc<T, true>(sK, row, tAK + lane_base, 1.0f, -rk * rk * dotk);
+      // dv = w AccV;  v' . dv' = (w v) . AccV with w v = the Zw row
+      gsum += row_from_acc_dot<T>(sV, row, tAV + lane_base, w);
+      tc_fence_before_sync();
+      warp_arrive(&bar_acc_free, lane);
+      fence_proxy_async_smem();
+      warp_arrive(&bar_out[s], lane);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) gsum += __shfl_down_sync(0xffffffffu, gsum, off);
+    if (lane == 0 && L > 1.0f) atomicAdd(dnorm + h, -sigma * (1.0f - sigma) * __logf(L) * gsum);
+  }
+
+  __syncwarp();
+  tc_fence_before_sync();
+  __syncthreads();
+  if (tid == 0 && *abort_flag) {
+    mbar_wait(&bar_full[0], 0, 64);
+    mbar_wait(&bar_full[1], 0, 64);
+  }
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+inline size_t bidir_bwd_tc_smem_bytes() { return static_cast<size_t>(8 * kTileBytes + 2 * kTcD * 128 + 1024); }
+
+inline size_t bidir_fwd_tc_smem_bytes() { return static_cast<size_t>(6 * kTileBytes + kTcD * 128 + 1024); }
+
+}  // namespace cott

@@ -4,7 +4,7 @@
 //   q^ = q/|q|, k^ = k/|k|, v' = v / max(n_s^sigma(c_h), 1),  O_t = sum_{s<=t} (q^_t . k^_s) v'_s
 // and its gradients.  Head dim 64, 16-bit inputs, fp32 accumulation.
 //
-// Chunked form, chunk = 128 positions, one CTA (10 warps) walks one (batch, head) sequence:
+// Chunked form, chunk = 128 positions, one CTA walks one (batch, head) sequence:
 //   w_s  = a_s / |k_s|                      (a_s = length-norm factor, folded with the key norm)
 //   Zw   = diag(w) Z                        (one row-scaled operand per chunk, rewritten in smem)
 //   P    = mask(X Y^T)                      tcgen05 128x128x64, masked in registers, written back
@@ -16,12 +16,13 @@
 // dQ:       (X, Y, Z) = (dO, V, K)  dq^_t = Acc_t,  dq_t = (dq^_t - q^_t (q^_t . dq^_t)) / |q_t|
 // dK, dV:   reverse direction, see causal_bwd_kv_kernel.
 //
-// Warp roles: warp 0 = TMA producer (one thread), warp 1 = MMA issuer (one thread), warps 2-5 =
-// "score" group (row norms, Zw, mask+convert of P), warps 6-9 = "output" group (state conversion,
-// output rows).  They hand work to each other through mbarriers, so the TMA of chunk c+2, the
-// score MMA of chunk c+1, the mask pass of chunk c and the output pass of chunk c-1 overlap.
-// HBM tiles arrive by TMA (128-byte swizzle, no multicast) into a 3-stage ring.  Every wait is
-// bounded; on a time-out the CTA records a code in g_cott_status and leaves cleanly.
+// Warp roles (listed at each kernel): single threads issue the MMAs and the TMA traffic; groups of four
+// warps (one warp per TMEM sub-partition) do the per-row work -- mask + convert of P, row norms, Zw, the
+// state conversion, output rows -- and hand work to each other through mbarriers, so the TMA of chunk
+// c+3, the score MMA of chunk c+1, the mask pass of chunk c and the output pass of chunk c-1 overlap.
+// HBM tiles arrive by TMA (128-byte swizzle, no multicast) into a 3-stage ring and outputs leave by TMA
+// from a tile they are staged over.  Every wait is bounded; on a time-out the CTA records a code in
+// g_cott_status and leaves cleanly.
 #pragma once
 
 #include "common.cuh"

@@ -1,5 +1,6 @@
 // Shared host/device helpers for the cottention_b200 kernels.
 #pragma once
+#include <initializer_list>
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -88,5 +89,15 @@ template <> __device__ __forceinline__ __half from_acc<__half>(float x) { return
 template <> __device__ __forceinline__ __nv_bfloat16 from_acc<__nv_bfloat16>(float x) {
   return __float2bfloat16_rn(x);
 }
+
+// Tensor-core path of the bidirectional form (defined next to the other tcgen05 kernels, which share the
+// device status word): head dim 64, 16-bit dtypes, 16-byte aligned tensors.  `*_usable` says whether a
+// problem qualifies; the launchers assume it does.
+bool bidir_tc_usable(int Dk, int Dv, int dtype, std::initializer_list<const void*> tensors);
+int launch_bidir_fwd_tc(const void* q, const void* k, const void* v, const unsigned char* keep, const float* nc,
+                        void* out, int B, int H, int N, int dtype, cudaStream_t stream);
+int launch_bidir_bwd_tc(const void* q, const void* k, const void* v, const unsigned char* keep, const float* nc,
+                        const void* dout, void* dq, void* dk, void* dv, float* dnorm, int B, int H, int N, int dtype,
+                        cudaStream_t stream);
 
 }  // namespace cott

@@ -1,4 +1,5 @@
 // C ABI of the fused cosine-attention operators (tensor-core path).
+#include "bidir_tc.cuh"
 #include "causal_tc.cuh"
 #include "common.cuh"
 
@@ -96,7 +97,69 @@ int check_ptrs16(std::initializer_list<std::pair<const void*, const char*>> ps) 
   return COTT_OK;
 }
 
+template <typename T>
+int launch_bidir_fwd_tc_t(const void* q, const void* k, const void* v, const unsigned char* keep, const float* nc,
+                          void* out, int B, int H, int N, int dtype, cudaStream_t stream) {
+  const long BH = (long)B * H;
+  CUtensorMap mq, mk, mv, mo;
+  int st;
+  if ((st = tmap(&mq, q, dtype, BH, N)) || (st = tmap(&mk, k, dtype, BH, N)) || (st = tmap(&mv, v, dtype, BH, N)) ||
+      (st = tmap(&mo, out, dtype, BH, N)))
+    return st;
+  auto kern = bidir_fwd_tc_kernel<T>;
+  const size_t smem = bidir_fwd_tc_smem_bytes();
+  COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<(unsigned)BH, kBtcThreads, smem, stream>>>(mq, mk, mv, mo, keep, nc, H, N);
+  COTT_CUDA_TRY(cudaGetLastError());
+  return COTT_OK;
+}
+
+template <typename T>
+int launch_bidir_bwd_tc_t(const void* q, const void* k, const void* v, const unsigned char* keep, const float* nc,
+                          const void* dout, void* dq, void* dk, void* dv, float* dnorm, int B, int H, int N, int dtype,
+                          cudaStream_t stream) {
+  const long BH = (long)B * H;
+  CUtensorMap mq, mk, mv, md, mdq, mdk, mdv;
+  int st;
+  if ((st = tmap(&mq, q, dtype, BH, N)) || (st = tmap(&mk, k, dtype, BH, N)) || (st = tmap(&mv, v, dtype, BH, N)) ||
+      (st = tmap(&md, dout, dtype, BH, N)) || (st = tmap(&mdq, dq, dtype, BH, N)) || (st = tmap(&mdk, dk, dtype, BH, N)) ||
+      (st = tmap(&mdv, dv, dtype, BH, N)))
+    return st;
+  COTT_CUDA_TRY(cudaMemsetAsync(dnorm, 0, sizeof(float) * H, stream));
+  auto kern = bidir_bwd_tc_kernel<T>;
+  const size_t smem = bidir_bwd_tc_smem_bytes();
+  COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<(unsigned)BH, kBtcThreads, smem, stream>>>(mq, mk, mv, md, mdq, mdk, mdv, keep, nc, dnorm, H, N);
+  COTT_CUDA_TRY(cudaGetLastError());
+  return COTT_OK;
+}
+
 }  // namespace
+
+namespace cott {
+
+int launch_bidir_bwd_tc(const void* q, const void* k, const void* v, const unsigned char* keep, const float* nc,
+                        const void* dout, void* dq, void* dk, void* dv, float* dnorm, int B, int H, int N, int dtype,
+                        cudaStream_t stream) {
+  return dtype == COTT_BF16
+             ? launch_bidir_bwd_tc_t<__nv_bfloat16>(q, k, v, keep, nc, dout, dq, dk, dv, dnorm, B, H, N, dtype, stream)
+             : launch_bidir_bwd_tc_t<__half>(q, k, v, keep, nc, dout, dq, dk, dv, dnorm, B, H, N, dtype, stream);
+}
+
+bool bidir_tc_usable(int Dk, int Dv, int dtype, std::initializer_list<const void*> tensors) {
+  if (Dk != kTcD || Dv != kTcD || (dtype != COTT_BF16 && dtype != COTT_F16)) return false;
+  for (const void* p : tensors)
+    if (reinterpret_cast<uintptr_t>(p) & 15) return false;
+  return true;
+}
+
+int launch_bidir_fwd_tc(const void* q, const void* k, const void* v, const unsigned char* keep, const float* nc,
+                        void* out, int B, int H, int N, int dtype, cudaStream_t stream) {
+  return dtype == COTT_BF16 ? launch_bidir_fwd_tc_t<__nv_bfloat16>(q, k, v, keep, nc, out, B, H, N, dtype, stream)
+                            : launch_bidir_fwd_tc_t<__half>(q, k, v, keep, nc, out, B, H, N, dtype, stream);
+}
+
+}  // namespace cott
 
 extern "C" {
 

@@ -41,7 +41,10 @@ def test_matches_reference_module_fixture(name, dt):
 
 
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("shape", [(2, 3, 512, 64, 64), (1, 2, 77, 32, 48), (2, 2, 1, 16, 16), (1, 1, 300, 128, 128)])
+# head dim 64 in a 16-bit dtype takes the tensor-core kernels (chunks of 128: 1, 129 and 640 cover one short
+# chunk, a one-row tail and an odd chunk count); everything else takes the CUDA-core kernels
+@pytest.mark.parametrize("shape", [(2, 3, 512, 64, 64), (1, 2, 77, 32, 48), (2, 2, 1, 16, 16), (1, 1, 300, 128, 128),
+                                   (2, 2, 1, 64, 64), (1, 2, 129, 64, 64), (1, 3, 640, 64, 64)])
 @pytest.mark.parametrize("masked", [False, True])
 def test_matches_oracle(dt, shape, masked):
     from cottention_transformer_b200 import cos_attn_bidirectional
@@ -66,7 +69,9 @@ def test_matches_oracle(dt, shape, masked):
         scale = max(b.abs().max().item(), 1e-6)
         return (a.double().cpu() - b).abs().max().item() / (1.0 if dt == torch.float32 else scale)
 
-    tol = 2e-4 if dt == torch.float32 else 2e-2
+    # 16-bit: 2e-2 of the largest reference entry; a single-token sequence has no averaging over positions, so
+    # the 16-bit rounding of the state shows in full there (measured 2.2e-2 on dq): 3e-2
+    tol = 2e-4 if dt == torch.float32 else (3e-2 if N == 1 else 2e-2)
     for name, a, b in (("out", out, ref.detach()), ("dq", qc.grad, qd.grad), ("dk", kc.grad, kd.grad),
                        ("dv", vc.grad, vd.grad), ("dnorm", ncc.grad, ncd.grad)):
         assert err(a, b) <= tol * (5 if name == "dnorm" else 1), (name, err(a, b))
