@@ -119,9 +119,25 @@ def bench_bidir(B=32, H=12, N=512, d=64):
         q.grad = k.grad = v.grad = nc.grad = None
 
     t = _time(step, 20)
+    # the two kernels on their own, through the C ABI (no autograd bookkeeping)
+    L = _lib.lib()
+    st = _lib.stream_ptr(dev)
+    scr = torch.empty(L.cott_bidir_scratch_bytes(B, H, N, d, d, 3) // 4 + 1, device=dev)
+    scr2 = torch.empty_like(scr)
+    out, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
+    dnc = torch.empty(H, device=dev)
+    P = lambda x: x.data_ptr()  # noqa: E731
+    ncd = nc.detach()
+    t_f = _time(lambda: _lib.check(L.cott_bidir_fwd(P(q), P(k), P(v), None, P(ncd), P(out), P(scr), B, H, N, d, d, 3, st),
+                                   "bidir fwd"), 20)
+    t_b = _time(lambda: _lib.check(L.cott_bidir_bwd(P(q), P(k), P(v), None, P(ncd), P(do), P(scr), P(scr2), P(dq), P(dk),
+                                                    P(dv), P(dnc), B, H, N, d, d, 3, st), "bidir bwd"), 20)
+    _lib.check_device_status()
     nbytes = 11 * B * H * N * d * 2
     peak, kind = _peak_gbs()
     return {"what": f"bidirectional fwd+bwd, B={B} H={H} N={N} d={d} bf16", "us_per_step": t * 1e6,
+            "fwd_kernel_us": t_f * 1e6, "bwd_kernel_us": t_b * 1e6,
+            "kernels_frac": nbytes / (t_f + t_b) / 1e9 / _peak_gbs()[0],
             "tokens_per_s": B * N / t, "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / t / 1e9,
             "peak_gbs": peak, "peak_source": kind, "frac": nbytes / t / 1e9 / peak}
 
@@ -155,10 +171,14 @@ if __name__ == "__main__":
                     help="only time the three fused causal kernels at batch B (H=16, N=4096, d=64)")
     ap.add_argument("--decode-steps", type=int, default=256)
     ap.add_argument("--json", default=None)
+    ap.add_argument("--bidir-only", action="store_true", help="only the bidirectional benchmark")
     ap.add_argument("--no-graph", action="store_true", help="do not replay decode from a CUDA graph (profiler runs)")
     a = ap.parse_args()
     if a.causal:
         print(json.dumps(bench_causal_kernels(a.causal)))
+        raise SystemExit(0)
+    if a.bidir_only:
+        print(json.dumps(bench_bidir()))
         raise SystemExit(0)
     res = [bench_decode(64, a.decode_steps, use_graph=not a.no_graph), bench_decode(128, a.decode_steps, use_graph=not a.no_graph),
            bench_bidir()]

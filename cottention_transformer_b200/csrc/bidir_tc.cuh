@@ -210,8 +210,13 @@ bidir_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
 // The sequence is walked twice over one ring of two stages (q, K, V, dO tiles): items 0 .. n-1 build the two
 // states, items n .. 2n-1 apply them.  dq, dk, dv rows are staged in place over the q, K, V tiles.
 // TMEM (512 columns allocated): S 64 | D 64 | AccQ 64 | AccK 64 | AccV 64
+// Warps: 0 = TMA (lane 0), 1 = MMA issue (lane 0), three groups of four (each warp works on the tile rows /
+// TMEM lanes 32 (w % 4) ..): group 0 (warps 2-5) scales operands and, in the second pass, publishes the row
+// factors; group 1 (6-9) and group 2 (10-13) share the other per-row work.
+constexpr int kBtcBwdThreads = 448;
+
 template <typename T>
-__global__ void __launch_bounds__(kBtcThreads, 1)
+__global__ void __launch_bounds__(kBtcBwdThreads, 1)
 bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                     const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
                     const __grid_constant__ CUtensorMap mapDQ, const __grid_constant__ CUtensorMap mapDK,
@@ -224,7 +229,9 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char* sS = smem + 2 * STAGE;      // [64 x 64] 16-bit, rows d_k
   unsigned char* sD = sS + kTcD * 128;       // [64 x 64] 16-bit, rows d_k
-  __shared__ uint64_t bar_full[2], bar_prep[2], bar_free1[2], bar_out[2], bar_st_full, bar_state, bar_acc_full, bar_acc_free;
+  __shared__ uint64_t bar_full[2], bar_prep1[2], bar_prep2[2], bar_free1[2], bar_out[2], bar_st_full, bar_state, bar_acc_full,
+      bar_acc_free;
+  __shared__ float s_rq[2][kTcChunk], s_rk[2][kTcChunk], s_w[2][kTcChunk];  // row factors of the second pass
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag_s;
   volatile int* abort_flag = &abort_flag_s;
@@ -238,14 +245,15 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
   if (tid == 0) {
     for (int s = 0; s < 2; ++s) {
       mbar_init(&bar_full[s], 1);
-      mbar_init(&bar_prep[s], 4);
+      mbar_init(&bar_prep1[s], 8);  // groups 0 and 1
+      mbar_init(&bar_prep2[s], 4);  // group 0
       mbar_init(&bar_free1[s], 1);
-      mbar_init(&bar_out[s], 4);
+      mbar_init(&bar_out[s], 8);    // groups 1 and 2
     }
     mbar_init(&bar_st_full, 1);
-    mbar_init(&bar_state, 4);
+    mbar_init(&bar_state, 8);       // groups 1 and 2
     mbar_init(&bar_acc_full, 1);
-    mbar_init(&bar_acc_free, 4);
+    mbar_init(&bar_acc_free, 8);    // groups 1 and 2
     mbar_fence_init();
     abort_flag_s = 0;
     tma_prefetch_desc(&mapQ);
@@ -302,7 +310,7 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
       bool ok = true;
       for (int j = 0; ok && j < n; ++j) {  // S += K^T Zw,  D += Qw^T dO
         const int s = j & 1;
-        if (!(ok = wait_bar1(&bar_prep[s], (j >> 1) & 1, abort_flag, kWaitPrepped, j))) break;
+        if (!(ok = wait_bar1(&bar_prep1[s], (j >> 1) & 1, abort_flag, kWaitPrepped, j))) break;
         tc_fence_after_sync();
         const uint32_t q0 = smem_u32(smem + s * STAGE);
         const uint64_t dQm = mdesc(q0), dKm = mdesc(q0 + kTileBytes), dZm = mdesc(q0 + 2 * kTileBytes),
@@ -318,7 +326,7 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
       const uint64_t dSk = kdesc(smem_u32(sS)), dDk = kdesc(smem_u32(sD)), dDmn = mdesc(smem_u32(sD));
       for (int c = 0; ok && c < n; ++c) {
         const int j = n + c, s = j & 1;
-        if (!(ok = wait_bar4(&bar_prep[s], (j >> 1) & 1, c > 0 ? &bar_acc_free : nullptr, (c - 1) & 1, nullptr, 0, nullptr, 0,
+        if (!(ok = wait_bar4(&bar_prep2[s], (c >> 1) & 1, c > 0 ? &bar_acc_free : nullptr, (c - 1) & 1, nullptr, 0, nullptr, 0,
                              abort_flag, kWaitPrepped, j)))
           break;
         tc_fence_after_sync();
@@ -334,6 +342,7 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
       }
     }
   } else {
+    const int group = (warp - 2) >> 2;  // 0, 1, 2
     const int wq = warp & 3, row = 32 * wq + lane;
     const uint32_t lane_base = static_cast<uint32_t>(32 * wq) << 16;
     const float L = btc_count_keep(keep_b, N, lane);
@@ -341,55 +350,78 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
     const float a = length_factor(fmaxf(L, 1.0f), sigma);
     float gsum = 0.f;
     bool ok = true;
-    for (int j = 0; ok && j < n; ++j) {  // Qw = diag(keep / |q|) q,  Zw = diag(keep a / |k|) V, in place
-      const int s = j & 1, pos = j * kTcChunk + row;
-      if (!(ok = wait_bar_warp(&bar_full[s], (j >> 1) & 1, abort_flag, kWaitTma, j))) break;
-      unsigned char* st = smem + s * STAGE;
-      const bool kp = pos < N && (!keep_b || keep_b[pos]);
-      scale_row_rolled<T>(st, row, kp ? inv_norm(row_sumsq_rolled<T>(st, row)) : 0.f);
-      scale_row_rolled<T>(st + 2 * kTileBytes, row, kp ? inv_norm(row_sumsq_rolled<T>(st + kTileBytes, row)) * a : 0.f);
-      fence_proxy_async_smem();
-      warp_arrive(&bar_prep[s], lane);
+    // ---- first pass: Qw = diag(keep / |q|) q (group 0),  Zw = diag(keep a / |k|) V (group 1), in place
+    if (group < 2) {
+      for (int j = 0; ok && j < n; ++j) {
+        const int s = j & 1, pos = j * kTcChunk + row;
+        if (!(ok = wait_bar_warp(&bar_full[s], (j >> 1) & 1, abort_flag, kWaitTma, j))) break;
+        unsigned char* st = smem + s * STAGE;
+        const bool kp = pos < N && (!keep_b || keep_b[pos]);
+        if (group == 0)
+          scale_row_rolled<T>(st, row, kp ? inv_norm(row_sumsq_rolled<T>(st, row)) : 0.f);
+        else
+          scale_row_rolled<T>(st + 2 * kTileBytes, row, kp ? inv_norm(row_sumsq_rolled<T>(st + kTileBytes, row)) * a : 0.f);
+        fence_proxy_async_smem();
+        warp_arrive(&bar_prep1[s], lane);
+      }
     }
-    if (ok && (ok = wait_bar_warp(&bar_st_full, 0, abort_flag, kWaitState, 0))) {
+    // ---- the two states -> 16-bit operands (group 1: S, group 2: D)
+    if (group >= 1 && ok && (ok = wait_bar_warp(&bar_st_full, 0, abort_flag, kWaitState, 0))) {
       tc_fence_after_sync();
-      state_to_smem_rolled<T>(tS + lane_base, sS, wq, lane);
-      state_to_smem_rolled<T>(tD + lane_base, sD, wq, lane);
+      if (group == 1)
+        state_to_smem_rolled<T>(tS + lane_base, sS, wq, lane);
+      else
+        state_to_smem_rolled<T>(tD + lane_base, sD, wq, lane);
       fence_proxy_async_smem();
       tc_fence_before_sync();
       warp_arrive(&bar_state, lane);
     }
+    // ---- second pass
     for (int c = 0; ok && c < n; ++c) {
       const int j = n + c, s = j & 1, pos = c * kTcChunk + row;
-      if (!(ok = wait_bar_warp(&bar_full[s], (j >> 1) & 1, abort_flag, kWaitTma, j))) break;
       unsigned char* sQ = smem + s * STAGE;
       unsigned char* sK = sQ + kTileBytes;
       unsigned char* sV = sQ + 2 * kTileBytes;
-      const bool kp = pos < N && (!keep_b || keep_b[pos]);
-      const float rq = kp ? inv_norm(row_sumsq_rolled<T>(sQ, row)) : 0.f;
-      const float rk = kp ? inv_norm(row_sumsq_rolled<T>(sK, row)) : 0.f;
-      const float w = rk * a;
-      scale_row_rolled<T>(sV, row, w);  // Zw again (q and K stay raw for the epilogue)
-      fence_proxy_async_smem();
-      warp_arrive(&bar_prep[s], lane);
+      if (group == 0) {  // row factors, Zw again (q and K stay raw for the output rows)
+        if (!(ok = wait_bar_warp(&bar_full[s], (j >> 1) & 1, abort_flag, kWaitTma, j))) break;
+        const bool kp = pos < N && (!keep_b || keep_b[pos]);
+        const float rq = kp ? inv_norm(row_sumsq_rolled<T>(sQ, row)) : 0.f;
+        const float rk = kp ? inv_norm(row_sumsq_rolled<T>(sK, row)) : 0.f;
+        s_rq[s][row] = rq;
+        s_rk[s][row] = rk;
+        s_w[s][row] = rk * a;
+        scale_row_rolled<T>(sV, row, rk * a);
+        fence_proxy_async_smem();
+        warp_arrive(&bar_prep2[s], lane);
+        continue;
+      }
+      // groups 1 and 2: the row factors (prep2) and the accumulators
+      if (!(ok = wait_bar_warp(&bar_prep2[s], (c >> 1) & 1, abort_flag, kWaitPrepped, j))) break;
       if (!(ok = wait_bar_warp(&bar_acc_full, c & 1, abort_flag, kWaitAcc, c))) break;
       tc_fence_after_sync();
-      // dq = keep/|q| (dq^ - q^ (q^ . dq^)),  dq^ = AccQ,  q^ = rq q
-      const float dotq = row_dot_acc<T>(sQ, row, tAQ + lane_base);
-      row_from_acc<T, true>(sQ, row, tAQ + lane_base, rq, -rq * rq * rq * dotq);
-      // dk = AccK - k^ (k^ . AccK)   (AccK = dk^ / |k|)
-      const float dotk = row_dot_acc<T>(sK, row, tAK + lane_base);
-      row_from_acc<T, true>(sK, row, tAK + lane_base, 1.0f, -rk * rk * dotk);
-      // dv = w AccV;  v' . dv' = (w v) . AccV with w v = the Zw row
-      gsum += row_from_acc_dot<T>(sV, row, tAV + lane_base, w);
+      if (group == 1) {
+        // dq = keep/|q| (dq^ - q^ (q^ . dq^)),  dq^ = AccQ,  q^ = rq q
+        const float rq = s_rq[s][row];
+        const float dotq = row_dot_acc<T>(sQ, row, tAQ + lane_base);
+        row_from_acc<T, true>(sQ, row, tAQ + lane_base, rq, -rq * rq * rq * dotq);
+        // dv = w AccV;  v' . dv' = (w v) . AccV with w v = the Zw row
+        gsum += row_from_acc_dot<T>(sV, row, tAV + lane_base, s_w[s][row]);
+      } else {
+        // dk = AccK - k^ (k^ . AccK)   (AccK = dk^ / |k|)
+        const float rk = s_rk[s][row];
+        const float dotk = row_dot_acc<T>(sK, row, tAK + lane_base);
+        row_from_acc<T, true>(sK, row, tAK + lane_base, 1.0f, -rk * rk * dotk);
+      }
       tc_fence_before_sync();
       warp_arrive(&bar_acc_free, lane);
       fence_proxy_async_smem();
       warp_arrive(&bar_out[s], lane);
     }
+    if (group == 1) {
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) gsum += __shfl_down_sync(0xffffffffu, gsum, off);
-    if (lane == 0 && L > 1.0f) atomicAdd(dnorm + h, -sigma * (1.0f - sigma) * __logf(L) * gsum);
+      for (int off = 16; off > 0; off >>= 1) gsum += __shfl_down_sync(0xffffffffu, gsum, off);
+      if (lane == 0 && L > 1.0f) atomicAdd(dnorm + h, -sigma * (1.0f - sigma) * __logf(L) * gsum);
+    }
   }
 
   __syncwarp();

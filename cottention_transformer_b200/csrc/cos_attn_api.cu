@@ -129,7 +129,7 @@ int launch_bidir_bwd_tc_t(const void* q, const void* k, const void* v, const uns
   auto kern = bidir_bwd_tc_kernel<T>;
   const size_t smem = bidir_bwd_tc_smem_bytes();
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<(unsigned)BH, kBtcThreads, smem, stream>>>(mq, mk, mv, md, mdq, mdk, mdv, keep, nc, dnorm, H, N);
+  kern<<<(unsigned)BH, kBtcBwdThreads, smem, stream>>>(mq, mk, mv, md, mdq, mdk, mdv, keep, nc, dnorm, H, N);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
