@@ -30,6 +30,9 @@ _SIGNATURES = {
     "cott_cos_attn_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "cott_cos_attn_bwd_dq": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "cott_cos_attn_bwd_dkdv": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "cott_cos_attn_seg_count": [_I, _I, _I],
+    "cott_cos_attn_fwd_seg": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "cott_cos_attn_bwd_seg": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "cott_decode_step": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, ctypes.c_longlong, _P, _P],
     "cott_decode_steps": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, ctypes.c_longlong, _P, _P],
     "cott_bidir_fwd": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
@@ -38,7 +41,7 @@ _SIGNATURES = {
     "cott_check_status": [ctypes.POINTER(ctypes.c_int)],
 }
 _STR = {"cott_version": [], "cott_last_error": [], "cott_status_string": [_I]}
-_SIZE = {"cott_bidir_scratch_bytes": [_I, _I, _I, _I, _I, _I]}
+_SIZE = {"cott_bidir_scratch_bytes": [_I, _I, _I, _I, _I, _I], "cott_cos_attn_seg_workspace_bytes": [_I, _I, _I, _I]}
 
 _lib = None
 launch_count = 0  # kernels launched through this binding (bookkeeping for the benchmark)

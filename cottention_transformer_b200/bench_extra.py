@@ -165,17 +165,51 @@ def bench_causal_kernels(B, H=16, N=4096, d=64, iters=20):
     return res
 
 
+def bench_long_context(N, B=1, H=16, d=64, iters=5):
+    """Prefill forward + backward at B=1 (few sequences, long): segment-parallel against one CTA per head."""
+    L = _lib.lib()
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(1234)
+    q, k, v, do = (torch.randn(B, H, N, d, device=dev, generator=g).bfloat16() for _ in range(4))
+    out, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
+    nc, dnc = 0.5 * torch.ones(H, device=dev), torch.empty(H, device=dev)
+    st = _lib.stream_ptr(dev)
+    P = lambda t: t.data_ptr()  # noqa: E731
+    nseg = L.cott_cos_attn_seg_count(B, H, N)
+    ws = torch.empty(max(L.cott_cos_attn_seg_workspace_bytes(B, H, N, nseg), 16), dtype=torch.uint8, device=dev)
+
+    def step(n):
+        _lib.check(L.cott_cos_attn_fwd_seg(P(q), P(k), P(v), P(nc), P(out), P(ws), n, B, H, N, d, d, 3, st), "fwd_seg")
+        _lib.check(L.cott_cos_attn_bwd_seg(P(q), P(k), P(v), P(nc), P(do), P(ws), n, P(dq), P(dk), P(dv), P(dnc), B, H, N, d, d,
+                                           3, st), "bwd_seg")
+
+    t_seg = _time(lambda: step(nseg), iters, warmup=2)
+    t_one = _time(lambda: step(1), iters, warmup=2)
+    _lib.check_device_status()
+    nbytes = 11 * B * H * N * d * 2
+    peak, kind = _peak_gbs()
+    return {"what": f"causal fwd+bwd prefill, B={B} H={H} N={N} d={d} bf16", "segments": nseg, "us_per_step": t_seg * 1e6,
+            "tokens_per_s": B * N / t_seg, "one_cta_per_head_us": t_one * 1e6, "speedup_vs_one_cta_per_head": t_one / t_seg,
+            "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / t_seg / 1e9, "peak_gbs": peak, "peak_source": kind,
+            "frac": nbytes / t_seg / 1e9 / peak}
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--causal", type=int, default=0, metavar="B",
                     help="only time the three fused causal kernels at batch B (H=16, N=4096, d=64)")
     ap.add_argument("--decode-steps", type=int, default=256)
     ap.add_argument("--json", default=None)
+    ap.add_argument("--long-context", action="store_true", help="only the B=1 long-sequence prefill sweep")
     ap.add_argument("--bidir-only", action="store_true", help="only the bidirectional benchmark")
     ap.add_argument("--no-graph", action="store_true", help="do not replay decode from a CUDA graph (profiler runs)")
     a = ap.parse_args()
     if a.causal:
         print(json.dumps(bench_causal_kernels(a.causal)))
+        raise SystemExit(0)
+    if a.long_context:
+        for n in (16384, 65536, 262144):
+            print(json.dumps(bench_long_context(n)))
         raise SystemExit(0)
     if a.bidir_only:
         print(json.dumps(bench_bidir()))

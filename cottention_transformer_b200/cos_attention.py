@@ -33,19 +33,29 @@ def fused_supported(q, k, v, keep=None) -> bool:
 
 class _FusedCausal(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, norm_const):
+    def forward(ctx, q, k, v, norm_const, segments=None):
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         B, H, N, D = q.shape
         nc = norm_const.detach().reshape(-1).to(device=q.device, dtype=torch.float32).contiguous()
         if nc.numel() != H:
             raise RuntimeError(f"norm_const must have one entry per head ({H}), got {nc.numel()}")
         out = torch.empty_like(v)
+        L = _lib.lib()
         with torch.cuda.device(q.device):
-            st = _lib.lib().cott_cos_attn_fwd(
-                _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(nc), _lib.ptr(out), B, H, N, D, D,
-                _lib.DTYPE_CODE[q.dtype], _lib.stream_ptr(q.device))
+            # few (batch, head) pairs and a long sequence: cut every sequence into segments that run on
+            # different SMs (the library says how many for this device; 1 = not worth it)
+            nseg = L.cott_cos_attn_seg_count(B, H, N) if segments is None else int(segments)
+            if nseg > 1:
+                ws = torch.empty(L.cott_cos_attn_seg_workspace_bytes(B, H, N, nseg), dtype=torch.uint8, device=q.device)
+                st = L.cott_cos_attn_fwd_seg(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(nc), _lib.ptr(out), _lib.ptr(ws),
+                                             nseg, B, H, N, D, D, _lib.DTYPE_CODE[q.dtype], _lib.stream_ptr(q.device))
+            else:
+                ws = None
+                st = L.cott_cos_attn_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(nc), _lib.ptr(out), B, H, N, D, D,
+                                         _lib.DTYPE_CODE[q.dtype], _lib.stream_ptr(q.device))
         _lib.check(st, "cott_cos_attn_fwd")
         ctx.save_for_backward(q, k, v, nc)
+        ctx.ws, ctx.nseg = ws, nseg
         ctx.nc_shape, ctx.nc_dtype = norm_const.shape, norm_const.dtype
         return out
 
@@ -57,11 +67,17 @@ class _FusedCausal(torch.autograd.Function):
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         dnc = torch.empty(H, dtype=torch.float32, device=q.device)
         with torch.cuda.device(q.device):
-            st = _lib.lib().cott_cos_attn_bwd(
-                _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(nc), _lib.ptr(dout), _lib.ptr(dq), _lib.ptr(dk),
-                _lib.ptr(dv), _lib.ptr(dnc), B, H, N, D, D, _lib.DTYPE_CODE[q.dtype], _lib.stream_ptr(q.device))
+            if ctx.nseg > 1:
+                st = _lib.lib().cott_cos_attn_bwd_seg(
+                    _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(nc), _lib.ptr(dout), _lib.ptr(ctx.ws), ctx.nseg,
+                    _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(dnc), B, H, N, D, D, _lib.DTYPE_CODE[q.dtype],
+                    _lib.stream_ptr(q.device))
+            else:
+                st = _lib.lib().cott_cos_attn_bwd(
+                    _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(nc), _lib.ptr(dout), _lib.ptr(dq), _lib.ptr(dk),
+                    _lib.ptr(dv), _lib.ptr(dnc), B, H, N, D, D, _lib.DTYPE_CODE[q.dtype], _lib.stream_ptr(q.device))
         _lib.check(st, "cott_cos_attn_bwd")
-        return dq, dk, dv, dnc.reshape(ctx.nc_shape).to(ctx.nc_dtype)
+        return dq, dk, dv, dnc.reshape(ctx.nc_shape).to(ctx.nc_dtype), None
 
 
 def _exact_causal(q, k, v, norm_const, keep):
@@ -81,17 +97,19 @@ def _exact_causal(q, k, v, norm_const, keep):
     return CustomAttention.apply(qh, kh, vp)
 
 
-def cos_attn_causal(q, k, v, norm_const, keep=None):
+def cos_attn_causal(q, k, v, norm_const, keep=None, segments=None):
     """Causal cosine attention with the learned length-norm.
 
     q, k, v: ``[B, H, N, d]`` CUDA tensors; ``norm_const``: H values (any shape, e.g. the module's
     ``[1, H, 1, 1]`` parameter); ``keep``: optional ``[B, N]`` bool, True = un-masked
     (``attention_mask == 0`` in the reference, ``GPTCosAttention.py:232``).
+    ``segments``: how many segments each sequence is cut into on the fused path (they run on different SMs;
+    same results); ``None`` lets the library choose -- more than one only for few (batch, head) pairs.
     """
     if not (q.is_cuda and k.is_cuda and v.is_cuda):
         raise RuntimeError("cos_attn_causal needs CUDA tensors (there is no CPU path)")
     if fused_supported(q, k, v, keep):
-        return _FusedCausal.apply(q, k, v, norm_const)
+        return _FusedCausal.apply(q, k, v, norm_const, segments)
     return _exact_causal(q, k, v, norm_const, keep)
 
 

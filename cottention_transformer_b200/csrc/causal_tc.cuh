@@ -578,6 +578,36 @@ __device__ __forceinline__ void state_to_smem_rolled(uint32_t tS_lane, unsigned 
   }
 }
 
+// A segment's starting state (fp32 [64 x 64], row-major) -> TMEM in the M=64 accumulator layout (lanes 16-31
+// of the warp belong to no row of that layout and receive a copy of lanes 0-15) and, as 16 bits, into the
+// swizzled smem operand.  The caller waits for the TMEM stores (tcgen05.wait::st) and fences.
+template <typename T>
+__device__ __forceinline__ void load_init_state(const float* state, uint32_t tS_lane, unsigned char* sS, int wq, int lane) {
+  const float* src = state + (16 * wq + (lane & 15)) * kTcD;
+#pragma unroll 1
+  for (int half = 0; half < 2; ++half) {
+    uint32_t r[32];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float4 f = *reinterpret_cast<const float4*>(src + 32 * half + 4 * j);
+      r[4 * j] = __float_as_uint(f.x), r[4 * j + 1] = __float_as_uint(f.y);
+      r[4 * j + 2] = __float_as_uint(f.z), r[4 * j + 3] = __float_as_uint(f.w);
+    }
+    ptx::tmem_st_x32(tS_lane + 32 * half, r);
+    if (lane < 16) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 u;
+        u.x = Pack2<T>::pack(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+        u.y = Pack2<T>::pack(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+        u.z = Pack2<T>::pack(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+        u.w = Pack2<T>::pack(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+        *tile_piece(sS, 16 * wq + lane, 4 * half + j) = u;
+      }
+    }
+  }
+}
+
 // Descriptors of a [rows x 64] 16-bit tile with the 128-byte swizzle (see sm100_ptx.cuh).
 // K-major: advance K by 16 elements = +32 B = +2 in descriptor units; MN-major: +2048 B = +128.
 __device__ __forceinline__ uint64_t kdesc(uint32_t saddr) { return ptx::make_smem_desc(saddr, 16, 1024); }
@@ -600,7 +630,8 @@ template <typename T, int MODE>
 __global__ void __launch_bounds__(kTcThreads, 1)
 causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapY,
                  const __grid_constant__ CUtensorMap mapZ, const __grid_constant__ CUtensorMap mapQ,
-                 const __grid_constant__ CUtensorMap mapOut, const float* __restrict__ norm_const, int H, int N) {
+                 const __grid_constant__ CUtensorMap mapOut, const float* __restrict__ norm_const, int H, int N,
+                 const float* __restrict__ init_state, int chunks_per_seg) {
   using namespace ptx;
   // Shared memory: NS stages of the tiles that are only read (forward: Y, Z; dQ: X, Y, Z), a ring of
   // kTcRing tiles for the tile that doubles as the output staging buffer (forward: X; dQ: q), the 16-bit
@@ -623,7 +654,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   auto ring_of = [&](int c) { return ring + (c % kTcRing) * kTileBytes; };
   auto tile_x = [&](int c) { return MODE == kModeFwd ? ring_of(c) : stage_of(c); };
   __shared__ uint64_t bar_full[NS], bar_free_in[NS], bar_out[NS], bar_prep[NS], bar_p_full[2], bar_p_ready[2], bar_acc_full[2],
-      bar_acc_free[2], bar_s_full, bar_state[2], bar_state2;
+      bar_acc_free[2], bar_s_full, bar_state[2], bar_state2, bar_init;
   __shared__ uint32_t tmem_slot;
   COTT_TRACE_DECL
   __shared__ int abort_flag_s;
@@ -633,7 +664,14 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // broadcast: provably warp-uniform
   const int bh = blockIdx.x;
   const int h = bh % H;
-  const int nchunks = (N + kTcChunk - 1) / kTcChunk;
+  // Segment-parallel launches (gridDim.y > 1) give each CTA `chunks_per_seg` consecutive chunks of the
+  // sequence and the state before its first chunk (`init_state[bh][seg]`, fp32 [64 x 64] in this kernel's
+  // own state layout, rows = columns of Y); chunk numbers below are local, `chunk0 + c` is the position.
+  const int total_chunks = (N + kTcChunk - 1) / kTcChunk;
+  const int seg = blockIdx.y;
+  const int chunk0 = seg * chunks_per_seg;
+  const int nchunks = min(chunks_per_seg, total_chunks - chunk0);
+  const bool has_init = init_state != nullptr && seg > 0;
 
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
@@ -652,6 +690,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
     mbar_init(&bar_state[0], 4);
     mbar_init(&bar_state[1], 4);
     mbar_init(&bar_state2, 4);
+    mbar_init(&bar_init, 4);
     mbar_fence_init();
     abort_flag_s = 0;
     tma_prefetch_desc(&mapX);
@@ -722,13 +761,13 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       for (int c = 0; c + 1 < nchunks; ++c) {
         {
           // state update of chunk c: Zw(c), and the conversion of S after chunk c-1
-          if (!wait_bar4(&bar_prep[c % NS], (c / NS) & 1, c > 0 ? &bar_state2 : nullptr, (c - 1) & 1, nullptr, 0,
-                         nullptr, 0, abort_flag, kWaitPrepped, c))
+          if (!wait_bar4(&bar_prep[c % NS], (c / NS) & 1, c > 0 ? &bar_state2 : (has_init ? &bar_init : nullptr),
+                         c > 0 ? ((c - 1) & 1) : 0, nullptr, 0, nullptr, 0, abort_flag, kWaitPrepped, c))
             break;
           tc_fence_after_sync();
           const uint32_t y0 = smem_u32(stage_of(c) + kIdxY * kTileBytes);
           const uint64_t dYm = mdesc(y0), dZm = mdesc(y0 + kTileBytes);
-          mma_ss(tS, dYm, dZm, kIdescS, c > 0 ? 1u : 0u);
+          mma_ss(tS, dYm, dZm, kIdescS, (c > 0 || has_init) ? 1u : 0u);
 #pragma unroll
           for (int k = 1; k < 8; ++k) mma_ss(tS, dYm + 128 * k, dZm + 128 * k, kIdescS, 1u);
           mma_commit(&bar_s_full);
@@ -751,10 +790,10 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         }
 #endif
         mbar_expect_tx(&bar_full[s], STAGE + kTileBytes);
-        if (MODE == kModeDq) tma_load_3d(st, &mapX, &bar_full[s], 0, c * kTcChunk, bh);
-        tma_load_3d(st + kIdxY * kTileBytes, &mapY, &bar_full[s], 0, c * kTcChunk, bh);
-        tma_load_3d(st + kIdxZ * kTileBytes, &mapZ, &bar_full[s], 0, c * kTcChunk, bh);
-        tma_load_3d(ring_of(c), MODE == kModeDq ? &mapQ : &mapX, &bar_full[s], 0, c * kTcChunk, bh);
+        if (MODE == kModeDq) tma_load_3d(st, &mapX, &bar_full[s], 0, (chunk0 + c) * kTcChunk, bh);
+        tma_load_3d(st + kIdxY * kTileBytes, &mapY, &bar_full[s], 0, (chunk0 + c) * kTcChunk, bh);
+        tma_load_3d(st + kIdxZ * kTileBytes, &mapZ, &bar_full[s], 0, (chunk0 + c) * kTcChunk, bh);
+        tma_load_3d(ring_of(c), MODE == kModeDq ? &mapQ : &mapX, &bar_full[s], 0, (chunk0 + c) * kTcChunk, bh);
         COTT_TRACE_EV(0, c);
       };
       for (int c = 0; c < NS && c < nchunks; ++c) issue_loads(c);
@@ -769,7 +808,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         }
         if (!wait_bar(&bar_out[s], (c / NS) & 1, abort_flag, kWaitStageFree, c)) break;
 #if !(COTT_SKEL & 16)
-        tma_store_3d(&mapOut, ring_of(c), 0, c * kTcChunk, bh);
+        tma_store_3d(&mapOut, ring_of(c), 0, (chunk0 + c) * kTcChunk, bh);
         tma_store_commit();
 #endif
       }
@@ -784,19 +823,20 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         const uint64_t dX = kdesc(smem_u32(tile_x(c))), dZm = mdesc(smem_u32(stage_of(c) + kIdxZ * kTileBytes));
         const uint32_t tP = tP0 + 128 * b, tAcc = tAcc0 + 64 * b;
         // masked scores of chunk c, the 16-bit state after chunk c-1, the accumulator buffer read out, Zw(c)
-        if (!wait_bar4(&bar_p_ready[b], (c >> 1) & 1, c > 0 ? &bar_state[(c - 1) & 1] : nullptr, ((c - 1) >> 1) & 1,
+        if (!wait_bar4(&bar_p_ready[b], (c >> 1) & 1, c > 0 ? &bar_state[(c - 1) & 1] : (has_init ? &bar_init : nullptr),
+                       c > 0 ? (((c - 1) >> 1) & 1) : 0,
                        c >= 2 ? &bar_acc_free[b] : nullptr, ((c >> 1) - 1) & 1, &bar_prep[s], (c / NS) & 1, abort_flag,
                        kWaitScoreReady, c))
           break;
         tc_fence_after_sync();
         COTT_TRACE_EV(0, c);
-        if (c > 0) {
+        if (c > 0 || has_init) {
           const uint64_t dS = dS0 + static_cast<uint64_t>(b * ((kTcD * 128) >> 4));
 #pragma unroll
           for (int k = 0; k < 4; ++k)  // Acc = X S   (S as MN-major B operand)
             mma_ss(tAcc, dX + 2 * k, dS + 128 * k, kIdescAcc, k > 0);
         }
-        mma_ts(tAcc, tP, dZm, kIdescAcc, c > 0 ? 1u : 0u);  // Acc += P Zw   (P from TMEM, Zw MN-major)
+        mma_ts(tAcc, tP, dZm, kIdescAcc, (c > 0 || has_init) ? 1u : 0u);  // Acc += P Zw   (P from TMEM, Zw MN-major)
 #pragma unroll
         for (int k = 1; k < 8; ++k) mma_ts(tAcc, tP + 8 * k, dZm + 128 * k, kIdescAcc, 1u);
         mma_commit(&bar_acc_full[b]);
@@ -823,6 +863,14 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
     // ---------------------------------------------------------------- state group
     const int wq = warp & 3;
     const uint32_t lane_base = static_cast<uint32_t>(32 * wq) << 16;
+    if (has_init) {
+      // the state before this segment: fp32 into TMEM, 16-bit into the operand buffer of chunk 0
+      load_init_state<T>(init_state + (static_cast<size_t>(bh) * gridDim.y + seg) * (kTcD * kTcD), tS + lane_base, sS, wq, lane);
+      tmem_st_wait();
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      warp_arrive(&bar_init, lane);
+    }
     for (int c = 0; c + 1 < nchunks; ++c) {
       // S after chunk c -> 16-bit operand for chunk c+1 (buffer (c+1)&1)
       if (!wait_bar_warp(&bar_s_full, c & 1, abort_flag, kWaitState, c)) break;
@@ -877,7 +925,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       unsigned char* sK = (MODE == kModeDq) ? sZ : stage_of(c) + kIdxY * kTileBytes;
 #if !(COTT_SKEL & 2)
       const float rk = inv_norm(row_sumsq_rolled<T>(sK, row));
-      const float a = length_factor(static_cast<float>(c * kTcChunk + row + 1), sigma);
+      const float a = length_factor(static_cast<float>((chunk0 + c) * kTcChunk + row + 1), sigma);
       scale_row_rolled<T>(sZ, row, rk * a);
 #endif
       fence_proxy_async_smem();
@@ -962,7 +1010,8 @@ __global__ void __launch_bounds__(kKvThreads, 1)
 causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                      const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
                      const __grid_constant__ CUtensorMap mapDK, const __grid_constant__ CUtensorMap mapDV, float* __restrict__ dnorm,
-                     const float* __restrict__ norm_const, int H, int N) {
+                     const float* __restrict__ norm_const, int H, int N, const float* __restrict__ init_state,
+                     int chunks_per_seg) {
   using namespace ptx;
   constexpr int STAGE = 4 * kTileBytes;
   constexpr int NS = kTcStages;
@@ -974,7 +1023,7 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char* sR = smem + NS * STAGE;  // 2 x [64 x 64] 16-bit state operand (rows = d_k, cols = d_v), double-buffered
   __shared__ uint64_t bar_full[NS], bar_free_in[NS], bar_out[NS], bar_prep[NS], bar_p_full, bar_p_ready, bar_acc_full, bar_acc_free,
-      bar_state, bar_state2, bar_r_full;
+      bar_state, bar_state2, bar_r_full, bar_init;
   __shared__ uint32_t tmem_slot;
   COTT_TRACE_DECL
   __shared__ int abort_flag_s;
@@ -984,7 +1033,15 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // broadcast: provably warp-uniform
   const int bh = blockIdx.x;
   const int h = bh % H;
-  const int nchunks = (N + kTcChunk - 1) / kTcChunk;
+  // Segment-parallel launches (gridDim.y > 1): this CTA owns `chunks_per_seg` consecutive chunks, walks them
+  // backwards, and starts from the state of everything after them (`init_state[bh][seg]`, fp32 [64 x 64],
+  // rows d_k).  `ci` is local; the position of item ci is chunk `last_chunk - ci`.
+  const int total_chunks = (N + kTcChunk - 1) / kTcChunk;
+  const int seg = blockIdx.y;
+  const int chunk0 = seg * chunks_per_seg;
+  const int nchunks = min(chunks_per_seg, total_chunks - chunk0);
+  const int last_chunk = chunk0 + nchunks - 1;
+  const bool has_init = init_state != nullptr && seg + 1 < static_cast<int>(gridDim.y);
 
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
@@ -1000,6 +1057,7 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     mbar_init(&bar_state, 4);
     mbar_init(&bar_state2, 4);
     mbar_init(&bar_r_full, 1);
+    mbar_init(&bar_init, 4);
     mbar_fence_init();
     abort_flag_s = 0;
     tma_prefetch_desc(&mapQ);
@@ -1032,7 +1090,7 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     if (lane == 0) {
       auto load_inputs = [&](int ci) {
         const int s = ci % NS;
-        const int y = (nchunks - 1 - ci) * kTcChunk;
+        const int y = (last_chunk - ci) * kTcChunk;
         unsigned char* st = smem + s * STAGE;
         mbar_expect_tx(&bar_full[s], STAGE);
         tma_load_3d(st, &mapQ, &bar_full[s], 0, y, bh);
@@ -1040,7 +1098,7 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       };
       auto load_staging = [&](int ci) {
         const int s = ci % NS;
-        const int y = (nchunks - 1 - ci) * kTcChunk;
+        const int y = (last_chunk - ci) * kTcChunk;
         unsigned char* st = smem + s * STAGE;
         tma_load_3d(st + kTileBytes, &mapK, &bar_full[s], 0, y, bh);
         tma_load_3d(st + 2 * kTileBytes, &mapV, &bar_full[s], 0, y, bh);
@@ -1051,7 +1109,7 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       }
       for (int ci = 0; ci < nchunks; ++ci) {
         const int s = ci % NS;
-        const int y = (nchunks - 1 - ci) * kTcChunk;
+        const int y = (last_chunk - ci) * kTcChunk;
         const bool refill = ci + NS < nchunks;
         if (refill) {
           if (!wait_bar(&bar_free_in[s], (ci / NS) & 1, abort_flag, kWaitStageFree, ci)) break;
@@ -1091,11 +1149,12 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
           // state of chunk ci (Qw(ci) was waited for before its score tiles were issued); the 16-bit
           // conversion after chunk ci-1 must have finished reading the TMEM state
           if (ci > 0 && !(ok = wait_bar1(&bar_state2, (ci - 1) & 1, abort_flag, kWaitState, ci))) break;
+          if (ci == 0 && has_init && !(ok = wait_bar1(&bar_init, 0, abort_flag, kWaitState, ci))) break;
           tc_fence_after_sync();
           COTT_TRACE_EV(0, ci);
           const uint32_t q0 = smem_u32(smem + (ci % NS) * STAGE);
           const uint64_t dQm = mdesc(q0), dDm = mdesc(q0 + 3 * kTileBytes);
-          mma_ss(tR, dQm, dDm, kIdescR, ci > 0 ? 1u : 0u);
+          mma_ss(tR, dQm, dDm, kIdescR, (ci > 0 || has_init) ? 1u : 0u);
 #pragma unroll
           for (int k = 1; k < 8; ++k) mma_ss(tR, dQm + 128 * k, dDm + 128 * k, kIdescR, 1u);
           mma_commit(&bar_r_full);
@@ -1121,11 +1180,13 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         const uint32_t q0 = smem_u32(smem + s * STAGE);
         const uint64_t dK = kdesc(q0 + kTileBytes), dV = kdesc(q0 + 2 * kTileBytes), dQm = mdesc(q0),
                        dDm = mdesc(q0 + 3 * kTileBytes);
-        const uint32_t acc0 = ci > 0 ? 1u : 0u;
-        if (ci > 0) {
+        const uint32_t acc0 = (ci > 0 || has_init) ? 1u : 0u;
+        if (ci > 0 || has_init) {
           // the state terms need the 16-bit state after chunk ci-1 and the accumulators read out, not the
           // masked scores: they are issued while the score tiles are still being masked
-          if (!wait_bar2(&bar_state, (ci - 1) & 1, &bar_acc_free, (ci - 1) & 1, abort_flag, kWaitState, ci)) break;
+          if (ci > 0 ? !wait_bar2(&bar_state, (ci - 1) & 1, &bar_acc_free, (ci - 1) & 1, abort_flag, kWaitState, ci)
+                     : !wait_bar1(&bar_init, 0, abort_flag, kWaitState, ci))
+            break;
           tc_fence_after_sync();
           const uint32_t rb = r0 + (ci & 1) * (kTcD * 128);
           const uint64_t dRk = kdesc(rb), dRm = mdesc(rb);
@@ -1181,6 +1242,13 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     // operand group: mask + convert F, then the fp32 state after this chunk -> 16-bit operand
     const int wq = warp & 3, row = 32 * wq + lane;
     const uint32_t lane_base = static_cast<uint32_t>(32 * wq) << 16;
+    if (has_init) {  // the state after this segment: fp32 into TMEM, 16-bit into the operand buffer of item 0
+      load_init_state<T>(init_state + (static_cast<size_t>(bh) * gridDim.y + seg) * (kTcD * kTcD), tR + lane_base, sR, wq, lane);
+      tmem_st_wait();
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      warp_arrive(&bar_init, lane);
+    }
     for (int ci = 0; ci < nchunks; ++ci) {
       if (!wait_bar_warp(&bar_p_full, ci & 1, abort_flag, kWaitScore, ci)) break;
       tc_fence_after_sync();
@@ -1208,7 +1276,7 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       const int s = ci % NS;
       unsigned char* sK = smem + s * STAGE + kTileBytes;
       unsigned char* sV = smem + s * STAGE + 2 * kTileBytes;
-      const int pos = (nchunks - 1 - ci) * kTcChunk + row;
+      const int pos = (last_chunk - ci) * kTcChunk + row;
       if (!wait_bar_warp(&bar_full[s], (ci / NS) & 1, abort_flag, kWaitTma, ci)) break;
       const float rk = inv_norm(row_sumsq_rolled<T>(sK, row));
       const float a = length_factor(static_cast<float>(pos + 1), sigma);

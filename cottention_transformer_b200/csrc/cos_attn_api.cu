@@ -1,5 +1,6 @@
 // C ABI of the fused cosine-attention operators (tensor-core path).
 #include "bidir_tc.cuh"
+#include "causal_seg.cuh"
 #include "causal_tc.cuh"
 #include "common.cuh"
 
@@ -34,9 +35,24 @@ int tmap(CUtensorMap* m, const void* p, int dtype, long BH, long N) {
   return COTT_OK;
 }
 
+// One segment (`nseg` = 1, `init` = nullptr) or segment-parallel: gridDim.y = nseg CTAs per (b, h), each starting
+// from init[bh][seg].
+struct SegPlan {
+  int nseg = 1;  // segments actually launched
+  int cps = 0;   // chunks per segment
+};
+SegPlan plan_segments(int N, int nseg_requested) {
+  const int total = (N + kTcChunk - 1) / kTcChunk;
+  SegPlan p;
+  const int want = nseg_requested < 1 ? 1 : (nseg_requested > total ? total : nseg_requested);
+  p.cps = (total + want - 1) / want;
+  p.nseg = (total + p.cps - 1) / p.cps;
+  return p;
+}
+
 template <typename T>
 int launch_fwd(const void* q, const void* k, const void* v, const float* nc, void* out, int B, int H, int N,
-               int dtype, cudaStream_t stream) {
+               int dtype, cudaStream_t stream, const float* init = nullptr, SegPlan plan = SegPlan()) {
   const long BH = (long)B * H;
   CUtensorMap mq, mk, mv, mo;
   int st;
@@ -46,14 +62,15 @@ int launch_fwd(const void* q, const void* k, const void* v, const float* nc, voi
   auto kern = causal_tc_kernel<T, kModeFwd>;
   const size_t smem = causal_tc_smem_bytes(kModeFwd);
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<(unsigned)BH, kTcThreads, smem, stream>>>(mq, mk, mv, mq, mo, nc, H, N);
+  if (plan.cps == 0) plan = plan_segments(N, 1);
+  kern<<<dim3((unsigned)BH, plan.nseg), kTcThreads, smem, stream>>>(mq, mk, mv, mq, mo, nc, H, N, init, plan.cps);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
 
 template <typename T>
 int launch_bwd_dq(const void* q, const void* k, const void* v, const float* nc, const void* dout, void* dq, int B,
-                  int H, int N, int dtype, cudaStream_t stream) {
+                  int H, int N, int dtype, cudaStream_t stream, const float* init = nullptr, SegPlan plan = SegPlan()) {
   const long BH = (long)B * H;
   CUtensorMap mq, mk, mv, md, mo;
   int st;
@@ -64,14 +81,16 @@ int launch_bwd_dq(const void* q, const void* k, const void* v, const float* nc, 
   auto kern = causal_tc_kernel<T, kModeDq>;
   const size_t smem = causal_tc_smem_bytes(kModeDq);
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<(unsigned)BH, kTcThreads, smem, stream>>>(md, mv, mk, mq, mo, nc, H, N);
+  if (plan.cps == 0) plan = plan_segments(N, 1);
+  kern<<<dim3((unsigned)BH, plan.nseg), kTcThreads, smem, stream>>>(md, mv, mk, mq, mo, nc, H, N, init, plan.cps);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
 
 template <typename T>
 int launch_bwd_dkdv(const void* q, const void* k, const void* v, const float* nc, const void* dout, void* dk,
-                    void* dv, float* dnorm, int B, int H, int N, int dtype, cudaStream_t stream) {
+                    void* dv, float* dnorm, int B, int H, int N, int dtype, cudaStream_t stream,
+                    const float* init = nullptr, SegPlan plan = SegPlan()) {
   const long BH = (long)B * H;
   CUtensorMap mq, mk, mv, md, mdk, mdv;
   int st;
@@ -83,9 +102,63 @@ int launch_bwd_dkdv(const void* q, const void* k, const void* v, const float* nc
   auto kern = causal_bwd_kv_kernel<T>;
   const size_t smem = causal_bwd_kv_smem_bytes();
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<(unsigned)BH, kKvThreads, smem, stream>>>(mq, mk, mv, md, mdk, mdv, dnorm, nc, H, N);
+  if (plan.cps == 0) plan = plan_segments(N, 1);
+  kern<<<dim3((unsigned)BH, plan.nseg), kKvThreads, smem, stream>>>(mq, mk, mv, md, mdk, mdv, dnorm, nc, H, N, init, plan.cps);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
+}
+
+// state[bh][seg] of every segment: Y^T Z with one operand row-scaled (see seg_state_kernel)
+template <typename T, int MODE>
+int launch_seg_state(const void* y, const void* z, const float* nc, float* state, int B, int H, int N, int dtype,
+                     SegPlan plan, cudaStream_t stream) {
+  const long BH = (long)B * H;
+  CUtensorMap my, mz;
+  int st;
+  if ((st = tmap(&my, y, dtype, BH, N)) || (st = tmap(&mz, z, dtype, BH, N))) return st;
+  auto kern = seg_state_kernel<T, MODE>;
+  const size_t smem = seg_state_smem_bytes();
+  COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<dim3((unsigned)BH, plan.nseg), kSegThreads, smem, stream>>>(my, mz, nc, state, H, N, plan.cps);
+  COTT_CUDA_TRY(cudaGetLastError());
+  return COTT_OK;
+}
+
+// workspace of the segment-parallel path: five arrays of B*H*nseg fp32 [64 x 64] matrices
+//   0 forward segment states | 1 their exclusive prefix | 2 the prefix transposed | 3 reverse segment states |
+//   4 their exclusive suffix
+size_t seg_array_floats(int B, int H, int nseg) { return (size_t)B * H * nseg * kTcD * kTcD; }
+
+template <typename T>
+int run_fwd_seg(const void* q, const void* k, const void* v, const float* nc, void* out, float* ws, int nseg, int B, int H,
+                int N, int dtype, cudaStream_t stream) {
+  const SegPlan plan = plan_segments(N, nseg);
+  if (plan.nseg == 1) return launch_fwd<T>(q, k, v, nc, out, B, H, N, dtype, stream);
+  const size_t A = seg_array_floats(B, H, plan.nseg);
+  int st = launch_seg_state<T, kSegFwdState>(k, v, nc, ws, B, H, N, dtype, plan, stream);
+  if (st) return st;
+  seg_scan_kernel<<<(unsigned)((long)B * H), 256, 0, stream>>>(ws, ws + A, ws + 2 * A, nullptr, plan.nseg);
+  COTT_CUDA_TRY(cudaGetLastError());
+  return launch_fwd<T>(q, k, v, nc, out, B, H, N, dtype, stream, ws + A, plan);
+}
+
+template <typename T>
+int run_bwd_seg(const void* q, const void* k, const void* v, const float* nc, const void* dout, float* ws, int nseg,
+                void* dq, void* dk, void* dv, float* dnorm, int B, int H, int N, int dtype, cudaStream_t stream) {
+  const SegPlan plan = plan_segments(N, nseg);
+  if (plan.nseg == 1) {
+    int st = launch_bwd_dq<T>(q, k, v, nc, dout, dq, B, H, N, dtype, stream);
+    return st ? st : launch_bwd_dkdv<T>(q, k, v, nc, dout, dk, dv, dnorm, B, H, N, dtype, stream);
+  }
+  const size_t A = seg_array_floats(B, H, plan.nseg);
+  // dQ: the forward prefix states, transposed (written by the forward call into the same workspace)
+  int st = launch_bwd_dq<T>(q, k, v, nc, dout, dq, B, H, N, dtype, stream, ws + 2 * A, plan);
+  if (st) return st;
+  // dK, dV: reverse states of the segments, their exclusive suffix
+  if ((st = launch_seg_state<T, kSegRevState>(q, dout, nc, ws + 3 * A, B, H, N, dtype, plan, stream))) return st;
+  seg_scan_kernel<<<(unsigned)((long)B * H), 256, 0, stream>>>(ws + 3 * A, nullptr, nullptr, ws + 4 * A, plan.nseg);
+  COTT_CUDA_TRY(cudaGetLastError());
+  return launch_bwd_dkdv<T>(q, k, v, nc, dout, dk, dv, dnorm, B, H, N, dtype, stream, ws + 4 * A, plan);
 }
 
 int check_ptrs16(std::initializer_list<std::pair<const void*, const char*>> ps) {
@@ -219,6 +292,61 @@ int cott_cos_attn_bwd(const void* q, const void* k, const void* v, const float* 
   int st = cott_cos_attn_bwd_dq(q, k, v, norm_const, dout, dq, B, H, N, Dk, Dv, dtype, stream);
   if (st) return st;
   return cott_cos_attn_bwd_dkdv(q, k, v, norm_const, dout, dk, dv, dnorm_const, B, H, N, Dk, Dv, dtype, stream);
+}
+
+int cott_cos_attn_seg_count(int B, int H, int N) {
+  const long BH = (long)B * H;
+  const int total = (N + kTcChunk - 1) / kTcChunk;
+  if (BH <= 0 || total < 4) return 1;
+  int sm = 148;
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, dev);
+  long nseg = sm / BH;              // one CTA per SM; more sequences than half the SMs: no gain
+  if (nseg > total / 2) nseg = total / 2;  // at least two chunks per segment
+  return nseg < 2 ? 1 : (int)nseg;
+}
+
+size_t cott_cos_attn_seg_workspace_bytes(int B, int H, int N, int nseg) {
+  if (B <= 0 || H <= 0 || N <= 0) return 0;
+  return 5 * seg_array_floats(B, H, plan_segments(N, nseg).nseg) * sizeof(float);
+}
+
+int cott_cos_attn_fwd_seg(const void* q, const void* k, const void* v, const float* norm_const, void* out,
+                          void* workspace, int nseg, int B, int H, int N, int Dk, int Dv, int dtype, void* stream) {
+  int st = check_fused_args(B, H, N, Dk, Dv, dtype);
+  if (st) return st;
+  if ((long)B * H * N == 0) return COTT_OK;
+  if ((st = check_ptrs16({{q, "q"}, {k, "k"}, {v, "v"}, {out, "out"}, {workspace, "workspace"}}))) return st;
+  if (!norm_const) return fail(COTT_ERR_NULL, "null pointer: norm_const");
+  DeviceScope scope(q);
+  COTT_CUDA_TRY(scope.status());
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  float* ws = static_cast<float*>(workspace);
+  return dtype == COTT_BF16 ? run_fwd_seg<__nv_bfloat16>(q, k, v, norm_const, out, ws, nseg, B, H, N, dtype, s)
+                            : run_fwd_seg<__half>(q, k, v, norm_const, out, ws, nseg, B, H, N, dtype, s);
+}
+
+int cott_cos_attn_bwd_seg(const void* q, const void* k, const void* v, const float* norm_const, const void* dout,
+                          void* workspace, int nseg, void* dq, void* dk, void* dv, float* dnorm_const, int B, int H,
+                          int N, int Dk, int Dv, int dtype, void* stream) {
+  int st = check_fused_args(B, H, N, Dk, Dv, dtype);
+  if (st) return st;
+  if (!dnorm_const && H > 0) return fail(COTT_ERR_NULL, "null pointer: dnorm_const");
+  if ((long)B * H * N == 0) {
+    if (H > 0) COTT_CUDA_TRY(cudaMemsetAsync(dnorm_const, 0, sizeof(float) * H, static_cast<cudaStream_t>(stream)));
+    return COTT_OK;
+  }
+  if ((st = check_ptrs16({{q, "q"}, {k, "k"}, {v, "v"}, {dout, "dout"}, {dq, "dq"}, {dk, "dk"}, {dv, "dv"},
+                          {workspace, "workspace"}})))
+    return st;
+  if (!norm_const) return fail(COTT_ERR_NULL, "null pointer: norm_const");
+  DeviceScope scope(q);
+  COTT_CUDA_TRY(scope.status());
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  float* ws = static_cast<float*>(workspace);
+  return dtype == COTT_BF16
+             ? run_bwd_seg<__nv_bfloat16>(q, k, v, norm_const, dout, ws, nseg, dq, dk, dv, dnorm_const, B, H, N, dtype, s)
+             : run_bwd_seg<__half>(q, k, v, norm_const, dout, ws, nseg, dq, dk, dv, dnorm_const, B, H, N, dtype, s);
 }
 
 int cott_check_status(int* detail) {

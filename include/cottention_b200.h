@@ -114,6 +114,25 @@ int cott_cos_attn_bwd_dkdv(const void* q, const void* k, const void* v, const fl
                            int Dk, int Dv, int dtype, void* stream);
 
 /*
+ * Segment-parallel form of the three calls above, for long sequences with few (batch, head) pairs
+ * (B = 1, H = 16, N = 16k .. 256k): every sequence is cut into `nseg` segments that run on different
+ * SMs.  The results are those of cott_cos_attn_fwd / cott_cos_attn_bwd (the state is carried across
+ * segment boundaries in fp32; summation order differs).  No counterpart in the reference, whose kernel
+ * (combined_kernel_general.cu:96-251) is sequential in N with one block per (batch, head, output column).
+ *   cott_cos_attn_seg_count            suggested nseg for this device (1 = use the plain calls)
+ *   cott_cos_attn_seg_workspace_bytes  size of `workspace` (device memory, 16-byte aligned) for that nseg
+ *   _fwd_seg writes the segment states into `workspace`; pass the same buffer and nseg, untouched, to _bwd_seg.
+ */
+int cott_cos_attn_seg_count(int B, int H, int N);
+size_t cott_cos_attn_seg_workspace_bytes(int B, int H, int N, int nseg);
+int cott_cos_attn_fwd_seg(const void* q, const void* k, const void* v, const float* norm_const, void* out,
+                          void* workspace, int nseg, int B, int H, int N, int Dk, int Dv, int dtype,
+                          void* stream);
+int cott_cos_attn_bwd_seg(const void* q, const void* k, const void* v, const float* norm_const,
+                          const void* dout, void* workspace, int nseg, void* dq, void* dk, void* dv,
+                          float* dnorm_const, int B, int H, int N, int Dk, int Dv, int dtype, void* stream);
+
+/*
  * Recurrent decode.  Per (batch, head) a float32 state[b,h,j,i] ([B,H,Dv,Dk], updated in place) is
  * advanced by one token:
  *   q^ = q/|q|, k^ = k/|k|, v' = v / max(pos^sigmoid(norm_const[h]), 1)

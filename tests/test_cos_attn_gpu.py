@@ -31,7 +31,10 @@ def _truth(q, k, v, do, nc):
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("shape", [(1, 1, 128), (1, 2, 1), (2, 3, 100), (1, 2, 129), (2, 2, 640), (1, 1, 1000)])
 @pytest.mark.parametrize("normalized", [True, False])
-def test_fused_forward_backward_matches_oracle(dt, shape, normalized):
+# 1 = one CTA per (batch, head); None = the library's choice (segment-parallel for these few sequences);
+# 3 = three segments where the sequence has that many chunks (ragged last segment at 640 and 1000)
+@pytest.mark.parametrize("segments", [1, None, 3])
+def test_fused_forward_backward_matches_oracle(dt, shape, normalized, segments):
     from cottention_transformer_b200 import cos_attn_causal, _lib
     B, H, N = shape
     q, k, v, do, _ = O.make_inputs(B, H, N, 64, 64, seed=N + H, normalize=normalized, dtype=dt)
@@ -41,7 +44,7 @@ def test_fused_forward_backward_matches_oracle(dt, shape, normalized):
     out_t, dq_t, dk_t, dv_t, dnc_t = _truth(q, k, v, do, nc)
     qc, kc, vc = (t.cuda().requires_grad_() for t in (q, k, v))
     ncc = nc.cuda().requires_grad_()
-    out = cos_attn_causal(qc, kc, vc, ncc)
+    out = cos_attn_causal(qc, kc, vc, ncc, segments=segments)
     out.backward(do.cuda())
     _lib.check_device_status()
     for name, a, ref in (("out", out, out_t), ("dq", qc.grad, dq_t), ("dk", kc.grad, dk_t), ("dv", vc.grad, dv_t)):
@@ -113,3 +116,29 @@ def test_full_size_config_properties():
                               v1[b:b + 1, h:h + 1].double().cpu(), nc[h:h + 1].double().cpu(),
                               scan=lambda a, bb, c: O.scan_recurrent(a, bb, c, False, "f64"))
     assert _rel(o1[b:b + 1, h:h + 1], truth)[0] <= REL16
+
+
+def test_segment_parallel_agrees_with_one_cta_per_sequence_long():
+    """B=1, H=2, N=16384 (128 chunks): nine segments against the plain kernels on the same inputs, and a
+    head against the fp64 recurrence; the two paths differ only in where the fp32 state is carried."""
+    from cottention_transformer_b200 import cos_attn_causal, _lib
+    B, H, N = 1, 2, 16384
+    q, k, v, do, _ = O.make_inputs(B, H, N, 64, 64, seed=7, normalize=True, dtype=torch.bfloat16)
+    nc = torch.tensor([0.5, -0.3])
+    res = {}
+    for seg in (1, 9):
+        qc, kc, vc = (t.cuda().requires_grad_() for t in (q, k, v))
+        ncc = nc.cuda().requires_grad_()
+        out = cos_attn_causal(qc, kc, vc, ncc, segments=seg)
+        out.backward(do.cuda())
+        _lib.check_device_status()
+        res[seg] = (out.detach(), qc.grad, kc.grad, vc.grad, ncc.grad)
+    for name, a, b in zip(("out", "dq", "dk", "dv"), res[9], res[1]):
+        e_max, e_fro = _rel(a, b)
+        assert e_max <= 1e-2 and e_fro <= 5e-3, (name, e_max, e_fro)
+    assert torch.allclose(res[9][4], res[1][4], rtol=1e-2, atol=1e-3), (res[9][4], res[1][4])
+    ref = O.scan_recurrent_head(q[0, 1].double(), k[0, 1].double(), v[0, 1].double(), nc[1].double()) if hasattr(
+        O, "scan_recurrent_head") else None
+    if ref is not None:
+        e_max, e_fro = _rel(res[9][0][0, 1], ref)
+        assert e_max <= REL16 and e_fro <= REL16, (e_max, e_fro)
