@@ -137,8 +137,8 @@ def test_segment_parallel_agrees_with_one_cta_per_sequence_long():
         e_max, e_fro = _rel(a, b)
         assert e_max <= 1e-2 and e_fro <= 5e-3, (name, e_max, e_fro)
     assert torch.allclose(res[9][4], res[1][4], rtol=1e-2, atol=1e-3), (res[9][4], res[1][4])
-    ref = O.scan_recurrent_head(q[0, 1].double(), k[0, 1].double(), v[0, 1].double(), nc[1].double()) if hasattr(
-        O, "scan_recurrent_head") else None
-    if ref is not None:
-        e_max, e_fro = _rel(res[9][0][0, 1], ref)
-        assert e_max <= REL16 and e_fro <= REL16, (e_max, e_fro)
+    # one head against the fp64 recurrence
+    truth = O.cos_attn_causal(q[:, 1:2].double(), k[:, 1:2].double(), v[:, 1:2].double(), nc[1:2].double(),
+                              scan=lambda a, bb, c: O.scan_recurrent(a, bb, c, False, "f64"))
+    e_max, e_fro = _rel(res[9][0][:, 1:2], truth)
+    assert e_max <= REL16 and e_fro <= REL16, (e_max, e_fro)
