@@ -27,13 +27,14 @@ FUSED_DTYPES = (torch.float16, torch.bfloat16)
 def fused_supported(q, k, v, keep=None) -> bool:
     return (
         q.is_cuda and q.dtype in FUSED_DTYPES and k.dtype == q.dtype and v.dtype == q.dtype
-        and q.shape[-1] == 64 and v.shape[-1] == 64 and keep is None
+        and q.shape[-1] == 64 and v.shape[-1] == 64
+        and (keep is None or tuple(keep.shape) == (q.shape[0], q.shape[2]))
     )
 
 
 class _FusedCausal(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, norm_const, segments=None):
+    def forward(ctx, q, k, v, norm_const, segments=None, keep=None):
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         B, H, N, D = q.shape
         nc = norm_const.detach().reshape(-1).to(device=q.device, dtype=torch.float32).contiguous()
@@ -45,17 +46,19 @@ class _FusedCausal(torch.autograd.Function):
             # few (batch, head) pairs and a long sequence: cut every sequence into segments that run on
             # different SMs (the library says how many for this device; 1 = not worth it)
             nseg = L.cott_cos_attn_seg_count(B, H, N) if segments is None else int(segments)
-            if nseg > 1:
+            kp = None if keep is None else keep.to(device=q.device, dtype=torch.uint8).contiguous()
+            if nseg > 1 or kp is not None:  # the general entry point: segments and / or a padding mask
                 ws = torch.empty(L.cott_cos_attn_seg_workspace_bytes(B, H, N, nseg), dtype=torch.uint8, device=q.device)
-                st = L.cott_cos_attn_fwd_seg(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(nc), _lib.ptr(out), _lib.ptr(ws),
-                                             nseg, B, H, N, D, D, _lib.DTYPE_CODE[q.dtype], _lib.stream_ptr(q.device))
+                st = L.cott_cos_attn_fwd_seg(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(kp), _lib.ptr(nc), _lib.ptr(out),
+                                             _lib.ptr(ws), nseg, B, H, N, D, D, _lib.DTYPE_CODE[q.dtype],
+                                             _lib.stream_ptr(q.device))
             else:
                 ws = None
                 st = L.cott_cos_attn_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(nc), _lib.ptr(out), B, H, N, D, D,
                                          _lib.DTYPE_CODE[q.dtype], _lib.stream_ptr(q.device))
         _lib.check(st, "cott_cos_attn_fwd")
         ctx.save_for_backward(q, k, v, nc)
-        ctx.ws, ctx.nseg = ws, nseg
+        ctx.ws, ctx.nseg, ctx.kp = ws, nseg, kp
         ctx.nc_shape, ctx.nc_dtype = norm_const.shape, norm_const.dtype
         return out
 
@@ -67,9 +70,9 @@ class _FusedCausal(torch.autograd.Function):
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         dnc = torch.empty(H, dtype=torch.float32, device=q.device)
         with torch.cuda.device(q.device):
-            if ctx.nseg > 1:
+            if ctx.ws is not None:
                 st = _lib.lib().cott_cos_attn_bwd_seg(
-                    _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(nc), _lib.ptr(dout), _lib.ptr(ctx.ws), ctx.nseg,
+                    _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(ctx.kp), _lib.ptr(nc), _lib.ptr(dout), _lib.ptr(ctx.ws), ctx.nseg,
                     _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(dnc), B, H, N, D, D, _lib.DTYPE_CODE[q.dtype],
                     _lib.stream_ptr(q.device))
             else:
@@ -77,7 +80,7 @@ class _FusedCausal(torch.autograd.Function):
                     _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(nc), _lib.ptr(dout), _lib.ptr(dq), _lib.ptr(dk),
                     _lib.ptr(dv), _lib.ptr(dnc), B, H, N, D, D, _lib.DTYPE_CODE[q.dtype], _lib.stream_ptr(q.device))
         _lib.check(st, "cott_cos_attn_bwd")
-        return dq, dk, dv, dnc.reshape(ctx.nc_shape).to(ctx.nc_dtype), None
+        return dq, dk, dv, dnc.reshape(ctx.nc_shape).to(ctx.nc_dtype), None, None
 
 
 def _exact_causal(q, k, v, norm_const, keep):
@@ -109,7 +112,7 @@ def cos_attn_causal(q, k, v, norm_const, keep=None, segments=None):
     if not (q.is_cuda and k.is_cuda and v.is_cuda):
         raise RuntimeError("cos_attn_causal needs CUDA tensors (there is no CPU path)")
     if fused_supported(q, k, v, keep):
-        return _FusedCausal.apply(q, k, v, norm_const, segments)
+        return _FusedCausal.apply(q, k, v, norm_const, segments, keep)
     return _exact_causal(q, k, v, norm_const, keep)
 
 

@@ -23,7 +23,8 @@ enum { kSegFwdState = 0, kSegRevState = 1 };
 template <typename T, int MODE>
 __global__ void __launch_bounds__(kSegThreads, 2)
 seg_state_kernel(const __grid_constant__ CUtensorMap mapY, const __grid_constant__ CUtensorMap mapZ,
-                 const float* __restrict__ norm_const, float* __restrict__ state, int H, int N, int chunks_per_seg) {
+                 const float* __restrict__ norm_const, float* __restrict__ state, int H, int N, int chunks_per_seg,
+                 const unsigned char* __restrict__ keep, const int* __restrict__ count) {
   using namespace ptx;
   constexpr bool BF = Pack2<T>::kBf16;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -39,6 +40,8 @@ seg_state_kernel(const __grid_constant__ CUtensorMap mapY, const __grid_constant
   const int total_chunks = (N + kTcChunk - 1) / kTcChunk;
   const int chunk0 = seg * chunks_per_seg;
   const int nchunks = min(chunks_per_seg, total_chunks - chunk0);
+  const unsigned char* keep_b = keep ? keep + static_cast<size_t>(bh / H) * N : nullptr;
+  const int* count_b = count ? count + static_cast<size_t>(bh / H) * N : nullptr;
 
   if (tid == 0) {
     for (int s = 0; s < 2; ++s) {
@@ -97,12 +100,12 @@ seg_state_kernel(const __grid_constant__ CUtensorMap mapY, const __grid_constant
       const int s = c & 1;
       if (!(ok = wait_bar_warp(&bar_full[s], (c >> 1) & 1, abort_flag, kWaitTma, c))) break;
       unsigned char* sY = smem + s * 2 * kTileBytes;
-      if (MODE == kSegFwdState) {
-        const float a = length_factor(static_cast<float>((chunk0 + c) * kTcChunk + row + 1), sigma);
-        scale_row_rolled<T>(sY + kTileBytes, row, inv_norm(row_sumsq_rolled<T>(sY, row)) * a);
-      } else {
-        scale_row_rolled<T>(sY, row, inv_norm(row_sumsq_rolled<T>(sY, row)));
-      }
+      const RowMask m = row_mask(keep_b, count_b, (chunk0 + c) * kTcChunk + row, N);
+      const float r = m.kp ? inv_norm(row_sumsq_rolled<T>(sY, row)) : 0.f;
+      if (MODE == kSegFwdState)
+        scale_row_rolled<T>(sY + kTileBytes, row, r * length_factor(m.n, sigma));
+      else
+        scale_row_rolled<T>(sY, row, r);
       fence_proxy_async_smem();
       warp_arrive(&bar_prep[s], lane);
     }
@@ -164,6 +167,25 @@ __global__ void seg_scan_kernel(const float* __restrict__ state, float* __restri
         run += state[base + static_cast<size_t>(s) * (kTcD * kTcD) + e];
       }
     }
+  }
+}
+
+// count[b][s] = number of kept positions among 0 .. s of batch entry b (inclusive).  grid = B, block = 256.
+__global__ void keep_count_kernel(const unsigned char* __restrict__ keep, int* __restrict__ count, int N) {
+  __shared__ int part[256];
+  const unsigned char* kb = keep + static_cast<size_t>(blockIdx.x) * N;
+  int* cb = count + static_cast<size_t>(blockIdx.x) * N;
+  const int per = (N + blockDim.x - 1) / blockDim.x;
+  const int lo = min(static_cast<int>(threadIdx.x) * per, N), hi = min(lo + per, N);
+  int sum = 0;
+  for (int s = lo; s < hi; ++s) sum += kb[s] ? 1 : 0;
+  part[threadIdx.x] = sum;
+  __syncthreads();
+  int run = 0;
+  for (int t = 0; t < static_cast<int>(threadIdx.x); ++t) run += part[t];
+  for (int s = lo; s < hi; ++s) {
+    run += kb[s] ? 1 : 0;
+    cb[s] = run;
   }
 }
 

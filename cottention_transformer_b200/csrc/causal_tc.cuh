@@ -218,6 +218,20 @@ __device__ __forceinline__ float length_factor(float n, float sigma) {
   return fminf(exp2f(-sigma * __log2f(n)), 1.0f);
 }
 
+// Padding: `keep` ([B, N] bytes, non-zero = un-masked) and `count` ([B, N] int32, inclusive running count of
+// keep along the sequence) are both null (no padding: n_s = s + 1) or both set (GPTCosAttention.py:232-248:
+// masked rows of q^, k^, v' are zero and n_s counts the un-masked positions up to s).
+struct RowMask {
+  bool kp;   // row takes part
+  float n;   // n_s >= 1
+};
+__device__ __forceinline__ RowMask row_mask(const unsigned char* keep_b, const int* count_b, int pos, int N) {
+  RowMask m;
+  m.kp = pos < N && (!keep_b || keep_b[pos]);
+  m.n = (count_b && pos < N) ? fmaxf(static_cast<float>(count_b[pos]), 1.0f) : static_cast<float>(pos + 1);
+  return m;
+}
+
 // Bounded wait that also gives up when another role of the CTA has raised `abort_flag`.
 // On its own time-out it raises the flag and records (code << 16 | chunk) in g_cott_status.
 __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code,
@@ -631,7 +645,8 @@ __global__ void __launch_bounds__(kTcThreads, 1)
 causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapY,
                  const __grid_constant__ CUtensorMap mapZ, const __grid_constant__ CUtensorMap mapQ,
                  const __grid_constant__ CUtensorMap mapOut, const float* __restrict__ norm_const, int H, int N,
-                 const float* __restrict__ init_state, int chunks_per_seg) {
+                 const float* __restrict__ init_state, int chunks_per_seg, const unsigned char* __restrict__ keep,
+                 const int* __restrict__ count) {
   using namespace ptx;
   // Shared memory: NS stages of the tiles that are only read (forward: Y, Z; dQ: X, Y, Z), a ring of
   // kTcRing tiles for the tile that doubles as the output staging buffer (forward: X; dQ: q), the 16-bit
@@ -672,6 +687,8 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   const int chunk0 = seg * chunks_per_seg;
   const int nchunks = min(chunks_per_seg, total_chunks - chunk0);
   const bool has_init = init_state != nullptr && seg > 0;
+  const unsigned char* keep_b = keep ? keep + static_cast<size_t>(bh / H) * N : nullptr;
+  const int* count_b = count ? count + static_cast<size_t>(bh / H) * N : nullptr;
 
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
@@ -924,9 +941,9 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       unsigned char* sZ = stage_of(c) + kIdxZ * kTileBytes;
       unsigned char* sK = (MODE == kModeDq) ? sZ : stage_of(c) + kIdxY * kTileBytes;
 #if !(COTT_SKEL & 2)
-      const float rk = inv_norm(row_sumsq_rolled<T>(sK, row));
-      const float a = length_factor(static_cast<float>((chunk0 + c) * kTcChunk + row + 1), sigma);
-      scale_row_rolled<T>(sZ, row, rk * a);
+      const RowMask m = row_mask(keep_b, count_b, (chunk0 + c) * kTcChunk + row, N);
+      const float rk = m.kp ? inv_norm(row_sumsq_rolled<T>(sK, row)) : 0.f;
+      scale_row_rolled<T>(sZ, row, rk * length_factor(m.n, sigma));
 #endif
       fence_proxy_async_smem();
       warp_arrive(&bar_prep[s], lane);
@@ -946,7 +963,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       if ((c & 1) != mine) continue;
       COTT_TRACE_EV(7, c);
 #if !(COTT_SKEL & 4)
-      const float rq = inv_norm(row_sumsq_rolled<T>(sQ, row));
+      const float rq = row_mask(keep_b, count_b, (chunk0 + c) * kTcChunk + row, N).kp ? inv_norm(row_sumsq_rolled<T>(sQ, row)) : 0.f;
 #else
       const float rq = 1.f;
 #endif
@@ -1011,7 +1028,7 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                      const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
                      const __grid_constant__ CUtensorMap mapDK, const __grid_constant__ CUtensorMap mapDV, float* __restrict__ dnorm,
                      const float* __restrict__ norm_const, int H, int N, const float* __restrict__ init_state,
-                     int chunks_per_seg) {
+                     int chunks_per_seg, const unsigned char* __restrict__ keep, const int* __restrict__ count) {
   using namespace ptx;
   constexpr int STAGE = 4 * kTileBytes;
   constexpr int NS = kTcStages;
@@ -1042,6 +1059,8 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   const int nchunks = min(chunks_per_seg, total_chunks - chunk0);
   const int last_chunk = chunk0 + nchunks - 1;
   const bool has_init = init_state != nullptr && seg + 1 < static_cast<int>(gridDim.y);
+  const unsigned char* keep_b = keep ? keep + static_cast<size_t>(bh / H) * N : nullptr;
+  const int* count_b = count ? count + static_cast<size_t>(bh / H) * N : nullptr;
 
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
@@ -1219,7 +1238,9 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       const int s = ci % NS;
       if (!wait_bar_warp(&bar_full[s], (ci / NS) & 1, abort_flag, kWaitTma, ci)) return false;
       unsigned char* sQ = smem + s * STAGE;
-      scale_row_rolled<T>(sQ, row, inv_norm(row_sumsq_rolled<T>(sQ, row)));
+      scale_row_rolled<T>(sQ, row, row_mask(keep_b, count_b, (last_chunk - ci) * kTcChunk + row, N).kp
+                                       ? inv_norm(row_sumsq_rolled<T>(sQ, row))
+                                       : 0.f);
       fence_proxy_async_smem();
       warp_arrive(&bar_prep[s], lane);
       return true;
@@ -1278,8 +1299,9 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       unsigned char* sV = smem + s * STAGE + 2 * kTileBytes;
       const int pos = (last_chunk - ci) * kTcChunk + row;
       if (!wait_bar_warp(&bar_full[s], (ci / NS) & 1, abort_flag, kWaitTma, ci)) break;
-      const float rk = inv_norm(row_sumsq_rolled<T>(sK, row));
-      const float a = length_factor(static_cast<float>(pos + 1), sigma);
+      const RowMask m = row_mask(keep_b, count_b, pos, N);
+      const float rk = m.kp ? inv_norm(row_sumsq_rolled<T>(sK, row)) : 0.f;
+      const float a = length_factor(m.n, sigma);
       COTT_TRACE_EV(0, ci);
       if (!wait_bar_warp(&bar_acc_full, ci & 1, abort_flag, kWaitAcc, ci)) break;
       tc_fence_after_sync();
@@ -1299,7 +1321,7 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       COTT_TRACE_EV(5, ci);
       ptx::fence_proxy_async_smem();
       warp_arrive(&bar_out[s], lane);
-      if (pos > 0 && pos < N) gsum += logf(static_cast<float>(pos + 1)) * eps;
+      if (m.n > 1.0f && pos < N) gsum += logf(m.n) * eps;
       COTT_TRACE_EV(6, ci);
     }
 #pragma unroll

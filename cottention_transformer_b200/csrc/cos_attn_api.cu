@@ -40,6 +40,8 @@ int tmap(CUtensorMap* m, const void* p, int dtype, long BH, long N) {
 struct SegPlan {
   int nseg = 1;  // segments actually launched
   int cps = 0;   // chunks per segment
+  const unsigned char* keep = nullptr;  // padding: [B, N] keep flags and their inclusive running count, or both null
+  const int* count = nullptr;
 };
 SegPlan plan_segments(int N, int nseg_requested) {
   const int total = (N + kTcChunk - 1) / kTcChunk;
@@ -62,8 +64,8 @@ int launch_fwd(const void* q, const void* k, const void* v, const float* nc, voi
   auto kern = causal_tc_kernel<T, kModeFwd>;
   const size_t smem = causal_tc_smem_bytes(kModeFwd);
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  if (plan.cps == 0) plan = plan_segments(N, 1);
-  kern<<<dim3((unsigned)BH, plan.nseg), kTcThreads, smem, stream>>>(mq, mk, mv, mq, mo, nc, H, N, init, plan.cps);
+  if (plan.cps == 0) plan.cps = plan_segments(N, 1).cps;
+  kern<<<dim3((unsigned)BH, plan.nseg), kTcThreads, smem, stream>>>(mq, mk, mv, mq, mo, nc, H, N, init, plan.cps, plan.keep, plan.count);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
@@ -81,8 +83,8 @@ int launch_bwd_dq(const void* q, const void* k, const void* v, const float* nc, 
   auto kern = causal_tc_kernel<T, kModeDq>;
   const size_t smem = causal_tc_smem_bytes(kModeDq);
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  if (plan.cps == 0) plan = plan_segments(N, 1);
-  kern<<<dim3((unsigned)BH, plan.nseg), kTcThreads, smem, stream>>>(md, mv, mk, mq, mo, nc, H, N, init, plan.cps);
+  if (plan.cps == 0) plan.cps = plan_segments(N, 1).cps;
+  kern<<<dim3((unsigned)BH, plan.nseg), kTcThreads, smem, stream>>>(md, mv, mk, mq, mo, nc, H, N, init, plan.cps, plan.keep, plan.count);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
@@ -102,8 +104,8 @@ int launch_bwd_dkdv(const void* q, const void* k, const void* v, const float* nc
   auto kern = causal_bwd_kv_kernel<T>;
   const size_t smem = causal_bwd_kv_smem_bytes();
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  if (plan.cps == 0) plan = plan_segments(N, 1);
-  kern<<<dim3((unsigned)BH, plan.nseg), kKvThreads, smem, stream>>>(mq, mk, mv, md, mdk, mdv, dnorm, nc, H, N, init, plan.cps);
+  if (plan.cps == 0) plan.cps = plan_segments(N, 1).cps;
+  kern<<<dim3((unsigned)BH, plan.nseg), kKvThreads, smem, stream>>>(mq, mk, mv, md, mdk, mdv, dnorm, nc, H, N, init, plan.cps, plan.keep, plan.count);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
@@ -119,7 +121,7 @@ int launch_seg_state(const void* y, const void* z, const float* nc, float* state
   auto kern = seg_state_kernel<T, MODE>;
   const size_t smem = seg_state_smem_bytes();
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<dim3((unsigned)BH, plan.nseg), kSegThreads, smem, stream>>>(my, mz, nc, state, H, N, plan.cps);
+  kern<<<dim3((unsigned)BH, plan.nseg), kSegThreads, smem, stream>>>(my, mz, nc, state, H, N, plan.cps, plan.keep, plan.count);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
@@ -130,11 +132,18 @@ int launch_seg_state(const void* y, const void* z, const float* nc, float* state
 size_t seg_array_floats(int B, int H, int nseg) { return (size_t)B * H * nseg * kTcD * kTcD; }
 
 template <typename T>
-int run_fwd_seg(const void* q, const void* k, const void* v, const float* nc, void* out, float* ws, int nseg, int B, int H,
-                int N, int dtype, cudaStream_t stream) {
-  const SegPlan plan = plan_segments(N, nseg);
-  if (plan.nseg == 1) return launch_fwd<T>(q, k, v, nc, out, B, H, N, dtype, stream);
+int run_fwd_seg(const void* q, const void* k, const void* v, const unsigned char* keep, const float* nc, void* out,
+                float* ws, int nseg, int B, int H, int N, int dtype, cudaStream_t stream) {
+  SegPlan plan = plan_segments(N, nseg);
   const size_t A = seg_array_floats(B, H, plan.nseg);
+  if (keep) {  // running count of the kept positions, behind the five state arrays
+    int* count = reinterpret_cast<int*>(ws + 5 * A);
+    keep_count_kernel<<<(unsigned)B, 256, 0, stream>>>(keep, count, N);
+    COTT_CUDA_TRY(cudaGetLastError());
+    plan.keep = keep;
+    plan.count = count;
+  }
+  if (plan.nseg == 1) return launch_fwd<T>(q, k, v, nc, out, B, H, N, dtype, stream, nullptr, plan);
   int st = launch_seg_state<T, kSegFwdState>(k, v, nc, ws, B, H, N, dtype, plan, stream);
   if (st) return st;
   seg_scan_kernel<<<(unsigned)((long)B * H), 256, 0, stream>>>(ws, ws + A, ws + 2 * A, nullptr, plan.nseg);
@@ -143,14 +152,19 @@ int run_fwd_seg(const void* q, const void* k, const void* v, const float* nc, vo
 }
 
 template <typename T>
-int run_bwd_seg(const void* q, const void* k, const void* v, const float* nc, const void* dout, float* ws, int nseg,
-                void* dq, void* dk, void* dv, float* dnorm, int B, int H, int N, int dtype, cudaStream_t stream) {
-  const SegPlan plan = plan_segments(N, nseg);
-  if (plan.nseg == 1) {
-    int st = launch_bwd_dq<T>(q, k, v, nc, dout, dq, B, H, N, dtype, stream);
-    return st ? st : launch_bwd_dkdv<T>(q, k, v, nc, dout, dk, dv, dnorm, B, H, N, dtype, stream);
-  }
+int run_bwd_seg(const void* q, const void* k, const void* v, const unsigned char* keep, const float* nc, const void* dout,
+                float* ws, int nseg, void* dq, void* dk, void* dv, float* dnorm, int B, int H, int N, int dtype,
+                cudaStream_t stream) {
+  SegPlan plan = plan_segments(N, nseg);
   const size_t A = seg_array_floats(B, H, plan.nseg);
+  if (keep) {  // the forward call left the running count in the workspace
+    plan.keep = keep;
+    plan.count = reinterpret_cast<const int*>(ws + 5 * A);
+  }
+  if (plan.nseg == 1) {
+    int st = launch_bwd_dq<T>(q, k, v, nc, dout, dq, B, H, N, dtype, stream, nullptr, plan);
+    return st ? st : launch_bwd_dkdv<T>(q, k, v, nc, dout, dk, dv, dnorm, B, H, N, dtype, stream, nullptr, plan);
+  }
   // dQ: the forward prefix states, transposed (written by the forward call into the same workspace)
   int st = launch_bwd_dq<T>(q, k, v, nc, dout, dq, B, H, N, dtype, stream, ws + 2 * A, plan);
   if (st) return st;
@@ -308,11 +322,12 @@ int cott_cos_attn_seg_count(int B, int H, int N) {
 
 size_t cott_cos_attn_seg_workspace_bytes(int B, int H, int N, int nseg) {
   if (B <= 0 || H <= 0 || N <= 0) return 0;
-  return 5 * seg_array_floats(B, H, plan_segments(N, nseg).nseg) * sizeof(float);
+  return 5 * seg_array_floats(B, H, plan_segments(N, nseg).nseg) * sizeof(float) + (size_t)B * N * sizeof(int);
 }
 
-int cott_cos_attn_fwd_seg(const void* q, const void* k, const void* v, const float* norm_const, void* out,
-                          void* workspace, int nseg, int B, int H, int N, int Dk, int Dv, int dtype, void* stream) {
+int cott_cos_attn_fwd_seg(const void* q, const void* k, const void* v, const unsigned char* keep,
+                          const float* norm_const, void* out, void* workspace, int nseg, int B, int H, int N, int Dk,
+                          int Dv, int dtype, void* stream) {
   int st = check_fused_args(B, H, N, Dk, Dv, dtype);
   if (st) return st;
   if ((long)B * H * N == 0) return COTT_OK;
@@ -322,13 +337,13 @@ int cott_cos_attn_fwd_seg(const void* q, const void* k, const void* v, const flo
   COTT_CUDA_TRY(scope.status());
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   float* ws = static_cast<float*>(workspace);
-  return dtype == COTT_BF16 ? run_fwd_seg<__nv_bfloat16>(q, k, v, norm_const, out, ws, nseg, B, H, N, dtype, s)
-                            : run_fwd_seg<__half>(q, k, v, norm_const, out, ws, nseg, B, H, N, dtype, s);
+  return dtype == COTT_BF16 ? run_fwd_seg<__nv_bfloat16>(q, k, v, keep, norm_const, out, ws, nseg, B, H, N, dtype, s)
+                            : run_fwd_seg<__half>(q, k, v, keep, norm_const, out, ws, nseg, B, H, N, dtype, s);
 }
 
-int cott_cos_attn_bwd_seg(const void* q, const void* k, const void* v, const float* norm_const, const void* dout,
-                          void* workspace, int nseg, void* dq, void* dk, void* dv, float* dnorm_const, int B, int H,
-                          int N, int Dk, int Dv, int dtype, void* stream) {
+int cott_cos_attn_bwd_seg(const void* q, const void* k, const void* v, const unsigned char* keep,
+                          const float* norm_const, const void* dout, void* workspace, int nseg, void* dq, void* dk,
+                          void* dv, float* dnorm_const, int B, int H, int N, int Dk, int Dv, int dtype, void* stream) {
   int st = check_fused_args(B, H, N, Dk, Dv, dtype);
   if (st) return st;
   if (!dnorm_const && H > 0) return fail(COTT_ERR_NULL, "null pointer: dnorm_const");
@@ -345,8 +360,8 @@ int cott_cos_attn_bwd_seg(const void* q, const void* k, const void* v, const flo
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   float* ws = static_cast<float*>(workspace);
   return dtype == COTT_BF16
-             ? run_bwd_seg<__nv_bfloat16>(q, k, v, norm_const, dout, ws, nseg, dq, dk, dv, dnorm_const, B, H, N, dtype, s)
-             : run_bwd_seg<__half>(q, k, v, norm_const, dout, ws, nseg, dq, dk, dv, dnorm_const, B, H, N, dtype, s);
+             ? run_bwd_seg<__nv_bfloat16>(q, k, v, keep, norm_const, dout, ws, nseg, dq, dk, dv, dnorm_const, B, H, N, dtype, s)
+             : run_bwd_seg<__half>(q, k, v, keep, norm_const, dout, ws, nseg, dq, dk, dv, dnorm_const, B, H, N, dtype, s);
 }
 
 int cott_check_status(int* detail) {

@@ -122,15 +122,19 @@ int cott_cos_attn_bwd_dkdv(const void* q, const void* k, const void* v, const fl
  *   cott_cos_attn_seg_count            suggested nseg for this device (1 = use the plain calls)
  *   cott_cos_attn_seg_workspace_bytes  size of `workspace` (device memory, 16-byte aligned) for that nseg
  *   _fwd_seg writes the segment states into `workspace`; pass the same buffer and nseg, untouched, to _bwd_seg.
+ * These two calls also take the padding mask of GPTCosAttention.py:232-248: `keep` ([B, N] bytes, non-zero =
+ * un-masked, NULL = no padding) zeroes the masked rows of q^, k^, v' and makes n_s the running count of
+ * un-masked positions; nseg = 1 is allowed (one CTA per sequence, workspace still needed for the count).
  */
 int cott_cos_attn_seg_count(int B, int H, int N);
 size_t cott_cos_attn_seg_workspace_bytes(int B, int H, int N, int nseg);
-int cott_cos_attn_fwd_seg(const void* q, const void* k, const void* v, const float* norm_const, void* out,
-                          void* workspace, int nseg, int B, int H, int N, int Dk, int Dv, int dtype,
-                          void* stream);
-int cott_cos_attn_bwd_seg(const void* q, const void* k, const void* v, const float* norm_const,
-                          const void* dout, void* workspace, int nseg, void* dq, void* dk, void* dv,
-                          float* dnorm_const, int B, int H, int N, int Dk, int Dv, int dtype, void* stream);
+int cott_cos_attn_fwd_seg(const void* q, const void* k, const void* v, const unsigned char* keep,
+                          const float* norm_const, void* out, void* workspace, int nseg, int B, int H, int N,
+                          int Dk, int Dv, int dtype, void* stream);
+int cott_cos_attn_bwd_seg(const void* q, const void* k, const void* v, const unsigned char* keep,
+                          const float* norm_const, const void* dout, void* workspace, int nseg, void* dq,
+                          void* dk, void* dv, float* dnorm_const, int B, int H, int N, int Dk, int Dv,
+                          int dtype, void* stream);
 
 /*
  * Recurrent decode.  Per (batch, head) a float32 state[b,h,j,i] ([B,H,Dv,Dk], updated in place) is

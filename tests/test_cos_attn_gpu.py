@@ -142,3 +142,35 @@ def test_segment_parallel_agrees_with_one_cta_per_sequence_long():
                               scan=lambda a, bb, c: O.scan_recurrent(a, bb, c, False, "f64"))
     e_max, e_fro = _rel(res[9][0][:, 1:2], truth)
     assert e_max <= REL16 and e_fro <= REL16, (e_max, e_fro)
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(2, 2, 100), (2, 3, 640), (3, 1, 1000)])
+@pytest.mark.parametrize("segments", [1, 3])
+def test_fused_with_padding_mask_matches_oracle(dt, shape, segments):
+    """Padding as in GPTCosAttention.py:232-248: right-padded, left-padded and holed batch entries; n_s is the
+    running count of kept positions, masked rows give zero outputs and zero gradients."""
+    from cottention_transformer_b200 import cos_attn_causal, _lib
+    B, H, N = shape
+    q, k, v, do, _ = O.make_inputs(B, H, N, 64, 64, seed=3 * N + H, normalize=False, dtype=dt)
+    nc = torch.linspace(-0.5, 1.0, H)
+    keep = torch.ones(B, N, dtype=torch.bool)
+    keep[0, (2 * N) // 3:] = False          # right padding
+    keep[-1, : N // 4] = False              # left padding
+    keep[-1, N // 2: N // 2 + 5] = False    # a hole
+    qd, kd, vd = (t.double().requires_grad_() for t in (q, k, v))
+    ncd = nc.double().requires_grad_()
+    ref = O.cos_attn_causal(qd, kd, vd, ncd, keep)
+    (ref * do.double()).sum().backward()
+    qc, kc, vc = (t.cuda().requires_grad_() for t in (q, k, v))
+    ncc = nc.cuda().requires_grad_()
+    out = cos_attn_causal(qc, kc, vc, ncc, keep.cuda(), segments=segments)
+    out.backward(do.cuda())
+    _lib.check_device_status()
+    for name, a, r in (("out", out, ref.detach()), ("dq", qc.grad, qd.grad), ("dk", kc.grad, kd.grad), ("dv", vc.grad, vd.grad)):
+        e_max, e_fro = _rel(a, r)
+        assert e_max <= REL16 and e_fro <= REL16, (name, e_max, e_fro)
+    masked = ~keep
+    assert out.detach().cpu()[masked.view(B, 1, N).expand(B, H, N)].abs().max().item() == 0.0
+    e = (ncc.grad.double().cpu() - ncd.grad).abs().max().item()
+    assert e <= REL16 * max(ncd.grad.abs().max().item(), 1e-3), (e, ncd.grad)
