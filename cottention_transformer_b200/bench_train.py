@@ -1,0 +1,146 @@
+"""Whole-model training-step harnesses around the cosine-attention op (synthetic data, random weights).
+
+    python -m cottention_transformer_b200.bench_train --model gpt  [--steps 10 --warmup 3]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        -m cottention_transformer_b200.bench_train --model bert
+
+gpt:  24 layers, d_model 1024, 16 heads of 64, MLP 4096 (GELU), pre-LayerNorm, vocab 50304, sequence 1024,
+      batch 8 per GPU, causal cosine attention (``cos_attn_causal``), next-token loss.
+bert: 12 layers, hidden 768, 12 heads of 64, intermediate 3072, vocab 30522, sequence 512, batch 32 per GPU,
+      bidirectional cosine attention (``cos_attn_bidirectional``), masked-LM loss on 15 % of the positions.
+bf16 autocast, fused AdamW, DDP over NCCL when launched with more than one rank.  These are minimal models
+with the reference trainers' attention call sites (GPT_Trainer/GPTCosAttention.py:282,
+BERT_Trainer/BertCosAttention.py:249), not the reference's HuggingFace model classes; token ids are uniform
+random, so the loss value means nothing -- the harness measures tokens/s of a full step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .cos_attention import cos_attn_bidirectional, cos_attn_causal
+
+
+class CosSelfAttention(nn.Module):
+    def __init__(self, d_model, n_heads, causal):
+        super().__init__()
+        self.h, self.causal = n_heads, causal
+        self.qkv = nn.Linear(d_model, 3 * d_model, bias=not causal)
+        self.proj = nn.Linear(d_model, d_model, bias=not causal)
+        self.norm_const = nn.Parameter(0.5 * torch.ones(1, n_heads, 1, 1))  # GPTCosAttention.py:89
+
+    def forward(self, x):
+        B, S, D = x.shape
+        qkv = self.qkv(x).view(B, S, 3, self.h, D // self.h).permute(2, 0, 3, 1, 4).contiguous()  # [3,B,H,S,d]
+        op = cos_attn_causal if self.causal else cos_attn_bidirectional
+        o = op(qkv[0], qkv[1], qkv[2], self.norm_const)
+        return self.proj(o.transpose(1, 2).reshape(B, S, D))
+
+
+class Block(nn.Module):
+    def __init__(self, d_model, n_heads, d_ff, causal, pre_ln):
+        super().__init__()
+        self.pre_ln = pre_ln
+        self.attn = CosSelfAttention(d_model, n_heads, causal)
+        self.ln1, self.ln2 = nn.LayerNorm(d_model), nn.LayerNorm(d_model)
+        self.fc1, self.fc2 = nn.Linear(d_model, d_ff), nn.Linear(d_ff, d_model)
+
+    def forward(self, x):
+        if self.pre_ln:
+            x = x + self.attn(self.ln1(x))
+            return x + self.fc2(F.gelu(self.fc1(self.ln2(x))))
+        x = self.ln1(x + self.attn(x))
+        return self.ln2(x + self.fc2(F.gelu(self.fc1(x))))
+
+
+class Model(nn.Module):
+    def __init__(self, vocab, seq, d_model, n_layers, n_heads, d_ff, causal):
+        super().__init__()
+        self.tok, self.pos = nn.Embedding(vocab, d_model), nn.Embedding(seq, d_model)
+        self.blocks = nn.ModuleList(Block(d_model, n_heads, d_ff, causal, pre_ln=causal) for _ in range(n_layers))
+        self.ln_f = nn.LayerNorm(d_model)
+        self.head = nn.Linear(d_model, vocab, bias=False)
+        self.head.weight = self.tok.weight  # tied
+
+    def forward(self, ids):
+        x = self.tok(ids) + self.pos(torch.arange(ids.shape[1], device=ids.device))
+        for b in self.blocks:
+            x = b(x)
+        return self.head(self.ln_f(x))
+
+
+CONFIGS = {
+    "gpt": dict(vocab=50304, seq=1024, d_model=1024, n_layers=24, n_heads=16, d_ff=4096, causal=True, batch=8),
+    "bert": dict(vocab=30522, seq=512, d_model=768, n_layers=12, n_heads=12, d_ff=3072, causal=False, batch=32),
+}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", choices=list(CONFIGS), default="gpt")
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (smoke runs)")
+    a = ap.parse_args()
+    world, rank, local = (int(os.environ.get(k, d)) for k, d in (("WORLD_SIZE", 1), ("RANK", 0), ("LOCAL_RANK", 0)))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=dev)
+    cfg = dict(CONFIGS[a.model])
+    batch = cfg.pop("batch")
+    if a.layers:
+        cfg["n_layers"] = a.layers
+    torch.manual_seed(1234)
+    model = Model(**cfg).to(dev)
+    n_params = sum(p.numel() for p in model.parameters())
+    net = nn.parallel.DistributedDataParallel(model, device_ids=[local]) if world > 1 else model
+    opt = torch.optim.AdamW(net.parameters(), lr=1e-4, fused=True)
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    ids = torch.randint(0, cfg["vocab"], (batch, cfg["seq"]), device=dev, generator=g)
+    if cfg["causal"]:
+        inp, labels = ids, torch.roll(ids, -1, 1)
+    else:  # 15 % of the positions are replaced by a mask id and carry the label
+        pick = torch.rand(ids.shape, device=dev, generator=g) < 0.15
+        inp, labels = torch.where(pick, torch.full_like(ids, 103), ids), torch.where(pick, ids, torch.full_like(ids, -100))
+
+    def step():
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            logits = net(inp)
+        loss = F.cross_entropy(logits.float().view(-1, cfg["vocab"]), labels.view(-1), ignore_index=-100)
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return loss
+
+    for _ in range(a.warmup):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        torch.distributed.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.steps):
+        loss = step()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / a.steps], device=dev)
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    if rank == 0:
+        ms = t.item()
+        print(json.dumps({"what": f"{a.model} training step, {cfg['n_layers']} layers, bf16 autocast, AdamW"
+                                  + (", DDP" if world > 1 else ""), "params_M": n_params / 1e6, "n_gpus": world,
+                          "batch_per_gpu": batch, "seq_len": cfg["seq"], "ms_per_step": ms,
+                          "tokens_per_s": world * batch * cfg["seq"] / ms * 1e3, "loss": float(loss), "data": "synthetic"}))
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

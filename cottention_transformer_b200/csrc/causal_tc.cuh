@@ -97,64 +97,6 @@ __device__ __forceinline__ uint4* tile_piece(unsigned char* tile, int row, int j
   return reinterpret_cast<uint4*>(tile + row * 128 + ((j ^ (row & 7)) << 4));
 }
 
-template <typename T>
-__device__ __forceinline__ void load_row(unsigned char* tile, int row, float* x /*64*/) {
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    uint4 u = *tile_piece(tile, row, j);
-    float2 a = Pack2<T>::unpack(u.x), b = Pack2<T>::unpack(u.y), c = Pack2<T>::unpack(u.z),
-           d = Pack2<T>::unpack(u.w);
-    x[8 * j + 0] = a.x; x[8 * j + 1] = a.y; x[8 * j + 2] = b.x; x[8 * j + 3] = b.y;
-    x[8 * j + 4] = c.x; x[8 * j + 5] = c.y; x[8 * j + 6] = d.x; x[8 * j + 7] = d.y;
-  }
-}
-
-// (packed 16-bit row u) . y : 8 independent chains of 8, then a tree
-template <typename T>
-__device__ __forceinline__ float packed_dot64(const uint4* u, const float* y) {
-  float s[8];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    float2 a = Pack2<T>::unpack(u[j].x), b = Pack2<T>::unpack(u[j].y), c = Pack2<T>::unpack(u[j].z),
-           d = Pack2<T>::unpack(u[j].w);
-    const float* yy = y + 8 * j;
-    s[j] = fmaf(a.x, yy[0], fmaf(b.x, yy[2], fmaf(c.x, yy[4], d.x * yy[6]))) +
-           fmaf(a.y, yy[1], fmaf(b.y, yy[3], fmaf(c.y, yy[5], d.y * yy[7])));
-  }
-  return ((s[0] + s[1]) + (s[2] + s[3])) + ((s[4] + s[5]) + (s[6] + s[7]));
-}
-// y = beta y + alpha (packed 16-bit row u)
-template <typename T>
-__device__ __forceinline__ void packed_axpby64(const uint4* u, float alpha, float beta, float* y) {
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    float2 a = Pack2<T>::unpack(u[j].x), b = Pack2<T>::unpack(u[j].y), c = Pack2<T>::unpack(u[j].z),
-           d = Pack2<T>::unpack(u[j].w);
-    float* yy = y + 8 * j;
-    yy[0] = fmaf(beta, yy[0], alpha * a.x); yy[1] = fmaf(beta, yy[1], alpha * a.y);
-    yy[2] = fmaf(beta, yy[2], alpha * b.x); yy[3] = fmaf(beta, yy[3], alpha * b.y);
-    yy[4] = fmaf(beta, yy[4], alpha * c.x); yy[5] = fmaf(beta, yy[5], alpha * c.y);
-    yy[6] = fmaf(beta, yy[6], alpha * d.x); yy[7] = fmaf(beta, yy[7], alpha * d.y);
-  }
-}
-
-template <typename T>
-__device__ __forceinline__ float row_sumsq(unsigned char* tile, int row) {
-  // all loads first, then 16 independent chains of 4: the row is on the critical path of its role
-  uint4 u[8];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) u[j] = *tile_piece(tile, row, j);
-  float s[8];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    float2 a = Pack2<T>::unpack(u[j].x), b = Pack2<T>::unpack(u[j].y), c = Pack2<T>::unpack(u[j].z),
-           d = Pack2<T>::unpack(u[j].w);
-    s[j] = fmaf(a.x, a.x, fmaf(b.x, b.x, fmaf(c.x, c.x, d.x * d.x))) +
-           fmaf(a.y, a.y, fmaf(b.y, b.y, fmaf(c.y, c.y, d.y * d.y)));
-  }
-  return ((s[0] + s[1]) + (s[2] + s[3])) + ((s[4] + s[5]) + (s[6] + s[7]));
-}
-
 // tile[row] *= w (in place), in packed 16-bit arithmetic.  w is split into a 16-bit head and a
 // 16-bit tail, and x*w = fma(x, w_hi, x*w_lo): the tail product is tiny, so the result carries one
 // 16-bit rounding, the same as converting the fp32 product -- at 2 instructions per element pair.
@@ -169,44 +111,6 @@ template <> struct Vec2<__half> {
   static __device__ __forceinline__ type bcast(float x) { return __float2half2_rn(x); }
   static __device__ __forceinline__ float head(float x) { return __half2float(__float2half_rn(x)); }
 };
-template <typename T>
-__device__ __forceinline__ void scale_row(unsigned char* tile, int row, float w) {
-  if constexpr (Pack2<T>::kBf16) {
-    using V = typename Vec2<T>::type;
-    const float wh = Vec2<T>::head(w);
-    const V whi = Vec2<T>::bcast(wh), wlo = Vec2<T>::bcast(w - wh);
-    // loads, arithmetic and stores in three separate sweeps: the compiler cannot tell that the eight
-    // pieces do not alias, and would otherwise chain load -> store -> load
-    uint4 u[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) u[j] = *tile_piece(tile, row, j);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      V* x = reinterpret_cast<V*>(&u[j]);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) x[e] = __hfma2(x[e], whi, __hmul2(x[e], wlo));
-    }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) *tile_piece(tile, row, j) = u[j];
-  } else {
-    // float16 has too little range to hold the factor itself (1/|k| of a small row): multiply in fp32
-    uint4 u[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) u[j] = *tile_piece(tile, row, j);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float2 a = Pack2<T>::unpack(u[j].x), b = Pack2<T>::unpack(u[j].y), c = Pack2<T>::unpack(u[j].z),
-             d = Pack2<T>::unpack(u[j].w);
-      u[j].x = Pack2<T>::pack(a.x * w, a.y * w);
-      u[j].y = Pack2<T>::pack(b.x * w, b.y * w);
-      u[j].z = Pack2<T>::pack(c.x * w, c.y * w);
-      u[j].w = Pack2<T>::pack(d.x * w, d.y * w);
-    }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) *tile_piece(tile, row, j) = u[j];
-  }
-}
-
 // One MUFU.RSQ.  A non-zero 16-bit row has |x| >= 6e-8 > 1e-12, so the epsilon only ever matters for
 // an all-zero row, whose normalised value is zero whatever the factor: return 0 there (a huge factor
 // would overflow the 16-bit operand it is folded into).
@@ -310,7 +214,6 @@ __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
 // 32-column blocks that hold at least one surviving element for ANY row of the warp (warp-uniform).
 template <typename T>
 __device__ __forceinline__ void mask_pack_inplace(uint32_t taddr_lane, int lo, int hi, int blk_lo, int blk_hi) {
-#ifndef COTT_MASK_UNROLLED
   // One 32-column block per iteration of a loop that is NOT unrolled: the fully unrolled form is four
   // times the code, and the roles of this kernel already overflow the instruction cache.  Packed block
   // b lands on fp32 columns 16b .. 16b+15, which belong to block b/2 <= b: already read.
@@ -335,90 +238,10 @@ __device__ __forceinline__ void mask_pack_inplace(uint32_t taddr_lane, int lo, i
     ptx::tmem_st_x16(taddr_lane + 16 * blk, packed);
   }
   ptx::tmem_st_wait();
-  return;
-#endif
-#pragma unroll
-  for (int p = 0; p < 2; ++p) {
-    uint32_t packed[32];
-    if (2 * p + 1 < blk_lo || 2 * p > blk_hi) {  // warp-uniform: the whole 64-column half is masked out
-#pragma unroll
-      for (int j = 0; j < 32; ++j) packed[j] = 0u;
-    } else {
-      uint32_t r[64];
-      ptx::tmem_ld_x64(taddr_lane + 64 * p, r);
-      ptx::tmem_ld_wait();
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const int s0 = 64 * p + 2 * j;
-        const float x0 = (s0 >= lo && s0 <= hi) ? __uint_as_float(r[2 * j]) : 0.f;
-        const float x1 = (s0 + 1 >= lo && s0 + 1 <= hi) ? __uint_as_float(r[2 * j + 1]) : 0.f;
-        packed[j] = Pack2<T>::pack(x0, x1);
-      }
-    }
-    ptx::tmem_st_x32(taddr_lane + 32 * p, packed);
-  }
-  ptx::tmem_st_wait();
-}
-
-// 64 fp32 columns of this thread's TMEM lane -> registers
-__device__ __forceinline__ void tmem_row64(uint32_t taddr_lane, float* x) {
-  uint32_t r[64];
-  ptx::tmem_ld_x64(taddr_lane, r);
-  ptx::tmem_ld_wait();
-#pragma unroll
-  for (int j = 0; j < 64; ++j) x[j] = __uint_as_float(r[j]);
-}
-
-// Row `row` of a swizzled [128 x 64] 16-bit tile <- 64 floats (the layout a TMA store with the same
-// 128-byte swizzle reads).
-template <typename T>
-__device__ __forceinline__ void write_row64(unsigned char* tile, int row, const float* x) {
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    uint4 u;
-    u.x = Pack2<T>::pack(x[8 * j + 0], x[8 * j + 1]);
-    u.y = Pack2<T>::pack(x[8 * j + 2], x[8 * j + 3]);
-    u.z = Pack2<T>::pack(x[8 * j + 4], x[8 * j + 5]);
-    u.w = Pack2<T>::pack(x[8 * j + 6], x[8 * j + 7]);
-    *tile_piece(tile, row, j) = u;
-  }
-}
-
-template <typename T>
-__device__ __forceinline__ void store_row64(T* dst_row, const float* x) {
-  uint4* dst = reinterpret_cast<uint4*>(dst_row);
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    uint4 u;
-    u.x = Pack2<T>::pack(x[8 * j + 0], x[8 * j + 1]);
-    u.y = Pack2<T>::pack(x[8 * j + 2], x[8 * j + 3]);
-    u.z = Pack2<T>::pack(x[8 * j + 4], x[8 * j + 5]);
-    u.w = Pack2<T>::pack(x[8 * j + 6], x[8 * j + 7]);
-    dst[j] = u;
-  }
 }
 
 // fp32 state (M=64 accumulator: row i sits in TMEM lane 32*(i/16) + i%16, so lanes 0-15 of the warp
 // that owns sub-partition q hold rows 16q .. 16q+15) -> 16-bit [64 x 64] swizzled smem operand.
-template <typename T>
-__device__ __forceinline__ void state_to_smem(uint32_t tS_lane, unsigned char* sS, int wq, int lane) {
-  uint32_t r[64];
-  ptx::tmem_ld_x64(tS_lane, r);
-  ptx::tmem_ld_wait();
-  if (lane < 16) {
-    const int i = 16 * wq + lane;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      uint4 u;
-      u.x = Pack2<T>::pack(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
-      u.y = Pack2<T>::pack(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
-      u.z = Pack2<T>::pack(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
-      u.w = Pack2<T>::pack(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
-      *tile_piece(sS, i, j) = u;
-    }
-  }
-}
-
 // ---- rolled row routines ---------------------------------------------------------------------------
 // The per-row work below is written as loops that are NOT unrolled (16 columns = two 16-byte pieces per
 // trip).  Every role of these kernels runs on every scheduler, so the roles' code competes for one
@@ -596,7 +419,7 @@ __device__ __forceinline__ void state_to_smem_rolled(uint32_t tS_lane, unsigned 
 // of the warp belong to no row of that layout and receive a copy of lanes 0-15) and, as 16 bits, into the
 // swizzled smem operand.  The caller waits for the TMEM stores (tcgen05.wait::st) and fences.
 template <typename T>
-__device__ __forceinline__ void load_init_state(const float* state, uint32_t tS_lane, unsigned char* sS, int wq, int lane) {
+__device__ __noinline__ void load_init_state(const float* state, uint32_t tS_lane, unsigned char* sS, int wq, int lane) {
   const float* src = state + (16 * wq + (lane & 15)) * kTcD;
 #pragma unroll 1
   for (int half = 0; half < 2; ++half) {
@@ -640,13 +463,15 @@ constexpr int kKvThreads = 480;  // dK/dV: 2 issuing warps, 3 groups of 4 warps,
 constexpr int kTcStages = 3;
 constexpr int kTcRing = kTcStages + 1;  // slots of the tile that doubles as output staging buffer (forward / dQ)
 
-template <typename T, int MODE>
+// EXT = false compiles the segment / padding arguments away (they must be null / one segment): these kernels are
+// sensitive to every instruction added to their loops, and the common case needs neither.
+template <typename T, int MODE, bool EXT>
 __global__ void __launch_bounds__(kTcThreads, 1)
 causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapY,
                  const __grid_constant__ CUtensorMap mapZ, const __grid_constant__ CUtensorMap mapQ,
                  const __grid_constant__ CUtensorMap mapOut, const float* __restrict__ norm_const, int H, int N,
-                 const float* __restrict__ init_state, int chunks_per_seg, const unsigned char* __restrict__ keep,
-                 const int* __restrict__ count) {
+                 const float* __restrict__ init_state_arg, int chunks_per_seg_arg,
+                 const unsigned char* __restrict__ keep_arg, const int* __restrict__ count_arg) {
   using namespace ptx;
   // Shared memory: NS stages of the tiles that are only read (forward: Y, Z; dQ: X, Y, Z), a ring of
   // kTcRing tiles for the tile that doubles as the output staging buffer (forward: X; dQ: q), the 16-bit
@@ -683,12 +508,14 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   // sequence and the state before its first chunk (`init_state[bh][seg]`, fp32 [64 x 64] in this kernel's
   // own state layout, rows = columns of Y); chunk numbers below are local, `chunk0 + c` is the position.
   const int total_chunks = (N + kTcChunk - 1) / kTcChunk;
-  const int seg = blockIdx.y;
+  const float* init_state = EXT ? init_state_arg : nullptr;
+  const int chunks_per_seg = EXT ? chunks_per_seg_arg : total_chunks;
+  const int seg = EXT ? static_cast<int>(blockIdx.y) : 0;
   const int chunk0 = seg * chunks_per_seg;
-  const int nchunks = min(chunks_per_seg, total_chunks - chunk0);
-  const bool has_init = init_state != nullptr && seg > 0;
-  const unsigned char* keep_b = keep ? keep + static_cast<size_t>(bh / H) * N : nullptr;
-  const int* count_b = count ? count + static_cast<size_t>(bh / H) * N : nullptr;
+  const int nchunks = EXT ? min(chunks_per_seg, total_chunks - chunk0) : total_chunks;
+  const bool has_init = EXT && init_state != nullptr && seg > 0;
+  const unsigned char* keep_b = (EXT && keep_arg) ? keep_arg + static_cast<size_t>(bh / H) * N : nullptr;
+  const int* count_b = (EXT && count_arg) ? count_arg + static_cast<size_t>(bh / H) * N : nullptr;
 
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
@@ -1022,13 +849,14 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
 //   d norm_const[h] += -sigma (1 - sigma) sum_s ln(n_s) eps_s         (GPTCosAttention.py:241 by the chain rule)
 // Same warp roles as causal_tc_kernel; the two score tiles fill TMEM, so they are single-buffered:
 // the score MMAs of chunk c+1 are queued right behind the accumulator MMAs of chunk c.
-template <typename T>
+template <typename T, bool EXT>
 __global__ void __launch_bounds__(kKvThreads, 1)
 causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                      const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
                      const __grid_constant__ CUtensorMap mapDK, const __grid_constant__ CUtensorMap mapDV, float* __restrict__ dnorm,
-                     const float* __restrict__ norm_const, int H, int N, const float* __restrict__ init_state,
-                     int chunks_per_seg, const unsigned char* __restrict__ keep, const int* __restrict__ count) {
+                     const float* __restrict__ norm_const, int H, int N, const float* __restrict__ init_state_arg,
+                     int chunks_per_seg_arg, const unsigned char* __restrict__ keep_arg,
+                     const int* __restrict__ count_arg) {
   using namespace ptx;
   constexpr int STAGE = 4 * kTileBytes;
   constexpr int NS = kTcStages;
@@ -1054,13 +882,15 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   // backwards, and starts from the state of everything after them (`init_state[bh][seg]`, fp32 [64 x 64],
   // rows d_k).  `ci` is local; the position of item ci is chunk `last_chunk - ci`.
   const int total_chunks = (N + kTcChunk - 1) / kTcChunk;
-  const int seg = blockIdx.y;
+  const float* init_state = EXT ? init_state_arg : nullptr;
+  const int chunks_per_seg = EXT ? chunks_per_seg_arg : total_chunks;
+  const int seg = EXT ? static_cast<int>(blockIdx.y) : 0;
   const int chunk0 = seg * chunks_per_seg;
-  const int nchunks = min(chunks_per_seg, total_chunks - chunk0);
+  const int nchunks = EXT ? min(chunks_per_seg, total_chunks - chunk0) : total_chunks;
   const int last_chunk = chunk0 + nchunks - 1;
-  const bool has_init = init_state != nullptr && seg + 1 < static_cast<int>(gridDim.y);
-  const unsigned char* keep_b = keep ? keep + static_cast<size_t>(bh / H) * N : nullptr;
-  const int* count_b = count ? count + static_cast<size_t>(bh / H) * N : nullptr;
+  const bool has_init = EXT && init_state != nullptr && seg + 1 < static_cast<int>(gridDim.y);
+  const unsigned char* keep_b = (EXT && keep_arg) ? keep_arg + static_cast<size_t>(bh / H) * N : nullptr;
+  const int* count_b = (EXT && count_arg) ? count_arg + static_cast<size_t>(bh / H) * N : nullptr;
 
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {

@@ -61,7 +61,8 @@ int launch_fwd(const void* q, const void* k, const void* v, const float* nc, voi
   if ((st = tmap(&mq, q, dtype, BH, N)) || (st = tmap(&mk, k, dtype, BH, N)) || (st = tmap(&mv, v, dtype, BH, N)) ||
       (st = tmap(&mo, out, dtype, BH, N)))
     return st;
-  auto kern = causal_tc_kernel<T, kModeFwd>;
+  const bool ext = plan.nseg > 1 || init || plan.keep;
+  auto kern = ext ? causal_tc_kernel<T, kModeFwd, true> : causal_tc_kernel<T, kModeFwd, false>;
   const size_t smem = causal_tc_smem_bytes(kModeFwd);
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   if (plan.cps == 0) plan.cps = plan_segments(N, 1).cps;
@@ -80,7 +81,8 @@ int launch_bwd_dq(const void* q, const void* k, const void* v, const float* nc, 
       (st = tmap(&mv, v, dtype, BH, N)) || (st = tmap(&md, dout, dtype, BH, N)) ||
       (st = tmap(&mo, dq, dtype, BH, N)))
     return st;
-  auto kern = causal_tc_kernel<T, kModeDq>;
+  const bool ext = plan.nseg > 1 || init || plan.keep;
+  auto kern = ext ? causal_tc_kernel<T, kModeDq, true> : causal_tc_kernel<T, kModeDq, false>;
   const size_t smem = causal_tc_smem_bytes(kModeDq);
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   if (plan.cps == 0) plan.cps = plan_segments(N, 1).cps;
@@ -101,7 +103,8 @@ int launch_bwd_dkdv(const void* q, const void* k, const void* v, const float* nc
       (st = tmap(&mdk, dk, dtype, BH, N)) || (st = tmap(&mdv, dv, dtype, BH, N)))
     return st;
   COTT_CUDA_TRY(cudaMemsetAsync(dnorm, 0, sizeof(float) * H, stream));
-  auto kern = causal_bwd_kv_kernel<T>;
+  const bool ext = plan.nseg > 1 || init || plan.keep;
+  auto kern = ext ? causal_bwd_kv_kernel<T, true> : causal_bwd_kv_kernel<T, false>;
   const size_t smem = causal_bwd_kv_smem_bytes();
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   if (plan.cps == 0) plan.cps = plan_segments(N, 1).cps;

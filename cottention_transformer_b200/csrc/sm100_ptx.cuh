@@ -192,44 +192,6 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
       "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-// Warp-uniform issue: the WHOLE warp executes the call with identical (uniform) operands and only
-// the lane for which `elected` is non-zero issues.  Keeping the operand arithmetic warp-uniform lets
-// the compiler keep descriptors in uniform registers, which makes the issue much cheaper than a
-// single-lane `if (lane == 0)` region when the scheduler is shared with busy warps.
-__device__ __forceinline__ void mma_ss_e(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                         uint32_t accumulate, uint32_t elected) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p, q;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "setp.ne.b32 q, %5, 0;\n"
-      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-      "}\n" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(elected)
-      : "memory");
-}
-__device__ __forceinline__ void mma_ts_e(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                         uint32_t accumulate, uint32_t elected) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p, q;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "setp.ne.b32 q, %5, 0;\n"
-      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
-      "}\n" ::"r"(d_tmem),
-      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(elected)
-      : "memory");
-}
-__device__ __forceinline__ void mma_commit_e(uint64_t* bar, uint32_t elected) {
-  asm volatile(
-      "{\n"
-      ".reg .pred q;\n"
-      "setp.ne.b32 q, %1, 0;\n"
-      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
-      "}\n" ::"r"(smem_u32(bar)),
-      "r"(elected)
-      : "memory");
-}
 // Arrive on an mbarrier when all MMAs issued so far by this thread have completed.
 // Implies tcgen05.fence::before_thread_sync.
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
