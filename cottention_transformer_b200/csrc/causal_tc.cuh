@@ -461,7 +461,7 @@ enum {
 constexpr int kTcThreads = 896;  // forward / dQ: 3 issuing warps, 6 groups of 4 warps, 1 TMA warp
 constexpr int kKvThreads = 480;  // dK/dV: 2 issuing warps, 3 groups of 4 warps, 1 TMA warp
 constexpr int kTcStages = 3;
-constexpr int kTcRing = kTcStages + 1;  // slots of the tile that doubles as output staging buffer (forward / dQ)
+constexpr int kTcStagesFwd = 4;  // the forward kernel has the shared memory for a deeper ring (2 tiles per stage)
 
 // EXT = false compiles the segment / padding arguments away (they must be null / one segment): these kernels are
 // sensitive to every instruction added to their loops, and the common case needs neither.
@@ -474,12 +474,13 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
                  const unsigned char* __restrict__ keep_arg, const int* __restrict__ count_arg) {
   using namespace ptx;
   // Shared memory: NS stages of the tiles that are only read (forward: Y, Z; dQ: X, Y, Z), a ring of
-  // kTcRing tiles for the tile that doubles as the output staging buffer (forward: X; dQ: q), the 16-bit
+  // NS + 1 tiles for the tile that doubles as the output staging buffer (forward: X; dQ: q), the 16-bit
   // state operand (2 x 8 KB).  The ring is one slot longer than the stage count, so the tile of chunk c+NS
   // is loaded into the slot chunk c-1 left, while chunk c's output is still being written and stored.
   constexpr int NIN = (MODE == kModeFwd) ? 2 : 3;  // read-only tiles per stage
   constexpr int STAGE = NIN * kTileBytes;
-  constexpr int NS = kTcStages;
+  constexpr int NS = (MODE == kModeFwd) ? kTcStagesFwd : kTcStages;
+  constexpr int RING = NS + 1;
   constexpr int kIdxY = (MODE == kModeFwd) ? 0 : 1, kIdxZ = kIdxY + 1;  // tile index inside a stage (dQ: X = 0)
   constexpr bool BF = Pack2<T>::kBf16;
 
@@ -489,9 +490,9 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   // compiler, so tile accesses compile to LDS/STS rather than generic loads and stores)
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char* ring = smem + NS * STAGE;
-  unsigned char* sS = ring + kTcRing * kTileBytes;  // 2 x [64 x 64] 16-bit state operand (double-buffered)
+  unsigned char* sS = ring + RING * kTileBytes;  // 2 x [64 x 64] 16-bit state operand (double-buffered)
   auto stage_of = [&](int c) { return smem + (c % NS) * STAGE; };
-  auto ring_of = [&](int c) { return ring + (c % kTcRing) * kTileBytes; };
+  auto ring_of = [&](int c) { return ring + (c % RING) * kTileBytes; };
   auto tile_x = [&](int c) { return MODE == kModeFwd ? ring_of(c) : stage_of(c); };
   __shared__ uint64_t bar_full[NS], bar_free_in[NS], bar_out[NS], bar_prep[NS], bar_p_full[2], bar_p_ready[2], bar_acc_full[2],
       bar_acc_free[2], bar_s_full, bar_state[2], bar_state2, bar_init;
@@ -1177,7 +1178,8 @@ inline size_t causal_bwd_kv_smem_bytes() {
 
 inline size_t causal_tc_smem_bytes(int mode) {
   const int nin = mode == kModeFwd ? 2 : 3;
-  return static_cast<size_t>((kTcStages * nin + kTcRing) * kTileBytes + 2 * kTcD * 128 + 1024);
+  const int ns = mode == kModeFwd ? kTcStagesFwd : kTcStages;
+  return static_cast<size_t>((ns * nin + ns + 1) * kTileBytes + 2 * kTcD * 128 + 1024);
 }
 
 }  // namespace cott
