@@ -210,29 +210,35 @@ __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
 
 // Mask + convert a 128-column fp32 score row held in this thread's TMEM lane and write it back to the
 // same columns as packed 16-bit pairs (packed column j = elements 2j, 2j+1), for use as a tcgen05
-// A operand from TMEM.  Element (row, s) survives iff lo <= s <= hi.  `blk_lo..blk_hi` are the
-// 32-column blocks that hold at least one surviving element for ANY row of the warp (warp-uniform).
-template <typename T>
-__device__ __forceinline__ void mask_pack_inplace(uint32_t taddr_lane, int lo, int hi, int blk_lo, int blk_hi) {
+// A operand from TMEM.  LOWER: element (row, s) survives iff s <= row (forward, dQ); else iff s >= row (dK/dV).
+template <typename T, bool LOWER>
+__device__ __forceinline__ void mask_pack_inplace(uint32_t taddr_lane, int lane, int wq) {
   // One 32-column block per iteration of a loop that is NOT unrolled: the fully unrolled form is four
   // times the code, and the roles of this kernel already overflow the instruction cache.  Packed block
   // b lands on fp32 columns 16b .. 16b+15, which belong to block b/2 <= b: already read.
+  // The warp owns rows 32 wq .. 32 wq + 31 (row = 32 wq + lane): of the four column blocks, those on one
+  // side of block wq are kept whole, those on the other side are zero, and only block wq needs the
+  // per-element test (LOWER: column e of it survives iff e <= lane; else iff e >= lane).
 #pragma unroll 1
   for (int blk = 0; blk < 4; ++blk) {
     uint32_t packed[16];
-    if (blk < blk_lo || blk > blk_hi) {  // warp-uniform: nothing of this block survives for any row
+    if (LOWER ? blk > wq : blk < wq) {  // warp-uniform: nothing of this block survives for any row
 #pragma unroll
       for (int j = 0; j < 16; ++j) packed[j] = 0u;
     } else {
       uint32_t r[32];
       ptx::tmem_ld_x32(taddr_lane + 32 * blk, r);
       ptx::tmem_ld_wait();
-      const int s0 = 32 * blk;
+      if (blk == wq) {
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const float x0 = (s0 + 2 * j >= lo && s0 + 2 * j <= hi) ? __uint_as_float(r[2 * j]) : 0.f;
-        const float x1 = (s0 + 2 * j + 1 >= lo && s0 + 2 * j + 1 <= hi) ? __uint_as_float(r[2 * j + 1]) : 0.f;
-        packed[j] = Pack2<T>::pack(x0, x1);
+        for (int j = 0; j < 16; ++j) {
+          const bool k0 = LOWER ? (2 * j <= lane) : (2 * j >= lane);
+          const bool k1 = LOWER ? (2 * j + 1 <= lane) : (2 * j + 1 >= lane);
+          packed[j] = Pack2<T>::pack(k0 ? __uint_as_float(r[2 * j]) : 0.f, k1 ? __uint_as_float(r[2 * j + 1]) : 0.f);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) packed[j] = Pack2<T>::pack(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
       }
     }
     ptx::tmem_st_x16(taddr_lane + 16 * blk, packed);
@@ -698,7 +704,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       tc_fence_after_sync();
       COTT_TRACE_EV(0, c);
 #if !(COTT_SKEL & 1)
-      mask_pack_inplace<T>(tP0 + 128 * b + lane_base, 0, row, 0, wq);
+      mask_pack_inplace<T, true>(tP0 + 128 * b + lane_base, lane, wq);
 #endif
       tc_fence_before_sync();
       warp_arrive(&bar_p_ready[b], lane);
@@ -1081,7 +1087,7 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       if (!(ok = wait_bar_warp(&bar_p_full, ci & 1, abort_flag, kWaitScore, ci))) break;
       tc_fence_after_sync();
       COTT_TRACE_EV(1, ci);
-      mask_pack_inplace<T>(tE + lane_base, row, 127, wq, 3);
+      mask_pack_inplace<T, false>(tE + lane_base, lane, wq);
       COTT_TRACE_EV(2, ci);
       tc_fence_before_sync();
       warp_arrive(&bar_p_ready, lane);
@@ -1104,7 +1110,7 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     for (int ci = 0; ci < nchunks; ++ci) {
       if (!wait_bar_warp(&bar_p_full, ci & 1, abort_flag, kWaitScore, ci)) break;
       tc_fence_after_sync();
-      mask_pack_inplace<T>(tF + lane_base, row, 127, wq, 3);
+      mask_pack_inplace<T, false>(tF + lane_base, lane, wq);
       tc_fence_before_sync();
       warp_arrive(&bar_p_ready, lane);
       if (ci + 1 < nchunks) {  // R after chunk ci -> 16-bit operand of chunk ci+1 (buffer (ci+1)&1)
