@@ -87,3 +87,18 @@ def test_kernel_rejects_cpu_tensors_like_the_reference():
     x = torch.zeros(1, 1, 4, 32)
     with pytest.raises(RuntimeError, match="Q must be a CUDA tensor"):
         kernel.float32(x, x, x, 1, False, False)
+
+
+def test_segment_plan_is_host_arithmetic(lib):
+    """cott_cos_attn_seg_count / _seg_workspace_bytes need no GPU: few sequences and a long N get segments
+    (148 SMs assumed when no device answers), many sequences or short ones do not."""
+    L = lib
+    L.cott_cos_attn_seg_workspace_bytes.restype = ctypes.c_size_t
+    assert L.cott_cos_attn_seg_count(8, 16, 4096) == 1          # 128 sequences: one per SM already
+    assert L.cott_cos_attn_seg_count(1, 16, 262144) == 9        # 16 heads -> 9 segments each (144 CTAs)
+    assert L.cott_cos_attn_seg_count(1, 1, 256) == 1            # two chunks: nothing to cut
+    assert L.cott_cos_attn_seg_count(1, 1, 1024) == 4           # at least two chunks per segment
+    n = L.cott_cos_attn_seg_workspace_bytes(1, 16, 262144, 9)
+    assert n == 5 * 16 * 9 * 64 * 64 * 4 + 262144 * 4
+    # a segment count the sequence cannot use is clamped (1000 tokens = 8 chunks -> at most 8 segments)
+    assert L.cott_cos_attn_seg_workspace_bytes(1, 1, 1000, 50) == 5 * 8 * 64 * 64 * 4 + 1000 * 4
