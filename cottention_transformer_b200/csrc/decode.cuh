@@ -18,7 +18,9 @@
 
 namespace cott {
 
-constexpr int kDecodeThreads = 256;
+// Threads per CTA: 128 for d <= 64 (8 CTAs per SM: the 1024 (b,h) states of a batch-64, 16-head step are then
+// resident in one wave of 148 x 8 CTAs, and twice the bytes are in flight per SM), 256 for d = 128.
+template <int DK> struct DecodeCfg { static constexpr int kThreads = DK <= 64 ? 128 : 256, kCtasPerSm = DK <= 64 ? 8 : 2; };
 
 template <typename T>
 __device__ __forceinline__ float ld_as_float(const T* p) { return to_acc(*p); }
@@ -26,16 +28,15 @@ __device__ __forceinline__ float ld_as_float(const T* p) { return to_acc(*p); }
 // q, k: [B,H,T,Dk]  v, out: [B,H,T,Dv] (T = 1 for a single step); state: [B,H,Dv,Dk] fp32.
 // positions: optional [B] int64 array of the 1-based position of the FIRST token of this call for
 // each batch entry; if null, `pos0` is used for all.  LPR = lanes per state row = Dk/4.
-// (the register cap keeps 4 CTAs per SM resident for d <= 64, 2 for d = 128: the kernel is latency-bound
-// on its state loads, so resident CTAs are what hides the HBM latency)
-template <typename T, int DK>
-__global__ void __launch_bounds__(kDecodeThreads, (DK <= 64 ? 4 : 2))
+// (the kernel is latency-bound on its state loads, so resident CTAs are what hides the HBM latency)
+template <typename T, int DK, int MAX_DV>
+__global__ void __launch_bounds__(DecodeCfg<DK>::kThreads, DecodeCfg<DK>::kCtasPerSm)
 decode_kernel(float* __restrict__ state, const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
               const float* __restrict__ norm_const, T* __restrict__ out, int H, int Dv, int Tsteps, long long pos0,
               const long long* __restrict__ positions) {
+  constexpr int kDecodeThreads = DecodeCfg<DK>::kThreads;
   constexpr int LPR = DK / 4;                    // lanes per row (4, 8, 16 or 32)
   constexpr int ROWS_PER_PASS = kDecodeThreads / LPR;
-  constexpr int MAX_DV = 128;
   constexpr int MAXR = (MAX_DV + ROWS_PER_PASS - 1) / ROWS_PER_PASS;  // state rows held per thread
   __shared__ float sq[DK], sk[DK], sv[MAX_DV];
   __shared__ float red[2][kDecodeThreads / 32];
@@ -123,10 +124,14 @@ int launch_decode(float* state, const void* q, const void* k, const void* v, con
   const unsigned grid = static_cast<unsigned>(static_cast<long>(B) * H);
 #define COTT_DECODE_CASE(DK)                                                                                     \
   case DK:                                                                                                       \
-    decode_kernel<T, DK><<<grid, kDecodeThreads, 0, stream>>>(state, static_cast<const T*>(q),                   \
-                                                              static_cast<const T*>(k), static_cast<const T*>(v), \
-                                                              nc, static_cast<T*>(out), H, Dv, T_steps, pos0,    \
-                                                              positions);                                        \
+    if (Dv <= 64)                                                                                                \
+      decode_kernel<T, DK, 64><<<grid, DecodeCfg<DK>::kThreads, 0, stream>>>(                                    \
+          state, static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v), nc,               \
+          static_cast<T*>(out), H, Dv, T_steps, pos0, positions);                                                \
+    else                                                                                                         \
+      decode_kernel<T, DK, 128><<<grid, DecodeCfg<DK>::kThreads, 0, stream>>>(                                   \
+          state, static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v), nc,               \
+          static_cast<T*>(out), H, Dv, T_steps, pos0, positions);                                                \
     break;
   switch (Dk) {
     COTT_DECODE_CASE(16)
