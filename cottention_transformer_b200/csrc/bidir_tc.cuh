@@ -39,10 +39,15 @@ __device__ __forceinline__ float btc_count_keep(const unsigned char* keep_b, int
 
 // -------------------------------------------------------------------------------------------------
 // forward
-// shared memory: 2 x (K, V) tiles | 2 x Q tile (also the output staging buffer) | 16-bit state
-// TMEM (256 columns): state 64 | accumulators 2 x 64
+// shared memory: kBtcKv x (K, V) tiles | 2 x Q tile (also the output staging buffer) | 16-bit state
+// TMEM (128 columns): state 64 | accumulator 64
+// Sized for three CTAs per SM (73 KB of shared memory, 128 TMEM columns each): the 384 (b,h) sequences of a
+// BERT-base batch are then resident in one wave, and the CTAs of an SM cover each other's load and hand-off
+// latency, which a deeper ring inside one CTA would otherwise have to.
+constexpr int kBtcKv = 1;   // (K, V) stages
+constexpr int kBtcAcc = 1;  // accumulator buffers
 template <typename T>
-__global__ void __launch_bounds__(kBtcThreads, 2)
+__global__ void __launch_bounds__(kBtcThreads, 3)
 bidir_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                     const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapOut,
                     const unsigned char* __restrict__ keep, const float* __restrict__ norm_const, int H, int N) {
@@ -50,9 +55,9 @@ bidir_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
   constexpr bool BF = Pack2<T>::kBf16;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  unsigned char* sKV = smem;                      // [2][K tile, V tile]
-  unsigned char* sQ = smem + 4 * kTileBytes;      // [2]
-  unsigned char* sS = smem + 6 * kTileBytes;      // [64 x 64] 16-bit
+  unsigned char* sKV = smem;                                 // [kBtcKv][K tile, V tile]
+  unsigned char* sQ = smem + 2 * kBtcKv * kTileBytes;        // [2]
+  unsigned char* sS = smem + (2 * kBtcKv + 2) * kTileBytes;  // [64 x 64] 16-bit
   __shared__ uint64_t bar_full1[2], bar_prep1[2], bar_free1[2], bar_s_full, bar_state, bar_fullq[2], bar_acc_full[2],
       bar_acc_free[2], bar_out[2];
   __shared__ uint32_t tmem_slot;
@@ -85,7 +90,7 @@ bidir_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
     tma_prefetch_desc(&mapOut);
   }
   if (warp == 1) {
-    tmem_alloc(&tmem_slot, 256);
+    tmem_alloc(&tmem_slot, 128);
     tmem_relinquish();
   }
   tc_fence_before_sync();
@@ -104,8 +109,8 @@ bidir_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
         tma_load_3d(sQ + c * kTileBytes, &mapQ, &bar_fullq[c], 0, c * kTcChunk, bh);
       }
       for (int c = 0; ok && c < nchunks; ++c) {
-        const int s = c & 1;
-        if (c >= 2 && !(ok = wait_bar(&bar_free1[s], ((c >> 1) - 1) & 1, abort_flag, kWaitStageFree, c))) break;
+        const int s = c % kBtcKv;
+        if (c >= kBtcKv && !(ok = wait_bar(&bar_free1[s], (c / kBtcKv - 1) & 1, abort_flag, kWaitStageFree, c))) break;
         unsigned char* st = sKV + s * 2 * kTileBytes;
         mbar_expect_tx(&bar_full1[s], 2 * kTileBytes);
         tma_load_3d(st, &mapK, &bar_full1[s], 0, c * kTcChunk, bh);
@@ -128,8 +133,8 @@ bidir_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
     if (lane == 0) {
       bool ok = true;
       for (int c = 0; ok && c < nchunks; ++c) {  // S += K^T Zw
-        const int s = c & 1;
-        if (!(ok = wait_bar1(&bar_prep1[s], (c >> 1) & 1, abort_flag, kWaitPrepped, c))) break;
+        const int s = c % kBtcKv;
+        if (!(ok = wait_bar1(&bar_prep1[s], (c / kBtcKv) & 1, abort_flag, kWaitPrepped, c))) break;
         tc_fence_after_sync();
         const uint32_t k0 = smem_u32(sKV + s * 2 * kTileBytes);
         const uint64_t dKm = mdesc(k0), dZm = mdesc(k0 + kTileBytes);
@@ -141,15 +146,15 @@ bidir_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
       ok = ok && wait_bar1(&bar_state, 0, abort_flag, kWaitState, 0);
       const uint64_t dS = mdesc(smem_u32(sS));
       for (int c = 0; ok && c < nchunks; ++c) {  // Acc = Q S
-        const int s = c & 1;
-        if (!(ok = wait_bar4(&bar_fullq[s], (c >> 1) & 1, c >= 2 ? &bar_acc_free[s] : nullptr, ((c >> 1) - 1) & 1, nullptr,
-                             0, nullptr, 0, abort_flag, kWaitTma, c)))
+        const int s = c & 1, ab = c % kBtcAcc;
+        if (!(ok = wait_bar4(&bar_fullq[s], (c >> 1) & 1, c >= kBtcAcc ? &bar_acc_free[ab] : nullptr,
+                             (c / kBtcAcc - 1) & 1, nullptr, 0, nullptr, 0, abort_flag, kWaitTma, c)))
           break;
         tc_fence_after_sync();
         const uint64_t dX = kdesc(smem_u32(sQ + s * kTileBytes));
 #pragma unroll
-        for (int k = 0; k < 4; ++k) mma_ss(tAcc0 + 64 * s, dX + 2 * k, dS + 128 * k, kIdescAcc, k > 0);
-        mma_commit(&bar_acc_full[s]);
+        for (int k = 0; k < 4; ++k) mma_ss(tAcc0 + 64 * ab, dX + 2 * k, dS + 128 * k, kIdescAcc, k > 0);
+        mma_commit(&bar_acc_full[ab]);
       }
     }
   } else {
@@ -160,8 +165,8 @@ bidir_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
     const float a = length_factor(fmaxf(L, 1.0f), sigma);
     bool ok = true;
     for (int c = 0; ok && c < nchunks; ++c) {  // Zw = diag(keep a / |k|) V, in place
-      const int s = c & 1, pos = c * kTcChunk + row;
-      if (!(ok = wait_bar_warp(&bar_full1[s], (c >> 1) & 1, abort_flag, kWaitTma, c))) break;
+      const int s = c % kBtcKv, pos = c * kTcChunk + row;
+      if (!(ok = wait_bar_warp(&bar_full1[s], (c / kBtcKv) & 1, abort_flag, kWaitTma, c))) break;
       unsigned char* sK = sKV + s * 2 * kTileBytes;
       const bool kp = pos < N && (!keep_b || keep_b[pos]);
       const float w = kp ? inv_norm(row_sumsq_rolled<T>(sK, row)) * a : 0.f;
@@ -182,11 +187,12 @@ bidir_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
       if (!(ok = wait_bar_warp(&bar_fullq[s], (c >> 1) & 1, abort_flag, kWaitTma, c))) break;
       const bool kp = pos < N && (!keep_b || keep_b[pos]);
       const float rq = kp ? inv_norm(row_sumsq_rolled<T>(q, row)) : 0.f;
-      if (!(ok = wait_bar_warp(&bar_acc_full[s], (c >> 1) & 1, abort_flag, kWaitAcc, c))) break;
+      const int ab = c % kBtcAcc;
+      if (!(ok = wait_bar_warp(&bar_acc_full[ab], (c / kBtcAcc) & 1, abort_flag, kWaitAcc, c))) break;
       tc_fence_after_sync();
-      row_from_acc<T, false>(q, row, tAcc0 + 64 * s + lane_base, rq, 0.f);
+      row_from_acc<T, false>(q, row, tAcc0 + 64 * ab + lane_base, rq, 0.f);
       tc_fence_before_sync();
-      warp_arrive(&bar_acc_free[s], lane);
+      warp_arrive(&bar_acc_free[ab], lane);
       fence_proxy_async_smem();
       warp_arrive(&bar_out[s], lane);
     }
@@ -202,7 +208,7 @@ bidir_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
     }
   }
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem, 256);
+  if (warp == 1) tmem_dealloc(tmem, 128);
 }
 
 // -------------------------------------------------------------------------------------------------
@@ -437,6 +443,6 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
 
 inline size_t bidir_bwd_tc_smem_bytes() { return static_cast<size_t>(8 * kTileBytes + 2 * kTcD * 128 + 1024); }
 
-inline size_t bidir_fwd_tc_smem_bytes() { return static_cast<size_t>(6 * kTileBytes + kTcD * 128 + 1024); }
+inline size_t bidir_fwd_tc_smem_bytes() { return static_cast<size_t>((2 * kBtcKv + 2) * kTileBytes + kTcD * 128 + 1024); }
 
 }  // namespace cott
