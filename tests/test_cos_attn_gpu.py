@@ -174,3 +174,31 @@ def test_fused_with_padding_mask_matches_oracle(dt, shape, segments):
     assert out.detach().cpu()[masked.view(B, 1, N).expand(B, H, N)].abs().max().item() == 0.0
     e = (ncc.grad.double().cpu() - ncd.grad).abs().max().item()
     assert e <= REL16 * max(ncd.grad.abs().max().item(), 1e-3), (e, ncd.grad)
+
+
+@pytest.mark.parametrize("shape,segments", [((8, 16, 4096), 1), ((1, 16, 16384), 9), ((2, 3, 1000), 3)])
+def test_repeated_cold_launches_give_identical_results(shape, segments):
+    """Every kernel synchronised before the next one starts (cold pipelines: the condition under which a role
+    that skipped a barrier phase once ran ahead), 40 times: no wait gives up and the results are bit-identical."""
+    from cottention_transformer_b200 import _lib
+    B, H, N = shape
+    L = _lib.lib()
+    g = torch.Generator(device="cuda").manual_seed(5)
+    q, k, v, do = (torch.randn(B, H, N, 64, device="cuda", generator=g).bfloat16() for _ in range(4))
+    nc, dnc = 0.5 * torch.ones(H, device="cuda"), torch.zeros(H, device="cuda")
+    out, dq, dk, dv = (torch.zeros_like(q) for _ in range(4))
+    ws = torch.empty(max(L.cott_cos_attn_seg_workspace_bytes(B, H, N, segments), 16), dtype=torch.uint8, device="cuda")
+    st, P = _lib.stream_ptr(q.device), (lambda t: t.data_ptr())
+    first = None
+    for _ in range(40):
+        _lib.check(L.cott_cos_attn_fwd_seg(P(q), P(k), P(v), None, P(nc), P(out), P(ws), segments, B, H, N, 64, 64, 3, st), "fwd")
+        torch.cuda.synchronize()
+        _lib.check(L.cott_cos_attn_bwd_seg(P(q), P(k), P(v), None, P(nc), P(do), P(ws), segments, P(dq), P(dk), P(dv), P(dnc),
+                                           B, H, N, 64, 64, 3, st), "bwd")
+        torch.cuda.synchronize()
+        _lib.check_device_status()
+        cur = [t.clone() for t in (out, dq, dk, dv)]
+        if first is None:
+            first = cur
+        else:
+            assert all(torch.equal(a, b) for a, b in zip(cur, first))
