@@ -170,6 +170,20 @@ __global__ void seg_scan_kernel(const float* __restrict__ state, float* __restri
   }
 }
 
+// Decode state of a whole prompt from its segment states: state[bh][j][i] (+)= sum_seg seg_state[bh][seg][i][j]
+// (the decode kernel keeps the value index first, GPTCosAttention.py:264).  grid = B*H, any block size.
+__global__ void seg_to_decode_state_kernel(const float* __restrict__ seg_state, float* __restrict__ state, int nseg,
+                                           int accumulate) {
+  const size_t base = static_cast<size_t>(blockIdx.x) * nseg * (kTcD * kTcD);
+  float* dst = state + static_cast<size_t>(blockIdx.x) * (kTcD * kTcD);
+  for (int e = threadIdx.x; e < kTcD * kTcD; e += blockDim.x) {
+    const int j = e / kTcD, i = e % kTcD;  // output element [j][i] = input element [i][j]
+    float sum = accumulate ? dst[e] : 0.f;
+    for (int s = 0; s < nseg; ++s) sum += seg_state[base + static_cast<size_t>(s) * (kTcD * kTcD) + i * kTcD + j];
+    dst[e] = sum;
+  }
+}
+
 // count[b][s] = number of kept positions among 0 .. s of batch entry b (inclusive).  grid = B, block = 256.
 __global__ void keep_count_kernel(const unsigned char* __restrict__ keep, int* __restrict__ count, int N) {
   __shared__ int part[256];

@@ -367,6 +367,31 @@ int cott_cos_attn_bwd_seg(const void* q, const void* k, const void* v, const uns
              : run_bwd_seg<__half>(q, k, v, keep, norm_const, dout, ws, nseg, dq, dk, dv, dnorm_const, B, H, N, dtype, s);
 }
 
+int cott_cos_attn_prefill_state(const void* k, const void* v, const float* norm_const, float* state, void* workspace,
+                                int nseg, int accumulate, int B, int H, int N, int Dk, int Dv, int dtype, void* stream) {
+  int st = check_fused_args(B, H, N, Dk, Dv, dtype);
+  if (st) return st;
+  if ((long)B * H == 0) return COTT_OK;
+  if (!state) return fail(COTT_ERR_NULL, "null pointer: state");
+  DeviceScope scope(state);
+  COTT_CUDA_TRY(scope.status());
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (N == 0) {
+    if (!accumulate) COTT_CUDA_TRY(cudaMemsetAsync(state, 0, sizeof(float) * (size_t)B * H * kTcD * kTcD, s));
+    return COTT_OK;
+  }
+  if ((st = check_ptrs16({{k, "k"}, {v, "v"}, {workspace, "workspace"}, {state, "state"}}))) return st;
+  if (!norm_const) return fail(COTT_ERR_NULL, "null pointer: norm_const");
+  const SegPlan plan = plan_segments(N, nseg);
+  float* ws = static_cast<float*>(workspace);
+  st = dtype == COTT_BF16 ? launch_seg_state<__nv_bfloat16, kSegFwdState>(k, v, norm_const, ws, B, H, N, dtype, plan, s)
+                          : launch_seg_state<__half, kSegFwdState>(k, v, norm_const, ws, B, H, N, dtype, plan, s);
+  if (st) return st;
+  seg_to_decode_state_kernel<<<(unsigned)((long)B * H), 256, 0, s>>>(ws, state, plan.nseg, accumulate != 0);
+  COTT_CUDA_TRY(cudaGetLastError());
+  return COTT_OK;
+}
+
 int cott_check_status(int* detail) {
   int v = 0;
   COTT_CUDA_TRY(cudaDeviceSynchronize());

@@ -23,6 +23,28 @@ class CosAttnDecodeState:
         self.state.zero_()
         self.cur_s = 1
 
+    def prefill(self, q, k, v, norm_const):
+        """Absorb a whole prompt at once (fresh state only): the outputs come from the fused causal kernels and the
+        state from the segment-state kernels, instead of T recurrent steps.  bf16 / fp16, head dim 64; anything
+        else falls back to ``step``.  Returns ``[B, H, T, d_v]``."""
+        from .cos_attention import cos_attn_causal, fused_supported
+        if self.cur_s != 1 or not fused_supported(q, k, v):
+            return self.step(q, k, v, norm_const)
+        B, H, T, D = q.shape
+        k, v = k.contiguous(), v.contiguous()
+        with torch.no_grad():
+            out = cos_attn_causal(q, k, v, norm_const)
+        L = _lib.lib()
+        nc = norm_const.detach().reshape(-1).to(device=q.device, dtype=torch.float32).contiguous()
+        with torch.cuda.device(q.device):
+            nseg = L.cott_cos_attn_seg_count(B, H, T)
+            ws = torch.empty(max(L.cott_cos_attn_seg_workspace_bytes(B, H, T, nseg), 16), dtype=torch.uint8, device=q.device)
+            st = L.cott_cos_attn_prefill_state(_lib.ptr(k), _lib.ptr(v), _lib.ptr(nc), _lib.ptr(self.state), _lib.ptr(ws), nseg,
+                                               0, B, H, T, D, D, _lib.DTYPE_CODE[q.dtype], _lib.stream_ptr(q.device))
+        _lib.check(st, "cott_cos_attn_prefill_state")
+        self.cur_s += T
+        return out
+
     def step(self, q, k, v, norm_const):
         """q, k: ``[B, H, T, d_k]``; v: ``[B, H, T, d_v]`` (T >= 1 tokens, e.g. a prompt or one new
         token).  Returns ``[B, H, T, d_v]`` and advances the state and the position by T."""

@@ -137,6 +137,18 @@ int cott_cos_attn_bwd_seg(const void* q, const void* k, const void* v, const uns
                           int dtype, void* stream);
 
 /*
+ * Prefill -> decode hand-off: the decode state (cott_decode_step layout, float32 [B,H,Dv,Dk]) that a prompt of N
+ * tokens at positions 1..N leaves behind, state[b,h,j,i] = sum_s v'_s[j] k^_s[i], computed with the segment-state
+ * kernels instead of N recurrent steps (the reference absorbs a prompt token by token, GPTCosAttention.py:253-272).
+ * `accumulate` != 0 adds to `state` instead of overwriting it -- only meaningful for a state that is still at
+ * position 0, since the length factor uses positions 1..N.  `workspace`: cott_cos_attn_seg_workspace_bytes(B, H, N,
+ * nseg) bytes.  bf16 / fp16 prompts, head dim 64.  The prompt's outputs come from cott_cos_attn_fwd(_seg).
+ */
+int cott_cos_attn_prefill_state(const void* k, const void* v, const float* norm_const, float* state,
+                                void* workspace, int nseg, int accumulate, int B, int H, int N, int Dk, int Dv,
+                                int dtype, void* stream);
+
+/*
  * Recurrent decode.  Per (batch, head) a float32 state[b,h,j,i] ([B,H,Dv,Dk], updated in place) is
  * advanced by one token:
  *   q^ = q/|q|, k^ = k/|k|, v' = v / max(pos^sigmoid(norm_const[h]), 1)

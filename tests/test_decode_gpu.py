@@ -78,3 +78,29 @@ def test_decode_rejects_bad_arguments():
     assert L.cott_decode_step(*args, 1, 1, 48, 64, 0, 1, None, None) == 2     # Dk not supported
     assert L.cott_decode_step(*args, 1, 1, 64, 64, 1, 1, None, None) == 3     # float64 tokens
     assert L.cott_decode_step(*args, 1, 1, 64, 64, 0, 0, None, None) == 2     # positions are 1-based
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(2, 3, 300), (1, 16, 4096)])
+def test_prefill_hands_the_state_to_decode(dt, shape):
+    """A prompt absorbed by ``prefill`` (fused causal kernels + segment-state kernels) followed by single-token
+    steps gives what the recurrent kernel gives for the whole stream (state and outputs)."""
+    from cottention_transformer_b200 import CosAttnDecodeState
+    B, H, N = shape
+    T = 5
+    q, k, v, _, _ = O.make_inputs(B, H, N + T, 64, 64, seed=N, normalize=False, dtype=dt)
+    q, k, v = q.cuda(), k.cuda(), v.cuda()
+    nc = torch.linspace(-0.5, 1.0, H).cuda()
+    ref = CosAttnDecodeState(B, H, 64)
+    out_ref = ref.step(q, k, v, nc)                      # every token through the recurrent kernel (fp32 state)
+    fast = CosAttnDecodeState(B, H, 64)
+    out_p = fast.prefill(q[:, :, :N], k[:, :, :N], v[:, :, :N], nc)
+    assert fast.cur_s == N + 1
+    outs = [fast.step(q[:, :, N + t:N + t + 1], k[:, :, N + t:N + t + 1], v[:, :, N + t:N + t + 1], nc) for t in range(T)]
+    out_fast = torch.cat([out_p] + outs, dim=2)
+    scale = out_ref.float().abs().max().item()
+    assert (out_fast.float() - out_ref.float()).abs().max().item() <= 2e-2 * scale
+    # the decode tokens only see the state: they isolate the hand-off
+    assert (out_fast[:, :, N:].float() - out_ref[:, :, N:].float()).abs().max().item() <= 2e-2 * scale
+    s_scale = ref.state.abs().max().item()
+    assert (fast.state - ref.state).abs().max().item() <= 1e-2 * s_scale
