@@ -31,8 +31,8 @@ _SIGNATURES = {
     "cott_cos_attn_bwd_dq": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "cott_cos_attn_bwd_dkdv": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "cott_cos_attn_seg_count": [_I, _I, _I],
-    "cott_cos_attn_fwd_seg": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
-    "cott_cos_attn_bwd_seg": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "cott_cos_attn_fwd_seg": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P],
+    "cott_cos_attn_bwd_seg": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "cott_cos_attn_prefill_state": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "cott_decode_step": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, ctypes.c_longlong, _P, _P],
     "cott_decode_steps": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, ctypes.c_longlong, _P, _P],
@@ -43,6 +43,11 @@ _SIGNATURES = {
 }
 _STR = {"cott_version": [], "cott_last_error": [], "cott_status_string": [_I]}
 _SIZE = {"cott_bidir_scratch_bytes": [_I, _I, _I, _I, _I, _I], "cott_cos_attn_seg_workspace_bytes": [_I, _I, _I, _I]}
+
+class CottLayout(ctypes.Structure):
+    """``cott_layout``: element strides (batch, head, position) of q/k/v/dq/dk/dv and of out/dout."""
+    _fields_ = [(n, ctypes.c_longlong) for n in ("in_b", "in_h", "in_n", "out_b", "out_h", "out_n")]
+
 
 _lib = None
 launch_count = 0  # kernels launched through this binding (bookkeeping for the benchmark)

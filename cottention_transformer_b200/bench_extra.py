@@ -179,8 +179,8 @@ def bench_long_context(N, B=1, H=16, d=64, iters=5):
     ws = torch.empty(max(L.cott_cos_attn_seg_workspace_bytes(B, H, N, nseg), 16), dtype=torch.uint8, device=dev)
 
     def step(n):
-        _lib.check(L.cott_cos_attn_fwd_seg(P(q), P(k), P(v), None, P(nc), P(out), P(ws), n, B, H, N, d, d, 3, st), "fwd_seg")
-        _lib.check(L.cott_cos_attn_bwd_seg(P(q), P(k), P(v), None, P(nc), P(do), P(ws), n, P(dq), P(dk), P(dv), P(dnc), B, H, N, d, d,
+        _lib.check(L.cott_cos_attn_fwd_seg(P(q), P(k), P(v), None, P(nc), P(out), P(ws), n, None, B, H, N, d, d, 3, st), "fwd_seg")
+        _lib.check(L.cott_cos_attn_bwd_seg(P(q), P(k), P(v), None, P(nc), P(do), P(ws), n, None, P(dq), P(dk), P(dv), P(dnc), B, H, N, d, d,
                                            3, st), "bwd_seg")
 
     t_seg = _time(lambda: step(nseg), iters, warmup=2)

@@ -23,10 +23,12 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .cos_attention import cos_attn_bidirectional, cos_attn_causal
+from .cos_attention import cos_attn_bidirectional, cos_attn_causal, cos_attn_causal_packed
 
 
 class CosSelfAttention(nn.Module):
+    permute = False  # True: the reference's layout handling (permute + contiguous copies around the op)
+
     def __init__(self, d_model, n_heads, causal):
         super().__init__()
         self.h, self.causal = n_heads, causal
@@ -36,7 +38,10 @@ class CosSelfAttention(nn.Module):
 
     def forward(self, x):
         B, S, D = x.shape
-        qkv = self.qkv(x).view(B, S, 3, self.h, D // self.h).permute(2, 0, 3, 1, 4).contiguous()  # [3,B,H,S,d]
+        qkv = self.qkv(x).view(B, S, 3, self.h, D // self.h)
+        if self.causal and not self.permute:  # strided tensor maps: no head split / merge copies
+            return self.proj(cos_attn_causal_packed(qkv, self.norm_const).reshape(B, S, D))
+        qkv = qkv.permute(2, 0, 3, 1, 4).contiguous()  # [3,B,H,S,d]
         op = cos_attn_causal if self.causal else cos_attn_bidirectional
         o = op(qkv[0], qkv[1], qkv[2], self.norm_const)
         return self.proj(o.transpose(1, 2).reshape(B, S, D))
@@ -86,7 +91,9 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (smoke runs)")
+    ap.add_argument("--permute", action="store_true", help="gpt: permute + copy around the op instead of the packed layout")
     a = ap.parse_args()
+    CosSelfAttention.permute = a.permute
     world, rank, local = (int(os.environ.get(k, d)) for k, d in (("WORLD_SIZE", 1), ("RANK", 0), ("LOCAL_RANK", 0)))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)

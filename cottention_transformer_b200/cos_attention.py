@@ -16,6 +16,8 @@ Two modes, chosen by dtype (not a fallback chain -- each mode is a CUDA path of 
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from . import _lib
@@ -50,7 +52,7 @@ class _FusedCausal(torch.autograd.Function):
             if nseg > 1 or kp is not None:  # the general entry point: segments and / or a padding mask
                 ws = torch.empty(L.cott_cos_attn_seg_workspace_bytes(B, H, N, nseg), dtype=torch.uint8, device=q.device)
                 st = L.cott_cos_attn_fwd_seg(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(kp), _lib.ptr(nc), _lib.ptr(out),
-                                             _lib.ptr(ws), nseg, B, H, N, D, D, _lib.DTYPE_CODE[q.dtype],
+                                             _lib.ptr(ws), nseg, None, B, H, N, D, D, _lib.DTYPE_CODE[q.dtype],
                                              _lib.stream_ptr(q.device))
             else:
                 ws = None
@@ -72,7 +74,7 @@ class _FusedCausal(torch.autograd.Function):
         with torch.cuda.device(q.device):
             if ctx.ws is not None:
                 st = _lib.lib().cott_cos_attn_bwd_seg(
-                    _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(ctx.kp), _lib.ptr(nc), _lib.ptr(dout), _lib.ptr(ctx.ws), ctx.nseg,
+                    _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(ctx.kp), _lib.ptr(nc), _lib.ptr(dout), _lib.ptr(ctx.ws), ctx.nseg, None,
                     _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(dnc), B, H, N, D, D, _lib.DTYPE_CODE[q.dtype],
                     _lib.stream_ptr(q.device))
             else:
@@ -81,6 +83,61 @@ class _FusedCausal(torch.autograd.Function):
                     _lib.ptr(dv), _lib.ptr(dnc), B, H, N, D, D, _lib.DTYPE_CODE[q.dtype], _lib.stream_ptr(q.device))
         _lib.check(st, "cott_cos_attn_bwd")
         return dq, dk, dv, dnc.reshape(ctx.nc_shape).to(ctx.nc_dtype), None, None
+
+
+class _FusedCausalPacked(torch.autograd.Function):
+    """The fused causal op on the packed output of a QKV projection: ``qkv`` is ``[B, N, 3, H, 64]`` and the result
+    ``[B, N, H, 64]``; q, k, v, the output and all gradients are read and written in place through strided tensor
+    maps, so the head split / merge permutes (GPTCosAttention.py:447-449,478-479,500) cost no copy."""
+
+    @staticmethod
+    def forward(ctx, qkv, norm_const, keep=None):
+        qkv = qkv.contiguous()
+        B, N, three, H, D = qkv.shape
+        nc = norm_const.detach().reshape(-1).to(device=qkv.device, dtype=torch.float32).contiguous()
+        out = torch.empty(B, N, H, D, dtype=qkv.dtype, device=qkv.device)
+        lay = _lib.CottLayout(N * 3 * H * D, D, 3 * H * D, N * H * D, D, H * D)
+        L = _lib.lib()
+        q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+        kp = None if keep is None else keep.to(device=qkv.device, dtype=torch.uint8).contiguous()
+        with torch.cuda.device(qkv.device):
+            nseg = L.cott_cos_attn_seg_count(B, H, N)
+            ws = torch.empty(L.cott_cos_attn_seg_workspace_bytes(B, H, N, nseg), dtype=torch.uint8, device=qkv.device)
+            st = L.cott_cos_attn_fwd_seg(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(kp), _lib.ptr(nc), _lib.ptr(out),
+                                         _lib.ptr(ws), nseg, ctypes.byref(lay), B, H, N, D, D, _lib.DTYPE_CODE[qkv.dtype],
+                                         _lib.stream_ptr(qkv.device))
+        _lib.check(st, "cott_cos_attn_fwd_seg")
+        ctx.save_for_backward(qkv, nc)
+        ctx.ws, ctx.nseg, ctx.kp, ctx.lay = ws, nseg, kp, lay
+        ctx.nc_shape, ctx.nc_dtype = norm_const.shape, norm_const.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, nc = ctx.saved_tensors
+        B, N, three, H, D = qkv.shape
+        dout = dout.contiguous().to(qkv.dtype)
+        dqkv = torch.empty_like(qkv)
+        dnc = torch.empty(H, dtype=torch.float32, device=qkv.device)
+        with torch.cuda.device(qkv.device):
+            st = _lib.lib().cott_cos_attn_bwd_seg(
+                _lib.ptr(qkv[:, :, 0]), _lib.ptr(qkv[:, :, 1]), _lib.ptr(qkv[:, :, 2]), _lib.ptr(ctx.kp), _lib.ptr(nc),
+                _lib.ptr(dout), _lib.ptr(ctx.ws), ctx.nseg, ctypes.byref(ctx.lay), _lib.ptr(dqkv[:, :, 0]),
+                _lib.ptr(dqkv[:, :, 1]), _lib.ptr(dqkv[:, :, 2]), _lib.ptr(dnc), B, H, N, D, D, _lib.DTYPE_CODE[qkv.dtype],
+                _lib.stream_ptr(qkv.device))
+        _lib.check(st, "cott_cos_attn_bwd_seg")
+        return dqkv, dnc.reshape(ctx.nc_shape).to(ctx.nc_dtype), None
+
+
+def cos_attn_causal_packed(qkv, norm_const, keep=None):
+    """Causal cosine attention on a packed ``[B, N, 3, H, 64]`` bf16 / fp16 tensor (the reshaped output of one QKV
+    projection); returns ``[B, N, H, 64]`` (reshape to ``[B, N, H*64]`` for the output projection).  Same function
+    as ``cos_attn_causal`` on the permuted tensors, without the permute copies in either direction."""
+    if not qkv.is_cuda:
+        raise RuntimeError("cos_attn_causal_packed needs a CUDA tensor (there is no CPU path)")
+    if qkv.dim() != 5 or qkv.shape[2] != 3 or qkv.shape[-1] != 64 or qkv.dtype not in FUSED_DTYPES:
+        raise RuntimeError("cos_attn_causal_packed takes a [B, N, 3, H, 64] bfloat16 / float16 tensor")
+    return _FusedCausalPacked.apply(qkv, norm_const, keep)
 
 
 def _exact_causal(q, k, v, norm_const, keep):

@@ -66,7 +66,7 @@ bidir_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
 
   const int tid = threadIdx.x, lane = tid & 31;
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
-  const int bh = blockIdx.x, h = bh % H, b = bh / H;
+  const int bh = blockIdx.x, h = bh % H, b = bh / H, bb = b;
   const int nchunks = (N + kTcChunk - 1) / kTcChunk;
   const unsigned char* keep_b = keep ? keep + static_cast<size_t>(b) * N : nullptr;
 
@@ -106,25 +106,25 @@ bidir_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
       bool ok = true;
       for (int c = 0; c < 2 && c < nchunks; ++c) {  // the first two Q tiles travel while the state is built
         mbar_expect_tx(&bar_fullq[c], kTileBytes);
-        tma_load_3d(sQ + c * kTileBytes, &mapQ, &bar_fullq[c], 0, c * kTcChunk, bh);
+        tma_load_tile(sQ + c * kTileBytes, &mapQ, &bar_fullq[c], c * kTcChunk, h, bb);
       }
       for (int c = 0; ok && c < nchunks; ++c) {
         const int s = c % kBtcKv;
         if (c >= kBtcKv && !(ok = wait_bar(&bar_free1[s], (c / kBtcKv - 1) & 1, abort_flag, kWaitStageFree, c))) break;
         unsigned char* st = sKV + s * 2 * kTileBytes;
         mbar_expect_tx(&bar_full1[s], 2 * kTileBytes);
-        tma_load_3d(st, &mapK, &bar_full1[s], 0, c * kTcChunk, bh);
-        tma_load_3d(st + kTileBytes, &mapV, &bar_full1[s], 0, c * kTcChunk, bh);
+        tma_load_tile(st, &mapK, &bar_full1[s], c * kTcChunk, h, bb);
+        tma_load_tile(st + kTileBytes, &mapV, &bar_full1[s], c * kTcChunk, h, bb);
       }
       for (int c = 0; ok && c < nchunks; ++c) {
         const int s = c & 1;
         if (!(ok = wait_bar(&bar_out[s], (c >> 1) & 1, abort_flag, kWaitStageFree, c))) break;
-        tma_store_3d(&mapOut, sQ + s * kTileBytes, 0, c * kTcChunk, bh);
+        tma_store_tile(&mapOut, sQ + s * kTileBytes, c * kTcChunk, h, bb);
         tma_store_commit();
         if (c + 2 < nchunks) {
           tma_store_wait_read<0>();
           mbar_expect_tx(&bar_fullq[s], kTileBytes);
-          tma_load_3d(sQ + s * kTileBytes, &mapQ, &bar_fullq[s], 0, (c + 2) * kTcChunk, bh);
+          tma_load_tile(sQ + s * kTileBytes, &mapQ, &bar_fullq[s], (c + 2) * kTcChunk, h, bb);
         }
       }
       tma_store_wait<0>();
@@ -244,7 +244,7 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
 
   const int tid = threadIdx.x, lane = tid & 31;
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
-  const int bh = blockIdx.x, h = bh % H, b = bh / H;
+  const int bh = blockIdx.x, h = bh % H, b = bh / H, bb = b;
   const int n = (N + kTcChunk - 1) / kTcChunk;  // chunks; the ring carries 2n items
   const unsigned char* keep_b = keep ? keep + static_cast<size_t>(b) * N : nullptr;
 
@@ -291,9 +291,9 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
         if (!wait_bar(&bar_out[s], ((i - n) >> 1) & 1, abort_flag, kWaitStageFree, i)) return false;
         unsigned char* st = smem + s * STAGE;
         const int y = (i - n) * kTcChunk;
-        tma_store_3d(&mapDQ, st, 0, y, bh);
-        tma_store_3d(&mapDK, st + kTileBytes, 0, y, bh);
-        tma_store_3d(&mapDV, st + 2 * kTileBytes, 0, y, bh);
+        tma_store_tile(&mapDQ, st, y, h, bb);
+        tma_store_tile(&mapDK, st + kTileBytes, y, h, bb);
+        tma_store_tile(&mapDV, st + 2 * kTileBytes, y, h, bb);
         tma_store_commit();
         tma_store_wait_read<0>();
         return true;
@@ -303,10 +303,10 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
         if (j >= 2 && !(ok = retire(j - 2))) break;
         unsigned char* st = smem + s * STAGE;
         mbar_expect_tx(&bar_full[s], STAGE);
-        tma_load_3d(st, &mapQ, &bar_full[s], 0, y, bh);
-        tma_load_3d(st + kTileBytes, &mapK, &bar_full[s], 0, y, bh);
-        tma_load_3d(st + 2 * kTileBytes, &mapV, &bar_full[s], 0, y, bh);
-        tma_load_3d(st + 3 * kTileBytes, &mapDO, &bar_full[s], 0, y, bh);
+        tma_load_tile(st, &mapQ, &bar_full[s], y, h, bb);
+        tma_load_tile(st + kTileBytes, &mapK, &bar_full[s], y, h, bb);
+        tma_load_tile(st + 2 * kTileBytes, &mapV, &bar_full[s], y, h, bb);
+        tma_load_tile(st + 3 * kTileBytes, &mapDO, &bar_full[s], y, h, bb);
       }
       for (int i = (2 * n >= 2 ? 2 * n - 2 : 0); ok && i < 2 * n; ++i) ok = retire(i);
       tma_store_wait<0>();

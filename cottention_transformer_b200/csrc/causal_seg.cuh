@@ -36,7 +36,7 @@ seg_state_kernel(const __grid_constant__ CUtensorMap mapY, const __grid_constant
 
   const int tid = threadIdx.x, lane = tid & 31;
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
-  const int bh = blockIdx.x, h = bh % H, seg = blockIdx.y;
+  const int bh = blockIdx.x, h = bh % H, bb = bh / H, seg = blockIdx.y;
   const int total_chunks = (N + kTcChunk - 1) / kTcChunk;
   const int chunk0 = seg * chunks_per_seg;
   const int nchunks = min(chunks_per_seg, total_chunks - chunk0);
@@ -72,8 +72,8 @@ seg_state_kernel(const __grid_constant__ CUtensorMap mapY, const __grid_constant
         if (c >= 2 && !wait_bar(&bar_free[s], ((c >> 1) - 1) & 1, abort_flag, kWaitStageFree, c)) break;
         unsigned char* st = smem + s * 2 * kTileBytes;
         mbar_expect_tx(&bar_full[s], 2 * kTileBytes);
-        tma_load_3d(st, &mapY, &bar_full[s], 0, (chunk0 + c) * kTcChunk, bh);
-        tma_load_3d(st + kTileBytes, &mapZ, &bar_full[s], 0, (chunk0 + c) * kTcChunk, bh);
+        tma_load_tile(st, &mapY, &bar_full[s], (chunk0 + c) * kTcChunk, h, bb);
+        tma_load_tile(st + kTileBytes, &mapZ, &bar_full[s], (chunk0 + c) * kTcChunk, h, bb);
       }
     }
   } else if (warp == 1) {

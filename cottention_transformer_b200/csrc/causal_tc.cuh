@@ -510,7 +510,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   const int tid = threadIdx.x, lane = tid & 31;
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // broadcast: provably warp-uniform
   const int bh = blockIdx.x;
-  const int h = bh % H;
+  const int h = bh % H, bb = bh / H;
   // Segment-parallel launches (gridDim.y > 1) give each CTA `chunks_per_seg` consecutive chunks of the
   // sequence and the state before its first chunk (`init_state[bh][seg]`, fp32 [64 x 64] in this kernel's
   // own state layout, rows = columns of Y); chunk numbers below are local, `chunk0 + c` is the position.
@@ -641,10 +641,10 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         }
 #endif
         mbar_expect_tx(&bar_full[s], STAGE + kTileBytes);
-        if (MODE == kModeDq) tma_load_3d(st, &mapX, &bar_full[s], 0, (chunk0 + c) * kTcChunk, bh);
-        tma_load_3d(st + kIdxY * kTileBytes, &mapY, &bar_full[s], 0, (chunk0 + c) * kTcChunk, bh);
-        tma_load_3d(st + kIdxZ * kTileBytes, &mapZ, &bar_full[s], 0, (chunk0 + c) * kTcChunk, bh);
-        tma_load_3d(ring_of(c), MODE == kModeDq ? &mapQ : &mapX, &bar_full[s], 0, (chunk0 + c) * kTcChunk, bh);
+        if (MODE == kModeDq) tma_load_tile(st, &mapX, &bar_full[s], (chunk0 + c) * kTcChunk, h, bb);
+        tma_load_tile(st + kIdxY * kTileBytes, &mapY, &bar_full[s], (chunk0 + c) * kTcChunk, h, bb);
+        tma_load_tile(st + kIdxZ * kTileBytes, &mapZ, &bar_full[s], (chunk0 + c) * kTcChunk, h, bb);
+        tma_load_tile(ring_of(c), MODE == kModeDq ? &mapQ : &mapX, &bar_full[s], (chunk0 + c) * kTcChunk, h, bb);
         COTT_TRACE_EV(0, c);
       };
       for (int c = 0; c < NS && c < nchunks; ++c) issue_loads(c);
@@ -659,7 +659,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         }
         if (!wait_bar(&bar_out[s], (c / NS) & 1, abort_flag, kWaitStageFree, c)) break;
 #if !(COTT_SKEL & 16)
-        tma_store_3d(&mapOut, ring_of(c), 0, (chunk0 + c) * kTcChunk, bh);
+        tma_store_tile(&mapOut, ring_of(c), (chunk0 + c) * kTcChunk, h, bb);
         tma_store_commit();
 #endif
       }
@@ -884,7 +884,7 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   const int tid = threadIdx.x, lane = tid & 31;
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // broadcast: provably warp-uniform
   const int bh = blockIdx.x;
-  const int h = bh % H;
+  const int h = bh % H, bb = bh / H;
   // Segment-parallel launches (gridDim.y > 1): this CTA owns `chunks_per_seg` consecutive chunks, walks them
   // backwards, and starts from the state of everything after them (`init_state[bh][seg]`, fp32 [64 x 64],
   // rows d_k).  `ci` is local; the position of item ci is chunk `last_chunk - ci`.
@@ -949,15 +949,15 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         const int y = (last_chunk - ci) * kTcChunk;
         unsigned char* st = smem + s * STAGE;
         mbar_expect_tx(&bar_full[s], STAGE);
-        tma_load_3d(st, &mapQ, &bar_full[s], 0, y, bh);
-        tma_load_3d(st + 3 * kTileBytes, &mapDO, &bar_full[s], 0, y, bh);
+        tma_load_tile(st, &mapQ, &bar_full[s], y, h, bb);
+        tma_load_tile(st + 3 * kTileBytes, &mapDO, &bar_full[s], y, h, bb);
       };
       auto load_staging = [&](int ci) {
         const int s = ci % NS;
         const int y = (last_chunk - ci) * kTcChunk;
         unsigned char* st = smem + s * STAGE;
-        tma_load_3d(st + kTileBytes, &mapK, &bar_full[s], 0, y, bh);
-        tma_load_3d(st + 2 * kTileBytes, &mapV, &bar_full[s], 0, y, bh);
+        tma_load_tile(st + kTileBytes, &mapK, &bar_full[s], y, h, bb);
+        tma_load_tile(st + 2 * kTileBytes, &mapV, &bar_full[s], y, h, bb);
       };
       for (int ci = 0; ci < NS && ci < nchunks; ++ci) {
         load_inputs(ci);
@@ -973,8 +973,8 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
           load_inputs(ci + NS);
         }
         if (!wait_bar(&bar_out[s], (ci / NS) & 1, abort_flag, kWaitStageFree, ci)) break;
-        tma_store_3d(&mapDV, smem + s * STAGE + 2 * kTileBytes, 0, y, bh);
-        tma_store_3d(&mapDK, smem + s * STAGE + kTileBytes, 0, y, bh);
+        tma_store_tile(&mapDV, smem + s * STAGE + 2 * kTileBytes, y, h, bb);
+        tma_store_tile(&mapDK, smem + s * STAGE + kTileBytes, y, h, bb);
         tma_store_commit();
         if (refill) {
           tma_store_wait_read<0>();

@@ -28,10 +28,12 @@ int aligned16(const void* p, const char* name) {
   return COTT_OK;
 }
 
-int tmap(CUtensorMap* m, const void* p, int dtype, long BH, long N) {
-  int r = make_tmap_rows64(m, p, dtype == COTT_BF16, BH, N, kTcD, kTcChunk);
+int tmap(CUtensorMap* m, const void* p, int dtype, long B, long H, long N, TileStrides st) {
+  if ((st.b | st.h | st.n) & 7 || st.b <= 0 || st.h <= 0 || st.n <= 0)
+    return fail(COTT_ERR_ALIGN, "tensor strides must be positive multiples of 8 elements (got %lld, %lld, %lld)", st.b, st.h, st.n);
+  int r = make_tmap_rows64(m, p, dtype == COTT_BF16, B, H, N, st, kTcChunk);
   if (r == 1) return fail(COTT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-  if (r) return fail(COTT_ERR_CUDA, "cuTensorMapEncodeTiled failed: CUresult %d (ptr %p, BH %ld, N %ld)", r - 100, p, BH, N);
+  if (r) return fail(COTT_ERR_CUDA, "cuTensorMapEncodeTiled failed: CUresult %d (ptr %p, B %ld, H %ld, N %ld)", r - 100, p, B, H, N);
   return COTT_OK;
 }
 
@@ -42,7 +44,10 @@ struct SegPlan {
   int cps = 0;   // chunks per segment
   const unsigned char* keep = nullptr;  // padding: [B, N] keep flags and their inclusive running count, or both null
   const int* count = nullptr;
+  TileStrides in{0, 0, 0}, out{0, 0, 0};  // strides of q, k, v, dq, dk, dv / of out, dout; all zero = contiguous [B,H,N,64]
 };
+TileStrides in_strides(const SegPlan& p, long H, long N) { return p.in.n ? p.in : contiguous_bhnd(H, N); }
+TileStrides out_strides(const SegPlan& p, long H, long N) { return p.out.n ? p.out : contiguous_bhnd(H, N); }
 SegPlan plan_segments(int N, int nseg_requested) {
   const int total = (N + kTcChunk - 1) / kTcChunk;
   SegPlan p;
@@ -58,8 +63,8 @@ int launch_fwd(const void* q, const void* k, const void* v, const float* nc, voi
   const long BH = (long)B * H;
   CUtensorMap mq, mk, mv, mo;
   int st;
-  if ((st = tmap(&mq, q, dtype, BH, N)) || (st = tmap(&mk, k, dtype, BH, N)) || (st = tmap(&mv, v, dtype, BH, N)) ||
-      (st = tmap(&mo, out, dtype, BH, N)))
+  if ((st = tmap(&mq, q, dtype, B, H, N, in_strides(plan, H, N))) || (st = tmap(&mk, k, dtype, B, H, N, in_strides(plan, H, N))) || (st = tmap(&mv, v, dtype, B, H, N, in_strides(plan, H, N))) ||
+      (st = tmap(&mo, out, dtype, B, H, N, out_strides(plan, H, N))))
     return st;
   const bool ext = plan.nseg > 1 || init || plan.keep;
   auto kern = ext ? causal_tc_kernel<T, kModeFwd, true> : causal_tc_kernel<T, kModeFwd, false>;
@@ -77,9 +82,9 @@ int launch_bwd_dq(const void* q, const void* k, const void* v, const float* nc, 
   const long BH = (long)B * H;
   CUtensorMap mq, mk, mv, md, mo;
   int st;
-  if ((st = tmap(&mq, q, dtype, BH, N)) || (st = tmap(&mk, k, dtype, BH, N)) ||
-      (st = tmap(&mv, v, dtype, BH, N)) || (st = tmap(&md, dout, dtype, BH, N)) ||
-      (st = tmap(&mo, dq, dtype, BH, N)))
+  if ((st = tmap(&mq, q, dtype, B, H, N, in_strides(plan, H, N))) || (st = tmap(&mk, k, dtype, B, H, N, in_strides(plan, H, N))) ||
+      (st = tmap(&mv, v, dtype, B, H, N, in_strides(plan, H, N))) || (st = tmap(&md, dout, dtype, B, H, N, out_strides(plan, H, N))) ||
+      (st = tmap(&mo, dq, dtype, B, H, N, in_strides(plan, H, N))))
     return st;
   const bool ext = plan.nseg > 1 || init || plan.keep;
   auto kern = ext ? causal_tc_kernel<T, kModeDq, true> : causal_tc_kernel<T, kModeDq, false>;
@@ -98,9 +103,9 @@ int launch_bwd_dkdv(const void* q, const void* k, const void* v, const float* nc
   const long BH = (long)B * H;
   CUtensorMap mq, mk, mv, md, mdk, mdv;
   int st;
-  if ((st = tmap(&mq, q, dtype, BH, N)) || (st = tmap(&mk, k, dtype, BH, N)) ||
-      (st = tmap(&mv, v, dtype, BH, N)) || (st = tmap(&md, dout, dtype, BH, N)) ||
-      (st = tmap(&mdk, dk, dtype, BH, N)) || (st = tmap(&mdv, dv, dtype, BH, N)))
+  if ((st = tmap(&mq, q, dtype, B, H, N, in_strides(plan, H, N))) || (st = tmap(&mk, k, dtype, B, H, N, in_strides(plan, H, N))) ||
+      (st = tmap(&mv, v, dtype, B, H, N, in_strides(plan, H, N))) || (st = tmap(&md, dout, dtype, B, H, N, out_strides(plan, H, N))) ||
+      (st = tmap(&mdk, dk, dtype, B, H, N, in_strides(plan, H, N))) || (st = tmap(&mdv, dv, dtype, B, H, N, in_strides(plan, H, N))))
     return st;
   COTT_CUDA_TRY(cudaMemsetAsync(dnorm, 0, sizeof(float) * H, stream));
   const bool ext = plan.nseg > 1 || init || plan.keep;
@@ -115,12 +120,12 @@ int launch_bwd_dkdv(const void* q, const void* k, const void* v, const float* nc
 
 // state[bh][seg] of every segment: Y^T Z with one operand row-scaled (see seg_state_kernel)
 template <typename T, int MODE>
-int launch_seg_state(const void* y, const void* z, const float* nc, float* state, int B, int H, int N, int dtype,
-                     SegPlan plan, cudaStream_t stream) {
+int launch_seg_state(const void* y, const void* z, TileStrides sy, TileStrides sz, const float* nc, float* state, int B,
+                     int H, int N, int dtype, SegPlan plan, cudaStream_t stream) {
   const long BH = (long)B * H;
   CUtensorMap my, mz;
   int st;
-  if ((st = tmap(&my, y, dtype, BH, N)) || (st = tmap(&mz, z, dtype, BH, N))) return st;
+  if ((st = tmap(&my, y, dtype, B, H, N, sy)) || (st = tmap(&mz, z, dtype, B, H, N, sz))) return st;
   auto kern = seg_state_kernel<T, MODE>;
   const size_t smem = seg_state_smem_bytes();
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -134,10 +139,17 @@ int launch_seg_state(const void* y, const void* z, const float* nc, float* state
 //   4 their exclusive suffix
 size_t seg_array_floats(int B, int H, int nseg) { return (size_t)B * H * nseg * kTcD * kTcD; }
 
+void apply_layout(SegPlan& plan, const cott_layout* l) {
+  if (!l) return;
+  plan.in = TileStrides{l->in_b, l->in_h, l->in_n};
+  plan.out = TileStrides{l->out_b, l->out_h, l->out_n};
+}
+
 template <typename T>
 int run_fwd_seg(const void* q, const void* k, const void* v, const unsigned char* keep, const float* nc, void* out,
-                float* ws, int nseg, int B, int H, int N, int dtype, cudaStream_t stream) {
+                float* ws, int nseg, const cott_layout* layout, int B, int H, int N, int dtype, cudaStream_t stream) {
   SegPlan plan = plan_segments(N, nseg);
+  apply_layout(plan, layout);
   const size_t A = seg_array_floats(B, H, plan.nseg);
   if (keep) {  // running count of the kept positions, behind the five state arrays
     int* count = reinterpret_cast<int*>(ws + 5 * A);
@@ -147,7 +159,7 @@ int run_fwd_seg(const void* q, const void* k, const void* v, const unsigned char
     plan.count = count;
   }
   if (plan.nseg == 1) return launch_fwd<T>(q, k, v, nc, out, B, H, N, dtype, stream, nullptr, plan);
-  int st = launch_seg_state<T, kSegFwdState>(k, v, nc, ws, B, H, N, dtype, plan, stream);
+  int st = launch_seg_state<T, kSegFwdState>(k, v, in_strides(plan, H, N), in_strides(plan, H, N), nc, ws, B, H, N, dtype, plan, stream);
   if (st) return st;
   seg_scan_kernel<<<(unsigned)((long)B * H), 256, 0, stream>>>(ws, ws + A, ws + 2 * A, nullptr, plan.nseg);
   COTT_CUDA_TRY(cudaGetLastError());
@@ -156,9 +168,10 @@ int run_fwd_seg(const void* q, const void* k, const void* v, const unsigned char
 
 template <typename T>
 int run_bwd_seg(const void* q, const void* k, const void* v, const unsigned char* keep, const float* nc, const void* dout,
-                float* ws, int nseg, void* dq, void* dk, void* dv, float* dnorm, int B, int H, int N, int dtype,
-                cudaStream_t stream) {
+                float* ws, int nseg, const cott_layout* layout, void* dq, void* dk, void* dv, float* dnorm, int B, int H,
+                int N, int dtype, cudaStream_t stream) {
   SegPlan plan = plan_segments(N, nseg);
+  apply_layout(plan, layout);
   const size_t A = seg_array_floats(B, H, plan.nseg);
   if (keep) {  // the forward call left the running count in the workspace
     plan.keep = keep;
@@ -172,7 +185,8 @@ int run_bwd_seg(const void* q, const void* k, const void* v, const unsigned char
   int st = launch_bwd_dq<T>(q, k, v, nc, dout, dq, B, H, N, dtype, stream, ws + 2 * A, plan);
   if (st) return st;
   // dK, dV: reverse states of the segments, their exclusive suffix
-  if ((st = launch_seg_state<T, kSegRevState>(q, dout, nc, ws + 3 * A, B, H, N, dtype, plan, stream))) return st;
+  if ((st = launch_seg_state<T, kSegRevState>(q, dout, in_strides(plan, H, N), out_strides(plan, H, N), nc, ws + 3 * A, B, H, N, dtype, plan,
+                                              stream))) return st;
   seg_scan_kernel<<<(unsigned)((long)B * H), 256, 0, stream>>>(ws + 3 * A, nullptr, nullptr, ws + 4 * A, plan.nseg);
   COTT_CUDA_TRY(cudaGetLastError());
   return launch_bwd_dkdv<T>(q, k, v, nc, dout, dk, dv, dnorm, B, H, N, dtype, stream, ws + 4 * A, plan);
@@ -193,8 +207,8 @@ int launch_bidir_fwd_tc_t(const void* q, const void* k, const void* v, const uns
   const long BH = (long)B * H;
   CUtensorMap mq, mk, mv, mo;
   int st;
-  if ((st = tmap(&mq, q, dtype, BH, N)) || (st = tmap(&mk, k, dtype, BH, N)) || (st = tmap(&mv, v, dtype, BH, N)) ||
-      (st = tmap(&mo, out, dtype, BH, N)))
+  if ((st = tmap(&mq, q, dtype, B, H, N, contiguous_bhnd(H, N))) || (st = tmap(&mk, k, dtype, B, H, N, contiguous_bhnd(H, N))) || (st = tmap(&mv, v, dtype, B, H, N, contiguous_bhnd(H, N))) ||
+      (st = tmap(&mo, out, dtype, B, H, N, contiguous_bhnd(H, N))))
     return st;
   auto kern = bidir_fwd_tc_kernel<T>;
   const size_t smem = bidir_fwd_tc_smem_bytes();
@@ -211,9 +225,9 @@ int launch_bidir_bwd_tc_t(const void* q, const void* k, const void* v, const uns
   const long BH = (long)B * H;
   CUtensorMap mq, mk, mv, md, mdq, mdk, mdv;
   int st;
-  if ((st = tmap(&mq, q, dtype, BH, N)) || (st = tmap(&mk, k, dtype, BH, N)) || (st = tmap(&mv, v, dtype, BH, N)) ||
-      (st = tmap(&md, dout, dtype, BH, N)) || (st = tmap(&mdq, dq, dtype, BH, N)) || (st = tmap(&mdk, dk, dtype, BH, N)) ||
-      (st = tmap(&mdv, dv, dtype, BH, N)))
+  if ((st = tmap(&mq, q, dtype, B, H, N, contiguous_bhnd(H, N))) || (st = tmap(&mk, k, dtype, B, H, N, contiguous_bhnd(H, N))) || (st = tmap(&mv, v, dtype, B, H, N, contiguous_bhnd(H, N))) ||
+      (st = tmap(&md, dout, dtype, B, H, N, contiguous_bhnd(H, N))) || (st = tmap(&mdq, dq, dtype, B, H, N, contiguous_bhnd(H, N))) || (st = tmap(&mdk, dk, dtype, B, H, N, contiguous_bhnd(H, N))) ||
+      (st = tmap(&mdv, dv, dtype, B, H, N, contiguous_bhnd(H, N))))
     return st;
   COTT_CUDA_TRY(cudaMemsetAsync(dnorm, 0, sizeof(float) * H, stream));
   auto kern = bidir_bwd_tc_kernel<T>;
@@ -329,8 +343,8 @@ size_t cott_cos_attn_seg_workspace_bytes(int B, int H, int N, int nseg) {
 }
 
 int cott_cos_attn_fwd_seg(const void* q, const void* k, const void* v, const unsigned char* keep,
-                          const float* norm_const, void* out, void* workspace, int nseg, int B, int H, int N, int Dk,
-                          int Dv, int dtype, void* stream) {
+                          const float* norm_const, void* out, void* workspace, int nseg, const cott_layout* layout,
+                          int B, int H, int N, int Dk, int Dv, int dtype, void* stream) {
   int st = check_fused_args(B, H, N, Dk, Dv, dtype);
   if (st) return st;
   if ((long)B * H * N == 0) return COTT_OK;
@@ -340,13 +354,14 @@ int cott_cos_attn_fwd_seg(const void* q, const void* k, const void* v, const uns
   COTT_CUDA_TRY(scope.status());
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   float* ws = static_cast<float*>(workspace);
-  return dtype == COTT_BF16 ? run_fwd_seg<__nv_bfloat16>(q, k, v, keep, norm_const, out, ws, nseg, B, H, N, dtype, s)
-                            : run_fwd_seg<__half>(q, k, v, keep, norm_const, out, ws, nseg, B, H, N, dtype, s);
+  return dtype == COTT_BF16 ? run_fwd_seg<__nv_bfloat16>(q, k, v, keep, norm_const, out, ws, nseg, layout, B, H, N, dtype, s)
+                            : run_fwd_seg<__half>(q, k, v, keep, norm_const, out, ws, nseg, layout, B, H, N, dtype, s);
 }
 
 int cott_cos_attn_bwd_seg(const void* q, const void* k, const void* v, const unsigned char* keep,
-                          const float* norm_const, const void* dout, void* workspace, int nseg, void* dq, void* dk,
-                          void* dv, float* dnorm_const, int B, int H, int N, int Dk, int Dv, int dtype, void* stream) {
+                          const float* norm_const, const void* dout, void* workspace, int nseg,
+                          const cott_layout* layout, void* dq, void* dk, void* dv, float* dnorm_const, int B, int H,
+                          int N, int Dk, int Dv, int dtype, void* stream) {
   int st = check_fused_args(B, H, N, Dk, Dv, dtype);
   if (st) return st;
   if (!dnorm_const && H > 0) return fail(COTT_ERR_NULL, "null pointer: dnorm_const");
@@ -363,8 +378,8 @@ int cott_cos_attn_bwd_seg(const void* q, const void* k, const void* v, const uns
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   float* ws = static_cast<float*>(workspace);
   return dtype == COTT_BF16
-             ? run_bwd_seg<__nv_bfloat16>(q, k, v, keep, norm_const, dout, ws, nseg, dq, dk, dv, dnorm_const, B, H, N, dtype, s)
-             : run_bwd_seg<__half>(q, k, v, keep, norm_const, dout, ws, nseg, dq, dk, dv, dnorm_const, B, H, N, dtype, s);
+             ? run_bwd_seg<__nv_bfloat16>(q, k, v, keep, norm_const, dout, ws, nseg, layout, dq, dk, dv, dnorm_const, B, H, N, dtype, s)
+             : run_bwd_seg<__half>(q, k, v, keep, norm_const, dout, ws, nseg, layout, dq, dk, dv, dnorm_const, B, H, N, dtype, s);
 }
 
 int cott_cos_attn_prefill_state(const void* k, const void* v, const float* norm_const, float* state, void* workspace,
@@ -384,8 +399,10 @@ int cott_cos_attn_prefill_state(const void* k, const void* v, const float* norm_
   if (!norm_const) return fail(COTT_ERR_NULL, "null pointer: norm_const");
   const SegPlan plan = plan_segments(N, nseg);
   float* ws = static_cast<float*>(workspace);
-  st = dtype == COTT_BF16 ? launch_seg_state<__nv_bfloat16, kSegFwdState>(k, v, norm_const, ws, B, H, N, dtype, plan, s)
-                          : launch_seg_state<__half, kSegFwdState>(k, v, norm_const, ws, B, H, N, dtype, plan, s);
+  st = dtype == COTT_BF16 ? launch_seg_state<__nv_bfloat16, kSegFwdState>(k, v, contiguous_bhnd(H, N), contiguous_bhnd(H, N), norm_const, ws, B, H, N,
+                                                                        dtype, plan, s)
+                          : launch_seg_state<__half, kSegFwdState>(k, v, contiguous_bhnd(H, N), contiguous_bhnd(H, N), norm_const, ws, B, H, N, dtype,
+                                                                 plan, s);
   if (st) return st;
   seg_to_decode_state_kernel<<<(unsigned)((long)B * H), 256, 0, s>>>(ws, state, plan.nseg, accumulate != 0);
   COTT_CUDA_TRY(cudaGetLastError());

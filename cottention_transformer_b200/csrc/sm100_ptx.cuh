@@ -98,21 +98,23 @@ __device__ __forceinline__ void tc_fence_after_sync() {
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
-// 3-D tiled load global -> shared, completion on an mbarrier (bytes).  Coordinates are
-// (x = innermost, y, z); x * element size must be a multiple of 16 bytes.
-__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x,
-                                            int y, int z) {
+// 4-D tiled load global -> shared, completion on an mbarrier (bytes).  The tensors of this library are
+// [batch, head, position, 64] with arbitrary (16-byte aligned) strides for batch, head and position: the
+// map's dimensions are (64, N, H, B) and a tile is addressed by (0, y = first position, h, b).  The innermost
+// coordinate is always 0, so the 16-byte rule for it holds trivially.
+__device__ __forceinline__ void tma_load_tile(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int y, int h,
+                                              int b) {
   asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y),
-      "r"(z)
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(0), "r"(y), "r"(h),
+      "r"(b)
       : "memory");
 }
-// 3-D tiled store shared -> global (bulk group completion).  Never start at a negative coordinate.
-__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* smem_src, int x, int y, int z) {
-  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+// 4-D tiled store shared -> global (bulk group completion).  Never start at a negative coordinate.
+__device__ __forceinline__ void tma_store_tile(const CUtensorMap* map, const void* smem_src, int y, int h, int b) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
                    reinterpret_cast<uint64_t>(map)),
-               "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+               "r"(smem_u32(smem_src)), "r"(0), "r"(y), "r"(h), "r"(b)
                : "memory");
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
@@ -271,17 +273,24 @@ inline PFN_encodeTiled get_encode_tiled() {
   }
   return fn;
 }
-// Tensor map over a dense [BH, N, D] tensor of 16-bit elements, box = (64 columns, box_rows, 1),
-// 128-byte swizzle, out-of-range rows read as zero.  `col0` selects the 64-column block.
-inline int make_tmap_rows64(CUtensorMap* map, const void* base, int is_bf16, long BH, long N, int D,
+
+// Strides (in elements) of a [B, H, N, 64] tensor whose innermost dimension is contiguous.
+struct TileStrides {
+  long long b, h, n;
+};
+inline TileStrides contiguous_bhnd(long H, long N) { return TileStrides{H * N * 64, N * 64, 64}; }
+
+// Tensor map of a [B, H, N, 64] 16-bit tensor with the given strides: dimensions (64, N, H, B), box
+// (64, box_rows, 1, 1), 128-byte swizzle.  Returns 0, 1 (driver entry point missing) or 100 + CUresult.
+inline int make_tmap_rows64(CUtensorMap* map, const void* base, int is_bf16, long B, long H, long N, TileStrides st,
                             int box_rows) {
   PFN_encodeTiled enc = get_encode_tiled();
   if (!enc) return 1;
-  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)N, (cuuint64_t)BH};
-  cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)N * D * 2};
-  cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+  cuuint64_t dims[4] = {64, (cuuint64_t)N, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)st.n * 2, (cuuint64_t)st.h * 2, (cuuint64_t)st.b * 2};
+  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
                    const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);

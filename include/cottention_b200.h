@@ -125,16 +125,26 @@ int cott_cos_attn_bwd_dkdv(const void* q, const void* k, const void* v, const fl
  * These two calls also take the padding mask of GPTCosAttention.py:232-248: `keep` ([B, N] bytes, non-zero =
  * un-masked, NULL = no padding) zeroes the masked rows of q^, k^, v' and makes n_s the running count of
  * un-masked positions; nseg = 1 is allowed (one CTA per sequence, workspace still needed for the count).
+ * They also take strided tensors: `layout` (NULL = contiguous [B,H,N,64]) gives the element strides of the batch,
+ * head and position dimensions, one triple for q, k, v, dq, dk, dv and one for out, dout (multiples of 8
+ * elements; base pointers 16-byte aligned).  q, k, v may so be slices of the packed [B, N, 3, H, 64] output of a
+ * QKV projection and out the [B, N, H*64] input of the output projection: the head split / merge permutes of
+ * GPTCosAttention.py:447-449,478-479,500 cost no copy.
  */
+typedef struct cott_layout { /* element strides of [B, H, N, 64] views whose innermost dimension is contiguous */
+  long long in_b, in_h, in_n;    /* q, k, v and dq, dk, dv */
+  long long out_b, out_h, out_n; /* out and dout */
+} cott_layout;
 int cott_cos_attn_seg_count(int B, int H, int N);
 size_t cott_cos_attn_seg_workspace_bytes(int B, int H, int N, int nseg);
 int cott_cos_attn_fwd_seg(const void* q, const void* k, const void* v, const unsigned char* keep,
-                          const float* norm_const, void* out, void* workspace, int nseg, int B, int H, int N,
-                          int Dk, int Dv, int dtype, void* stream);
+                          const float* norm_const, void* out, void* workspace, int nseg,
+                          const cott_layout* layout, int B, int H, int N, int Dk, int Dv, int dtype,
+                          void* stream);
 int cott_cos_attn_bwd_seg(const void* q, const void* k, const void* v, const unsigned char* keep,
-                          const float* norm_const, const void* dout, void* workspace, int nseg, void* dq,
-                          void* dk, void* dv, float* dnorm_const, int B, int H, int N, int Dk, int Dv,
-                          int dtype, void* stream);
+                          const float* norm_const, const void* dout, void* workspace, int nseg,
+                          const cott_layout* layout, void* dq, void* dk, void* dv, float* dnorm_const, int B,
+                          int H, int N, int Dk, int Dv, int dtype, void* stream);
 
 /*
  * Prefill -> decode hand-off: the decode state (cott_decode_step layout, float32 [B,H,Dv,Dk]) that a prompt of N

@@ -191,9 +191,9 @@ def test_repeated_cold_launches_give_identical_results(shape, segments):
     st, P = _lib.stream_ptr(q.device), (lambda t: t.data_ptr())
     first = None
     for _ in range(40):
-        _lib.check(L.cott_cos_attn_fwd_seg(P(q), P(k), P(v), None, P(nc), P(out), P(ws), segments, B, H, N, 64, 64, 3, st), "fwd")
+        _lib.check(L.cott_cos_attn_fwd_seg(P(q), P(k), P(v), None, P(nc), P(out), P(ws), segments, None, B, H, N, 64, 64, 3, st), "fwd")
         torch.cuda.synchronize()
-        _lib.check(L.cott_cos_attn_bwd_seg(P(q), P(k), P(v), None, P(nc), P(do), P(ws), segments, P(dq), P(dk), P(dv), P(dnc),
+        _lib.check(L.cott_cos_attn_bwd_seg(P(q), P(k), P(v), None, P(nc), P(do), P(ws), segments, None, P(dq), P(dk), P(dv), P(dnc),
                                            B, H, N, 64, 64, 3, st), "bwd")
         torch.cuda.synchronize()
         _lib.check_device_status()
@@ -202,3 +202,33 @@ def test_repeated_cold_launches_give_identical_results(shape, segments):
             first = cur
         else:
             assert all(torch.equal(a, b) for a, b in zip(cur, first))
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(2, 3, 300), (1, 2, 1000), (2, 16, 1024)])
+@pytest.mark.parametrize("masked", [False, True])
+def test_packed_qkv_layout_matches_the_permuted_op(dt, shape, masked):
+    """q, k, v read as strided slices of a packed [B, N, 3, H, 64] tensor, out written as [B, N, H, 64], gradients
+    written into a packed tensor: bit-identical to the op on permuted contiguous copies (same kernels, same order
+    of operations; only the tensor maps differ)."""
+    from cottention_transformer_b200 import cos_attn_causal, cos_attn_causal_packed, _lib
+    B, H, N = shape
+    g = torch.Generator(device="cuda").manual_seed(N + H)
+    qkv = torch.randn(B, N, 3, H, 64, device="cuda", generator=g).to(dt).requires_grad_()
+    do = torch.randn(B, N, H, 64, device="cuda", generator=g).to(dt)
+    nc = torch.linspace(-0.5, 1.0, H, device="cuda").requires_grad_()
+    keep = None
+    if masked:
+        keep = torch.ones(B, N, dtype=torch.bool, device="cuda")
+        keep[0, (2 * N) // 3:] = False
+    out = cos_attn_causal_packed(qkv, nc, keep)
+    out.backward(do)
+    _lib.check_device_status()
+    q2, k2, v2 = (qkv.detach()[:, :, i].permute(0, 2, 1, 3).contiguous().requires_grad_() for i in range(3))
+    nc2 = nc.detach().clone().requires_grad_()
+    ref = cos_attn_causal(q2, k2, v2, nc2, keep)
+    ref.backward(do.permute(0, 2, 1, 3).contiguous())
+    assert torch.equal(out.detach(), ref.detach().permute(0, 2, 1, 3))
+    for i, gref in enumerate((q2.grad, k2.grad, v2.grad)):
+        assert torch.equal(qkv.grad[:, :, i], gref.permute(0, 2, 1, 3)), i
+    assert torch.allclose(nc.grad, nc2.grad, rtol=1e-5, atol=1e-6)
