@@ -23,7 +23,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .cos_attention import cos_attn_bidirectional, cos_attn_causal, cos_attn_causal_packed
+from .cos_attention import (cos_attn_bidirectional, cos_attn_bidirectional_packed, cos_attn_causal,
+                            cos_attn_causal_packed)
 
 
 class CosSelfAttention(nn.Module):
@@ -39,8 +40,9 @@ class CosSelfAttention(nn.Module):
     def forward(self, x):
         B, S, D = x.shape
         qkv = self.qkv(x).view(B, S, 3, self.h, D // self.h)
-        if self.causal and not self.permute:  # strided tensor maps: no head split / merge copies
-            return self.proj(cos_attn_causal_packed(qkv, self.norm_const).reshape(B, S, D))
+        if not self.permute:  # strided tensor maps: no head split / merge copies
+            op = cos_attn_causal_packed if self.causal else cos_attn_bidirectional_packed
+            return self.proj(op(qkv, self.norm_const).reshape(B, S, D))
         qkv = qkv.permute(2, 0, 3, 1, 4).contiguous()  # [3,B,H,S,d]
         op = cos_attn_causal if self.causal else cos_attn_bidirectional
         o = op(qkv[0], qkv[1], qkv[2], self.norm_const)
@@ -91,7 +93,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (smoke runs)")
-    ap.add_argument("--permute", action="store_true", help="gpt: permute + copy around the op instead of the packed layout")
+    ap.add_argument("--permute", action="store_true", help="permute + copy around the op instead of the packed layout")
     a = ap.parse_args()
     CosSelfAttention.permute = a.permute
     world, rank, local = (int(os.environ.get(k, d)) for k, d in (("WORLD_SIZE", 1), ("RANK", 0), ("LOCAL_RANK", 0)))

@@ -214,6 +214,53 @@ class _Bidirectional(torch.autograd.Function):
         return dq, dk, dv, dnc.reshape(ctx.nc_shape).to(ctx.nc_dtype), None
 
 
+class _BidirectionalPacked(torch.autograd.Function):
+    """Bidirectional op on a packed ``[B, N, 3, H, 64]`` tensor; see ``_FusedCausalPacked``."""
+
+    @staticmethod
+    def forward(ctx, qkv, norm_const, keep=None):
+        qkv = qkv.contiguous()
+        B, N, three, H, D = qkv.shape
+        nc = norm_const.detach().reshape(-1).to(device=qkv.device, dtype=torch.float32).contiguous()
+        out = torch.empty(B, N, H, D, dtype=qkv.dtype, device=qkv.device)
+        lay = _lib.CottLayout(N * 3 * H * D, D, 3 * H * D, N * H * D, D, H * D)
+        kp = None if keep is None else keep.to(device=qkv.device, dtype=torch.uint8).contiguous()
+        with torch.cuda.device(qkv.device):
+            st = _lib.lib().cott_bidir_fwd_strided(
+                _lib.ptr(qkv[:, :, 0]), _lib.ptr(qkv[:, :, 1]), _lib.ptr(qkv[:, :, 2]), _lib.ptr(kp), _lib.ptr(nc), _lib.ptr(out),
+                ctypes.byref(lay), B, H, N, D, D, _lib.DTYPE_CODE[qkv.dtype], _lib.stream_ptr(qkv.device))
+        _lib.check(st, "cott_bidir_fwd_strided")
+        ctx.save_for_backward(qkv, nc)
+        ctx.kp, ctx.lay = kp, lay
+        ctx.nc_shape, ctx.nc_dtype = norm_const.shape, norm_const.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, nc = ctx.saved_tensors
+        B, N, three, H, D = qkv.shape
+        dout = dout.contiguous().to(qkv.dtype)
+        dqkv = torch.empty_like(qkv)
+        dnc = torch.empty(H, dtype=torch.float32, device=qkv.device)
+        with torch.cuda.device(qkv.device):
+            st = _lib.lib().cott_bidir_bwd_strided(
+                _lib.ptr(qkv[:, :, 0]), _lib.ptr(qkv[:, :, 1]), _lib.ptr(qkv[:, :, 2]), _lib.ptr(ctx.kp), _lib.ptr(nc),
+                _lib.ptr(dout), ctypes.byref(ctx.lay), _lib.ptr(dqkv[:, :, 0]), _lib.ptr(dqkv[:, :, 1]), _lib.ptr(dqkv[:, :, 2]),
+                _lib.ptr(dnc), B, H, N, D, D, _lib.DTYPE_CODE[qkv.dtype], _lib.stream_ptr(qkv.device))
+        _lib.check(st, "cott_bidir_bwd_strided")
+        return dqkv, dnc.reshape(ctx.nc_shape).to(ctx.nc_dtype), None
+
+
+def cos_attn_bidirectional_packed(qkv, norm_const, keep=None):
+    """Bidirectional cosine attention on a packed ``[B, N, 3, H, 64]`` bf16 / fp16 tensor; returns ``[B, N, H, 64]``.
+    Same function as ``cos_attn_bidirectional`` on the permuted tensors, without the permute copies."""
+    if not qkv.is_cuda:
+        raise RuntimeError("cos_attn_bidirectional_packed needs a CUDA tensor (there is no CPU path)")
+    if qkv.dim() != 5 or qkv.shape[2] != 3 or qkv.shape[-1] != 64 or qkv.dtype not in FUSED_DTYPES:
+        raise RuntimeError("cos_attn_bidirectional_packed takes a [B, N, 3, H, 64] bfloat16 / float16 tensor")
+    return _BidirectionalPacked.apply(qkv, norm_const, keep)
+
+
 def cos_attn_bidirectional(q, k, v, norm_const, keep=None):
     """Bidirectional cosine attention with the learned length-norm, the cosine section of the
     reference's ``BertCosAttention.forward`` (``BERT_Trainer/BertCosAttention.py:162-178,249``).

@@ -133,4 +133,38 @@ int cott_bidir_bwd(const void* q, const void* k, const void* v, const unsigned c
   }
 }
 
+int cott_bidir_fwd_strided(const void* q, const void* k, const void* v, const unsigned char* keep,
+                           const float* norm_const, void* out, const cott_layout* layout, int B, int H, int N, int Dk,
+                           int Dv, int dtype, void* stream) {
+  int st = check_bidir(B, H, N, Dk, Dv, dtype);
+  if (st) return st;
+  if ((long)B * H * N == 0) return COTT_OK;
+  if (!q || !k || !v || !norm_const || !out) return fail(COTT_ERR_NULL, "null pointer");
+  if (!bidir_tc_usable(Dk, Dv, dtype, {q, k, v, out}))
+    return fail(COTT_ERR_UNSUPPORTED, "strided bidirectional attention needs head dim 64, a 16-bit dtype and 16-byte aligned tensors");
+  DeviceScope scope(q);
+  COTT_CUDA_TRY(scope.status());
+  return launch_bidir_fwd_tc(q, k, v, keep, norm_const, out, B, H, N, dtype, static_cast<cudaStream_t>(stream), layout);
+}
+
+int cott_bidir_bwd_strided(const void* q, const void* k, const void* v, const unsigned char* keep,
+                           const float* norm_const, const void* dout, const cott_layout* layout, void* dq, void* dk,
+                           void* dv, float* dnorm_const, int B, int H, int N, int Dk, int Dv, int dtype, void* stream) {
+  int st = check_bidir(B, H, N, Dk, Dv, dtype);
+  if (st) return st;
+  if (!dnorm_const && H > 0) return fail(COTT_ERR_NULL, "null pointer: dnorm_const");
+  if (H == 0) return COTT_OK;
+  DeviceScope scope(dnorm_const);
+  COTT_CUDA_TRY(scope.status());
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if ((long)B * H * N == 0) {
+    COTT_CUDA_TRY(cudaMemsetAsync(dnorm_const, 0, sizeof(float) * H, s));
+    return COTT_OK;
+  }
+  if (!q || !k || !v || !norm_const || !dout || !dq || !dk || !dv) return fail(COTT_ERR_NULL, "null pointer");
+  if (!bidir_tc_usable(Dk, Dv, dtype, {q, k, v, dout, dq, dk, dv}))
+    return fail(COTT_ERR_UNSUPPORTED, "strided bidirectional attention needs head dim 64, a 16-bit dtype and 16-byte aligned tensors");
+  return launch_bidir_bwd_tc(q, k, v, keep, norm_const, dout, dq, dk, dv, dnorm_const, B, H, N, dtype, s, layout);
+}
+
 }  // extern "C"

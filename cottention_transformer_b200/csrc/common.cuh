@@ -95,9 +95,9 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_acc<__nv_bfloat16>(flo
 // problem qualifies; the launchers assume it does.
 bool bidir_tc_usable(int Dk, int Dv, int dtype, std::initializer_list<const void*> tensors);
 int launch_bidir_fwd_tc(const void* q, const void* k, const void* v, const unsigned char* keep, const float* nc,
-                        void* out, int B, int H, int N, int dtype, cudaStream_t stream);
+                        void* out, int B, int H, int N, int dtype, cudaStream_t stream, const cott_layout* layout = nullptr);
 int launch_bidir_bwd_tc(const void* q, const void* k, const void* v, const unsigned char* keep, const float* nc,
                         const void* dout, void* dq, void* dk, void* dv, float* dnorm, int B, int H, int N, int dtype,
-                        cudaStream_t stream);
+                        cudaStream_t stream, const cott_layout* layout = nullptr);
 
 }  // namespace cott

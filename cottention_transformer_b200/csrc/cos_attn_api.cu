@@ -203,12 +203,12 @@ int check_ptrs16(std::initializer_list<std::pair<const void*, const char*>> ps) 
 
 template <typename T>
 int launch_bidir_fwd_tc_t(const void* q, const void* k, const void* v, const unsigned char* keep, const float* nc,
-                          void* out, int B, int H, int N, int dtype, cudaStream_t stream) {
+                          void* out, int B, int H, int N, int dtype, cudaStream_t stream, TileStrides si, TileStrides so) {
   const long BH = (long)B * H;
   CUtensorMap mq, mk, mv, mo;
   int st;
-  if ((st = tmap(&mq, q, dtype, B, H, N, contiguous_bhnd(H, N))) || (st = tmap(&mk, k, dtype, B, H, N, contiguous_bhnd(H, N))) || (st = tmap(&mv, v, dtype, B, H, N, contiguous_bhnd(H, N))) ||
-      (st = tmap(&mo, out, dtype, B, H, N, contiguous_bhnd(H, N))))
+  if ((st = tmap(&mq, q, dtype, B, H, N, si)) || (st = tmap(&mk, k, dtype, B, H, N, si)) || (st = tmap(&mv, v, dtype, B, H, N, si)) ||
+      (st = tmap(&mo, out, dtype, B, H, N, so)))
     return st;
   auto kern = bidir_fwd_tc_kernel<T>;
   const size_t smem = bidir_fwd_tc_smem_bytes();
@@ -221,13 +221,13 @@ int launch_bidir_fwd_tc_t(const void* q, const void* k, const void* v, const uns
 template <typename T>
 int launch_bidir_bwd_tc_t(const void* q, const void* k, const void* v, const unsigned char* keep, const float* nc,
                           const void* dout, void* dq, void* dk, void* dv, float* dnorm, int B, int H, int N, int dtype,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, TileStrides si, TileStrides so) {
   const long BH = (long)B * H;
   CUtensorMap mq, mk, mv, md, mdq, mdk, mdv;
   int st;
-  if ((st = tmap(&mq, q, dtype, B, H, N, contiguous_bhnd(H, N))) || (st = tmap(&mk, k, dtype, B, H, N, contiguous_bhnd(H, N))) || (st = tmap(&mv, v, dtype, B, H, N, contiguous_bhnd(H, N))) ||
-      (st = tmap(&md, dout, dtype, B, H, N, contiguous_bhnd(H, N))) || (st = tmap(&mdq, dq, dtype, B, H, N, contiguous_bhnd(H, N))) || (st = tmap(&mdk, dk, dtype, B, H, N, contiguous_bhnd(H, N))) ||
-      (st = tmap(&mdv, dv, dtype, B, H, N, contiguous_bhnd(H, N))))
+  if ((st = tmap(&mq, q, dtype, B, H, N, si)) || (st = tmap(&mk, k, dtype, B, H, N, si)) || (st = tmap(&mv, v, dtype, B, H, N, si)) ||
+      (st = tmap(&md, dout, dtype, B, H, N, so)) || (st = tmap(&mdq, dq, dtype, B, H, N, si)) || (st = tmap(&mdk, dk, dtype, B, H, N, si)) ||
+      (st = tmap(&mdv, dv, dtype, B, H, N, si)))
     return st;
   COTT_CUDA_TRY(cudaMemsetAsync(dnorm, 0, sizeof(float) * H, stream));
   auto kern = bidir_bwd_tc_kernel<T>;
@@ -244,10 +244,12 @@ namespace cott {
 
 int launch_bidir_bwd_tc(const void* q, const void* k, const void* v, const unsigned char* keep, const float* nc,
                         const void* dout, void* dq, void* dk, void* dv, float* dnorm, int B, int H, int N, int dtype,
-                        cudaStream_t stream) {
+                        cudaStream_t stream, const cott_layout* l) {
+  const TileStrides si = l ? TileStrides{l->in_b, l->in_h, l->in_n} : contiguous_bhnd(H, N);
+  const TileStrides so = l ? TileStrides{l->out_b, l->out_h, l->out_n} : contiguous_bhnd(H, N);
   return dtype == COTT_BF16
-             ? launch_bidir_bwd_tc_t<__nv_bfloat16>(q, k, v, keep, nc, dout, dq, dk, dv, dnorm, B, H, N, dtype, stream)
-             : launch_bidir_bwd_tc_t<__half>(q, k, v, keep, nc, dout, dq, dk, dv, dnorm, B, H, N, dtype, stream);
+             ? launch_bidir_bwd_tc_t<__nv_bfloat16>(q, k, v, keep, nc, dout, dq, dk, dv, dnorm, B, H, N, dtype, stream, si, so)
+             : launch_bidir_bwd_tc_t<__half>(q, k, v, keep, nc, dout, dq, dk, dv, dnorm, B, H, N, dtype, stream, si, so);
 }
 
 bool bidir_tc_usable(int Dk, int Dv, int dtype, std::initializer_list<const void*> tensors) {
@@ -258,9 +260,11 @@ bool bidir_tc_usable(int Dk, int Dv, int dtype, std::initializer_list<const void
 }
 
 int launch_bidir_fwd_tc(const void* q, const void* k, const void* v, const unsigned char* keep, const float* nc,
-                        void* out, int B, int H, int N, int dtype, cudaStream_t stream) {
-  return dtype == COTT_BF16 ? launch_bidir_fwd_tc_t<__nv_bfloat16>(q, k, v, keep, nc, out, B, H, N, dtype, stream)
-                            : launch_bidir_fwd_tc_t<__half>(q, k, v, keep, nc, out, B, H, N, dtype, stream);
+                        void* out, int B, int H, int N, int dtype, cudaStream_t stream, const cott_layout* l) {
+  const TileStrides si = l ? TileStrides{l->in_b, l->in_h, l->in_n} : contiguous_bhnd(H, N);
+  const TileStrides so = l ? TileStrides{l->out_b, l->out_h, l->out_n} : contiguous_bhnd(H, N);
+  return dtype == COTT_BF16 ? launch_bidir_fwd_tc_t<__nv_bfloat16>(q, k, v, keep, nc, out, B, H, N, dtype, stream, si, so)
+                            : launch_bidir_fwd_tc_t<__half>(q, k, v, keep, nc, out, B, H, N, dtype, stream, si, so);
 }
 
 }  // namespace cott

@@ -215,6 +215,21 @@ int cott_bidir_bwd(const void* q, const void* k, const void* v, const unsigned c
                    int dtype, void* stream);
 
 /*
+ * The bidirectional pair on strided tensors (`cott_layout`, see cott_cos_attn_fwd_seg; NULL = contiguous): head dim
+ * 64, bf16 / fp16 only (the tensor-core kernels, which keep the state on chip and need no scratch).  Lets
+ * BertCosAttention read q, k, v straight out of its projections' [B, N, H*64] outputs and write the context layer in
+ * the layout its output projection reads (BERT_Trainer/BertCosAttention.py:148-156,252-254: transpose_for_scores and
+ * the permute back cost no copy).
+ */
+int cott_bidir_fwd_strided(const void* q, const void* k, const void* v, const unsigned char* keep,
+                           const float* norm_const, void* out, const cott_layout* layout, int B, int H, int N,
+                           int Dk, int Dv, int dtype, void* stream);
+int cott_bidir_bwd_strided(const void* q, const void* k, const void* v, const unsigned char* keep,
+                           const float* norm_const, const void* dout, const cott_layout* layout, void* dq,
+                           void* dk, void* dv, float* dnorm_const, int B, int H, int N, int Dk, int Dv, int dtype,
+                           void* stream);
+
+/*
  * cott_bidir_fwd for callers that cannot allocate.  (No counterpart in the reference, whose
  * bidirectional path lets PyTorch allocate its einsum intermediates.)
  *

@@ -82,3 +82,30 @@ def test_rejects_unsupported_head_dim():
     x = torch.zeros(1, 1, 8, 24, device="cuda")
     with pytest.raises(RuntimeError, match="divisible by 16"):
         cos_attn_bidirectional(x, x, x, torch.zeros(1, device="cuda"))
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(2, 3, 300), (4, 12, 512)])
+@pytest.mark.parametrize("masked", [False, True])
+def test_packed_qkv_layout_matches_the_permuted_op(dt, shape, masked):
+    """Strided tensor maps over a packed [B, N, 3, H, 64] tensor: bit-identical to the op on permuted copies."""
+    from cottention_transformer_b200 import cos_attn_bidirectional, cos_attn_bidirectional_packed
+    B, H, N = shape
+    g = torch.Generator(device="cuda").manual_seed(N + H)
+    qkv = torch.randn(B, N, 3, H, 64, device="cuda", generator=g).to(dt).requires_grad_()
+    do = torch.randn(B, N, H, 64, device="cuda", generator=g).to(dt)
+    nc = torch.linspace(-0.5, 1.0, H, device="cuda").requires_grad_()
+    keep = None
+    if masked:
+        keep = torch.ones(B, N, dtype=torch.bool, device="cuda")
+        keep[0, (2 * N) // 3:] = False
+    out = cos_attn_bidirectional_packed(qkv, nc, keep)
+    out.backward(do)
+    q2, k2, v2 = (qkv.detach()[:, :, i].permute(0, 2, 1, 3).contiguous().requires_grad_() for i in range(3))
+    nc2 = nc.detach().clone().requires_grad_()
+    ref = cos_attn_bidirectional(q2, k2, v2, nc2, keep)
+    ref.backward(do.permute(0, 2, 1, 3).contiguous())
+    assert torch.equal(out.detach(), ref.detach().permute(0, 2, 1, 3))
+    for i, gref in enumerate((q2.grad, k2.grad, v2.grad)):
+        assert torch.equal(qkv.grad[:, :, i], gref.permute(0, 2, 1, 3)), i
+    assert torch.allclose(nc.grad, nc2.grad, rtol=1e-4, atol=1e-5)
