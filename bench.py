@@ -9,8 +9,9 @@ torchrun each rank (one per GPU) processes its own batch shard; there is no data
 
 Keys beyond the basic contract:
   value      whole-job tokens/s with inputs resident in HBM, device-timed (CUDA events), max over ranks
-  e2e        the same through the public Python op with pinned HOST buffers: every step copies
-             q, k, v, dO host->device and out, dq, dk, dv, dnorm device->host inside the timed region
+  e2e        the same through the public host-buffer call (``CausalHostStep``) with pinned HOST buffers: every
+             step copies q, k, v, dO host->device and out, dq, dk, dv, dnorm device->host inside the timed
+             region, pipelined over the batch on three streams (the PCIe link is full duplex)
   roofline   the dominant kernel (reverse-direction dK/dV pass): algorithmic bytes per launch /
              average launch duration (CUDA events on the launching stream, inside the timed region)
              against the measured HBM copy bandwidth
@@ -159,6 +160,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    ap.add_argument("--e2e-slices", type=int, default=8, help="batch slices of the pipelined host-buffer step")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -171,7 +173,8 @@ def main():
         return
 
     import torch.distributed as dist
-    from cottention_transformer_b200 import _lib, cos_attn_causal
+    from cottention_transformer_b200 import _lib
+    from cottention_transformer_b200.host_step import CausalHostStep
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
@@ -243,15 +246,10 @@ def main():
     h2d = sum(t.numel() * t.element_size() for t in host)
     d2h = sum(t.numel() * t.element_size() for t in host_out) + H * 4
 
+    host_step = CausalHostStep(B_PER_GPU, H, N, D, torch.bfloat16, dev, slices=args.e2e_slices)  # three streams
+
     def e2e_step():
-        qd, kd, vd, dod = (t.to(dev, non_blocking=True) for t in host)
-        qd.requires_grad_(), kd.requires_grad_(), vd.requires_grad_()
-        ncd = nc.detach().requires_grad_()
-        o = cos_attn_causal(qd, kd, vd, ncd)
-        o.backward(dod)
-        for dst, src in zip(host_out, (o.detach(), qd.grad, kd.grad, vd.grad)):
-            dst.copy_(src, non_blocking=True)
-        host_dnc.copy_(ncd.grad, non_blocking=True)
+        host_dnc.copy_(host_step(*host, nc, *host_out), non_blocking=True)
 
     e2e_steps = max(3, min(args.steps, 10))
     e2e_value = None
