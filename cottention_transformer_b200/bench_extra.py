@@ -165,6 +165,35 @@ def bench_causal_kernels(B, H=16, N=4096, d=64, iters=20):
     return res
 
 
+def bench_scan(B=8, H=16, N=4096, d=64):
+    """The reference's own operator (``FastAttention2.kernel.*`` = ``cott_scan``; ``CustomAttention`` backward =
+    ``cott_scan_bwd``, three scans) at the headline shape, per dtype.  bf16 / fp16 run on the tensor cores, fp32 /
+    fp64 on the exact CUDA-core kernel.  Algorithmic bytes: 4 tensor passes per scan."""
+    L = _lib.lib()
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(1234)
+    peak, kind = _peak_gbs()
+    res = {"what": f"bare scan (reference kernel API), B={B} H={H} N={N} d={d}", "peak_source": kind}
+    st = _lib.stream_ptr(dev)
+    P = lambda t: t.data_ptr()  # noqa: E731
+    for name, dt, iters in (("bf16", torch.bfloat16, 20), ("f16", torch.float16, 20), ("f32", torch.float32, 5),
+                            ("f64", torch.float64, 2)):
+        q, k, v, do = (torch.nn.functional.normalize(torch.randn(B, H, N, d, device=dev, generator=g), dim=-1).to(dt)
+                       for _ in range(4))
+        out, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
+        code = _lib.DTYPE_CODE[dt]
+        fwd = lambda r: _lib.check(L.cott_scan(P(q), P(k), P(v), P(out), B, H, N, d, d, code, r, st), "cott_scan")  # noqa: E731
+        bwd = lambda: _lib.check(L.cott_scan_bwd(P(q), P(k), P(v), P(do), P(dq), P(dk), P(dv), B, H, N, d, d, code, st),  # noqa: E731
+                                 "cott_scan_bwd")
+        t_f, t_r, t_b = _time(lambda: fwd(0), iters, 2), _time(lambda: fwd(1), iters, 2), _time(bwd, iters, 2)
+        nbytes = 4 * q.numel() * q.element_size()
+        res[name] = {"scan_us": t_f * 1e6, "scan_reversed_us": t_r * 1e6, "scan_bwd_us": t_b * 1e6,
+                     "scan_frac_of_hbm_peak": nbytes / t_f / 1e9 / peak,
+                     "fwd_bwd_tokens_per_s": B * N / (t_f + t_b)}
+    _lib.check_device_status()
+    return res
+
+
 def bench_long_context(N, B=1, H=16, d=64, iters=5):
     """Prefill forward + backward at B=1 (few sequences, long): segment-parallel against one CTA per head."""
     L = _lib.lib()
@@ -201,6 +230,7 @@ if __name__ == "__main__":
     ap.add_argument("--decode-steps", type=int, default=256)
     ap.add_argument("--json", default=None)
     ap.add_argument("--long-context", action="store_true", help="only the B=1 long-sequence prefill sweep")
+    ap.add_argument("--scan", action="store_true", help="only the bare scan of the reference's kernel API, per dtype")
     ap.add_argument("--bidir-only", action="store_true", help="only the bidirectional benchmark")
     ap.add_argument("--no-graph", action="store_true", help="do not replay decode from a CUDA graph (profiler runs)")
     a = ap.parse_args()
@@ -210,6 +240,9 @@ if __name__ == "__main__":
     if a.long_context:
         for n in (16384, 65536, 262144):
             print(json.dumps(bench_long_context(n)))
+        raise SystemExit(0)
+    if a.scan:
+        print(json.dumps(bench_scan()))
         raise SystemExit(0)
     if a.bidir_only:
         print(json.dumps(bench_bidir()))

@@ -456,7 +456,9 @@ __device__ __noinline__ void load_init_state(const float* state, uint32_t tS_lan
 __device__ __forceinline__ uint64_t kdesc(uint32_t saddr) { return ptx::make_smem_desc(saddr, 16, 1024); }
 __device__ __forceinline__ uint64_t mdesc(uint32_t saddr) { return ptx::make_smem_desc(saddr, 8192, 1024); }
 
-enum { kModeFwd = 0, kModeDq = 1 };
+// kModeScan / kModeScanRev: the bare scan out_t = sum_{s<=t} (x_t . y_s) z_s (s >= t when reversed, walking the
+// sequence backwards) with no normalisation: the forward kernel minus its row scalings.
+enum { kModeFwd = 0, kModeDq = 1, kModeScan = 2, kModeScanRev = 3 };
 
 // which wait gave up (recorded in g_cott_status)
 enum {
@@ -483,11 +485,13 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   // NS + 1 tiles for the tile that doubles as the output staging buffer (forward: X; dQ: q), the 16-bit
   // state operand (2 x 8 KB).  The ring is one slot longer than the stage count, so the tile of chunk c+NS
   // is loaded into the slot chunk c-1 left, while chunk c's output is still being written and stored.
-  constexpr int NIN = (MODE == kModeFwd) ? 2 : 3;  // read-only tiles per stage
+  constexpr bool kScan = MODE >= kModeScan, kRev = MODE == kModeScanRev;
+  static_assert(!(kScan && EXT), "the bare scan takes no segment / padding arguments");
+  constexpr int NIN = (MODE == kModeDq) ? 3 : 2;  // read-only tiles per stage
   constexpr int STAGE = NIN * kTileBytes;
-  constexpr int NS = (MODE == kModeFwd) ? kTcStagesFwd : kTcStages;
+  constexpr int NS = (MODE == kModeDq) ? kTcStages : kTcStagesFwd;
   constexpr int RING = NS + 1;
-  constexpr int kIdxY = (MODE == kModeFwd) ? 0 : 1, kIdxZ = kIdxY + 1;  // tile index inside a stage (dQ: X = 0)
+  constexpr int kIdxY = (MODE == kModeDq) ? 1 : 0, kIdxZ = kIdxY + 1;  // tile index inside a stage (dQ: X = 0)
   constexpr bool BF = Pack2<T>::kBf16;
 
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -499,7 +503,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   unsigned char* sS = ring + RING * kTileBytes;  // 2 x [64 x 64] 16-bit state operand (double-buffered)
   auto stage_of = [&](int c) { return smem + (c % NS) * STAGE; };
   auto ring_of = [&](int c) { return ring + (c % RING) * kTileBytes; };
-  auto tile_x = [&](int c) { return MODE == kModeFwd ? ring_of(c) : stage_of(c); };
+  auto tile_x = [&](int c) { return MODE == kModeDq ? stage_of(c) : ring_of(c); };
   __shared__ uint64_t bar_full[NS], bar_free_in[NS], bar_out[NS], bar_prep[NS], bar_p_full[2], bar_p_ready[2], bar_acc_full[2],
       bar_acc_free[2], bar_s_full, bar_state[2], bar_state2, bar_init;
   __shared__ uint32_t tmem_slot;
@@ -523,6 +527,8 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   const bool has_init = EXT && init_state != nullptr && seg > 0;
   const unsigned char* keep_b = (EXT && keep_arg) ? keep_arg + static_cast<size_t>(bh / H) * N : nullptr;
   const int* count_b = (EXT && count_arg) ? count_arg + static_cast<size_t>(bh / H) * N : nullptr;
+  // first row of local chunk c (the reversed scan starts at the end of the sequence)
+  auto row0_of = [&](int c) { return (kRev ? total_chunks - 1 - c : chunk0 + c) * kTcChunk; };
 
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
@@ -641,10 +647,10 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         }
 #endif
         mbar_expect_tx(&bar_full[s], STAGE + kTileBytes);
-        if (MODE == kModeDq) tma_load_tile(st, &mapX, &bar_full[s], (chunk0 + c) * kTcChunk, h, bb);
-        tma_load_tile(st + kIdxY * kTileBytes, &mapY, &bar_full[s], (chunk0 + c) * kTcChunk, h, bb);
-        tma_load_tile(st + kIdxZ * kTileBytes, &mapZ, &bar_full[s], (chunk0 + c) * kTcChunk, h, bb);
-        tma_load_tile(ring_of(c), MODE == kModeDq ? &mapQ : &mapX, &bar_full[s], (chunk0 + c) * kTcChunk, h, bb);
+        if (MODE == kModeDq) tma_load_tile(st, &mapX, &bar_full[s], row0_of(c), h, bb);
+        tma_load_tile(st + kIdxY * kTileBytes, &mapY, &bar_full[s], row0_of(c), h, bb);
+        tma_load_tile(st + kIdxZ * kTileBytes, &mapZ, &bar_full[s], row0_of(c), h, bb);
+        tma_load_tile(ring_of(c), MODE == kModeDq ? &mapQ : &mapX, &bar_full[s], row0_of(c), h, bb);
         COTT_TRACE_EV(0, c);
       };
       for (int c = 0; c < NS && c < nchunks; ++c) issue_loads(c);
@@ -659,7 +665,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         }
         if (!wait_bar(&bar_out[s], (c / NS) & 1, abort_flag, kWaitStageFree, c)) break;
 #if !(COTT_SKEL & 16)
-        tma_store_tile(&mapOut, ring_of(c), (chunk0 + c) * kTcChunk, h, bb);
+        tma_store_tile(&mapOut, ring_of(c), row0_of(c), h, bb);
         tma_store_commit();
 #endif
       }
@@ -704,7 +710,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       tc_fence_after_sync();
       COTT_TRACE_EV(0, c);
 #if !(COTT_SKEL & 1)
-      mask_pack_inplace<T, true>(tP0 + 128 * b + lane_base, lane, wq);
+      mask_pack_inplace<T, !kRev>(tP0 + 128 * b + lane_base, lane, wq);
 #endif
       tc_fence_before_sync();
       warp_arrive(&bar_p_ready[b], lane);
@@ -762,7 +768,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   } else if ((warp >= 15 && warp < 19) || warp >= 24) {
     // ---------------------------------------------------------------- operand groups (even / odd chunks)
     const int row = 32 * (warp & 3) + lane;
-    const float sigma = 1.0f / (1.0f + __expf(-norm_const[h]));
+    const float sigma = kScan ? 0.f : 1.0f / (1.0f + __expf(-norm_const[h]));
     const int mine = (warp >= 24) ? 1 : 0;
     for (int c = 0; c < nchunks; ++c) {  // Zw = diag(a_s / |k_s|) Z, in place
       const int s = c % NS;
@@ -775,9 +781,11 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       unsigned char* sZ = stage_of(c) + kIdxZ * kTileBytes;
       unsigned char* sK = (MODE == kModeDq) ? sZ : stage_of(c) + kIdxY * kTileBytes;
 #if !(COTT_SKEL & 2)
-      const RowMask m = row_mask(keep_b, count_b, (chunk0 + c) * kTcChunk + row, N);
-      const float rk = m.kp ? inv_norm(row_sumsq_rolled<T>(sK, row)) : 0.f;
-      scale_row_rolled<T>(sZ, row, rk * length_factor(m.n, sigma));
+      if constexpr (!kScan) {
+        const RowMask m = row_mask(keep_b, count_b, row0_of(c) + row, N);
+        const float rk = m.kp ? inv_norm(row_sumsq_rolled<T>(sK, row)) : 0.f;
+        scale_row_rolled<T>(sZ, row, rk * length_factor(m.n, sigma));
+      }
 #endif
       fence_proxy_async_smem();
       warp_arrive(&bar_prep[s], lane);
@@ -797,7 +805,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       if ((c & 1) != mine) continue;
       COTT_TRACE_EV(7, c);
 #if !(COTT_SKEL & 4)
-      const float rq = row_mask(keep_b, count_b, (chunk0 + c) * kTcChunk + row, N).kp ? inv_norm(row_sumsq_rolled<T>(sQ, row)) : 0.f;
+      const float rq = kScan ? 1.f : row_mask(keep_b, count_b, row0_of(c) + row, N).kp ? inv_norm(row_sumsq_rolled<T>(sQ, row)) : 0.f;
 #else
       const float rq = 1.f;
 #endif
@@ -813,8 +821,8 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       // output rows; the TMA thread stores the tile and refills it.
       const uint32_t tAcc = tAcc0 + 64 * b + lane_base;
 #if !(COTT_SKEL & 4)
-      if (MODE == kModeFwd) {
-        row_from_acc<T, false>(sQ, row, tAcc, rq, 0.f);  // o = acc / |q|
+      if (MODE != kModeDq) {
+        row_from_acc<T, false>(sQ, row, tAcc, rq, 0.f);  // o = acc / |q|  (the bare scan: o = acc)
       } else {
         // dq = (dq^ - q^ (q^ . dq^)) / |q| with dq^ = acc and q^ = rq q
         const float delta = row_dot_acc<T>(sQ, row, tAcc) * (rq * rq * rq);
@@ -1183,8 +1191,8 @@ inline size_t causal_bwd_kv_smem_bytes() {
 }
 
 inline size_t causal_tc_smem_bytes(int mode) {
-  const int nin = mode == kModeFwd ? 2 : 3;
-  const int ns = mode == kModeFwd ? kTcStagesFwd : kTcStages;
+  const int nin = mode == kModeDq ? 3 : 2;
+  const int ns = mode == kModeDq ? kTcStages : kTcStagesFwd;
   return static_cast<size_t>((ns * nin + ns + 1) * kTileBytes + 2 * kTcD * 128 + 1024);
 }
 

@@ -252,6 +252,32 @@ int launch_bidir_bwd_tc(const void* q, const void* k, const void* v, const unsig
              : launch_bidir_bwd_tc_t<__half>(q, k, v, keep, nc, dout, dq, dk, dv, dnorm, B, H, N, dtype, stream, si, so);
 }
 
+// The bare scan of cott_scan on the tensor cores (head dim 64, 16-bit dtypes): the forward kernel without its row
+// scalings, walking the sequence backwards when `reversed`.  `out` may be one of the inputs: a chunk's rows are
+// stored after every load of that chunk has completed, and no other chunk reads them.
+template <typename T>
+int launch_scan_tc_t(const void* q, const void* k, const void* v, void* out, int B, int H, int N, int dtype, int reversed,
+                     cudaStream_t stream) {
+  CUtensorMap mq, mk, mv, mo;
+  int st;
+  const TileStrides ts = contiguous_bhnd(H, N);
+  if ((st = tmap(&mq, q, dtype, B, H, N, ts)) || (st = tmap(&mk, k, dtype, B, H, N, ts)) || (st = tmap(&mv, v, dtype, B, H, N, ts)) ||
+      (st = tmap(&mo, out, dtype, B, H, N, ts)))
+    return st;
+  auto kern = reversed ? causal_tc_kernel<T, kModeScanRev, false> : causal_tc_kernel<T, kModeScan, false>;
+  const size_t smem = causal_tc_smem_bytes(kModeScan);
+  COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<dim3((unsigned)((long)B * H), 1), kTcThreads, smem, stream>>>(mq, mk, mv, mq, mo, nullptr, H, N, nullptr, 0, nullptr, nullptr);
+  COTT_CUDA_TRY(cudaGetLastError());
+  return COTT_OK;
+}
+
+int launch_scan_tc(const void* q, const void* k, const void* v, void* out, int B, int H, int N, int dtype, int reversed,
+                   cudaStream_t stream) {
+  return dtype == COTT_BF16 ? launch_scan_tc_t<__nv_bfloat16>(q, k, v, out, B, H, N, dtype, reversed, stream)
+                            : launch_scan_tc_t<__half>(q, k, v, out, B, H, N, dtype, reversed, stream);
+}
+
 bool bidir_tc_usable(int Dk, int Dv, int dtype, std::initializer_list<const void*> tensors) {
   if (Dk != kTcD || Dv != kTcD || (dtype != COTT_BF16 && dtype != COTT_F16)) return false;
   for (const void* p : tensors)

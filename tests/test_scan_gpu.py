@@ -107,6 +107,60 @@ def test_scan_matches_live_reference_kernel(K):
     assert (a - b).abs().max().item() < 1e-11
 
 
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_tensor_core_scan_inplace_and_against_exact_kernel(K, dt):
+    """Head dim 64 in a 16-bit dtype runs on the tensor cores: same answer (within 16-bit rounding) as the exact
+    kernel run in fp32 on the same inputs, in both directions, also when the output replaces V."""
+    q, k, v, _, _ = O.make_inputs(2, 3, 700, 64, 64, seed=11, dtype=dt)
+    q, k, v = q.cuda(), k.cuda(), v.cuda()
+    for rev in (False, True):
+        want = K.scan(q.float(), k.float(), v.float(), rev)
+        got = K.scan(q, k, v, rev)
+        assert got.dtype == dt
+        assert ((got.float() - want).abs().max() / want.abs().max()).item() < 1e-2
+        v2 = v.clone()
+        assert torch.equal(K.scan(q, k, v2, rev, out=v2), got)
+
+
+def test_tensor_core_scan_beats_the_live_reference_kernel(K, capsys):
+    """Headline shape, bf16, forward + the three backward scans of CustomAttention: ours against the reference
+    extension itself on the same GPU (CUDA events).  Prints the times; fails if the tensor-core path is slower."""
+    ref = load_reference_kernel()
+    if ref is None:
+        pytest.skip("oracle/_ref not built")
+    B, H, N, d = 8, 16, 4096, 64
+    g = torch.Generator(device="cuda").manual_seed(3)
+    q, k, v, do = (torch.nn.functional.normalize(torch.randn(B, H, N, d, device="cuda", generator=g), dim=-1).bfloat16()
+                   for _ in range(4))
+
+    def four_scans(f):  # Custom_Kernel.py:36-141: forward, then dq, dk, dv
+        f(q, k, v, 1, False, False), f(do, v, k, 1, False, False), f(v, do, q, 1, False, True), f(k, q, do, 1, False, True)
+
+    def timed(f, iters):
+        four_scans(f)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            four_scans(f)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    ours, theirs = timed(K.bfloat16, 5), timed(ref.bfloat16, 2)
+    a, b = K.bfloat16(q, k, v, 1, False, False).float(), ref.bfloat16(q, k, v, 1, False, False).float()
+    with capsys.disabled():
+        print(f"\n[scan fwd+bwd, B=8 H=16 N=4096 d=64 bf16] ours {ours:.3f} ms, reference kernel {theirs:.3f} ms, "
+              f"ratio {theirs / ours:.1f}x; max |ours - reference| = {(a - b).abs().max().item():.3g}")
+    assert ours < theirs
+    # the exact (CUDA-core) mode on the same shape in fp32
+    q, k, v, do = (t.float() for t in (q, k, v, do))
+    ours, theirs = timed(K.float32, 2), timed(ref.float32, 2)
+    with capsys.disabled():
+        print(f"[scan fwd+bwd, same shape, fp32] ours {ours:.3f} ms, reference kernel {theirs:.3f} ms, ratio {theirs / ours:.1f}x")
+    assert ours < theirs
+
+
 def test_gradcheck_fp64_like_the_reference():
     """Cuda_Kernel/Custom_Kernel.py:157,184-188: gradcheck at N,H,S,D = 1,2,63,128 in float64."""
     from cottention_transformer_b200 import CustomAttention
