@@ -161,6 +161,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     ap.add_argument("--e2e-slices", type=int, default=8, help="batch slices of the pipelined host-buffer step")
+    ap.add_argument("--e2e-no-graph", action="store_true", help="issue the host-buffer step call by call instead of replaying a CUDA graph")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -246,7 +247,7 @@ def main():
     h2d = sum(t.numel() * t.element_size() for t in host)
     d2h = sum(t.numel() * t.element_size() for t in host_out) + H * 4
 
-    host_step = CausalHostStep(B_PER_GPU, H, N, D, torch.bfloat16, dev, slices=args.e2e_slices)  # three streams
+    host_step = CausalHostStep(B_PER_GPU, H, N, D, torch.bfloat16, dev, slices=args.e2e_slices, graph=not args.e2e_no_graph)
 
     def e2e_step():
         host_dnc.copy_(host_step(*host, nc, *host_out), non_blocking=True)
