@@ -165,6 +165,22 @@ def bench_causal_kernels(B, H=16, N=4096, d=64, iters=20):
     return res
 
 
+def bench_scan_d128(B=1, H=16, N=16384, d=128):
+    """Head dim 128 (exact CUDA-core kernel for every dtype): one scan per dtype."""
+    L = _lib.lib()
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(1234)
+    res = {"what": f"bare scan, B={B} H={H} N={N} d={d} (CUDA-core kernel)"}
+    st = _lib.stream_ptr(dev)
+    for name, dt in (("bf16", torch.bfloat16), ("f32", torch.float32)):
+        q, k, v = (torch.nn.functional.normalize(torch.randn(B, H, N, d, device=dev, generator=g), dim=-1).to(dt) for _ in range(3))
+        out = torch.empty_like(q)
+        fn = lambda: _lib.check(L.cott_scan(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, H, N, d, d,  # noqa: E731
+                                            _lib.DTYPE_CODE[dt], 0, st), "cott_scan")
+        res[name + "_scan_us"] = _time(fn, 3, 1) * 1e6
+    return res
+
+
 def bench_scan(B=8, H=16, N=4096, d=64):
     """The reference's own operator (``FastAttention2.kernel.*`` = ``cott_scan``; ``CustomAttention`` backward =
     ``cott_scan_bwd``, three scans) at the headline shape, per dtype.  bf16 / fp16 run on the tensor cores, fp32 /
@@ -243,6 +259,7 @@ if __name__ == "__main__":
         raise SystemExit(0)
     if a.scan:
         print(json.dumps(bench_scan()))
+        print(json.dumps(bench_scan_d128()))
         raise SystemExit(0)
     if a.bidir_only:
         print(json.dumps(bench_bidir()))

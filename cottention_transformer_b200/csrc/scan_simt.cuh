@@ -28,7 +28,7 @@ inline size_t scan_simt_smem_bytes(int C, int Dk, int dvt) {
 // C = chunk length, DVT = columns of V (and of the state) one CTA owns.  Thread (ty, tx) of the 16 x 16 thread
 // grid owns rows ty + 16 a and columns tx + 16 b of every product, so each step of an inner loop is
 // (C/16 + DVT/16) shared-memory loads for (C/16) x (DVT/16) multiply-adds.
-template <typename T, int C, int DVT>
+template <typename T, int C, int DVT, int PRE>
 __global__ void __launch_bounds__(kSimtThreads)
 scan_simt_kernel(const T* Q, const T* K, const T* V, T* O, int N, int Dk, int Dv, int reversed) {
   using A = typename AccOf<T>::type;
@@ -54,9 +54,9 @@ scan_simt_kernel(const T* Q, const T* K, const T* V, T* O, int N, int Dk, int Dv
 
   // The rows of the next chunk are fetched into registers while the current one is worked on (their latency
   // was the largest stall of the kernel when the staging was synchronous).  Element m of a thread is flat index
-  // tid + 256 m of the [C][Dk] tile; PRE elements per tensor fit the register budget, wider tiles (Dk > 64 in
-  // fp32) are staged synchronously.
-  constexpr int PRE = 16, NV = C * DVT / kSimtThreads;
+  // tid + 256 m of the [C][Dk] tile; PRE elements per tensor fit the register budget (Dk <= 128), wider tiles
+  // are staged synchronously.
+  constexpr int NV = C * DVT / kSimtThreads;
   const int nqk = C * Dk / kSimtThreads;
   const bool pre = nqk <= PRE;
   const int r_first = tid / Dk, i_first = tid % Dk, r_step = kSimtThreads / Dk, i_step = kSimtThreads % Dk;
@@ -237,12 +237,12 @@ scan_simt_kernel(const T* Q, const T* K, const T* V, T* O, int N, int Dk, int Dv
   }
 }
 
-template <typename T, int C, int DVT>
-int launch_scan_simt_t(const void* q, const void* k, const void* v, void* out, int B, int H, int N, int Dk, int Dv,
+template <typename T, int C, int DVT, int PRE>
+int launch_scan_simt_p(const void* q, const void* k, const void* v, void* out, int B, int H, int N, int Dk, int Dv,
                        int reversed, cudaStream_t stream) {
   using A = typename AccOf<T>::type;
   const size_t smem = scan_simt_smem_bytes<A>(C, Dk, DVT);
-  auto kern = scan_simt_kernel<T, C, DVT>;
+  auto kern = scan_simt_kernel<T, C, DVT, PRE>;
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid((unsigned)((long)B * H), (unsigned)((Dv + DVT - 1) / DVT));
   kern<<<grid, kSimtThreads, smem, stream>>>(static_cast<const T*>(q), static_cast<const T*>(k),
@@ -250,6 +250,15 @@ int launch_scan_simt_t(const void* q, const void* k, const void* v, void* out, i
                                              Dv, reversed);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
+}
+
+// PRE = prefetch registers per tensor: 16 covers Dk <= 64 (Dk <= 128 in fp64), 32 covers Dk <= 128 in the 4-byte types
+template <typename T, int C, int DVT>
+int launch_scan_simt_t(const void* q, const void* k, const void* v, void* out, int B, int H, int N, int Dk, int Dv,
+                       int reversed, cudaStream_t stream) {
+  if (sizeof(typename AccOf<T>::type) <= 4 && C * Dk / kSimtThreads > 16)
+    return launch_scan_simt_p<T, C, DVT, 32>(q, k, v, out, B, H, N, Dk, Dv, reversed, stream);
+  return launch_scan_simt_p<T, C, DVT, 16>(q, k, v, out, B, H, N, Dk, Dv, reversed, stream);
 }
 
 // A CTA owns 64 columns of V when V has more than 16 and the tiles fit in 200 KB of shared memory, otherwise 16: the masked product Q K^T is the largest term and every column slice recomputes it.
