@@ -94,9 +94,11 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_acc<__nv_bfloat16>(flo
 // device status word): head dim 64, 16-bit dtypes, 16-byte aligned tensors.  `*_usable` says whether a
 // problem qualifies; the launchers assume it does.
 bool bidir_tc_usable(int Dk, int Dv, int dtype, std::initializer_list<const void*> tensors);
-// The same test decides whether cott_scan runs on the tensor cores (launch_scan_tc) or on the exact CUDA-core kernel.
-int launch_scan_tc(const void* q, const void* k, const void* v, void* out, int B, int H, int N, int dtype, int reversed,
-                   cudaStream_t stream);
+// cott_scan on the tensor cores: 16-bit dtypes, head dims that are multiples of 64 (up to 256), 16-byte aligned
+// tensors, in place only at head dim 64.
+bool scan_tc_usable(int Dk, int Dv, int dtype, const void* q, const void* k, const void* v, const void* out);
+int launch_scan_tc(const void* q, const void* k, const void* v, void* out, int B, int H, int N, int Dk, int Dv, int dtype,
+                   int reversed, cudaStream_t stream);
 int launch_bidir_fwd_tc(const void* q, const void* k, const void* v, const unsigned char* keep, const float* nc,
                         void* out, int B, int H, int N, int dtype, cudaStream_t stream, const cott_layout* layout = nullptr);
 int launch_bidir_bwd_tc(const void* q, const void* k, const void* v, const unsigned char* keep, const float* nc,

@@ -257,12 +257,11 @@ int launch_bidir_bwd_tc(const void* q, const void* k, const void* v, const unsig
 // stored after every load of that chunk has completed, and no other chunk reads them.
 template <typename T>
 int launch_scan_tc_t(const void* q, const void* k, const void* v, void* out, int B, int H, int N, int dtype, int reversed,
-                     cudaStream_t stream) {
+                     cudaStream_t stream, TileStrides sqk, TileStrides sv, TileStrides so) {
   CUtensorMap mq, mk, mv, mo;
   int st;
-  const TileStrides ts = contiguous_bhnd(H, N);
-  if ((st = tmap(&mq, q, dtype, B, H, N, ts)) || (st = tmap(&mk, k, dtype, B, H, N, ts)) || (st = tmap(&mv, v, dtype, B, H, N, ts)) ||
-      (st = tmap(&mo, out, dtype, B, H, N, ts)))
+  if ((st = tmap(&mq, q, dtype, B, H, N, sqk)) || (st = tmap(&mk, k, dtype, B, H, N, sqk)) || (st = tmap(&mv, v, dtype, B, H, N, sv)) ||
+      (st = tmap(&mo, out, dtype, B, H, N, so)))
     return st;
   auto kern = reversed ? causal_tc_kernel<T, kModeScanRev, false> : causal_tc_kernel<T, kModeScan, false>;
   const size_t smem = causal_tc_smem_bytes(kModeScan);
@@ -272,10 +271,71 @@ int launch_scan_tc_t(const void* q, const void* k, const void* v, void* out, int
   return COTT_OK;
 }
 
-int launch_scan_tc(const void* q, const void* k, const void* v, void* out, int B, int H, int N, int dtype, int reversed,
-                   cudaStream_t stream) {
-  return dtype == COTT_BF16 ? launch_scan_tc_t<__nv_bfloat16>(q, k, v, out, B, H, N, dtype, reversed, stream)
-                            : launch_scan_tc_t<__half>(q, k, v, out, B, H, N, dtype, reversed, stream);
+// dst[r][0..63] += src[r][0..63] for `rows` rows; dst rows are `dst_stride` elements apart, src is dense.
+template <typename T>
+__global__ void add_rows64_kernel(T* __restrict__ dst, long dst_stride, const T* __restrict__ src, long rows) {
+  const long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;  // one 8-element piece per thread
+  if (i >= rows * 8) return;
+  uint4* d = reinterpret_cast<uint4*>(dst + (i >> 3) * dst_stride + (i & 7) * 8);
+  uint4 a = *d;
+  const uint4 b = *reinterpret_cast<const uint4*>(src + i * 8);
+  uint32_t* x = reinterpret_cast<uint32_t*>(&a);
+  const uint32_t* y = reinterpret_cast<const uint32_t*>(&b);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 f = Pack2<T>::unpack(x[e]), g = Pack2<T>::unpack(y[e]);
+    x[e] = Pack2<T>::pack(f.x + g.x, f.y + g.y);
+  }
+  *d = a;
+}
+
+// Head dims that are multiples of 64: the scan is linear in 64-wide slices of the head dimension,
+//   scan(q, k, v)[:, J] = sum_I scan(q[:, I], k[:, I], v[:, J]),
+// so every (I, J) pair is one launch of the 64-wide kernel on strided views of the tensors; partial results of
+// I > 0 go through a stream-ordered scratch buffer and are added in.
+template <typename T>
+int launch_scan_tc_wide(const void* q, const void* k, const void* v, void* out, int B, int H, int N, int Dk, int Dv, int dtype,
+                        int reversed, cudaStream_t stream) {
+  const TileStrides sqk{(long long)H * N * Dk, (long long)N * Dk, Dk}, sv{(long long)H * N * Dv, (long long)N * Dv, Dv};
+  const TileStrides dense = contiguous_bhnd(H, N);
+  const long rows = (long)B * H * N;
+  const T *qq = static_cast<const T*>(q), *kk = static_cast<const T*>(k), *vv = static_cast<const T*>(v);
+  T* oo = static_cast<T*>(out);
+  T* tmp = nullptr;
+  if (Dk > kTcD) COTT_CUDA_TRY(cudaMallocAsync(reinterpret_cast<void**>(&tmp), sizeof(T) * rows * kTcD, stream));
+  int st = COTT_OK;
+  for (int j = 0; st == COTT_OK && j < Dv; j += kTcD)
+    for (int i = 0; st == COTT_OK && i < Dk; i += kTcD) {
+      st = i == 0 ? launch_scan_tc_t<T>(qq, kk, vv + j, oo + j, B, H, N, dtype, reversed, stream, sqk, sv, sv)
+                  : launch_scan_tc_t<T>(qq + i, kk + i, vv + j, tmp, B, H, N, dtype, reversed, stream, sqk, sv, dense);
+      if (st == COTT_OK && i > 0) {
+        add_rows64_kernel<T><<<(unsigned)((rows * 8 + 255) / 256), 256, 0, stream>>>(oo + j, Dv, tmp, rows);
+        if (cudaGetLastError() != cudaSuccess) st = fail(COTT_ERR_CUDA, "add_rows64_kernel launch failed");
+      }
+    }
+  if (tmp) COTT_CUDA_TRY(cudaFreeAsync(tmp, stream));
+  return st;
+}
+
+bool scan_tc_usable(int Dk, int Dv, int dtype, const void* q, const void* k, const void* v, const void* out) {
+  if (dtype != COTT_BF16 && dtype != COTT_F16) return false;
+  if (Dk % kTcD || Dv % kTcD || Dk > 256 || Dv > 256) return false;
+  for (const void* p : {q, k, v, out})
+    if (reinterpret_cast<uintptr_t>(p) & 15) return false;
+  // in place (out over an input) only for the single 64-wide launch: a wider head re-reads v after writing out
+  if ((Dk > kTcD || Dv > kTcD) && (out == q || out == k || out == v)) return false;
+  return true;
+}
+
+int launch_scan_tc(const void* q, const void* k, const void* v, void* out, int B, int H, int N, int Dk, int Dv, int dtype,
+                   int reversed, cudaStream_t stream) {
+  if (Dk == kTcD && Dv == kTcD) {
+    const TileStrides ts = contiguous_bhnd(H, N);
+    return dtype == COTT_BF16 ? launch_scan_tc_t<__nv_bfloat16>(q, k, v, out, B, H, N, dtype, reversed, stream, ts, ts, ts)
+                              : launch_scan_tc_t<__half>(q, k, v, out, B, H, N, dtype, reversed, stream, ts, ts, ts);
+  }
+  return dtype == COTT_BF16 ? launch_scan_tc_wide<__nv_bfloat16>(q, k, v, out, B, H, N, Dk, Dv, dtype, reversed, stream)
+                            : launch_scan_tc_wide<__half>(q, k, v, out, B, H, N, Dk, Dv, dtype, reversed, stream);
 }
 
 bool bidir_tc_usable(int Dk, int Dv, int dtype, std::initializer_list<const void*> tensors) {

@@ -23,9 +23,9 @@ int check_scan_args(const void* q, const void* k, const void* v, const void* out
 int scan_dispatch(const void* q, const void* k, const void* v, void* out, int B, int H, int N,
                   int Dk, int Dv, int dtype, int reversed, cudaStream_t stream) {
   if ((long)B * H * N == 0) return COTT_OK;
-  // head dim 64 in a 16-bit dtype: tensor cores (products rounded to the storage type between the two GEMMs of a
+  // head dims 64, 128, 192, 256 in a 16-bit dtype: tensor cores (products rounded to the storage type between the two GEMMs of a
   // chunk, fp32 accumulation); everything else: the exact CUDA-core kernel
-  if (bidir_tc_usable(Dk, Dv, dtype, {q, k, v, out})) return launch_scan_tc(q, k, v, out, B, H, N, dtype, reversed, stream);
+  if (scan_tc_usable(Dk, Dv, dtype, q, k, v, out)) return launch_scan_tc(q, k, v, out, B, H, N, Dk, Dv, dtype, reversed, stream);
   switch (dtype) {
     case COTT_F32: return launch_scan_simt<float>(q, k, v, out, B, H, N, Dk, Dv, reversed, stream);
     case COTT_F64: return launch_scan_simt<double>(q, k, v, out, B, H, N, Dk, Dv, reversed, stream);

@@ -54,6 +54,24 @@ def test_fused_forward_backward_matches_oracle(dt, shape, normalized, segments):
     assert e <= REL16 * max(dnc_t.abs().max().item(), 1e-3), (e, dnc_t)
 
 
+def test_head_dim_128_bf16_runs_on_wide_tensor_core_scans():
+    """d = 128 in bf16: the reference's structure around CustomAttention, whose scans run as 64-wide tensor-core
+    launches; q^, k^ and v' are rounded to bf16 before the scan (as in the reference under autocast), hence 3e-2."""
+    from cottention_transformer_b200 import cos_attn_causal
+    B, H, N = 2, 2, 500
+    q, k, v, do, _ = O.make_inputs(B, H, N, 128, 128, seed=77, dtype=torch.bfloat16)
+    nc = torch.linspace(-0.5, 1.0, H)
+    out_t, dq_t, dk_t, dv_t, dnc_t = _truth(q, k, v, do, nc)
+    qc, kc, vc = (t.cuda().requires_grad_() for t in (q, k, v))
+    ncc = nc.cuda().requires_grad_()
+    out = cos_attn_causal(qc, kc, vc, ncc)
+    out.backward(do.cuda())
+    for name, a, ref in (("out", out, out_t), ("dq", qc.grad, dq_t), ("dk", kc.grad, dk_t), ("dv", vc.grad, dv_t)):
+        e_max, e_fro = _rel(a, ref)
+        assert e_max <= 3e-2 and e_fro <= 3e-2, (name, e_max, e_fro)
+    assert (ncc.grad.double().cpu() - dnc_t).abs().max().item() <= 3e-2 * max(dnc_t.abs().max().item(), 1e-3)
+
+
 def test_fused_matches_reference_module_fixture():
     """Against gradients recorded from the reference's own (unmodified) recurrent branch."""
     from cottention_transformer_b200 import cos_attn_causal

@@ -122,6 +122,25 @@ def test_tensor_core_scan_inplace_and_against_exact_kernel(K, dt):
         assert torch.equal(K.scan(q, k, v2, rev, out=v2), got)
 
 
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("dims", [(128, 128), (128, 64), (64, 128), (256, 192)])
+def test_tensor_core_scan_wide_heads(K, dt, dims):
+    """Head dims that are multiples of 64 run as 64-wide tensor-core launches on strided slices (the scan is linear in
+    the slices of the head dimension): same answer as the exact kernel in fp32, forward, reversed and backward."""
+    Dk, Dv = dims
+    q, k, v, _, _ = O.make_inputs(2, 2, 333, Dk, Dv, seed=Dk + Dv, dtype=dt)
+    q, k, v = q.cuda(), k.cuda(), v.cuda()
+    for rev in (False, True):
+        want = K.scan(q.float(), k.float(), v.float(), rev)
+        got = K.scan(q, k, v, rev)
+        assert ((got.float() - want).abs().max() / want.abs().max()).item() < 1e-2
+    # in place falls back to the exact kernel (a wide head re-reads V after writing the output)
+    v2 = v.clone()
+    got = K.scan(q, k, v2, False, out=v2)
+    want = K.scan(q.float(), k.float(), v.float(), False)
+    assert ((got.float() - want).abs().max() / want.abs().max()).item() < 1e-2
+
+
 def test_tensor_core_scan_beats_the_live_reference_kernel(K, capsys):
     """Headline shape, bf16, forward + the three backward scans of CustomAttention: ours against the reference
     extension itself on the same GPU (CUDA events).  Prints the times; fails if the tensor-core path is slower."""
