@@ -15,10 +15,12 @@
 namespace cott {
 
 constexpr int kSegThreads = 192;
-enum { kSegFwdState = 0, kSegRevState = 1 };
+// kSegRawState / kSegRawStateRev: plain Y^T Z for the bare scan; Rev numbers the segments from the end of the sequence
+enum { kSegFwdState = 0, kSegRevState = 1, kSegRawState = 2, kSegRawStateRev = 3 };
 
 // state[bh][seg] = sum over the chunks of the segment of Y^T Z with one operand row-scaled in place:
 //   kSegFwdState: Y = K,  Z = diag(a_s / |k_s|) V      kSegRevState: Y = diag(1 / |q_t|) Q,  Z = dO
+//   kSegRawState / kSegRawStateRev: Y, Z as they are
 // shared memory: 2 x (Y, Z) tiles.  TMEM: 64 columns.
 template <typename T, int MODE>
 __global__ void __launch_bounds__(kSegThreads, 2)
@@ -72,8 +74,9 @@ seg_state_kernel(const __grid_constant__ CUtensorMap mapY, const __grid_constant
         if (c >= 2 && !wait_bar(&bar_free[s], ((c >> 1) - 1) & 1, abort_flag, kWaitStageFree, c)) break;
         unsigned char* st = smem + s * 2 * kTileBytes;
         mbar_expect_tx(&bar_full[s], 2 * kTileBytes);
-        tma_load_tile(st, &mapY, &bar_full[s], (chunk0 + c) * kTcChunk, h, bb);
-        tma_load_tile(st + kTileBytes, &mapZ, &bar_full[s], (chunk0 + c) * kTcChunk, h, bb);
+        const int y = (MODE == kSegRawStateRev ? total_chunks - 1 - (chunk0 + c) : chunk0 + c) * kTcChunk;
+        tma_load_tile(st, &mapY, &bar_full[s], y, h, bb);
+        tma_load_tile(st + kTileBytes, &mapZ, &bar_full[s], y, h, bb);
       }
     }
   } else if (warp == 1) {
@@ -94,18 +97,20 @@ seg_state_kernel(const __grid_constant__ CUtensorMap mapY, const __grid_constant
   } else {
     const int wq = warp & 3, row = 32 * wq + lane;
     const uint32_t lane_base = static_cast<uint32_t>(32 * wq) << 16;
-    const float sigma = 1.0f / (1.0f + __expf(-norm_const[h]));
+    const float sigma = MODE >= kSegRawState ? 0.f : 1.0f / (1.0f + __expf(-norm_const[h]));
     bool ok = true;
     for (int c = 0; ok && c < nchunks; ++c) {
       const int s = c & 1;
       if (!(ok = wait_bar_warp(&bar_full[s], (c >> 1) & 1, abort_flag, kWaitTma, c))) break;
       unsigned char* sY = smem + s * 2 * kTileBytes;
-      const RowMask m = row_mask(keep_b, count_b, (chunk0 + c) * kTcChunk + row, N);
-      const float r = m.kp ? inv_norm(row_sumsq_rolled<T>(sY, row)) : 0.f;
-      if (MODE == kSegFwdState)
-        scale_row_rolled<T>(sY + kTileBytes, row, r * length_factor(m.n, sigma));
-      else
-        scale_row_rolled<T>(sY, row, r);
+      if constexpr (MODE < kSegRawState) {
+        const RowMask m = row_mask(keep_b, count_b, (chunk0 + c) * kTcChunk + row, N);
+        const float r = m.kp ? inv_norm(row_sumsq_rolled<T>(sY, row)) : 0.f;
+        if (MODE == kSegFwdState)
+          scale_row_rolled<T>(sY + kTileBytes, row, r * length_factor(m.n, sigma));
+        else
+          scale_row_rolled<T>(sY, row, r);
+      }
       fence_proxy_async_smem();
       warp_arrive(&bar_prep[s], lane);
     }

@@ -486,7 +486,6 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   // state operand (2 x 8 KB).  The ring is one slot longer than the stage count, so the tile of chunk c+NS
   // is loaded into the slot chunk c-1 left, while chunk c's output is still being written and stored.
   constexpr bool kScan = MODE >= kModeScan, kRev = MODE == kModeScanRev;
-  static_assert(!(kScan && EXT), "the bare scan takes no segment / padding arguments");
   constexpr int NIN = (MODE == kModeDq) ? 3 : 2;  // read-only tiles per stage
   constexpr int STAGE = NIN * kTileBytes;
   constexpr int NS = (MODE == kModeDq) ? kTcStages : kTcStagesFwd;
@@ -527,8 +526,8 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   const bool has_init = EXT && init_state != nullptr && seg > 0;
   const unsigned char* keep_b = (EXT && keep_arg) ? keep_arg + static_cast<size_t>(bh / H) * N : nullptr;
   const int* count_b = (EXT && count_arg) ? count_arg + static_cast<size_t>(bh / H) * N : nullptr;
-  // first row of local chunk c (the reversed scan starts at the end of the sequence)
-  auto row0_of = [&](int c) { return (kRev ? total_chunks - 1 - c : chunk0 + c) * kTcChunk; };
+  // first row of local chunk c (the reversed scan numbers chunks and segments from the end of the sequence)
+  auto row0_of = [&](int c) { return (kRev ? total_chunks - 1 - (chunk0 + c) : chunk0 + c) * kTcChunk; };
 
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {

@@ -255,18 +255,32 @@ int launch_bidir_bwd_tc(const void* q, const void* k, const void* v, const unsig
 // The bare scan of cott_scan on the tensor cores (head dim 64, 16-bit dtypes): the forward kernel without its row
 // scalings, walking the sequence backwards when `reversed`.  `out` may be one of the inputs: a chunk's rows are
 // stored after every load of that chunk has completed, and no other chunk reads them.
+// `ws` (2 x B*H*nseg fp32 [64 x 64] matrices) is only used when plan.nseg > 1: the segments' own states and their
+// exclusive prefix in scan order.
 template <typename T>
 int launch_scan_tc_t(const void* q, const void* k, const void* v, void* out, int B, int H, int N, int dtype, int reversed,
-                     cudaStream_t stream, TileStrides sqk, TileStrides sv, TileStrides so) {
+                     cudaStream_t stream, TileStrides sqk, TileStrides sv, TileStrides so, SegPlan plan, float* ws) {
   CUtensorMap mq, mk, mv, mo;
   int st;
   if ((st = tmap(&mq, q, dtype, B, H, N, sqk)) || (st = tmap(&mk, k, dtype, B, H, N, sqk)) || (st = tmap(&mv, v, dtype, B, H, N, sv)) ||
       (st = tmap(&mo, out, dtype, B, H, N, so)))
     return st;
-  auto kern = reversed ? causal_tc_kernel<T, kModeScanRev, false> : causal_tc_kernel<T, kModeScan, false>;
+  const float* init = nullptr;
+  if (plan.nseg > 1) {
+    const size_t A = seg_array_floats(B, H, plan.nseg);
+    st = reversed ? launch_seg_state<T, kSegRawStateRev>(k, v, sqk, sv, nullptr, ws, B, H, N, dtype, plan, stream)
+                  : launch_seg_state<T, kSegRawState>(k, v, sqk, sv, nullptr, ws, B, H, N, dtype, plan, stream);
+    if (st) return st;
+    seg_scan_kernel<<<(unsigned)((long)B * H), 256, 0, stream>>>(ws, ws + A, nullptr, nullptr, plan.nseg);
+    COTT_CUDA_TRY(cudaGetLastError());
+    init = ws + A;
+  }
+  auto kern = plan.nseg > 1 ? (reversed ? causal_tc_kernel<T, kModeScanRev, true> : causal_tc_kernel<T, kModeScan, true>)
+                            : (reversed ? causal_tc_kernel<T, kModeScanRev, false> : causal_tc_kernel<T, kModeScan, false>);
   const size_t smem = causal_tc_smem_bytes(kModeScan);
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<dim3((unsigned)((long)B * H), 1), kTcThreads, smem, stream>>>(mq, mk, mv, mq, mo, nullptr, H, N, nullptr, 0, nullptr, nullptr);
+  kern<<<dim3((unsigned)((long)B * H), plan.nseg), kTcThreads, smem, stream>>>(mq, mk, mv, mq, mo, nullptr, H, N, init, plan.cps, nullptr,
+                                                                              nullptr);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
@@ -301,19 +315,25 @@ int launch_scan_tc_wide(const void* q, const void* k, const void* v, void* out, 
   const long rows = (long)B * H * N;
   const T *qq = static_cast<const T*>(q), *kk = static_cast<const T*>(k), *vv = static_cast<const T*>(v);
   T* oo = static_cast<T*>(out);
-  T* tmp = nullptr;
-  if (Dk > kTcD) COTT_CUDA_TRY(cudaMallocAsync(reinterpret_cast<void**>(&tmp), sizeof(T) * rows * kTcD, stream));
+  // few (batch, head) pairs and a long sequence: several CTAs per sequence, as in the fused path
+  const SegPlan plan = plan_segments(N, cott_cos_attn_seg_count(B, H, N));
+  const size_t ws_bytes = plan.nseg > 1 ? 2 * seg_array_floats(B, H, plan.nseg) * sizeof(float) : 0;
+  const size_t tmp_bytes = Dk > kTcD ? sizeof(T) * rows * kTcD : 0;
+  char* scratch = nullptr;  // stream-ordered: segment states, then the partial result of the slices I > 0
+  if (ws_bytes + tmp_bytes) COTT_CUDA_TRY(cudaMallocAsync(reinterpret_cast<void**>(&scratch), ws_bytes + tmp_bytes, stream));
+  float* ws = reinterpret_cast<float*>(scratch);
+  T* tmp = reinterpret_cast<T*>(scratch + ws_bytes);
   int st = COTT_OK;
   for (int j = 0; st == COTT_OK && j < Dv; j += kTcD)
     for (int i = 0; st == COTT_OK && i < Dk; i += kTcD) {
-      st = i == 0 ? launch_scan_tc_t<T>(qq, kk, vv + j, oo + j, B, H, N, dtype, reversed, stream, sqk, sv, sv)
-                  : launch_scan_tc_t<T>(qq + i, kk + i, vv + j, tmp, B, H, N, dtype, reversed, stream, sqk, sv, dense);
+      st = i == 0 ? launch_scan_tc_t<T>(qq, kk, vv + j, oo + j, B, H, N, dtype, reversed, stream, sqk, sv, sv, plan, ws)
+                  : launch_scan_tc_t<T>(qq + i, kk + i, vv + j, tmp, B, H, N, dtype, reversed, stream, sqk, sv, dense, plan, ws);
       if (st == COTT_OK && i > 0) {
         add_rows64_kernel<T><<<(unsigned)((rows * 8 + 255) / 256), 256, 0, stream>>>(oo + j, Dv, tmp, rows);
         if (cudaGetLastError() != cudaSuccess) st = fail(COTT_ERR_CUDA, "add_rows64_kernel launch failed");
       }
     }
-  if (tmp) COTT_CUDA_TRY(cudaFreeAsync(tmp, stream));
+  if (scratch) COTT_CUDA_TRY(cudaFreeAsync(scratch, stream));
   return st;
 }
 
@@ -329,11 +349,6 @@ bool scan_tc_usable(int Dk, int Dv, int dtype, const void* q, const void* k, con
 
 int launch_scan_tc(const void* q, const void* k, const void* v, void* out, int B, int H, int N, int Dk, int Dv, int dtype,
                    int reversed, cudaStream_t stream) {
-  if (Dk == kTcD && Dv == kTcD) {
-    const TileStrides ts = contiguous_bhnd(H, N);
-    return dtype == COTT_BF16 ? launch_scan_tc_t<__nv_bfloat16>(q, k, v, out, B, H, N, dtype, reversed, stream, ts, ts, ts)
-                              : launch_scan_tc_t<__half>(q, k, v, out, B, H, N, dtype, reversed, stream, ts, ts, ts);
-  }
   return dtype == COTT_BF16 ? launch_scan_tc_wide<__nv_bfloat16>(q, k, v, out, B, H, N, Dk, Dv, dtype, reversed, stream)
                             : launch_scan_tc_wide<__half>(q, k, v, out, B, H, N, Dk, Dv, dtype, reversed, stream);
 }

@@ -128,7 +128,7 @@ def test_tensor_core_scan_wide_heads(K, dt, dims):
     """Head dims that are multiples of 64 run as 64-wide tensor-core launches on strided slices (the scan is linear in
     the slices of the head dimension): same answer as the exact kernel in fp32, forward, reversed and backward."""
     Dk, Dv = dims
-    q, k, v, _, _ = O.make_inputs(2, 2, 333, Dk, Dv, seed=Dk + Dv, dtype=dt)
+    q, k, v, _, _ = O.make_inputs(2, 2, 700, Dk, Dv, seed=Dk + Dv, dtype=dt)  # six chunks: three segments per sequence
     q, k, v = q.cuda(), k.cuda(), v.cuda()
     for rev in (False, True):
         want = K.scan(q.float(), k.float(), v.float(), rev)
