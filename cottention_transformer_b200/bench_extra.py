@@ -239,6 +239,29 @@ def bench_long_context(N, B=1, H=16, d=64, iters=5):
             "frac": nbytes / t_seg / 1e9 / peak}
 
 
+def bench_long_context_d128(N, B=1, H=16, d=128, iters=3):
+    """Head dim 128 has no fused kernel: ``cos_attn_causal`` runs the reference's structure (PyTorch normalisation and
+    length factor, autograd) around ``CustomAttention``, whose four scans run on the tensor cores as 64-wide launches."""
+    from .cos_attention import cos_attn_causal
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(1234)
+    q, k, v = (torch.randn(B, H, N, d, device=dev, generator=g).bfloat16().requires_grad_() for _ in range(3))
+    do = torch.randn(B, H, N, d, device=dev, generator=g).bfloat16()
+    nc = (0.5 * torch.ones(1, H, 1, 1, device=dev)).requires_grad_()
+
+    def step():
+        q.grad = k.grad = v.grad = nc.grad = None
+        cos_attn_causal(q, k, v, nc).backward(do)
+
+    t = _time(step, iters, warmup=1)
+    _lib.check_device_status()
+    nbytes = 11 * B * H * N * d * 2
+    peak, kind = _peak_gbs()
+    return {"what": f"causal fwd+bwd prefill, B={B} H={H} N={N} d={d} bf16, composite op around tensor-core scans",
+            "us_per_step": t * 1e6, "tokens_per_s": B * N / t, "algorithmic_bytes": nbytes, "frac": nbytes / t / 1e9 / peak,
+            "peak_source": kind}
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--causal", type=int, default=0, metavar="B",
@@ -256,6 +279,8 @@ if __name__ == "__main__":
     if a.long_context:
         for n in (16384, 65536, 262144):
             print(json.dumps(bench_long_context(n)))
+        for n in (16384, 65536, 262144):
+            print(json.dumps(bench_long_context_d128(n)))
         raise SystemExit(0)
     if a.scan:
         print(json.dumps(bench_scan()))
