@@ -10,7 +10,9 @@ Two modes, chosen by dtype (not a fallback chain -- each mode is a CUDA path of 
 
 * float16 / bfloat16, head dim 64, no padding mask: ONE fused tensor-core kernel for the forward
   (``cott_cos_attn_fwd``) and two for the backward (``cott_cos_attn_bwd``), fp32 accumulation;
-* float32 / float64 (and any other shape or a padding mask): the reference's own structure --
+* float16 / bfloat16, head dim 128 / 192 / 256: the row factors pulled out of the scan, tensor-core scans on
+  64-wide slices of the head dimension, closed-form backward (``_WideCausal``);
+* float32 / float64 (and any other shape): the reference's own structure --
   elementwise torch ops around ``CustomAttention`` (the exact-mode scan kernel), gradients of
   ``norm_const`` by autograd exactly as in the reference.
 """
@@ -140,6 +142,71 @@ def cos_attn_causal_packed(qkv, norm_const, keep=None):
     return _FusedCausalPacked.apply(qkv, norm_const, keep)
 
 
+def wide_supported(q, k, v, keep=None) -> bool:
+    return (
+        q.is_cuda and q.dtype in FUSED_DTYPES and k.dtype == q.dtype and v.dtype == q.dtype
+        and q.shape[-1] in (128, 192, 256) and v.shape[-1] == q.shape[-1]
+        and (keep is None or tuple(keep.shape) == (q.shape[0], q.shape[2]))
+    )
+
+
+class _WideCausal(torch.autograd.Function):
+    """Head dims 128 / 192 / 256 in bf16 / fp16.  The row factors are pulled out of the scan,
+
+        out_t = r_t * scan(q, k, w v)_t      r_t = keep_t / |q_t|      w_s = keep_s / (|k_s| max(n_s^sigma, 1))
+
+    so q and k go into the tensor-core scans as they are, the factors stay in fp32 ``[B, H, N, 1]`` and the
+    backward is three more scans plus the derivatives of r and w in closed form (GPTCosAttention.py:229-248 by
+    the chain rule) -- a handful of elementwise passes instead of autograd through normalize / pow / div."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, norm_const, keep):
+        from .kernel import scan
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        B, H, N, D = q.shape
+        f32 = torch.float32
+        sig = torch.sigmoid(norm_const.detach().reshape(1, H, 1, 1).to(device=q.device, dtype=f32))
+        if keep is None:
+            n = torch.arange(1, N + 1, device=q.device, dtype=f32).view(1, 1, N, 1)
+            m = None
+        else:
+            m = keep.to(device=q.device, dtype=f32).view(B, 1, N, 1)
+            n = m.cumsum(2).clamp(min=1)
+        a = 1.0 / (n ** sig).clamp(min=1)                                                       # [B|1, H, N, 1]
+        rq = 1.0 / torch.linalg.vector_norm(q, dim=-1, keepdim=True, dtype=f32).clamp(min=1e-12)  # F.normalize eps
+        rk = 1.0 / torch.linalg.vector_norm(k, dim=-1, keepdim=True, dtype=f32).clamp(min=1e-12)
+        if m is not None:
+            rq, rk = rq * m, rk * m
+        w = a * rk
+        vw = (v * w).to(q.dtype)
+        out = scan(q, k, vw, False)
+        out.mul_(rq)
+        ctx.save_for_backward(q, k, v, vw, out, rq, rk, w, n, sig)
+        ctx.nc_shape, ctx.nc_dtype = norm_const.shape, norm_const.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from .kernel import scan
+        q, k, v, vw, out, rq, rk, w, n, sig = ctx.saved_tensors
+        f32 = torch.float32
+        dout = dout.contiguous().to(q.dtype)
+        d_r = (dout * out).sum(-1, keepdim=True, dtype=f32)        # = r_t (dO_t . scan_t)
+        g = (dout * rq).to(q.dtype)
+        dq = scan(g, vw, k, False)                                  # Custom_Kernel.py:106
+        dk = scan(vw, g, q, True)                                   # :107
+        dvw = scan(k, q, g, True)                                   # :108
+        dw = (dvw * v).sum(-1, keepdim=True, dtype=f32)
+        dq.addcmul_(q, (-(d_r * rq * rq)).to(q.dtype))              # d r / d q = -q r^3, and d_r carries one r
+        dk.addcmul_(k, (-(dw * w * rk * rk)).to(q.dtype))           # d w / d k = -k w rk^2
+        dv = dvw.mul_(w)
+        # d w / d sigma = -ln(n) w where n^sigma > 1
+        dsig = -(torch.log(n) * (n > 1) * dw * w).sum(dim=(0, 2, 3))
+        s1 = sig.reshape(-1)
+        dnc = (dsig * s1 * (1 - s1)).reshape(ctx.nc_shape).to(ctx.nc_dtype)
+        return dq, dk, dv, dnc, None
+
+
 def _exact_causal(q, k, v, norm_const, keep):
     """The reference's structure (GPTCosAttention.py:229-248,282) around the exact-mode scan."""
     B, H, N, _ = q.shape
@@ -170,6 +237,8 @@ def cos_attn_causal(q, k, v, norm_const, keep=None, segments=None):
         raise RuntimeError("cos_attn_causal needs CUDA tensors (there is no CPU path)")
     if fused_supported(q, k, v, keep):
         return _FusedCausal.apply(q, k, v, norm_const, segments, keep)
+    if wide_supported(q, k, v, keep):
+        return _WideCausal.apply(q, k, v, norm_const, keep)
     return _exact_causal(q, k, v, norm_const, keep)
 
 

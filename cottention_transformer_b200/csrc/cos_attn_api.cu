@@ -5,6 +5,7 @@
 #include "common.cuh"
 
 #include <initializer_list>
+#include <mutex>
 #include <utility>
 
 using namespace cott;
@@ -307,6 +308,31 @@ __global__ void add_rows64_kernel(T* __restrict__ dst, long dst_stride, const T*
 //   scan(q, k, v)[:, J] = sum_I scan(q[:, I], k[:, I], v[:, J]),
 // so every (I, J) pair is one launch of the 64-wide kernel on strided views of the tensors; partial results of
 // I > 0 go through a stream-ordered scratch buffer and are added in.
+// Stream-ordered scratch of the scan comes from a pool of the library's own that keeps what it has been given
+// (release threshold = max): the default pool hands memory back at every synchronisation, which turned each
+// long-sequence scan into a fresh device allocation.
+cudaError_t scratch_pool(cudaMemPool_t* pool) {
+  static cudaMemPool_t pools[64] = {};
+  static std::mutex mu;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!pools[dev]) {
+    cudaMemPoolProps props = {};
+    props.allocType = cudaMemAllocationTypePinned;
+    props.handleTypes = cudaMemHandleTypeNone;
+    props.location.type = cudaMemLocationTypeDevice;
+    props.location.id = dev;
+    if ((e = cudaMemPoolCreate(&pools[dev], &props)) != cudaSuccess) return e;
+    unsigned long long keep = ~0ull;
+    if ((e = cudaMemPoolSetAttribute(pools[dev], cudaMemPoolAttrReleaseThreshold, &keep)) != cudaSuccess) return e;
+  }
+  *pool = pools[dev];
+  return cudaSuccess;
+}
+
 template <typename T>
 int launch_scan_tc_wide(const void* q, const void* k, const void* v, void* out, int B, int H, int N, int Dk, int Dv, int dtype,
                         int reversed, cudaStream_t stream) {
@@ -320,7 +346,11 @@ int launch_scan_tc_wide(const void* q, const void* k, const void* v, void* out, 
   const size_t ws_bytes = plan.nseg > 1 ? 2 * seg_array_floats(B, H, plan.nseg) * sizeof(float) : 0;
   const size_t tmp_bytes = Dk > kTcD ? sizeof(T) * rows * kTcD : 0;
   char* scratch = nullptr;  // stream-ordered: segment states, then the partial result of the slices I > 0
-  if (ws_bytes + tmp_bytes) COTT_CUDA_TRY(cudaMallocAsync(reinterpret_cast<void**>(&scratch), ws_bytes + tmp_bytes, stream));
+  if (ws_bytes + tmp_bytes) {
+    cudaMemPool_t pool;
+    COTT_CUDA_TRY(scratch_pool(&pool));
+    COTT_CUDA_TRY(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&scratch), ws_bytes + tmp_bytes, pool, stream));
+  }
   float* ws = reinterpret_cast<float*>(scratch);
   T* tmp = reinterpret_cast<T*>(scratch + ws_bytes);
   int st = COTT_OK;
