@@ -41,6 +41,7 @@ _SIGNATURES = {
     "cott_bidir_fwd_strided": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "cott_bidir_bwd_strided": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "cott_bidir_fwd_static": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "cott_rotary": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, ctypes.c_longlong, _I, _I, _P],
     "cott_check_status": [ctypes.POINTER(ctypes.c_int)],
 }
 _STR = {"cott_version": [], "cott_last_error": [], "cott_status_string": [_I]}

@@ -24,11 +24,12 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .cos_attention import (cos_attn_bidirectional, cos_attn_bidirectional_packed, cos_attn_causal,
-                            cos_attn_causal_packed)
+                            cos_attn_causal_packed, rotary_packed_)
 
 
 class CosSelfAttention(nn.Module):
     permute = False  # True: the reference's layout handling (permute + contiguous copies around the op)
+    rotary = None    # (sin, cos) fp32 [S, 32]: GPT-J rotary on q and k (GPTCosAttention.py:458-476), packed path only
 
     def __init__(self, d_model, n_heads, causal):
         super().__init__()
@@ -39,7 +40,10 @@ class CosSelfAttention(nn.Module):
 
     def forward(self, x):
         B, S, D = x.shape
-        qkv = self.qkv(x).view(B, S, 3, self.h, D // self.h)
+        qkv = self.qkv(x)
+        if self.rotary is not None and self.causal and not self.permute:
+            qkv = rotary_packed_(qkv, self.rotary[0][:S], self.rotary[1][:S], heads=self.h)
+        qkv = qkv.view(B, S, 3, self.h, D // self.h)
         if not self.permute:  # strided tensor maps: no head split / merge copies
             op = cos_attn_causal_packed if self.causal else cos_attn_bidirectional_packed
             return self.proj(op(qkv, self.norm_const).reshape(B, S, D))
@@ -94,6 +98,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (smoke runs)")
     ap.add_argument("--permute", action="store_true", help="permute + copy around the op instead of the packed layout")
+    ap.add_argument("--rotary", action="store_true", help="gpt: rotary embedding on q and k (in place on the packed projection)")
     a = ap.parse_args()
     CosSelfAttention.permute = a.permute
     world, rank, local = (int(os.environ.get(k, d)) for k, d in (("WORLD_SIZE", 1), ("RANK", 0), ("LOCAL_RANK", 0)))
@@ -105,6 +110,9 @@ def main():
     batch = cfg.pop("batch")
     if a.layers:
         cfg["n_layers"] = a.layers
+    if a.rotary:
+        ang = torch.arange(cfg["seq"], device=dev).float()[:, None] / (10000 ** (torch.arange(0, 64, 2, device=dev).float() / 64))
+        CosSelfAttention.rotary = (torch.sin(ang), torch.cos(ang))
     torch.manual_seed(1234)
     model = Model(**cfg).to(dev)
     n_params = sum(p.numel() for p in model.parameters())
@@ -146,7 +154,7 @@ def main():
         print(json.dumps({"what": f"{a.model} training step, {cfg['n_layers']} layers, bf16 autocast, AdamW"
                                   + (", DDP" if world > 1 else ""), "params_M": n_params / 1e6, "n_gpus": world,
                           "batch_per_gpu": batch, "seq_len": cfg["seq"], "ms_per_step": ms,
-                          "tokens_per_s": world * batch * cfg["seq"] / ms * 1e3, "loss": float(loss), "data": "synthetic"}))
+                          "tokens_per_s": world * batch * cfg["seq"] / ms * 1e3, "loss": float(loss.detach()), "data": "synthetic"}))
     if world > 1:
         torch.distributed.destroy_process_group()
 

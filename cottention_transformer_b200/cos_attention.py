@@ -142,6 +142,53 @@ def cos_attn_causal_packed(qkv, norm_const, keep=None):
     return _FusedCausalPacked.apply(qkv, norm_const, keep)
 
 
+class _RotaryPacked(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, sin, cos, H, inverse=False):
+        B, N = x.shape[0], x.shape[1]
+        D = x.numel() // (B * N * 3 * H)
+        qkv = x.view(B, N, 3, H, D)
+        rot = 2 * sin.shape[-1]
+        lay = _lib.CottLayout(N * 3 * H * D, D, 3 * H * D, 0, 0, 0)
+        per_batch = sin.dim() == 3 and sin.shape[0] > 1
+        with torch.cuda.device(qkv.device):
+            st = _lib.lib().cott_rotary(_lib.ptr(qkv[:, :, 0]), _lib.ptr(qkv[:, :, 1]), _lib.ptr(sin), _lib.ptr(cos),
+                                        ctypes.byref(lay), B, H, N, D, rot, N * (rot // 2) if per_batch else 0, int(inverse),
+                                        _lib.DTYPE_CODE[qkv.dtype], _lib.stream_ptr(qkv.device))
+        _lib.check(st, "cott_rotary")
+        ctx.save_for_backward(sin, cos)
+        ctx.inverse, ctx.H = inverse, H
+        ctx.mark_dirty(x)
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        sin, cos = ctx.saved_tensors
+        g = g.contiguous()
+        return _RotaryPacked.apply(g, sin, cos, ctx.H, not ctx.inverse), None, None, None, None
+
+
+def rotary_packed_(qkv, sin, cos, heads=None):
+    """GPT-J rotary embedding (GPTCosAttention.py:458-476; transformers ``apply_rotary_pos_emb``) applied IN PLACE
+    to the q and k slices of a packed ``[B, N, 3, H, d]`` bf16 / fp16 tensor, one read and one write of q and k.
+    The tensor may also be given as the projection output itself, ``[B, N, 3*H*d]`` with ``heads=H`` (an in-place
+    op on a view costs autograd extra copies of the gradient; on the projection output it does not).
+    ``sin``, ``cos``: fp32 ``[N, rot/2]`` or ``[B, N, rot/2]`` (the two halves of ``embed_positions`` gathered at
+    ``position_ids``); the first ``rot`` elements of every head are rotated.  Differentiable (the backward is the
+    transposed rotation of the gradient, in place)."""
+    ok = qkv.is_cuda and qkv.dtype in FUSED_DTYPES and qkv.is_contiguous()
+    if ok and qkv.dim() == 5 and qkv.shape[2] == 3:
+        heads = qkv.shape[3]
+    elif not (ok and qkv.dim() == 3 and heads and qkv.shape[2] % (3 * heads * 8) == 0):
+        raise RuntimeError("rotary_packed_ takes a contiguous [B, N, 3, H, d] (or [B, N, 3*H*d] with heads=H) "
+                           "bfloat16 / float16 CUDA tensor")
+    sin = sin.to(device=qkv.device, dtype=torch.float32).contiguous()
+    cos = cos.to(device=qkv.device, dtype=torch.float32).contiguous()
+    if sin.shape != cos.shape or sin.shape[-2] != qkv.shape[1] or (sin.dim() == 3 and sin.shape[0] not in (1, qkv.shape[0])):
+        raise RuntimeError("sin / cos must be [N, rot/2] or [B, N, rot/2]")
+    return _RotaryPacked.apply(qkv, sin, cos, heads)
+
+
 def wide_supported(q, k, v, keep=None) -> bool:
     return (
         q.is_cuda and q.dtype in FUSED_DTYPES and k.dtype == q.dtype and v.dtype == q.dtype

@@ -268,6 +268,16 @@ int cott_bidir_fwd_static(const void* q, const void* k, const void* v, const uns
  */
 int cott_check_status(int* detail);
 
+/* Rotary position embedding of the reference's GPT module (GPT_Trainer/GPTCosAttention.py:458-476; transformers'
+ * apply_rotary_pos_emb / rotate_every_two), in place on q and k: x'[2i] = x[2i] cos_i - x[2i+1] sin_i,
+ * x'[2i+1] = x[2i+1] cos_i + x[2i] sin_i for i < rot_dim/2; elements from rot_dim on pass through.
+ * q, k: [B, H, N, D] views (float16 / bfloat16) with the element strides layout->in_b, in_h, in_n (NULL = dense), so
+ * the q and k slices of a packed [B, N, 3, H, D] projection output can be rotated where they lie.
+ * sin_table, cos_table: fp32 [N, rot_dim/2] (table_batch_stride = 0) or one table per batch entry
+ * (table_batch_stride = N * rot_dim/2).  inverse != 0 applies the transposed rotation (the backward of the op). */
+int cott_rotary(void* q, void* k, const float* sin_table, const float* cos_table, const cott_layout* layout, int B,
+                int H, int N, int D, int rot_dim, long long table_batch_stride, int inverse, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

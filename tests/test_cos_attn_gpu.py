@@ -262,3 +262,40 @@ def test_packed_qkv_layout_matches_the_permuted_op(dt, shape, masked):
     for i, gref in enumerate((q2.grad, k2.grad, v2.grad)):
         assert torch.equal(qkv.grad[:, :, i], gref.permute(0, 2, 1, 3)), i
     assert torch.allclose(nc.grad, nc2.grad, rtol=1e-5, atol=1e-6)
+
+
+def _rotary_reference(x, sin, cos):
+    """x: [B, N, H, d]; sin, cos: [B|1, N, rot/2].  The rotate-every-two form of GPTCosAttention.py:458-476."""
+    rot = 2 * sin.shape[-1]
+    xr, xp = x[..., :rot], x[..., rot:]
+    s = torch.repeat_interleave(sin[:, :, None, :], 2, 3)
+    c = torch.repeat_interleave(cos[:, :, None, :], 2, 3)
+    x1, x2 = xr[..., ::2], xr[..., 1::2]
+    rotated = torch.stack((-x2, x1), dim=-1).flatten(-2)
+    return torch.cat([xr * c + rotated * s, xp], dim=-1)
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("d,rot,per_batch", [(64, 64, False), (64, 32, True), (128, 64, False)])
+def test_rotary_packed_matches_rotate_every_two(dt, d, rot, per_batch):
+    from cottention_transformer_b200 import rotary_packed_
+    B, N, H = 2, 300, 3
+    g = torch.Generator(device="cuda").manual_seed(d + rot)
+    base = torch.randn(B, N, 3, H, d, device="cuda", generator=g).to(dt)
+    pos = torch.arange(N, device="cuda").float()[None, :, None] + (torch.arange(B, device="cuda").float()[:, None, None] * 7 if per_batch else 0)
+    inv_freq = 1.0 / (10000 ** (torch.arange(0, rot, 2, device="cuda").float() / rot))
+    ang = pos * inv_freq
+    sin, cos = torch.sin(ang), torch.cos(ang)                     # [B|1, N, rot/2]
+    tab = (sin, cos) if per_batch else (sin[0], cos[0])
+    x = base.clone().requires_grad_()
+    y = rotary_packed_((x * 1).view(B, N, 3 * H * d), *tab, heads=H).view(B, N, 3, H, d)  # in place on a non-leaf
+    w = torch.randn(B, N, 3, H, d, device="cuda", generator=g)
+    (y.float() * w).sum().backward()
+    xr = base.float().clone().requires_grad_()
+    ref = torch.stack([_rotary_reference(xr[:, :, 0], sin, cos), _rotary_reference(xr[:, :, 1], sin, cos), xr[:, :, 2]], dim=2)
+    (ref * w).sum().backward()
+    assert torch.equal(y[:, :, 2], base[:, :, 2])                 # v is not touched
+    tol = 2.0 ** -8 if dt == torch.bfloat16 else 2.0 ** -10         # one 16-bit rounding of values of size ~4
+    assert (y.float() - ref).abs().max().item() <= 4 * tol
+    # the backward rounds the fp32 gradient to 16 bits before rotating it back
+    assert (x.grad.float() - xr.grad).abs().max().item() <= 8 * tol * w.abs().max().item()
