@@ -31,7 +31,7 @@ template <> struct Pair16<__half> {
   }
 };
 
-// grid.x covers B*H*N*(rot_dim/8) pieces, grid.y = 2 (q, k)
+// one thread per 16-byte piece of a row, for q and k both (same sin / cos)
 template <typename T>
 __global__ void rotary_kernel(T* __restrict__ q, T* __restrict__ k, const float* __restrict__ sin_t,
                               const float* __restrict__ cos_t, long long sb, long long sh, long long sn, int H, int N,
@@ -44,18 +44,22 @@ __global__ void rotary_kernel(T* __restrict__ q, T* __restrict__ k, const float*
   const int n = static_cast<int>(h_inner ? (row / H) % N : row % N);
   const int h = static_cast<int>(h_inner ? row % H : (row / N) % H);
   const long long b = row / (static_cast<long long>(H) * N);
-  T* x = (blockIdx.y == 0 ? q : k) + b * sb + h * sh + n * sn + p * 8;
+  const long long off = b * sb + h * sh + n * sn + p * 8;
   const long long t = b * table_batch_stride + static_cast<long long>(n) * (pieces * 4) + p * 4;
   const float4 s4 = *reinterpret_cast<const float4*>(sin_t + t), c4 = *reinterpret_cast<const float4*>(cos_t + t);
   const float s[4] = {sign * s4.x, sign * s4.y, sign * s4.z, sign * s4.w}, c[4] = {c4.x, c4.y, c4.z, c4.w};
-  uint4 u = *reinterpret_cast<uint4*>(x);
-  uint32_t* w = reinterpret_cast<uint32_t*>(&u);
+  uint4 u[2] = {*reinterpret_cast<uint4*>(q + off), *reinterpret_cast<uint4*>(k + off)};
 #pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    const float2 f = Pair16<T>::unpack(w[e]);
-    w[e] = Pair16<T>::pack(f.x * c[e] - f.y * s[e], f.y * c[e] + f.x * s[e]);
+  for (int t2 = 0; t2 < 2; ++t2) {
+    uint32_t* w = reinterpret_cast<uint32_t*>(&u[t2]);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = Pair16<T>::unpack(w[e]);
+      w[e] = Pair16<T>::pack(f.x * c[e] - f.y * s[e], f.y * c[e] + f.x * s[e]);
+    }
   }
-  *reinterpret_cast<uint4*>(x) = u;
+  *reinterpret_cast<uint4*>(q + off) = u[0];
+  *reinterpret_cast<uint4*>(k + off) = u[1];
 }
 
 }  // namespace
@@ -79,7 +83,7 @@ extern "C" int cott_rotary(void* q, void* k, const float* sin_table, const float
   COTT_CUDA_TRY(scope.status());
   const int pieces = rot_dim / 8;
   const long long total = (long long)B * H * N * pieces;
-  const dim3 grid((unsigned)((total + 255) / 256), 2);
+  const dim3 grid((unsigned)((total + 255) / 256), 1);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const float sign = inverse ? -1.f : 1.f;
   if (dtype == COTT_BF16)
