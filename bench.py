@@ -18,7 +18,9 @@ Keys beyond the basic contract:
   cpu_baseline  the reference's PyTorch CPU formulation (cumsum form + autograd) restated in oracle/,
              timed on this host on a bounded sample of the same workload
 
-``--impl reference`` times that CPU formulation alone, with all host threads, as the reference arm.
+``--impl reference`` times that CPU formulation alone, with all host threads, as the reference arm; when the
+reference's CUDA extension has been built into oracle/_ref it also reports, under ``reference_cuda_kernel``, what that
+extension does on the GPU for the same shape (context only: the arm's ``value`` is the CPU figure).
 """
 from __future__ import annotations
 
@@ -127,6 +129,41 @@ def cpu_reference_sample(threads, budget_s=12.0, max_slices=64):
     return tokens / t_total, done, t_total
 
 
+def reference_cuda_kernel_sample(iters=3):
+    """The reference's own CUDA extension (built unmodified into oracle/_ref by oracle/build_ref.py), when it is
+    present and a GPU is visible: forward + the three backward scans of ``CustomAttention`` (Custom_Kernel.py:24,
+    106-108) at the bench shape in bf16, kernel calls only (the module's elementwise PyTorch ops are not counted).
+    Context for the CPU figure of this arm, which stays the arm's ``value``.  Returns a dict or None."""
+    so = os.path.join(ROOT, "oracle", "_ref", "FastAttention2", "kernel.so")
+    if not (os.path.exists(so) and torch.cuda.is_available()):
+        return None
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("kernel", so)  # the extension's init symbol is PyInit_kernel
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    g = torch.Generator(device=dev).manual_seed(1234)
+    q, k, v, do = (torch.nn.functional.normalize(torch.randn(B_PER_GPU, H, N, D, device=dev, generator=g), dim=-1).bfloat16()
+                   for _ in range(4))
+
+    def step():
+        ref.bfloat16(q, k, v, 1, False, False), ref.bfloat16(do, v, k, 1, False, False)
+        ref.bfloat16(v, do, q, 1, False, True), ref.bfloat16(k, q, do, 1, False, True)
+
+    step()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        step()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    ms = e0.elapsed_time(e1) / iters
+    return {"value": B_PER_GPU * N / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
+            "what": "reference CUDA extension (oracle/_ref), CustomAttention forward + backward = four kernel calls, "
+                    f"B={B_PER_GPU} H={H} N={N} d={D} bf16, one GPU, CUDA events"}
+
+
 def run_reference_arm(args, rank, world):
     if rank != 0:
         return
@@ -150,6 +187,9 @@ def run_reference_arm(args, rank, world):
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    gpu_ref = reference_cuda_kernel_sample()
+    if gpu_ref is not None:
+        line["reference_cuda_kernel"] = gpu_ref
     print(json.dumps(line), flush=True)
 
 
