@@ -43,6 +43,7 @@ _SIGNATURES = {
     "cott_bidir_fwd_static": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "cott_rotary": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, ctypes.c_longlong, _I, _I, _P],
     "cott_check_status": [ctypes.POINTER(ctypes.c_int)],
+    "cott_selftest_device_wait": [_I, _I, _I, _P],
 }
 _STR = {"cott_version": [], "cott_last_error": [], "cott_status_string": [_I]}
 _SIZE = {"cott_bidir_scratch_bytes": [_I, _I, _I, _I, _I, _I], "cott_cos_attn_seg_workspace_bytes": [_I, _I, _I, _I]}

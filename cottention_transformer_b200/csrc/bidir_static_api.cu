@@ -71,8 +71,11 @@ extern "C" int cott_bidir_fwd_static(const void* q, const void* k, const void* v
     return fail(COTT_ERR_SHAPE, "bidirectional attention needs head dims divisible by 16 in [16, 128] (got %d, %d)", Dk, Dv);
   const long BH = (long)B * H;
   if (BH > 0x7fffffffL) return fail(COTT_ERR_SHAPE, "B*H too large");
+  // 16-bit tensors with head dim 64 run on the tensor-core kernel, which keeps the state on chip: it needs no
+  // scratch at all (so no size limit applies) and allocates nothing either (tensor maps are built on the host stack)
+  const bool on_chip = bidir_tc_usable(Dk, Dv, dtype, {q, k, v, out});
   const size_t need = (size_t)BH * bidir_nsplit(BH, N) * Dk * Dv * (dtype == COTT_F64 ? 8 : 4);
-  if (need > kStaticScratchBytes)
+  if (!on_chip && need > kStaticScratchBytes)
     return fail(COTT_ERR_SHAPE,
                 "this problem needs %zu bytes of scratch but the built-in scratch of cott_bidir_fwd_static holds %zu "
                 "(COTT_BIDIR_STATIC_SCRATCH_BYTES); use cott_bidir_fwd with a caller-provided buffer",
@@ -81,6 +84,8 @@ extern "C" int cott_bidir_fwd_static(const void* q, const void* k, const void* v
   if (!q || !k || !v || !norm_const || !out) return fail(COTT_ERR_NULL, "null pointer");
   DeviceScope scope(q);
   COTT_CUDA_TRY(scope.status());
+  if (on_chip)
+    return launch_bidir_fwd_tc(q, k, v, keep, norm_const, out, B, H, N, dtype, static_cast<cudaStream_t>(stream));
   void* scratch = nullptr;
   int st = static_scratch(&scratch);
   if (st) return st;

@@ -32,39 +32,6 @@ namespace cott {
 
 __device__ int g_cott_status;  // 0 = ok; else (code << 16 | chunk) of the first wait that gave up
 
-// Optional timeline tracing (debug builds only, -DCOTT_TRACE): CTA 0 records clock64() at role events.
-#ifdef COTT_TRACE
-constexpr int kTraceWarps = 28, kTraceChunks = 32, kTraceEvents = 8;
-__device__ unsigned int g_cott_trace[kTraceWarps * kTraceChunks * kTraceEvents];
-// timestamps go to shared memory (a global store in the middle of a role would itself disturb the
-// fences and waits being timed) and are copied out when the kernel ends
-#define COTT_TRACE_DECL __shared__ unsigned int s_cott_trace[kTraceWarps * kTraceChunks * kTraceEvents];
-#define COTT_TRACE_EV(ev, c)                                                                      \
-  do {                                                                                            \
-    if ((threadIdx.x & 31) == 0 && (c) < kTraceChunks)                                            \
-      s_cott_trace[((threadIdx.x >> 5) * kTraceChunks + (c)) * kTraceEvents + (ev)] = (unsigned int)clock64(); \
-  } while (0)
-#define COTT_TRACE_FLUSH()                                                                        \
-  do {                                                                                            \
-    __syncthreads();                                                                              \
-    if (blockIdx.x == 0)                                                                          \
-      for (int i_ = threadIdx.x; i_ < kTraceWarps * kTraceChunks * kTraceEvents; i_ += blockDim.x) \
-        g_cott_trace[i_] = s_cott_trace[i_];                                                      \
-  } while (0)
-#else
-#define COTT_TRACE_DECL
-#define COTT_TRACE_EV(ev, c) \
-  do {                       \
-  } while (0)
-#define COTT_TRACE_FLUSH() \
-  do {                     \
-  } while (0)
-#endif
-
-#ifndef COTT_SKEL
-#define COTT_SKEL 0  // debug only: bit mask of role work to skip when timing the pipeline skeleton
-#endif
-
 constexpr int kTcChunk = 128;
 constexpr int kTcD = 64;
 constexpr int kTileBytes = kTcChunk * kTcD * 2;  // 16 KB: one [128 x 64] 16-bit tile
@@ -139,12 +106,9 @@ __device__ __forceinline__ RowMask row_mask(const unsigned char* keep_b, const i
 // Bounded wait that also gives up when another role of the CTA has raised `abort_flag`.
 // On its own time-out it raises the flag and records (code << 16 | chunk) in g_cott_status.
 __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code,
-                                         int chunk) {
-  for (uint32_t i = 0; i < ptx::kMaxPolls; ++i) {
+                                         int chunk, uint32_t max_polls = ptx::kMaxPolls) {
+  for (uint32_t i = 0; i < max_polls; ++i) {
     if (ptx::mbar_try_wait(bar, parity)) return true;
-#ifdef COTT_POLL_SLEEP
-    __nanosleep(COTT_POLL_SLEEP);
-#endif
     if (*abort_flag) return false;
   }
   *abort_flag = 1;
@@ -200,8 +164,8 @@ __device__ __forceinline__ bool wait_bar4(uint64_t* b0, uint32_t p0, uint64_t* b
 // to see TMA-written data) -- one warp-wide try_wait with a suspend hint, so a waiting warp sleeps in
 // hardware instead of spinning; the outcome is made warp-uniform.
 __device__ __forceinline__ bool wait_bar_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code,
-                                              int chunk) {
-  return __all_sync(0xffffffffu, wait_bar(bar, parity, abort_flag, code, chunk) ? 1 : 0) != 0;
+                                              int chunk, uint32_t max_polls = ptx::kMaxPolls) {
+  return __all_sync(0xffffffffu, wait_bar(bar, parity, abort_flag, code, chunk, max_polls) ? 1 : 0) != 0;
 }
 __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
   __syncwarp();
@@ -506,7 +470,6 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   __shared__ uint64_t bar_full[NS], bar_free_in[NS], bar_out[NS], bar_prep[NS], bar_p_full[2], bar_p_ready[2], bar_acc_full[2],
       bar_acc_free[2], bar_s_full, bar_state[2], bar_state2, bar_init;
   __shared__ uint32_t tmem_slot;
-  COTT_TRACE_DECL
   __shared__ int abort_flag_s;
   volatile int* abort_flag = &abort_flag_s;
 
@@ -590,7 +553,6 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
 #pragma unroll
         for (int k = 0; k < 4; ++k) mma_ss(tP, dX + 2 * k, dY + 2 * k, kIdescP, k > 0);
         mma_commit(&bar_p_full[c & 1]);
-        COTT_TRACE_EV(1, c);
       };
       bool ok = wait_bar1(&bar_full[0], 0, abort_flag, kWaitTma, 0);
       if (ok) {
@@ -627,7 +589,6 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
 #pragma unroll
           for (int k = 1; k < 8; ++k) mma_ss(tS, dYm + 128 * k, dZm + 128 * k, kIdescS, 1u);
           mma_commit(&bar_s_full);
-          COTT_TRACE_EV(2, c);
         }
       }
     }
@@ -639,18 +600,11 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       auto issue_loads = [&](int c) {
         const int s = c % NS;
         unsigned char* st = stage_of(c);
-#if COTT_SKEL & 8
-        if (c >= NS) {
-          mbar_arrive(&bar_full[s]);
-          return;
-        }
-#endif
         mbar_expect_tx(&bar_full[s], STAGE + kTileBytes);
         if (MODE == kModeDq) tma_load_tile(st, &mapX, &bar_full[s], row0_of(c), h, bb);
         tma_load_tile(st + kIdxY * kTileBytes, &mapY, &bar_full[s], row0_of(c), h, bb);
         tma_load_tile(st + kIdxZ * kTileBytes, &mapZ, &bar_full[s], row0_of(c), h, bb);
         tma_load_tile(ring_of(c), MODE == kModeDq ? &mapQ : &mapX, &bar_full[s], row0_of(c), h, bb);
-        COTT_TRACE_EV(0, c);
       };
       for (int c = 0; c < NS && c < nchunks; ++c) issue_loads(c);
       for (int c = 0; c < nchunks; ++c) {
@@ -663,10 +617,8 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
           issue_loads(c + NS);
         }
         if (!wait_bar(&bar_out[s], (c / NS) & 1, abort_flag, kWaitStageFree, c)) break;
-#if !(COTT_SKEL & 16)
         tma_store_tile(&mapOut, ring_of(c), row0_of(c), h, bb);
         tma_store_commit();
-#endif
       }
       tma_store_wait<0>();
     }
@@ -685,7 +637,6 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
                        kWaitScoreReady, c))
           break;
         tc_fence_after_sync();
-        COTT_TRACE_EV(0, c);
         if (c > 0 || has_init) {
           const uint64_t dS = dS0 + static_cast<uint64_t>(b * ((kTcD * 128) >> 4));
 #pragma unroll
@@ -696,7 +647,6 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
 #pragma unroll
         for (int k = 1; k < 8; ++k) mma_ts(tAcc, tP + 8 * k, dZm + 128 * k, kIdescAcc, 1u);
         mma_commit(&bar_acc_full[b]);
-        COTT_TRACE_EV(3, c);
       }
     }
   } else if (warp < 6) {
@@ -707,13 +657,9 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       const int b = c & 1;
       if (!wait_bar_warp(&bar_p_full[b], (c >> 1) & 1, abort_flag, kWaitScore, c)) break;
       tc_fence_after_sync();
-      COTT_TRACE_EV(0, c);
-#if !(COTT_SKEL & 1)
       mask_pack_inplace<T, !kRev>(tP0 + 128 * b + lane_base, lane, wq);
-#endif
       tc_fence_before_sync();
       warp_arrive(&bar_p_ready[b], lane);
-      COTT_TRACE_EV(1, c);
     }
   } else if (warp >= 10 && warp < 14) {
     // ---------------------------------------------------------------- state group
@@ -732,7 +678,6 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       if (!wait_bar_warp(&bar_s_full, c & 1, abort_flag, kWaitState, c)) break;
       tc_fence_after_sync();
       if (lane == 0) mbar_arrive(&bar_free_in[c % NS]);  // the state MMAs of chunk c have read its tiles
-      COTT_TRACE_EV(0, c);
       // The state MMA of chunk c+1 waits for this read of the fp32 state (and the accumulator MMAs of
       // chunk c+1 for the 16-bit copy): that loop sets the chunk period.  So the read is reported as soon
       // as the second half of the row has arrived, before its conversion and the shared-memory writes.
@@ -762,7 +707,6 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       }
       fence_proxy_async_smem();
       warp_arrive(&bar_state[c & 1], lane);
-      COTT_TRACE_EV(1, c);
     }
   } else if ((warp >= 15 && warp < 19) || warp >= 24) {
     // ---------------------------------------------------------------- operand groups (even / odd chunks)
@@ -776,19 +720,15 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       // chunks would skip every other phase of each `full` barrier.
       if (!wait_bar_warp(&bar_full[s], (c / NS) & 1, abort_flag, kWaitTma, c)) break;
       if ((c & 1) != mine) continue;
-      COTT_TRACE_EV(3, c);
       unsigned char* sZ = stage_of(c) + kIdxZ * kTileBytes;
       unsigned char* sK = (MODE == kModeDq) ? sZ : stage_of(c) + kIdxY * kTileBytes;
-#if !(COTT_SKEL & 2)
       if constexpr (!kScan) {
         const RowMask m = row_mask(keep_b, count_b, row0_of(c) + row, N);
         const float rk = m.kp ? inv_norm(row_sumsq_rolled<T>(sK, row)) : 0.f;
         scale_row_rolled<T>(sZ, row, rk * length_factor(m.n, sigma));
       }
-#endif
       fence_proxy_async_smem();
       warp_arrive(&bar_prep[s], lane);
-      COTT_TRACE_EV(7, c);
     }
   } else {
     // ---------------------------------------------------------------- output groups (even / odd chunks)
@@ -802,16 +742,9 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       // (every phase of `full` is observed, also for the other group's chunks: see the operand groups)
       if (!wait_bar_warp(&bar_full[s], (c / NS) & 1, abort_flag, kWaitTma, c)) break;
       if ((c & 1) != mine) continue;
-      COTT_TRACE_EV(7, c);
-#if !(COTT_SKEL & 4)
       const float rq = kScan ? 1.f : row_mask(keep_b, count_b, row0_of(c) + row, N).kp ? inv_norm(row_sumsq_rolled<T>(sQ, row)) : 0.f;
-#else
-      const float rq = 1.f;
-#endif
-      COTT_TRACE_EV(0, c);
       if (!wait_bar_warp(&bar_acc_full[b], (c >> 1) & 1, abort_flag, kWaitAcc, c)) break;
       tc_fence_after_sync();
-      COTT_TRACE_EV(2, c);
       // The score and accumulator MMAs of this chunk have completed (the operand group reports the state
       // MMAs): the stage can be refilled.
       if (lane == 0) mbar_arrive(&bar_free_in[s]);
@@ -819,7 +752,6 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       // q tile, which no MMA reads).  Its rows are replaced in place, in the swizzled layout, by the
       // output rows; the TMA thread stores the tile and refills it.
       const uint32_t tAcc = tAcc0 + 64 * b + lane_base;
-#if !(COTT_SKEL & 4)
       if (MODE != kModeDq) {
         row_from_acc<T, false>(sQ, row, tAcc, rq, 0.f);  // o = acc / |q|  (the bare scan: o = acc)
       } else {
@@ -827,13 +759,10 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         const float delta = row_dot_acc<T>(sQ, row, tAcc) * (rq * rq * rq);
         row_from_acc<T, true>(sQ, row, tAcc, rq, -delta);
       }
-#endif
       tc_fence_before_sync();
       warp_arrive(&bar_acc_free[b], lane);
-      COTT_TRACE_EV(3, c);
       fence_proxy_async_smem();
       warp_arrive(&bar_out[s], lane);
-      COTT_TRACE_EV(4, c);
     }
   }
 
@@ -847,7 +776,6 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   }
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, 512);
-  COTT_TRACE_FLUSH();
 }
 
 // -------------------------------------------------------------------------------------------------
@@ -884,7 +812,6 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   __shared__ uint64_t bar_full[NS], bar_free_in[NS], bar_out[NS], bar_prep[NS], bar_p_full, bar_p_ready, bar_acc_full, bar_acc_free,
       bar_state, bar_state2, bar_r_full, bar_init;
   __shared__ uint32_t tmem_slot;
-  COTT_TRACE_DECL
   __shared__ int abort_flag_s;
   volatile int* abort_flag = &abort_flag_s;
 
@@ -976,7 +903,6 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         const bool refill = ci + NS < nchunks;
         if (refill) {
           if (!wait_bar(&bar_free_in[s], (ci / NS) & 1, abort_flag, kWaitStageFree, ci)) break;
-          COTT_TRACE_EV(4, ci);
           load_inputs(ci + NS);
         }
         if (!wait_bar(&bar_out[s], (ci / NS) & 1, abort_flag, kWaitStageFree, ci)) break;
@@ -1014,14 +940,12 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
           if (ci > 0 && !(ok = wait_bar1(&bar_state2, (ci - 1) & 1, abort_flag, kWaitState, ci))) break;
           if (ci == 0 && has_init && !(ok = wait_bar1(&bar_init, 0, abort_flag, kWaitState, ci))) break;
           tc_fence_after_sync();
-          COTT_TRACE_EV(0, ci);
           const uint32_t q0 = smem_u32(smem + (ci % NS) * STAGE);
           const uint64_t dQm = mdesc(q0), dDm = mdesc(q0 + 3 * kTileBytes);
           mma_ss(tR, dQm, dDm, kIdescR, (ci > 0 || has_init) ? 1u : 0u);
 #pragma unroll
           for (int k = 1; k < 8; ++k) mma_ss(tR, dQm + 128 * k, dDm + 128 * k, kIdescR, 1u);
           mma_commit(&bar_r_full);
-          COTT_TRACE_EV(1, ci);
           // score tiles of chunk ci+1: single-buffered, so the accumulator MMAs of chunk ci (which read the
           // 16-bit scores from TMEM) must be complete
           const int s1 = (ci + 1) % NS;
@@ -1029,9 +953,7 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
                          nullptr, 0, abort_flag, kWaitTma, ci);
           if (!ok) break;
           tc_fence_after_sync();
-          COTT_TRACE_EV(2, ci);
           issue_scores(ci + 1);
-          COTT_TRACE_EV(3, ci);
         }
       }
     }
@@ -1063,7 +985,6 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         // masked scores of chunk ci (which implies Qw(ci))
         if (!wait_bar1(&bar_p_ready, ci & 1, abort_flag, kWaitScoreReady, ci)) break;
         tc_fence_after_sync();
-        COTT_TRACE_EV(0, ci);
         mma_ts(tK, tE, dQm, kIdescAccMN, acc0);
 #pragma unroll
         for (int k = 1; k < 8; ++k) mma_ts(tK, tE + 8 * k, dQm + 128 * k, kIdescAccMN, 1u);
@@ -1071,7 +992,6 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
 #pragma unroll
         for (int k = 1; k < 8; ++k) mma_ts(tV, tF + 8 * k, dDm + 128 * k, kIdescAccMN, 1u);
         mma_commit(&bar_acc_full);
-        COTT_TRACE_EV(1, ci);
       }
     }
   } else if (warp < 6) {
@@ -1093,15 +1013,11 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     for (int ci = 0; ok && ci < nchunks; ++ci) {
       if (!(ok = wait_bar_warp(&bar_p_full, ci & 1, abort_flag, kWaitScore, ci))) break;
       tc_fence_after_sync();
-      COTT_TRACE_EV(1, ci);
       mask_pack_inplace<T, false>(tE + lane_base, lane, wq);
-      COTT_TRACE_EV(2, ci);
       tc_fence_before_sync();
       warp_arrive(&bar_p_ready, lane);
-      COTT_TRACE_EV(3, ci);
       // Qw of the next chunk, while the accumulator MMAs of this one run
       if (ci + 1 < nchunks && !(ok = prepare(ci + 1))) break;
-      COTT_TRACE_EV(0, ci);
     }
   } else if (warp >= 10) {
     // operand group: mask + convert F, then the fp32 state after this chunk -> 16-bit operand
@@ -1146,10 +1062,8 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       const RowMask m = row_mask(keep_b, count_b, pos, N);
       const float rk = m.kp ? inv_norm(row_sumsq_rolled<T>(sK, row)) : 0.f;
       const float a = length_factor(m.n, sigma);
-      COTT_TRACE_EV(0, ci);
       if (!wait_bar_warp(&bar_acc_full, ci & 1, abort_flag, kWaitAcc, ci)) break;
       tc_fence_after_sync();
-      COTT_TRACE_EV(3, ci);
       // dV first (its row product with v gives eps), then dK; each is staged as soon as it is ready, in
       // the V / K tile of this stage: every MMA that reads them completed before acc_full and this thread
       // is done with its own rows, so they have no reader left.  The TMA thread stores and refills them.
@@ -1161,12 +1075,9 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       row_from_acc<T, true>(sK, row, tK + lane_base, c1, -rk * rk * eps);
       tc_fence_before_sync();
       warp_arrive(&bar_acc_free, lane);
-      COTT_TRACE_EV(4, ci);
-      COTT_TRACE_EV(5, ci);
       ptx::fence_proxy_async_smem();
       warp_arrive(&bar_out[s], lane);
       if (m.n > 1.0f && pos < N) gsum += logf(m.n) * eps;
-      COTT_TRACE_EV(6, ci);
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) gsum += __shfl_down_sync(0xffffffffu, gsum, off);
@@ -1182,7 +1093,6 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   }
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, 512);
-  COTT_TRACE_FLUSH();
 }
 
 inline size_t causal_bwd_kv_smem_bytes() {

@@ -193,6 +193,46 @@ int run_bwd_seg(const void* q, const void* k, const void* v, const unsigned char
   return launch_bwd_dkdv<T>(q, k, v, nc, dout, dk, dv, dnorm, B, H, N, dtype, stream, ws + 4 * A, plan);
 }
 
+// The time-out path of the tensor-core kernels on its own: one CTA sets up what those kernels set up (an
+// mbarrier, a TMEM allocation), three of its warps wait -- with the same bounded wait, a few polls long -- on a
+// barrier phase that nothing ever completes, and the CTA then leaves the way the kernels leave after a time-out:
+// status word written once, every role out of its loop, TMEM handed back.  Nothing faults and nothing spins
+// without a limit; the launch ends after about `polls` x 0.2 ms.
+__global__ void __launch_bounds__(128, 1) wait_selftest_kernel(int polls, int code, int chunk) {
+  using namespace ptx;
+  __shared__ uint64_t bar_never, bar_done;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag_s;
+  volatile int* abort_flag = &abort_flag_s;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar_never, 1);
+    mbar_init(&bar_done, 1);
+    mbar_fence_init();
+    abort_flag_s = 0;
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_slot, 32);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  if (warp == 0) {
+    // the role whose wait runs out: it raises the abort flag and records (code << 16 | chunk)
+    wait_bar_warp(&bar_never, 0, abort_flag, code, chunk, static_cast<uint32_t>(polls));
+  } else if (warp >= 2) {
+    // roles waiting for something else (with the full limit) must notice the abort flag and leave too
+    wait_bar_warp(&bar_done, 0, abort_flag, code + 1, chunk);
+  }
+  (void)lane;
+  __syncwarp();
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 32);
+}
+
 int check_ptrs16(std::initializer_list<std::pair<const void*, const char*>> ps) {
   for (auto& p : ps) {
     if (!p.first) return fail(COTT_ERR_NULL, "null pointer: %s", p.second);
@@ -540,6 +580,15 @@ int cott_cos_attn_prefill_state(const void* k, const void* v, const float* norm_
                                                                  plan, s);
   if (st) return st;
   seg_to_decode_state_kernel<<<(unsigned)((long)B * H), 256, 0, s>>>(ws, state, plan.nseg, accumulate != 0);
+  COTT_CUDA_TRY(cudaGetLastError());
+  return COTT_OK;
+}
+
+int cott_selftest_device_wait(int polls, int code, int chunk, void* stream) {
+  if (polls < 1 || polls > 64) return fail(COTT_ERR_SHAPE, "polls must be in [1, 64] (got %d)", polls);
+  if (code < 1 || code > 0x7fff || chunk < 0 || chunk > 0xffff)
+    return fail(COTT_ERR_SHAPE, "code must be in [1, 32767] and chunk in [0, 65535] (got %d, %d)", code, chunk);
+  wait_selftest_kernel<<<1, 128, 0, static_cast<cudaStream_t>(stream)>>>(polls, code, chunk);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }

@@ -268,6 +268,16 @@ int cott_bidir_fwd_static(const void* q, const void* k, const void* v, const uns
  */
 int cott_check_status(int* detail);
 
+/*
+ * Exercises that time-out path without a fault: launches one small CTA that sets up an mbarrier and a TMEM
+ * allocation like the tensor-core kernels, lets one warp wait (same bounded wait, `polls` tries of about 0.2 ms
+ * each, 1 <= polls <= 64) on a barrier phase that nothing completes while the other warps wait elsewhere with
+ * the normal limit, and leaves the way those kernels leave after a time-out.  Afterwards cott_check_status
+ * returns COTT_ERR_DEVICE_WAIT with detail == (code << 16) | chunk, and the device is usable as before.
+ * For tests of a host's handling of that status.  No counterpart in the reference.
+ */
+int cott_selftest_device_wait(int polls, int code, int chunk, void* stream);
+
 /* Rotary position embedding of the reference's GPT module (GPT_Trainer/GPTCosAttention.py:458-476; transformers'
  * apply_rotary_pos_emb / rotate_every_two), in place on q and k: x'[2i] = x[2i] cos_i - x[2i+1] sin_i,
  * x'[2i+1] = x[2i+1] cos_i + x[2i] sin_i for i < rot_dim/2; elements from rot_dim on pass through.
