@@ -17,6 +17,10 @@ Keys beyond the basic contract:
              against the measured HBM copy bandwidth
   cpu_baseline  the reference's PyTorch CPU formulation (cumsum form + autograd) restated in oracle/,
              timed on this host on a bounded sample of the same workload
+  extra      secondary workloads, each with its own algorithmic bytes, device time and fraction of the HBM peak:
+             ``prefill_long`` (B=1, H=16 heads split over the ranks, N in {16k, 64k, 256k}, d in {64, 128}, fwd+bwd)
+             and ``decode`` (batch 64 per GPU, 4096 single-token steps, fp32 state, d in {64, 128}) with the
+             reference's CPU recurrent loop timed beside it; ``--no-extra`` skips them
 
 ``--impl reference`` times that CPU formulation alone, with all host threads, as the reference arm; when the
 reference's CUDA extension has been built into oracle/_ref it also reports, under ``reference_cuda_kernel``, what that
@@ -41,9 +45,9 @@ import torch  # noqa: E402
 B_PER_GPU, H, N, D = 8, 16, 4096, 64
 WORKLOAD = "causal cosine attention fwd+bwd, B=8/GPU H=16 N=4096 d=64 bf16 (Q,K L2-normalised N(0,1), norm_const=0.5)"
 ELEM = 2  # bf16
-# ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of causal_bwd_kv_kernel at the bench shape
-# (profiles/causal_fwd_bwd_B8_H16_N4096_d64_bf16_three_groups.md: 268.5 MB read + 95.1 MB write).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 363_582_208
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of causal_bwd_kv_kernel at the bench shape, RECORDED from an
+# earlier ncu capture of this kernel (268.5 MB read + 95.1 MB write): a run of this file does not measure it.
+RECORDED_TRAFFIC_BYTES_PER_LAUNCH = 363_582_208
 
 
 def _peaks():
@@ -99,10 +103,35 @@ class ClockSampler(threading.Thread):
         }
 
 
+def _bind_to_gpu_numa_node(index):
+    """Restrict this process to the CPUs next to GPU `index` (sysfs: the PCI device's local_cpulist), so that the
+    pinned host buffers it allocates afterwards are first touched on that NUMA node.  Read-only with respect to
+    the GPU; returns what was found, or None when the topology is not exposed."""
+    try:
+        bus = torch.cuda.get_device_properties(index).pci_bus_id
+        domain = torch.cuda.get_device_properties(index).pci_domain_id
+        dev_id = torch.cuda.get_device_properties(index).pci_device_id
+        path = f"/sys/bus/pci/devices/{domain:04x}:{bus:02x}:{dev_id:02x}.0"
+        with open(os.path.join(path, "numa_node")) as f:
+            node = int(f.read().strip())
+        with open(os.path.join(path, "local_cpulist")) as f:
+            cpulist = f.read().strip()
+        cpus = set()
+        for part in cpulist.split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+        return {"node": node, "cpus": cpulist, "bound": bool(allowed)}
+    except Exception:
+        return None
+
+
 def _host_inputs(rank):
     """Seeded synthetic shard of this rank in pinned host memory (seed 1234 + rank)."""
-    from oracle import cott_oracle as O  # input recipe only (shared with the tests)
-    q, k, v, do, nc = O.make_inputs(B_PER_GPU, H, N, D, seed=1234 + rank, dtype=torch.bfloat16)
+    from cottention_transformer_b200.synthetic import make_inputs
+    q, k, v, do, nc = make_inputs(B_PER_GPU, H, N, D, seed=1234 + rank, dtype=torch.bfloat16)
     return [t.pin_memory() for t in (q, k, v, do)], nc
 
 
@@ -113,7 +142,7 @@ def cpu_reference_sample(threads, budget_s=12.0, max_slices=64):
     from oracle import cott_oracle as O
     torch.set_num_threads(threads)
     g = torch.Generator().manual_seed(1234)
-    done, t_total = 0, 0.0
+    done, t_total = -1, 0.0  # the first slice is a warm-up (thread pool, allocator) and is not counted
     while done < max_slices and t_total < budget_s:
         q = torch.nn.functional.normalize(torch.randn(1, 1, N, D, generator=g), dim=-1).requires_grad_()
         k = torch.nn.functional.normalize(torch.randn(1, 1, N, D, generator=g), dim=-1).requires_grad_()
@@ -123,10 +152,92 @@ def cpu_reference_sample(threads, budget_s=12.0, max_slices=64):
         t0 = time.perf_counter()
         out = O.cos_attn_causal(q, k, v, nc, scan=lambda a, b, c: O.scan_cumsum(a, b, c, False))
         out.backward(do)
-        t_total += time.perf_counter() - t0
+        if done >= 0:
+            t_total += time.perf_counter() - t0
         done += 1
     tokens = done * N / H  # one token = one position across all H heads
     return tokens / t_total, done, t_total
+
+
+def cpu_decode_sample(d, threads, steps=200, heads=16):
+    """The reference's recurrent decode loop on the CPU (GPTCosAttention.py:253-272 as restated in oracle/: batch 1,
+    float64 [1, H, d, d] state, torch ops per token).  Returns tokens/s."""
+    from oracle import cott_oracle as O
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(d)
+    q, k, v = (torch.randn(1, heads, steps + 8, d, generator=g) for _ in range(3))
+    nc = 0.5 * torch.ones(heads)
+    state = torch.zeros(1, heads, d, d, dtype=torch.float64)
+    for t in range(8):
+        state, _ = O.decode_step_torch(state, t + 1, q[:, :, t], k[:, :, t], v[:, :, t], nc)
+    t0 = time.perf_counter()
+    for t in range(8, steps + 8):
+        state, _ = O.decode_step_torch(state, t + 1, q[:, :, t], k[:, :, t], v[:, :, t], nc)
+    return steps / (time.perf_counter() - t0)
+
+
+def cpu_config1_forward(threads):
+    """The reference's CPU-runnable case whole: forward only, fp32, B=2, H=8, N=1024, d=64, PyTorch cumsum
+    formulation with the module math around it.  Returns seconds."""
+    from oracle import cott_oracle as O
+    torch.set_num_threads(threads)
+    q, k, v, _, nc = O.make_inputs(2, 8, 1024, 64, seed=1234)
+    best = None
+    for _ in range(2):
+        t0 = time.perf_counter()
+        with torch.no_grad():
+            O.cos_attn_causal(q, k, v, nc, scan=lambda a, b, c: O.scan_cumsum(a, b, c, False))
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return best
+
+
+def run_extras(world, rank, dev, with_cpu):
+    """Secondary workloads (every rank takes part; figures are the max over ranks of device-timed seconds)."""
+    import torch.distributed as dist
+    from cottention_transformer_b200 import bench_extra as X
+    from cottention_transformer_b200.sharding import shard_range
+    peak, kind = _peaks()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    heads = 16
+    h0, h1 = shard_range(heads, world, rank)
+    prefill = []
+    for d in (64, 128):
+        for n in (16384, 65536, 262144):
+            t = max_over_ranks(X.bench_prefill_sharded(n, d, world, rank, H=heads))
+            nbytes = 11 * heads * n * d * ELEM  # 4 (fwd) + 7 (bwd) tensor passes over all heads
+            prefill.append({"N": n, "d": d, "heads_on_rank0": h1 - h0, "us_per_step": t * 1e6, "tokens_per_s": n / t,
+                            "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / t / 1e9,
+                            "frac": nbytes / t / 1e9 / (world * peak)})
+            torch.cuda.empty_cache()
+    decode = []
+    for d in (64, 128):
+        r = X.bench_decode(d, 4096)
+        t = max_over_ranks(r["us_per_step"] * 1e-6)
+        row = {"d": d, "batch_per_gpu": 64, "heads": heads, "steps": 4096, "us_per_step": t * 1e6,
+               "tokens_per_s": world * 64 / t, "algorithmic_bytes_per_step_per_gpu": r["algorithmic_bytes_per_step"],
+               "achieved_gbs_per_gpu": r["algorithmic_bytes_per_step"] / t / 1e9,
+               "frac": r["algorithmic_bytes_per_step"] / t / 1e9 / peak, "cuda_graph": r["cuda_graph"],
+               "us_per_step_python_launch": r["us_per_step_python_launch"]}
+        if with_cpu and rank == 0:
+            threads = os.cpu_count() or 1
+            row["cpu_baseline"] = {"value": cpu_decode_sample(d, threads), "unit": "tokens/s", "cores": threads, "kind": "port",
+                                   "sample": "200 tokens at batch 1, float64 state, the reference's per-token torch loop"}
+        decode.append(row)
+    return {"peak_gbs": peak, "peak_source": kind,
+            "prefill_long": {"what": "causal fwd+bwd, B=1, H=16 heads split evenly over the GPUs (no collective), bf16; "
+                                     "frac = algorithmic bytes / time / (GPUs x HBM peak)", "scaling": "strong",
+                             "rows": prefill},
+            "decode": {"what": "recurrent decode, one launch per token replayed from a CUDA graph, batch 64 per GPU, "
+                               "bf16 tokens, fp32 state in HBM (8 state buffers in rotation: larger than L2 at d=128)",
+                       "scaling": "weak", "rows": decode}}
 
 
 def reference_cuda_kernel_sample(iters=3):
@@ -182,8 +293,8 @@ def run_reference_arm(args, rank, world):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "global_batch": B_PER_GPU * args.gpus, "seq_len": N, "heads": H, "head_dim": D},
         "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
-                         "sample": f"{slices} (batch,head) slices of N={N}, d={D} per step, fp32, PyTorch cumsum "
-                                   "formulation + autograd"},
+                         "sample": f"{slices} (batch,head) slices of N={N}, d={D} per step (after one untimed warm-up "
+                                   "slice), fp32, PyTorch cumsum formulation + autograd"},
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -203,6 +314,7 @@ def main():
     ap.add_argument("--e2e-slices", type=int, default=8, help="batch slices of the pipelined host-buffer step")
     ap.add_argument("--e2e-no-graph", action="store_true", help="issue the host-buffer step call by call instead of replaying a CUDA graph")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--no-extra", action="store_true", help="skip the secondary workloads (long prefill, decode)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -224,6 +336,7 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     L = _lib.lib()
+    numa = _bind_to_gpu_numa_node(local_rank)  # before any pinned allocation: first touch lands on the GPU's node
     host, nc_host = _host_inputs(rank)
     q, k, v, do = (t.to(dev) for t in host)
     nc = nc_host.to(dev)
@@ -294,6 +407,28 @@ def main():
 
     e2e_steps = max(3, min(args.steps, 10))
     e2e_value = None
+    copy_ceiling = None
+    if not args.no_e2e:
+        # the floor of the host-buffer step on this host: the same bytes both ways at once, no kernels
+        for _ in range(2):
+            host_step.copy_only(host, host_out)
+        barrier()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record()
+        for _ in range(e2e_steps):
+            host_step.copy_only(host, host_out)
+        c1.record()
+        barrier()
+        copy_ms = c0.elapsed_time(c1)
+        if world > 1:
+            t = torch.tensor([copy_ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            copy_ms = t.item()
+        copy_s = copy_ms * 1e-3 / e2e_steps
+        copy_ceiling = {"value": B_PER_GPU * N * world / copy_s, "unit": "tokens/s",
+                        "h2d_gbs_per_gpu": h2d / copy_s / 1e9, "d2h_gbs_per_gpu": (d2h - H * 4) / copy_s / 1e9,
+                        "what": "pinned cudaMemcpyAsync of the step's inputs and outputs, both directions at once, no kernels",
+                        "numa": numa}
     if not args.no_e2e:
         for _ in range(2):
             e2e_step()
@@ -311,6 +446,8 @@ def main():
             e2e_ms = t.item()
         e2e_value = tokens_per_step * e2e_steps / (e2e_ms * 1e-3)
 
+    extra = None if args.no_extra else run_extras(world, rank, dev, with_cpu=(world == 1 and not args.no_cpu_baseline))
+
     if rank == 0:
         peak, peak_kind = _peaks()
         per_launch = lambda passes: passes * B_PER_GPU * H * N * D * ELEM  # noqa: E731
@@ -326,10 +463,13 @@ def main():
                        "head_dim": D, "sharding": f"batch x heads, {B_PER_GPU * H} (b,h) sequences per GPU, no collective",
                        "l2": "inputs 268 MB + outputs 268 MB per step exceed the 126 MB L2"},
             "clocks": clocks,
-            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "copy_ceiling": copy_ceiling},
             "gpu_launches": 3 * args.steps,
             "roofline": {"bound": "hbm", "kernel": "causal_bwd_kv_kernel", "achieved": achieved, "peak": peak,
-                         "unit": "GB/s", "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                         "unit": "GB/s", "frac": achieved / peak, "traffic": RECORDED_TRAFFIC_BYTES_PER_LAUNCH,
+                         "traffic_source": "recorded: one ncu capture of this kernel at this shape (dram bytes read + "
+                                           "written per launch), not measured by this run",
                          "peak_source": peak_kind, "algorithmic_bytes_per_launch": kv_bytes,
                          "kernel_us": {"causal_tc_kernel<fwd>": t_fwd * 1e3, "causal_tc_kernel<dq>": t_dq * 1e3,
                                        "causal_bwd_kv_kernel": t_kv * 1e3},
@@ -341,7 +481,11 @@ def main():
             line["cpu_baseline"] = {
                 "value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
                 "sample": f"{slices} of {B_PER_GPU * H} (batch,head) slices at N={N}, d={D}, fp32, PyTorch cumsum "
-                          f"formulation + autograd, {secs:.1f} s"}
+                          f"formulation + autograd, {secs:.1f} s (after one untimed warm-up slice)",
+                "config1_forward_s": cpu_config1_forward(threads),
+                "config1": "forward only, fp32, B=2 H=8 N=1024 d=64, the same formulation, whole"}
+        if extra is not None:
+            line["extra"] = extra
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

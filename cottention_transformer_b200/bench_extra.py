@@ -39,9 +39,9 @@ def _time(fn, iters, warmup=5):
     return e0.elapsed_time(e1) / iters * 1e-3  # seconds per call
 
 
-def bench_decode(d, steps, B=64, H=16, use_graph=True):
+def bench_decode(d, steps, B=64, H=16):
     L = _lib.lib()
-    dev = torch.device("cuda")
+    dev = torch.device("cuda", torch.cuda.current_device())
     g = torch.Generator(device=dev).manual_seed(1234)
     nstates = 8  # rotate over several state buffers so that the state does not sit in L2 (8 x 16.8/67 MB)
     states = [torch.zeros(B, H, d, d, device=dev) for _ in range(nstates)]
@@ -64,8 +64,6 @@ def bench_decode(d, steps, B=64, H=16, use_graph=True):
     t = t_eager
     graphed = False
     try:
-        if not use_graph:
-            raise RuntimeError("disabled by --no-graph")
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -140,29 +138,6 @@ def bench_bidir(B=32, H=12, N=512, d=64):
             "kernels_frac": nbytes / (t_f + t_b) / 1e9 / _peak_gbs()[0],
             "tokens_per_s": B * N / t, "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / t / 1e9,
             "peak_gbs": peak, "peak_source": kind, "frac": nbytes / t / 1e9 / peak}
-
-
-def bench_causal_kernels(B, H=16, N=4096, d=64, iters=20):
-    """Each of the three fused kernels on its own, through the C ABI (small-batch profiler runs)."""
-    L = _lib.lib()
-    dev = torch.device("cuda")
-    g = torch.Generator(device=dev).manual_seed(1234)
-    q, k, v, do = (torch.randn(B, H, N, d, device=dev, generator=g).bfloat16() for _ in range(4))
-    out, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
-    nc, dnc = 0.5 * torch.ones(H, device=dev), torch.empty(H, device=dev)
-    st = _lib.stream_ptr(dev)
-    P = lambda t: t.data_ptr()  # noqa: E731
-    fns = {
-        "fwd": lambda: _lib.check(L.cott_cos_attn_fwd(P(q), P(k), P(v), P(nc), P(out), B, H, N, d, d, 3, st), "fwd"),
-        "dq": lambda: _lib.check(L.cott_cos_attn_bwd_dq(P(q), P(k), P(v), P(nc), P(do), P(dq), B, H, N, d, d, 3, st), "dq"),
-        "dkdv": lambda: _lib.check(L.cott_cos_attn_bwd_dkdv(P(q), P(k), P(v), P(nc), P(do), P(dk), P(dv), P(dnc), B, H, N,
-                                                            d, d, 3, st), "dkdv"),
-    }
-    res = {"what": f"fused causal kernels one by one, B={B} H={H} N={N} d={d} bf16"}
-    for name, fn in fns.items():
-        res[name + "_us"] = _time(fn, iters, warmup=3) * 1e6
-    _lib.check_device_status()
-    return res
 
 
 def bench_scan_d128(B=1, H=16, N=16384, d=128):
@@ -262,20 +237,44 @@ def bench_long_context_d128(N, B=1, H=16, d=128, iters=5):
             "peak_source": kind}
 
 
+def bench_prefill_sharded(N, d, world=1, rank=0, iters=3, H=16):
+    """Long-context prefill, forward + backward, B = 1, the H heads split over `world` GPUs (no tensor crosses GPUs:
+    every head is an independent sequence).  The full tensors are generated from one seed and sliced, so every GPU
+    count works on the same data.  Through the public op ``cos_attn_causal`` (head dim 64: fused tensor-core kernels,
+    segment-parallel; head dim 128: row factors around tensor-core scans).  Returns this rank's seconds per step."""
+    from .cos_attention import cos_attn_causal
+    from .sharding import shard_range
+    dev = torch.device("cuda", torch.cuda.current_device())
+    h0, h1 = shard_range(H, world, rank)
+    g = torch.Generator(device=dev).manual_seed(1234 + d)
+    loc = []
+    for i in range(4):  # q, k, v, dout: one full tensor at a time
+        full = torch.randn(1, H, N, d, device=dev, generator=g)
+        if i < 2:
+            full = torch.nn.functional.normalize(full, dim=-1)
+        loc.append(full[:, h0:h1].to(torch.bfloat16).contiguous())
+        del full
+    q, k, v, do = loc
+    q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
+    nc = (0.5 * torch.ones(h1 - h0, device=dev)).requires_grad_()
+
+    def step():
+        q.grad = k.grad = v.grad = nc.grad = None
+        cos_attn_causal(q, k, v, nc).backward(do)
+
+    t = _time(step, iters, warmup=2)
+    _lib.check_device_status()
+    return t
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--causal", type=int, default=0, metavar="B",
-                    help="only time the three fused causal kernels at batch B (H=16, N=4096, d=64)")
     ap.add_argument("--decode-steps", type=int, default=256)
     ap.add_argument("--json", default=None)
     ap.add_argument("--long-context", action="store_true", help="only the B=1 long-sequence prefill sweep")
     ap.add_argument("--scan", action="store_true", help="only the bare scan of the reference's kernel API, per dtype")
     ap.add_argument("--bidir-only", action="store_true", help="only the bidirectional benchmark")
-    ap.add_argument("--no-graph", action="store_true", help="do not replay decode from a CUDA graph (profiler runs)")
     a = ap.parse_args()
-    if a.causal:
-        print(json.dumps(bench_causal_kernels(a.causal)))
-        raise SystemExit(0)
     if a.long_context:
         for n in (16384, 65536, 262144):
             print(json.dumps(bench_long_context(n)))
@@ -289,7 +288,7 @@ if __name__ == "__main__":
     if a.bidir_only:
         print(json.dumps(bench_bidir()))
         raise SystemExit(0)
-    res = [bench_decode(64, a.decode_steps, use_graph=not a.no_graph), bench_decode(128, a.decode_steps, use_graph=not a.no_graph),
+    res = [bench_decode(64, a.decode_steps), bench_decode(128, a.decode_steps),
            bench_bidir()]
     for r in res:
         print(json.dumps(r))

@@ -266,18 +266,21 @@ __device__ __forceinline__ float row_dot_acc(unsigned char* tile, int row, uint3
   return s;
 }
 // tile row <- beta * (64 fp32 accumulator columns) + alpha * (tile row), in place (16-bit, swizzled)
+// (`dst` = the tile that receives the row; by default the row is replaced in place)
 template <typename T, bool kWithRow>
-__device__ __forceinline__ void row_from_acc(unsigned char* tile, int row, uint32_t taddr_lane, float beta, float alpha) {
+__device__ __forceinline__ void row_from_acc(unsigned char* tile, int row, uint32_t taddr_lane, float beta, float alpha,
+                                             unsigned char* dst = nullptr) {
+  if (dst == nullptr) dst = tile;
 #pragma unroll 1
   for (int blk = 0; blk < 4; ++blk) {
     uint32_t r[16];
     ptx::tmem_ld_x16(taddr_lane + 16 * blk, r);
-    uint4* p0 = tile_piece(tile, row, 2 * blk);
-    uint4* p1 = tile_piece(tile, row, 2 * blk + 1);
+    uint4* p0 = tile_piece(dst, row, 2 * blk);
+    uint4* p1 = tile_piece(dst, row, 2 * blk + 1);
     uint4 u = make_uint4(0, 0, 0, 0), w = make_uint4(0, 0, 0, 0);
     if (kWithRow) {
-      u = *p0;
-      w = *p1;
+      u = *tile_piece(tile, row, 2 * blk);
+      w = *tile_piece(tile, row, 2 * blk + 1);
     }
     ptx::tmem_ld_wait();
     float x[16];
@@ -303,15 +306,17 @@ __device__ __forceinline__ void row_from_acc(unsigned char* tile, int row, uint3
 // One pass that does both: returns (tile row) . (64 fp32 accumulator columns) and replaces the tile row by
 // beta * (those columns).  The accumulator is read once, so it can be handed back sooner.
 template <typename T>
-__device__ __forceinline__ float row_from_acc_dot(unsigned char* tile, int row, uint32_t taddr_lane, float beta) {
+__device__ __forceinline__ float row_from_acc_dot(unsigned char* tile, int row, uint32_t taddr_lane, float beta,
+                                                  unsigned char* dst = nullptr) {
+  if (dst == nullptr) dst = tile;
   float s = 0.f;
 #pragma unroll 1
   for (int blk = 0; blk < 4; ++blk) {
     uint32_t r[16];
     ptx::tmem_ld_x16(taddr_lane + 16 * blk, r);
-    uint4* p0 = tile_piece(tile, row, 2 * blk);
-    uint4* p1 = tile_piece(tile, row, 2 * blk + 1);
-    uint4 u = *p0, w = *p1;
+    uint4* p0 = tile_piece(dst, row, 2 * blk);
+    uint4* p1 = tile_piece(dst, row, 2 * blk + 1);
+    uint4 u = *tile_piece(tile, row, 2 * blk), w = *tile_piece(tile, row, 2 * blk + 1);
     ptx::tmem_ld_wait();
     s += dot16<T>(r, u, w);
     u.x = Pack2<T>::pack(beta * __uint_as_float(r[0]), beta * __uint_as_float(r[1]));
@@ -437,13 +442,16 @@ constexpr int kTcStagesFwd = 4;  // the forward kernel has the shared memory for
 
 // EXT = false compiles the segment / padding arguments away (they must be null / one segment): these kernels are
 // sensitive to every instruction added to their loops, and the common case needs neither.
-template <typename T, int MODE, bool EXT>
+// SAVE (forward only): the 16-bit state operand of every chunk -- the state BEFORE the chunk, [64 x 64], rows d_k --
+// is also written to `saved` ([B*H][chunks of the sequence][64][64], row-major), for the one-pass backward.
+template <typename T, int MODE, bool EXT, bool SAVE = false>
 __global__ void __launch_bounds__(kTcThreads, 1)
 causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapY,
                  const __grid_constant__ CUtensorMap mapZ, const __grid_constant__ CUtensorMap mapQ,
                  const __grid_constant__ CUtensorMap mapOut, const float* __restrict__ norm_const, int H, int N,
                  const float* __restrict__ init_state_arg, int chunks_per_seg_arg,
-                 const unsigned char* __restrict__ keep_arg, const int* __restrict__ count_arg) {
+                 const unsigned char* __restrict__ keep_arg, const int* __restrict__ count_arg,
+                 uint4* __restrict__ saved = nullptr) {
   using namespace ptx;
   // Shared memory: NS stages of the tiles that are only read (forward: Y, Z; dQ: X, Y, Z), a ring of
   // NS + 1 tiles for the tile that doubles as the output staging buffer (forward: X; dQ: q), the 16-bit
@@ -672,6 +680,11 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       fence_proxy_async_smem();
       tc_fence_before_sync();
       warp_arrive(&bar_init, lane);
+      if (SAVE && lane < 16) {  // the state before the segment's first chunk, as the operand buffer holds it
+        uint4* dst = saved + ((static_cast<size_t>(bh) * total_chunks + chunk0) * kTcD + 16 * wq + lane) * 8;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dst[j] = *tile_piece(sS, 16 * wq + lane, j);
+      }
     }
     for (int c = 0; c + 1 < nchunks; ++c) {
       // S after chunk c -> 16-bit operand for chunk c+1 (buffer (c+1)&1)
@@ -707,6 +720,11 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       }
       fence_proxy_async_smem();
       warp_arrive(&bar_state[c & 1], lane);
+      if (SAVE && lane < 16) {  // after the hand-off: the stores are off the loop that sets the chunk period
+        uint4* dst = saved + ((static_cast<size_t>(bh) * total_chunks + chunk0 + c + 1) * kTcD + 16 * wq + lane) * 8;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dst[j] = *tile_piece(sS + ((c + 1) & 1) * (kTcD * 128), 16 * wq + lane, j);
+      }
     }
   } else if ((warp >= 15 && warp < 19) || warp >= 24) {
     // ---------------------------------------------------------------- operand groups (even / odd chunks)

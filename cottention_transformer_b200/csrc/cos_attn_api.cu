@@ -1,5 +1,6 @@
 // C ABI of the fused cosine-attention operators (tensor-core path).
 #include "bidir_tc.cuh"
+#include "causal_bwd_fused.cuh"
 #include "causal_seg.cuh"
 #include "causal_tc.cuh"
 #include "common.cuh"
@@ -60,7 +61,7 @@ SegPlan plan_segments(int N, int nseg_requested) {
 
 template <typename T>
 int launch_fwd(const void* q, const void* k, const void* v, const float* nc, void* out, int B, int H, int N,
-               int dtype, cudaStream_t stream, const float* init = nullptr, SegPlan plan = SegPlan()) {
+               int dtype, cudaStream_t stream, const float* init = nullptr, SegPlan plan = SegPlan(), void* saved = nullptr) {
   const long BH = (long)B * H;
   CUtensorMap mq, mk, mv, mo;
   int st;
@@ -68,11 +69,13 @@ int launch_fwd(const void* q, const void* k, const void* v, const float* nc, voi
       (st = tmap(&mo, out, dtype, B, H, N, out_strides(plan, H, N))))
     return st;
   const bool ext = plan.nseg > 1 || init || plan.keep;
-  auto kern = ext ? causal_tc_kernel<T, kModeFwd, true> : causal_tc_kernel<T, kModeFwd, false>;
+  auto kern = saved ? (ext ? causal_tc_kernel<T, kModeFwd, true, true> : causal_tc_kernel<T, kModeFwd, false, true>)
+                    : (ext ? causal_tc_kernel<T, kModeFwd, true, false> : causal_tc_kernel<T, kModeFwd, false, false>);
   const size_t smem = causal_tc_smem_bytes(kModeFwd);
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   if (plan.cps == 0) plan.cps = plan_segments(N, 1).cps;
-  kern<<<dim3((unsigned)BH, plan.nseg), kTcThreads, smem, stream>>>(mq, mk, mv, mq, mo, nc, H, N, init, plan.cps, plan.keep, plan.count);
+  kern<<<dim3((unsigned)BH, plan.nseg), kTcThreads, smem, stream>>>(mq, mk, mv, mq, mo, nc, H, N, init, plan.cps, plan.keep, plan.count,
+                                                                   static_cast<uint4*>(saved));
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
@@ -92,7 +95,7 @@ int launch_bwd_dq(const void* q, const void* k, const void* v, const float* nc, 
   const size_t smem = causal_tc_smem_bytes(kModeDq);
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   if (plan.cps == 0) plan.cps = plan_segments(N, 1).cps;
-  kern<<<dim3((unsigned)BH, plan.nseg), kTcThreads, smem, stream>>>(md, mv, mk, mq, mo, nc, H, N, init, plan.cps, plan.keep, plan.count);
+  kern<<<dim3((unsigned)BH, plan.nseg), kTcThreads, smem, stream>>>(md, mv, mk, mq, mo, nc, H, N, init, plan.cps, plan.keep, plan.count, nullptr);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
@@ -115,6 +118,34 @@ int launch_bwd_dkdv(const void* q, const void* k, const void* v, const float* nc
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   if (plan.cps == 0) plan.cps = plan_segments(N, 1).cps;
   kern<<<dim3((unsigned)BH, plan.nseg), kKvThreads, smem, stream>>>(mq, mk, mv, md, mdk, mdv, dnorm, nc, H, N, init, plan.cps, plan.keep, plan.count);
+  COTT_CUDA_TRY(cudaGetLastError());
+  return COTT_OK;
+}
+
+// The one-pass backward: `saved` holds the forward's 16-bit state before every chunk ([B*H][chunks][64][64]).
+template <typename T>
+int launch_bwd_fused(const void* q, const void* k, const void* v, const float* nc, const void* dout, const void* saved,
+                     void* dq, void* dk, void* dv, float* dnorm, int B, int H, int N, int dtype, cudaStream_t stream,
+                     const float* init = nullptr, SegPlan plan = SegPlan()) {
+  const long BH = (long)B * H;
+  const long rows = (long)((N + kTcChunk - 1) / kTcChunk) * kTcD;  // state rows per (b, h)
+  CUtensorMap mq, mk, mv, md, ms, mdq, mdk, mdv;
+  int st;
+  if ((st = tmap(&mq, q, dtype, B, H, N, in_strides(plan, H, N))) || (st = tmap(&mk, k, dtype, B, H, N, in_strides(plan, H, N))) ||
+      (st = tmap(&mv, v, dtype, B, H, N, in_strides(plan, H, N))) || (st = tmap(&md, dout, dtype, B, H, N, out_strides(plan, H, N))) ||
+      (st = tmap(&mdq, dq, dtype, B, H, N, in_strides(plan, H, N))) || (st = tmap(&mdk, dk, dtype, B, H, N, in_strides(plan, H, N))) ||
+      (st = tmap(&mdv, dv, dtype, B, H, N, in_strides(plan, H, N))))
+    return st;
+  int r = make_tmap_rows64(&ms, saved, dtype == COTT_BF16, B, H, rows, contiguous_bhnd(H, rows), kTcD);
+  if (r) return fail(COTT_ERR_CUDA, "cuTensorMapEncodeTiled failed for the saved states: %d", r);
+  COTT_CUDA_TRY(cudaMemsetAsync(dnorm, 0, sizeof(float) * H, stream));
+  const bool ext = plan.nseg > 1 || init || plan.keep;
+  auto kern = ext ? causal_bwd_fused_kernel<T, true> : causal_bwd_fused_kernel<T, false>;
+  const size_t smem = causal_bwd_fused_smem_bytes();
+  COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  if (plan.cps == 0) plan.cps = plan_segments(N, 1).cps;
+  kern<<<dim3((unsigned)BH, plan.nseg), kBwThreads, smem, stream>>>(mq, mk, mv, md, ms, mdq, mdk, mdv, dnorm, nc, H, N, init, plan.cps,
+                                                                   plan.keep, plan.count);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
@@ -148,7 +179,8 @@ void apply_layout(SegPlan& plan, const cott_layout* l) {
 
 template <typename T>
 int run_fwd_seg(const void* q, const void* k, const void* v, const unsigned char* keep, const float* nc, void* out,
-                float* ws, int nseg, const cott_layout* layout, int B, int H, int N, int dtype, cudaStream_t stream) {
+                float* ws, int nseg, const cott_layout* layout, int B, int H, int N, int dtype, cudaStream_t stream,
+                void* saved = nullptr) {
   SegPlan plan = plan_segments(N, nseg);
   apply_layout(plan, layout);
   const size_t A = seg_array_floats(B, H, plan.nseg);
@@ -159,12 +191,12 @@ int run_fwd_seg(const void* q, const void* k, const void* v, const unsigned char
     plan.keep = keep;
     plan.count = count;
   }
-  if (plan.nseg == 1) return launch_fwd<T>(q, k, v, nc, out, B, H, N, dtype, stream, nullptr, plan);
+  if (plan.nseg == 1) return launch_fwd<T>(q, k, v, nc, out, B, H, N, dtype, stream, nullptr, plan, saved);
   int st = launch_seg_state<T, kSegFwdState>(k, v, in_strides(plan, H, N), in_strides(plan, H, N), nc, ws, B, H, N, dtype, plan, stream);
   if (st) return st;
   seg_scan_kernel<<<(unsigned)((long)B * H), 256, 0, stream>>>(ws, ws + A, ws + 2 * A, nullptr, plan.nseg);
   COTT_CUDA_TRY(cudaGetLastError());
-  return launch_fwd<T>(q, k, v, nc, out, B, H, N, dtype, stream, ws + A, plan);
+  return launch_fwd<T>(q, k, v, nc, out, B, H, N, dtype, stream, ws + A, plan, saved);
 }
 
 template <typename T>
@@ -231,6 +263,27 @@ __global__ void __launch_bounds__(128, 1) wait_selftest_kernel(int polls, int co
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, 32);
+}
+
+template <typename T>
+int run_bwd_train(const void* q, const void* k, const void* v, const unsigned char* keep, const float* nc, const void* dout,
+                  const void* saved, float* ws, int nseg, const cott_layout* layout, void* dq, void* dk, void* dv, float* dnorm,
+                  int B, int H, int N, int dtype, cudaStream_t stream) {
+  SegPlan plan = plan_segments(N, nseg);
+  apply_layout(plan, layout);
+  const size_t A = seg_array_floats(B, H, plan.nseg);
+  if (keep) {  // the forward call left the running count in the workspace
+    plan.keep = keep;
+    plan.count = reinterpret_cast<const int*>(ws + 5 * A);
+  }
+  if (plan.nseg == 1) return launch_bwd_fused<T>(q, k, v, nc, dout, saved, dq, dk, dv, dnorm, B, H, N, dtype, stream, nullptr, plan);
+  // reverse states of the segments and their exclusive suffix; the prefix states come from `saved`
+  int st = launch_seg_state<T, kSegRevState>(q, dout, in_strides(plan, H, N), out_strides(plan, H, N), nc, ws + 3 * A, B, H, N, dtype, plan,
+                                             stream);
+  if (st) return st;
+  seg_scan_kernel<<<(unsigned)((long)B * H), 256, 0, stream>>>(ws + 3 * A, nullptr, nullptr, ws + 4 * A, plan.nseg);
+  COTT_CUDA_TRY(cudaGetLastError());
+  return launch_bwd_fused<T>(q, k, v, nc, dout, saved, dq, dk, dv, dnorm, B, H, N, dtype, stream, ws + 4 * A, plan);
 }
 
 int check_ptrs16(std::initializer_list<std::pair<const void*, const char*>> ps) {
@@ -321,7 +374,7 @@ int launch_scan_tc_t(const void* q, const void* k, const void* v, void* out, int
   const size_t smem = causal_tc_smem_bytes(kModeScan);
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   kern<<<dim3((unsigned)((long)B * H), plan.nseg), kTcThreads, smem, stream>>>(mq, mk, mv, mq, mo, nullptr, H, N, init, plan.cps, nullptr,
-                                                                              nullptr);
+                                                                              nullptr, nullptr);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
@@ -555,6 +608,53 @@ int cott_cos_attn_bwd_seg(const void* q, const void* k, const void* v, const uns
   return dtype == COTT_BF16
              ? run_bwd_seg<__nv_bfloat16>(q, k, v, keep, norm_const, dout, ws, nseg, layout, dq, dk, dv, dnorm_const, B, H, N, dtype, s)
              : run_bwd_seg<__half>(q, k, v, keep, norm_const, dout, ws, nseg, layout, dq, dk, dv, dnorm_const, B, H, N, dtype, s);
+}
+
+size_t cott_cos_attn_saved_bytes(int B, int H, int N) {
+  if (B <= 0 || H <= 0 || N <= 0) return 0;
+  return (size_t)B * H * ((N + kTcChunk - 1) / kTcChunk) * kStateTileBytes;
+}
+
+int cott_cos_attn_fwd_train(const void* q, const void* k, const void* v, const unsigned char* keep,
+                            const float* norm_const, void* out, void* saved, void* workspace, int nseg,
+                            const cott_layout* layout, int B, int H, int N, int Dk, int Dv, int dtype, void* stream) {
+  int st = check_fused_args(B, H, N, Dk, Dv, dtype);
+  if (st) return st;
+  if ((long)B * H * N == 0) return COTT_OK;
+  if ((st = check_ptrs16({{q, "q"}, {k, "k"}, {v, "v"}, {out, "out"}, {saved, "saved"}}))) return st;
+  if (!norm_const) return fail(COTT_ERR_NULL, "null pointer: norm_const");
+  if ((nseg > 1 || keep) && (st = check_ptrs16({{workspace, "workspace"}}))) return st;
+  DeviceScope scope(q);
+  COTT_CUDA_TRY(scope.status());
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  float* ws = static_cast<float*>(workspace);
+  return dtype == COTT_BF16 ? run_fwd_seg<__nv_bfloat16>(q, k, v, keep, norm_const, out, ws, nseg, layout, B, H, N, dtype, s, saved)
+                            : run_fwd_seg<__half>(q, k, v, keep, norm_const, out, ws, nseg, layout, B, H, N, dtype, s, saved);
+}
+
+int cott_cos_attn_bwd_train(const void* q, const void* k, const void* v, const unsigned char* keep,
+                            const float* norm_const, const void* dout, const void* saved, void* workspace, int nseg,
+                            const cott_layout* layout, void* dq, void* dk, void* dv, float* dnorm_const, int B, int H,
+                            int N, int Dk, int Dv, int dtype, void* stream) {
+  int st = check_fused_args(B, H, N, Dk, Dv, dtype);
+  if (st) return st;
+  if (!dnorm_const && H > 0) return fail(COTT_ERR_NULL, "null pointer: dnorm_const");
+  if ((long)B * H * N == 0) {
+    if (H > 0) COTT_CUDA_TRY(cudaMemsetAsync(dnorm_const, 0, sizeof(float) * H, static_cast<cudaStream_t>(stream)));
+    return COTT_OK;
+  }
+  if ((st = check_ptrs16({{q, "q"}, {k, "k"}, {v, "v"}, {dout, "dout"}, {dq, "dq"}, {dk, "dk"}, {dv, "dv"}, {saved, "saved"}})))
+    return st;
+  if (!norm_const) return fail(COTT_ERR_NULL, "null pointer: norm_const");
+  if ((nseg > 1 || keep) && (st = check_ptrs16({{workspace, "workspace"}}))) return st;
+  DeviceScope scope(q);
+  COTT_CUDA_TRY(scope.status());
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  float* ws = static_cast<float*>(workspace);
+  return dtype == COTT_BF16 ? run_bwd_train<__nv_bfloat16>(q, k, v, keep, norm_const, dout, saved, ws, nseg, layout, dq, dk, dv,
+                                                           dnorm_const, B, H, N, dtype, s)
+                            : run_bwd_train<__half>(q, k, v, keep, norm_const, dout, saved, ws, nseg, layout, dq, dk, dv, dnorm_const,
+                                                    B, H, N, dtype, s);
 }
 
 int cott_cos_attn_prefill_state(const void* k, const void* v, const float* norm_const, float* state, void* workspace,

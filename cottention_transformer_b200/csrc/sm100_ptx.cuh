@@ -98,6 +98,14 @@ __device__ __forceinline__ void tma_load_tile(void* smem_dst, const CUtensorMap*
       "r"(b)
       : "memory");
 }
+// The same box fetched into L2 only (no shared-memory destination, nothing to wait for): a later tma_load_tile of
+// it is served from L2.
+__device__ __forceinline__ void tma_prefetch_tile(const CUtensorMap* map, int y, int h, int b) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(0), "r"(y), "r"(h), "r"(b)
+               : "memory");
+}
 // 4-D tiled store shared -> global (bulk group completion).  Never start at a negative coordinate.
 __device__ __forceinline__ void tma_store_tile(const CUtensorMap* map, const void* smem_src, int y, int h, int b) {
   asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(

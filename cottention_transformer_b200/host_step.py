@@ -82,6 +82,28 @@ class CausalHostStep:
             g.replay()
         return self.dnc_sum
 
+    def copy_only(self, host_in, host_out):
+        """The copies of a step without its kernels: the four inputs host -> device on one stream and four
+        tensors of the same size device -> host on another, at the same time, as whole-tensor copies.  What this
+        takes is the floor of ``__call__`` on this host: the step can at best hide its kernels behind it."""
+        cur = torch.cuda.current_stream(self.device)
+        start = torch.cuda.Event()
+        start.record(cur)
+        with torch.cuda.stream(self.s_in):
+            self.s_in.wait_event(start)
+            for d, h in zip(self.dev[:4], host_in):
+                d.copy_(h, non_blocking=True)
+            e_in = torch.cuda.Event()
+            e_in.record(self.s_in)
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_event(start)
+            for h, d in zip(host_out, self.dev[4:]):
+                h.copy_(d, non_blocking=True)
+            e_out = torch.cuda.Event()
+            e_out.record(self.s_out)
+        cur.wait_event(e_in)
+        cur.wait_event(e_out)
+
     def _issue(self, host_in, host_out):
         B, H, N, D = self.shape
         L, P = _lib.lib(), _lib.ptr

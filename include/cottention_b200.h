@@ -147,6 +147,32 @@ int cott_cos_attn_bwd_seg(const void* q, const void* k, const void* v, const uns
                           int H, int N, int Dk, int Dv, int dtype, void* stream);
 
 /*
+ * Training pair: forward that keeps what a ONE-pass backward needs, and that backward.
+ *
+ * cott_cos_attn_fwd_train is cott_cos_attn_fwd_seg (same arguments, same `out`) that also writes `saved`: the
+ * 16-bit state operand of every 128-position chunk, i.e. sum_{s < chunk} k_s (x) v'_s / |k_s| as the forward's
+ * tensor-core products consume it ([B*H][ceil(N/128)][64][64] elements of `dtype`, cott_cos_attn_saved_bytes(B, H, N)
+ * bytes = half the size of q; device memory, 16-byte aligned).  cott_cos_attn_bwd_train takes q, k, v, dout and
+ * `saved`, untouched, and produces dq, dk, dv, dnorm_const in a single reverse walk over the sequence: every input
+ * tensor is read once (7.5 tensor passes against the 11 of cott_cos_attn_bwd, whose two kernels walk in opposite
+ * directions and each read q, k, v, dout).  Same results as cott_cos_attn_bwd up to rounding.
+ * `workspace` is only needed (and only touched) when nseg > 1 or keep != NULL; pass the same buffer to both calls.
+ *
+ * Replaces CustomAttention.forward / .backward (Cuda_Kernel/Custom_Kernel.py:9-30,35-141) with the module math of
+ * GPTCosAttention.py:229-248 around them, as cott_cos_attn_fwd / _bwd do.  The reference's own sketch of a merged
+ * backward (Cuda_Kernel/backwardv2_comb.cu:58-149, not built by its setup.py) is the closest counterpart.
+ */
+size_t cott_cos_attn_saved_bytes(int B, int H, int N);
+int cott_cos_attn_fwd_train(const void* q, const void* k, const void* v, const unsigned char* keep,
+                            const float* norm_const, void* out, void* saved, void* workspace, int nseg,
+                            const cott_layout* layout, int B, int H, int N, int Dk, int Dv, int dtype,
+                            void* stream);
+int cott_cos_attn_bwd_train(const void* q, const void* k, const void* v, const unsigned char* keep,
+                            const float* norm_const, const void* dout, const void* saved, void* workspace,
+                            int nseg, const cott_layout* layout, void* dq, void* dk, void* dv,
+                            float* dnorm_const, int B, int H, int N, int Dk, int Dv, int dtype, void* stream);
+
+/*
  * Prefill -> decode hand-off: the decode state (cott_decode_step layout, float32 [B,H,Dv,Dk]) that a prompt of N
  * tokens at positions 1..N leaves behind, state[b,h,j,i] = sum_s v'_s[j] k^_s[i], computed with the segment-state
  * kernels instead of N recurrent steps (the reference absorbs a prompt token by token, GPTCosAttention.py:253-272).

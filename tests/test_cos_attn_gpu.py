@@ -55,6 +55,50 @@ def test_fused_forward_backward_matches_oracle(dt, shape, normalized, segments):
 
 
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(1, 1, 128), (1, 2, 1), (2, 3, 100), (1, 2, 129), (2, 2, 640), (1, 1, 1000), (2, 16, 2048)])
+@pytest.mark.parametrize("segments", [1, 3])
+@pytest.mark.parametrize("masked", [False, True])
+def test_one_pass_backward_matches_oracle(dt, shape, segments, masked):
+    """cott_cos_attn_fwd_train / _bwd_train (the forward keeps its 16-bit chunk states, the backward is one reverse
+    walk that reads every tensor once) against the fp64 oracle on the same rounded inputs, with and without a
+    padding mask and segments; the forward output is bit-identical to the plain forward's."""
+    from cottention_transformer_b200 import cos_attn_causal, _lib
+    B, H, N = shape
+    q, k, v, do, _ = O.make_inputs(B, H, N, 64, 64, seed=5 * N + H, normalize=False, dtype=dt)
+    nc = torch.linspace(-1.0, 1.5, H)
+    keep = None
+    if masked:
+        if N < 8:
+            pytest.skip("nothing would be left un-masked")
+        keep = torch.ones(B, N, dtype=torch.bool)
+        keep[0, (2 * N) // 3:] = False
+        keep[-1, : N // 4] = False
+    qd, kd, vd = (t.double().requires_grad_() for t in (q, k, v))
+    ncd = nc.double().requires_grad_()
+    ref = O.cos_attn_causal(qd, kd, vd, ncd, keep)
+    (ref * do.double()).sum().backward()
+    qc, kc, vc = (t.cuda().requires_grad_() for t in (q, k, v))
+    ncc = nc.cuda().requires_grad_()
+    kc_ = None if keep is None else keep.cuda()
+    out = cos_attn_causal(qc, kc, vc, ncc, kc_, segments=segments, one_pass_backward=True)
+    out.backward(do.cuda())
+    _lib.check_device_status()
+    with torch.no_grad():
+        assert torch.equal(out, cos_attn_causal(qc, kc, vc, ncc, kc_, segments=segments))
+    for name, a, r in (("out", out, ref.detach()), ("dq", qc.grad, qd.grad), ("dk", kc.grad, kd.grad), ("dv", vc.grad, vd.grad)):
+        e_max, e_fro = _rel(a, r)
+        assert e_max <= REL16 and e_fro <= REL16, (name, e_max, e_fro)
+    # The norm_const gradient is -sigma (1 - sigma) sum_s ln(n_s) eps_s with eps_s = v'_s . dv'_s = v_s . dv_s, a sum
+    # of terms of both signs (in the smallest masked shapes a few dozen that nearly cancel): its 16-bit error is
+    # measured against the sum of the magnitudes of its terms.
+    n = (torch.ones(B, N, dtype=torch.bool) if keep is None else keep).to(torch.int64).cumsum(-1).clamp(min=1).double()
+    sig = torch.sigmoid(nc.double())
+    terms = (torch.log(n).view(B, 1, N) * (vd.detach() * vd.grad).sum(-1)).abs().sum(dim=(0, 2)) * sig * (1 - sig)
+    e = (ncc.grad.double().cpu() - ncd.grad).abs()
+    assert (e <= REL16 * terms.clamp(min=1e-3)).all(), (e, terms, ncd.grad)
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("d", [128, 256])
 @pytest.mark.parametrize("masked", [False, True])
 def test_wide_heads_run_on_tensor_core_scans(dt, d, masked):
@@ -207,6 +251,35 @@ def test_fused_with_padding_mask_matches_oracle(dt, shape, segments):
 
 
 @pytest.mark.parametrize("shape,segments", [((8, 16, 4096), 1), ((1, 16, 16384), 9), ((2, 3, 1000), 3)])
+def test_one_pass_backward_repeated_cold_launches(shape, segments):
+    """The one-pass backward under the same cold-pipeline stress as the two-kernel one (every kernel synchronised
+    before the next starts, 30 times): no wait gives up, results bit-identical from run to run."""
+    from cottention_transformer_b200 import _lib
+    B, H, N = shape
+    L = _lib.lib()
+    g = torch.Generator(device="cuda").manual_seed(6)
+    q, k, v, do = (torch.randn(B, H, N, 64, device="cuda", generator=g).bfloat16() for _ in range(4))
+    nc, dnc = 0.5 * torch.ones(H, device="cuda"), torch.zeros(H, device="cuda")
+    out, dq, dk, dv = (torch.zeros_like(q) for _ in range(4))
+    ws = torch.empty(max(L.cott_cos_attn_seg_workspace_bytes(B, H, N, segments), 16), dtype=torch.uint8, device="cuda")
+    saved = torch.empty(L.cott_cos_attn_saved_bytes(B, H, N), dtype=torch.uint8, device="cuda")
+    st, P = _lib.stream_ptr(q.device), (lambda t: t.data_ptr())
+    first = None
+    for _ in range(30):
+        _lib.check(L.cott_cos_attn_fwd_train(P(q), P(k), P(v), None, P(nc), P(out), P(saved), P(ws), segments, None, B, H, N, 64, 64, 3, st), "fwd")
+        torch.cuda.synchronize()
+        _lib.check(L.cott_cos_attn_bwd_train(P(q), P(k), P(v), None, P(nc), P(do), P(saved), P(ws), segments, None, P(dq), P(dk), P(dv),
+                                             P(dnc), B, H, N, 64, 64, 3, st), "bwd")
+        torch.cuda.synchronize()
+        _lib.check_device_status()
+        cur = [t.clone() for t in (out, dq, dk, dv)]
+        if first is None:
+            first = cur
+        else:
+            assert all(torch.equal(a, b) for a, b in zip(cur, first))
+
+
+@pytest.mark.parametrize("shape,segments", [((8, 16, 4096), 1), ((1, 16, 16384), 9), ((2, 3, 1000), 3)])
 def test_repeated_cold_launches_give_identical_results(shape, segments):
     """Every kernel synchronised before the next one starts (cold pipelines: the condition under which a role
     that skipped a barrier phase once ran ahead), 40 times: no wait gives up and the results are bit-identical."""
@@ -299,3 +372,23 @@ def test_rotary_packed_matches_rotate_every_two(dt, d, rot, per_batch):
     assert (y.float() - ref).abs().max().item() <= 4 * tol
     # the backward rounds the fp32 gradient to 16 bits before rotating it back
     assert (x.grad.float() - xr.grad).abs().max().item() <= 8 * tol * w.abs().max().item()
+
+
+def test_rotary_backward_leaves_a_shared_gradient_alone():
+    """The rotated tensor and another tensor are summed: autograd hands the SAME gradient tensor to both branches.
+    The rotary backward works in place, so it must do so on a private copy -- the other branch has to receive the
+    un-rotated gradient."""
+    from cottention_transformer_b200 import rotary_packed_
+    B, N, H, d = 2, 64, 2, 64
+    g = torch.Generator(device="cuda").manual_seed(9)
+    x = torch.randn(B, N, 3 * H * d, device="cuda", generator=g).bfloat16().requires_grad_()
+    other = torch.randn(B, N, 3 * H * d, device="cuda", generator=g).bfloat16().requires_grad_()
+    ang = torch.arange(N, device="cuda").float()[:, None] / (10000 ** (torch.arange(0, d, 2, device="cuda").float() / d))
+    y = rotary_packed_(x * 1, torch.sin(ang), torch.cos(ang), heads=H)
+    w = torch.randn(B, N, 3 * H * d, device="cuda", generator=g).bfloat16()
+    (y + other).backward(w)
+    assert torch.equal(other.grad, w)
+    # and the rotated branch still gets the transposed rotation: q and k slices differ from w, v passes through
+    gx = x.grad.view(B, N, 3, H, d)
+    assert torch.equal(gx[:, :, 2], w.view(B, N, 3, H, d)[:, :, 2])
+    assert not torch.equal(gx[:, 1:, 0], w.view(B, N, 3, H, d)[:, 1:, 0])

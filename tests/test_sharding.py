@@ -81,10 +81,20 @@ def _failing_worker(rank, world, port):
     dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
     if rank == 1:
         os._exit(0)  # leaves between steps, nothing in flight
+    entered = []
+    real_all_reduce = dist.all_reduce
+
+    def spy(*a, **kw):
+        entered.append(True)
+        return real_all_reduce(*a, **kw)
+
+    dist.all_reduce = spy
     try:
         sharding.reduce_dnorm_const(torch.ones(4, dtype=torch.float64), 2, 4, world, rank)
+    except (RuntimeError, dist.DistBackendError):
+        os._exit(0 if entered else 4)  # 0: the collective was entered and ended with a distributed error
     except Exception:
-        os._exit(0)
+        os._exit(5)  # anything else (argument, shape, import errors) is a bug, not the lost rank
     os._exit(3)  # the collective must not succeed without its peer
 
 
@@ -95,4 +105,4 @@ def test_lost_rank_surfaces_as_an_error_not_a_hang():
     [p.start() for p in procs]
     [p.join(timeout=60) for p in procs]
     assert all(not p.is_alive() for p in procs), "a rank hung"
-    assert procs[0].exitcode == 0
+    assert procs[0].exitcode == 0, f"exit code {procs[0].exitcode}: 3 = the collective succeeded, 4 = error before it, 5 = other error"
