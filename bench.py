@@ -20,7 +20,9 @@ Keys beyond the basic contract:
   extra      secondary workloads, each with its own algorithmic bytes, device time and fraction of the HBM peak:
              ``prefill_long`` (B=1, H=16 heads split over the ranks, N in {16k, 64k, 256k}, d in {64, 128}, fwd+bwd)
              and ``decode`` (batch 64 per GPU, 4096 single-token steps, fp32 state, d in {64, 128}) with the
-             reference's CPU recurrent loop timed beside it; ``--no-extra`` skips them
+             reference's CPU recurrent loop timed beside it, and ``train`` (whole-model bf16 training steps of a
+             GPT-style decoder and a BERT-base encoder with the op inside, DDP when there are several ranks);
+             ``--no-extra`` skips them
 
 ``--impl reference`` times that CPU formulation alone, with all host threads, as the reference arm; when the
 reference's CUDA extension has been built into oracle/_ref it also reports, under ``reference_cuda_kernel``, what that
@@ -231,7 +233,13 @@ def run_extras(world, rank, dev, with_cpu):
             row["cpu_baseline"] = {"value": cpu_decode_sample(d, threads), "unit": "tokens/s", "cores": threads, "kind": "port",
                                    "sample": "200 tokens at batch 1, float64 state, the reference's per-token torch loop"}
         decode.append(row)
+    # whole-model training steps around the op (synthetic token ids, random weights; DDP over NCCL when world > 1)
+    from cottention_transformer_b200 import bench_train as T
+    train = [T.run_model(name, steps=4, warmup=2) for name in ("gpt", "bert")]
     return {"peak_gbs": peak, "peak_source": kind,
+            "train": {"what": "whole-model bf16 training step with the op inside (GPT-style decoder 24 x 1024, 16 heads, seq 1024, "
+                              "batch 8 per GPU; BERT-base encoder, seq 512, batch 32 per GPU), DDP gradient all-reduce over NCCL",
+                      "scaling": "weak", "rows": train},
             "prefill_long": {"what": "causal fwd+bwd, B=1, H=16 heads split evenly over the GPUs (no collective), bf16; "
                                      "frac = algorithmic bytes / time / (GPUs x HBM peak)", "scaling": "strong",
                              "rows": prefill},
