@@ -74,9 +74,31 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+BINDING = os.path.join(PKG, "cott_torch_binding.so")
+
+
+def build_torch_binding(force: bool = False, verbose: bool = False) -> str:
+    """Compile ``csrc_torch/torch_binding.cpp`` (host C++ only: the compiled torch binding over the C ABI) next to the
+    library it links, ``cott_torch_binding.so``.  Needs the library itself to exist."""
+    src = os.path.join(PKG, "csrc_torch", "torch_binding.cpp")
+    hdr = os.path.join(PKG, "..", "include", "cottention_b200.h")
+    if not force and os.path.exists(BINDING) and os.path.getmtime(BINDING) >= max(os.path.getmtime(src), os.path.getmtime(hdr)):
+        return BINDING
+    build(force=False)
+    from torch.utils.cpp_extension import load
+    bld = os.path.join(OBJ, "torch_binding")
+    os.makedirs(bld, exist_ok=True)
+    os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")  # no device code here; silences the arch probe on CPU-only hosts
+    load(name="cott_torch_binding", sources=[src], build_directory=bld, with_cuda=True, is_python_module=False, verbose=verbose,
+         extra_cflags=["-O2"], extra_ldflags=[f"-L{PKG}", "-l:libcottention_b200.so", "-Wl,-rpath,'$$ORIGIN'", "-Wl,-rpath,'$$ORIGIN/../..'"])  # ($$: ninja's escape for a literal $)
+    shutil.copy2(os.path.join(bld, "cott_torch_binding.so"), BINDING)
+    return BINDING
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("-v", "--verbose", action="store_true")
     a = ap.parse_args()
     print(build(a.force, a.verbose))
+    print(build_torch_binding(a.force, a.verbose))

@@ -22,7 +22,7 @@ import ctypes
 
 import torch
 
-from . import _lib
+from . import _binding, _lib
 from .custom_kernel import CustomAttention
 
 FUSED_DTYPES = (torch.float16, torch.bfloat16)
@@ -41,6 +41,16 @@ class _FusedCausal(torch.autograd.Function):
     def forward(ctx, q, k, v, norm_const, segments=None, keep=None, one_pass=False):
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         B, H, N, D = q.shape
+        ops = _binding.ops()
+        if ops is not None:  # one dispatcher call: validation, allocation and the launch happen in C++
+            kp = None if keep is None else keep.to(device=q.device, dtype=torch.uint8).contiguous()
+            nseg = 0 if segments is None else int(segments)
+            out, ws, saved = ops.causal_fwd(q, k, v, norm_const.detach(), kp, nseg, bool(one_pass))
+            ctx.save_for_backward(q, k, v, norm_const.detach())
+            ctx.ws, ctx.nseg, ctx.kp, ctx.saved, ctx.compiled = ws, nseg, kp, saved, True
+            ctx.nc_shape, ctx.nc_dtype = norm_const.shape, norm_const.dtype
+            return out
+        ctx.compiled = False
         nc = norm_const.detach().reshape(-1).to(device=q.device, dtype=torch.float32).contiguous()
         if nc.numel() != H:
             raise RuntimeError(f"norm_const must have one entry per head ({H}), got {nc.numel()}")
@@ -76,6 +86,9 @@ class _FusedCausal(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout):
         q, k, v, nc = ctx.saved_tensors
+        if ctx.compiled:
+            dq, dk, dv, dnc = _binding.ops().causal_bwd(q, k, v, nc, ctx.kp, dout, ctx.ws, ctx.saved, ctx.nseg)
+            return dq, dk, dv, dnc.reshape(ctx.nc_shape).to(ctx.nc_dtype), None, None, None
         dout = dout.contiguous().to(q.dtype)
         B, H, N, D = q.shape
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
@@ -313,6 +326,15 @@ class _Bidirectional(torch.autograd.Function):
         q, k, v = q.contiguous(), k.to(q.dtype).contiguous(), v.to(q.dtype).contiguous()
         B, H, N, Dk = q.shape
         Dv = v.shape[-1]
+        ops = _binding.ops()
+        ctx.compiled = ops is not None
+        if ops is not None:
+            kp = None if keep is None else keep.to(device=q.device, dtype=torch.uint8).contiguous()
+            out, scratch = ops.bidir_fwd(q, k, v, norm_const.detach(), kp)
+            ctx.save_for_backward(q, k, v, norm_const.detach(), scratch)
+            ctx.kp = kp
+            ctx.nc_shape, ctx.nc_dtype = norm_const.shape, norm_const.dtype
+            return out
         L = _lib.lib()
         code = _lib.DTYPE_CODE[q.dtype]
         nc = norm_const.detach().reshape(-1).to(device=q.device, dtype=torch.float32).contiguous()
@@ -333,6 +355,9 @@ class _Bidirectional(torch.autograd.Function):
     def backward(ctx, dout):
         q, k, v, nc, scratch = ctx.saved_tensors
         kp = ctx.kp
+        if ctx.compiled:
+            dq, dk, dv, dnc = _binding.ops().bidir_bwd(q, k, v, nc, kp, dout, scratch)
+            return dq, dk, dv, dnc.reshape(ctx.nc_shape).to(ctx.nc_dtype), None
         B, H, N, Dk = q.shape
         Dv = v.shape[-1]
         dout = dout.contiguous().to(q.dtype)

@@ -17,6 +17,10 @@ implemented by ``cott_scan`` of ``libcottention_b200.so``:
   ``inplace=True`` returns the (re-cast, contiguous) V holding the result (``:403-404``);
 * the checks of ``:355-374`` raise ``RuntimeError`` with the reference's messages.
 
+When the compiled torch binding has been built (``cott_torch_binding.so``, ``csrc_torch/torch_binding.cpp``) the four
+names are its functions -- the reference's pybind signature in C++ -- and the Python statement of the same checks
+below is the route without it.
+
 Differences, on purpose: sums are kept in fp32/fp64 rather than the storage type, and the launch
 goes to torch's current stream rather than the legacy default stream (``:262``).
 """
@@ -24,7 +28,7 @@ from __future__ import annotations
 
 import torch
 
-from . import _lib
+from . import _binding, _lib
 
 __all__ = ["float32", "float64", "float16", "bfloat16", "scan"]
 
@@ -84,16 +88,28 @@ def _forward(autocast_dtype: torch.dtype, Q, K, V, block_size, inplace=False, re
 
 
 def float32(Q, K, V, block_size, inplace=False, reversed=False):
+    m = _binding.module()
+    if m is not None:  # the compiled entry point (same checks, same C call)
+        return m.float32(Q, K, V, block_size, inplace, reversed)
     return _forward(torch.bfloat16, Q, K, V, block_size, inplace, reversed)
 
 
 def float64(Q, K, V, block_size, inplace=False, reversed=False):
+    m = _binding.module()
+    if m is not None:  # the compiled entry point (same checks, same C call)
+        return m.float64(Q, K, V, block_size, inplace, reversed)
     return _forward(torch.bfloat16, Q, K, V, block_size, inplace, reversed)
 
 
 def float16(Q, K, V, block_size, inplace=False, reversed=False):
+    m = _binding.module()
+    if m is not None:  # the compiled entry point (same checks, same C call)
+        return m.float16(Q, K, V, block_size, inplace, reversed)
     return _forward(torch.float16, Q, K, V, block_size, inplace, reversed)
 
 
 def bfloat16(Q, K, V, block_size, inplace=False, reversed=False):
+    m = _binding.module()
+    if m is not None:  # the compiled entry point (same checks, same C call)
+        return m.bfloat16(Q, K, V, block_size, inplace, reversed)
     return _forward(torch.bfloat16, Q, K, V, block_size, inplace, reversed)

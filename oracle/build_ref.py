@@ -45,12 +45,23 @@ def build(reference_root: str, verbose: bool = False) -> str:
     shutil.copy2(so, os.path.join(pkg, "kernel.so"))
     with open(os.path.join(pkg, "__init__.py"), "w") as f:
         f.write("import torch  # noqa: F401  (loads libtorch before the extension)\nfrom . import kernel  # noqa: F401\n")
+    copy_modules(reference_root)
     return pkg
+
+
+def copy_modules(reference_root: str) -> str:
+    """The reference's GPT attention module, byte for byte, for the drop-in test (it is imported there with this
+    library's Custom_Kernel / FastAttention2 shims first on sys.path).  Git-ignored like everything under _ref/."""
+    mods = os.path.join(OUT, "reference_modules")
+    os.makedirs(mods, exist_ok=True)
+    shutil.copy2(os.path.join(reference_root, "GPT_Trainer", "GPTCosAttention.py"), os.path.join(mods, "GPTCosAttention.py"))
+    return mods
 
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("COTT_REFERENCE_ROOT", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("COTT_REFERENCE_ROOT"), required="COTT_REFERENCE_ROOT" not in os.environ,
+                    help="path of the reference checkout (or set COTT_REFERENCE_ROOT)")
     ap.add_argument("-v", "--verbose", action="store_true")
     a = ap.parse_args()
     print(build(a.reference, a.verbose))

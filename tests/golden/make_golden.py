@@ -106,6 +106,46 @@ def gpt_train_branch(G, out):
     )
 
 
+def gpt_module_forward(G, out, rotary_dim):
+    """``GPTCosAttention.forward`` end to end (:427-511): projections, head split, rotary embedding through the
+    ``transformers`` helpers the module imports (:7, :458-476), permutes, ``_cos_attn`` with a padding mask, head
+    merge, output projection.  The kernel call is bound to the masked quadratic form as in ``gpt_train_branch``."""
+    torch.manual_seed(404 + (rotary_dim or 0))
+    B, H, S, d = 2, 2, 48, 64
+    cfg = types.SimpleNamespace(max_position_embeddings=128, attn_pdrop=0.0, resid_pdrop=0.0, hidden_size=H * d,
+                                num_attention_heads=H, rotary_dim=rotary_dim)
+    mod = G.GPTCosAttention(cfg).double()
+    with torch.no_grad():
+        mod.norm_const.copy_(torch.tensor([0.5, -0.4], dtype=torch.float64).view(1, H, 1, 1))
+    hs = torch.randn(B, S, H * d).double().requires_grad_()
+    keep = torch.ones(B, S, dtype=torch.bool)
+    keep[1, 37:] = False
+    add_mask = torch.zeros(B, 1, 1, S, dtype=torch.float64)
+    add_mask[~keep.view(B, 1, 1, S)] = torch.finfo(torch.float32).min
+    position_ids = torch.arange(S).unsqueeze(0).repeat(B, 1)
+    position_ids[1] += 5                                    # per-batch positions
+    # what the module gathers for these positions (:454-456), recorded so that the test needs no transformers
+    emb = mod._get_embed_positions(position_ids)
+    sincos = torch.gather(emb, 1, position_ids.unsqueeze(-1).repeat(1, 1, emb.shape[-1]))
+    sin, cos = torch.split(sincos, sincos.shape[-1] // 2, dim=-1)
+    saved = G.CustomAttention
+    G.CustomAttention = _QuadraticScan
+    try:
+        o = mod(hs, attention_mask=add_mask, position_ids=position_ids)[0]
+    finally:
+        G.CustomAttention = saved
+    do = torch.randn(o.shape).double()
+    (o * do).sum().backward()
+    np.savez_compressed(
+        out, hidden=_f32(hs), keep=keep.numpy(), position_ids=position_ids.numpy(), sin=sin.double().numpy(), cos=cos.double().numpy(),
+        wq=_f32(mod.q_proj.weight), wk=_f32(mod.k_proj.weight), wv=_f32(mod.v_proj.weight),
+        wo=_f32(mod.out_proj.weight), norm_const=mod.norm_const.detach().view(-1).numpy(),
+        out=o.detach().numpy(), dout=_f32(do), dhidden=hs.grad.numpy(), dnorm_const=mod.norm_const.grad.view(-1).numpy(),
+        dwq=mod.q_proj.weight.grad.numpy(), dwv=mod.v_proj.weight.grad.numpy(),
+        num_heads=np.int64(H), rotary_dim=np.int64(rotary_dim or 0),
+    )
+
+
 def gpt_recurrent_branch(G, out):
     """Unmodified reference code end to end: prompt of S tokens, then single-token steps."""
     torch.manual_seed(202)
@@ -169,11 +209,14 @@ def bert_forward(Bm, out, S, name_suffix=""):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("COTT_REFERENCE_ROOT", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("COTT_REFERENCE_ROOT"), required="COTT_REFERENCE_ROOT" not in os.environ,
+                    help="path of the reference checkout (or set COTT_REFERENCE_ROOT)")
     a = ap.parse_args()
     G, Bm = _import_reference(a.reference)
     gpt_train_branch(G, os.path.join(HERE, "gpt_cos_attn_train_branch.npz"))
     gpt_recurrent_branch(G, os.path.join(HERE, "gpt_cos_attn_recurrent.npz"))
+    gpt_module_forward(G, os.path.join(HERE, "gpt_module_forward_rot32.npz"), rotary_dim=32)
+    gpt_module_forward(G, os.path.join(HERE, "gpt_module_forward_rot64.npz"), rotary_dim=64)   # the trainer's setting (rotary_dim = head dim)
     bert_forward(Bm, os.path.join(HERE, "bert_cos_attn_s40.npz"), S=40)   # d <= S: Q (K^T V) order
     bert_forward(Bm, os.path.join(HERE, "bert_cos_attn_s12.npz"), S=12)   # d  > S: (Q K^T) V order
     for f in sorted(os.listdir(HERE)):

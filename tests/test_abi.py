@@ -113,3 +113,22 @@ def test_package_input_recipe_equals_the_oracles():
     for kw in (dict(seed=7), dict(seed=1234, normalize=False, dtype=torch.bfloat16)):
         a, b = make_inputs(2, 3, 50, 32, 16, **kw), O.make_inputs(2, 3, 50, 32, 16, **kw)
         assert all(torch.equal(x, y) for x, y in zip(a, b))
+
+
+def test_compiled_torch_binding_exports_the_reference_signature():
+    """The compiled binding (csrc_torch/torch_binding.cpp) registers the reference's four pybind functions
+    (combined_kernel_general.cu:444-454) with six arguments in the reference's order, and the fused operators as
+    torch.library ops.  No compute: loading and introspection only."""
+    import torch
+    from cottention_transformer_b200 import _binding, build
+    build.build_torch_binding()
+    m = _binding.module()
+    assert m is not None
+    for name in ("float32", "float64", "float16", "bfloat16"):
+        doc = getattr(m, name).__doc__
+        assert "Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, block_size" in doc and "inplace: bool = False, reversed: bool = False" in doc
+    for op in ("causal_fwd", "causal_bwd", "bidir_fwd", "bidir_bwd"):
+        assert hasattr(torch.ops.cottention_b200, op)
+    with __import__("pytest").raises(RuntimeError, match="Q must be a CUDA tensor"):
+        z = torch.zeros(1, 1, 8, 32)
+        m.float32(z, z, z, 1, False, False)
