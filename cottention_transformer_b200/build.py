@@ -89,8 +89,17 @@ def build_torch_binding(force: bool = False, verbose: bool = False) -> str:
     bld = os.path.join(OBJ, "torch_binding")
     os.makedirs(bld, exist_ok=True)
     os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")  # no device code here; silences the arch probe on CPU-only hosts
+    # Link the C++ runtime the process already runs on, by name.  (Some toolchain layouts resolve -lstdc++ to the static
+    # archive; a second, uninitialised copy of the iostream machinery inside the binding crashes on first use.)
+    import torch  # noqa: F401
+    stdcpp = []
+    with open("/proc/self/maps") as f:
+        for line in f:
+            if "libstdc++.so" in line:
+                stdcpp = [f"-L{os.path.dirname(line.split()[-1])}", "-l:libstdc++.so.6"]
+                break
     load(name="cott_torch_binding", sources=[src], build_directory=bld, with_cuda=True, is_python_module=False, verbose=verbose,
-         extra_cflags=["-O2"], extra_ldflags=[f"-L{PKG}", "-l:libcottention_b200.so", "-Wl,-rpath,'$$ORIGIN'", "-Wl,-rpath,'$$ORIGIN/../..'"])  # ($$: ninja's escape for a literal $)
+         extra_cflags=["-O2"], extra_ldflags=[*stdcpp, f"-L{PKG}", "-l:libcottention_b200.so", "-Wl,-rpath,'$$ORIGIN'", "-Wl,-rpath,'$$ORIGIN/../..'"])  # ($$: ninja's escape for a literal $)
     shutil.copy2(os.path.join(bld, "cott_torch_binding.so"), BINDING)
     return BINDING
 

@@ -188,6 +188,8 @@ TORCH_LIBRARY_IMPL(cottention_b200, CUDA, m) {
 // The reference registers its four functions with pybind (combined_kernel_general.cu:444-454); the argument names and
 // defaults are its own.
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  // how a non-zero status of the C ABI surfaces in Python: RuntimeError carrying the status text and the library's message
+  m.def("_raise_for_status", [](int status) { check(status, "cottention_b200"); }, py::arg("status"));
   m.def("float32", &forward_<at::kBFloat16>, "FastAttention forward (float32 entry point)", py::arg("Q"), py::arg("K"), py::arg("V"),
         py::arg("block_size"), py::arg("inplace") = false, py::arg("reversed") = false);
   m.def("float64", &forward_<at::kBFloat16>, "FastAttention forward (float64 entry point)", py::arg("Q"), py::arg("K"), py::arg("V"),

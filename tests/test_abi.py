@@ -132,3 +132,8 @@ def test_compiled_torch_binding_exports_the_reference_signature():
     with __import__("pytest").raises(RuntimeError, match="Q must be a CUDA tensor"):
         z = torch.zeros(1, 1, 8, 32)
         m.float32(z, z, z, 1, False, False)
+    # a failing C call becomes a RuntimeError with the status text (this also runs the binding's string formatting,
+    # which a statically linked second copy of the C++ runtime once crashed)
+    m._raise_for_status(0)
+    with __import__("pytest").raises(RuntimeError, match=r"cottention_b200: unsupported shape \(2\)"):
+        m._raise_for_status(2)
