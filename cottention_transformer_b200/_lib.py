@@ -35,6 +35,8 @@ _SIGNATURES = {
     "cott_cos_attn_bwd_seg": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "cott_cos_attn_fwd_train": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P],
     "cott_cos_attn_bwd_train": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "cott_cos_attn_wide_fwd": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "cott_cos_attn_wide_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "cott_cos_attn_prefill_state": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "cott_decode_step": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, ctypes.c_longlong, _P, _P],
     "cott_decode_steps": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, ctypes.c_longlong, _P, _P],
@@ -48,7 +50,8 @@ _SIGNATURES = {
     "cott_selftest_device_wait": [_I, _I, _I, _P],
 }
 _STR = {"cott_version": [], "cott_last_error": [], "cott_status_string": [_I]}
-_SIZE = {"cott_bidir_scratch_bytes": [_I, _I, _I, _I, _I, _I], "cott_cos_attn_saved_bytes": [_I, _I, _I], "cott_cos_attn_seg_workspace_bytes": [_I, _I, _I, _I]}
+_SIZE = {"cott_bidir_scratch_bytes": [_I, _I, _I, _I, _I, _I], "cott_cos_attn_saved_bytes": [_I, _I, _I],
+         "cott_cos_attn_wide_workspace_bytes": [_I, _I, _I], "cott_cos_attn_seg_workspace_bytes": [_I, _I, _I, _I]}
 
 class CottLayout(ctypes.Structure):
     """``cott_layout``: element strides (batch, head, position) of q/k/v/dq/dk/dv and of out/dout."""

@@ -10,7 +10,8 @@ Two modes, chosen by dtype (not a fallback chain -- each mode is a CUDA path of 
 
 * float16 / bfloat16, head dim 64, no padding mask: ONE fused tensor-core kernel for the forward
   (``cott_cos_attn_fwd``) and two for the backward (``cott_cos_attn_bwd``), fp32 accumulation;
-* float16 / bfloat16, head dim 128 / 192 / 256: the row factors pulled out of the scan, tensor-core scans on
+* float16 / bfloat16, head dim 128: the fused head-dim-128 kernels (``cott_cos_attn_wide_fwd`` / ``_bwd``);
+* float16 / bfloat16, head dim 192 / 256: the row factors pulled out of the scan, tensor-core scans on
   64-wide slices of the head dimension, closed-form backward (``_WideCausal``);
 * float32 / float64 (and any other shape): the reference's own structure --
   elementwise torch ops around ``CustomAttention`` (the exact-mode scan kernel), gradients of
@@ -216,6 +217,47 @@ def rotary_packed_(qkv, sin, cos, heads=None):
     return _RotaryPacked.apply(qkv, sin, cos, heads)
 
 
+class _FusedWide128(torch.autograd.Function):
+    """Head dim 128 in bf16 / fp16: ``cott_cos_attn_wide_fwd`` / ``_bwd`` -- one tensor-core pass forward (row norms,
+    length factor and output scaling inside the kernel), and a row-dot pass plus three tensor-core passes backward with
+    the normalisation terms in their epilogues.  The forward's row factors travel to the backward in ``ws``."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, norm_const, keep):
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        B, H, N, D = q.shape
+        L = _lib.lib()
+        nc = norm_const.detach().reshape(-1).to(device=q.device, dtype=torch.float32).contiguous()
+        if nc.numel() != H:
+            raise RuntimeError(f"norm_const must have one entry per head ({H}), got {nc.numel()}")
+        kp = None if keep is None else keep.to(device=q.device, dtype=torch.uint8).contiguous()
+        out = torch.empty_like(v)
+        with torch.cuda.device(q.device):
+            ws = torch.empty(max(L.cott_cos_attn_wide_workspace_bytes(B, H, N), 16), dtype=torch.uint8, device=q.device)
+            st = L.cott_cos_attn_wide_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(kp), _lib.ptr(nc), _lib.ptr(out),
+                                          _lib.ptr(ws), B, H, N, D, D, _lib.DTYPE_CODE[q.dtype], _lib.stream_ptr(q.device))
+        _lib.check(st, "cott_cos_attn_wide_fwd")
+        ctx.save_for_backward(q, k, v, out, nc, ws)
+        ctx.kp = kp
+        ctx.nc_shape, ctx.nc_dtype = norm_const.shape, norm_const.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, nc, ws = ctx.saved_tensors
+        B, H, N, D = q.shape
+        dout = dout.contiguous().to(q.dtype)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        dnc = torch.empty(H, dtype=torch.float32, device=q.device)
+        with torch.cuda.device(q.device):
+            st = _lib.lib().cott_cos_attn_wide_bwd(
+                _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(ctx.kp), _lib.ptr(nc), _lib.ptr(out), _lib.ptr(dout), _lib.ptr(ws),
+                _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(dnc), B, H, N, D, D, _lib.DTYPE_CODE[q.dtype],
+                _lib.stream_ptr(q.device))
+        _lib.check(st, "cott_cos_attn_wide_bwd")
+        return dq, dk, dv, dnc.reshape(ctx.nc_shape).to(ctx.nc_dtype), None
+
+
 def wide_supported(q, k, v, keep=None) -> bool:
     return (
         q.is_cuda and q.dtype in FUSED_DTYPES and k.dtype == q.dtype and v.dtype == q.dtype
@@ -316,6 +358,8 @@ def cos_attn_causal(q, k, v, norm_const, keep=None, segments=None, one_pass_back
     if fused_supported(q, k, v, keep):
         return _FusedCausal.apply(q, k, v, norm_const, segments, keep, bool(one_pass_backward))
     if wide_supported(q, k, v, keep):
+        if q.shape[-1] == 128:
+            return _FusedWide128.apply(q, k, v, norm_const, keep)
         return _WideCausal.apply(q, k, v, norm_const, keep)
     return _exact_causal(q, k, v, norm_const, keep)
 

@@ -3,6 +3,7 @@
 #include "causal_bwd_fused.cuh"
 #include "causal_seg.cuh"
 #include "causal_tc.cuh"
+#include "causal_wide.cuh"
 #include "common.cuh"
 
 #include <initializer_list>
@@ -265,6 +266,148 @@ __global__ void __launch_bounds__(128, 1) wait_selftest_kernel(int polls, int co
   if (warp == 1) tmem_dealloc(tmem, 32);
 }
 
+// ---- head dim 128: causal_wide.cuh ----------------------------------------------------------------------------
+struct WideTensors {  // X, Y: [B,H,N,128]; Z, C, out: [B,H,N,dz] (dz a multiple of 64), all dense
+  const void *x, *y, *z, *c;
+  void* out;
+  int dz;
+};
+inline TileStrides dense_rows(long H, long N, long D) { return TileStrides{H * N * D, N * D, D}; }
+
+template <typename T, bool REV, bool NORMS, bool STATE_ONLY>
+int launch_wide_t(const WideTensors& t, WideArgs a, int B, int H, int N, int dtype, int nseg, cudaStream_t stream) {
+  CUtensorMap mx, my, mz, mc, mo;
+  const int bf = dtype == COTT_BF16;
+  int r;
+  const void* xs = t.x ? t.x : t.y;  // STATE_ONLY launches have no X
+  if ((r = make_tmap_rows64(&mx, xs, bf, B, H, N, dense_rows(H, N, 128), kTcChunk, 128)) ||
+      (r = make_tmap_rows64(&my, t.y, bf, B, H, N, dense_rows(H, N, 128), kTcChunk, 128)) ||
+      (r = make_tmap_rows64(&mz, t.z, bf, B, H, N, dense_rows(H, N, t.dz), kTcChunk, t.dz)) ||
+      (r = make_tmap_rows64(&mc, t.c ? t.c : t.z, bf, B, H, N, dense_rows(H, N, t.dz), kTcChunk, t.dz)) ||
+      (r = make_tmap_rows64(&mo, t.out ? t.out : t.z, bf, B, H, N, dense_rows(H, N, t.dz), kTcChunk, t.dz)))
+    return fail(COTT_ERR_CUDA, "cuTensorMapEncodeTiled failed for a head-dim-128 tensor: %d", r);
+  a.has_c = t.c != nullptr;
+  a.H = H;
+  a.N = N;
+  auto kern = wide_kernel<T, REV, NORMS, STATE_ONLY>;
+  const size_t smem = wide_smem_bytes();
+  COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<dim3((unsigned)((long)B * H), t.dz / 64, nseg), kWdThreads, smem, stream>>>(mx, my, mz, mc, mo, a);
+  COTT_CUDA_TRY(cudaGetLastError());
+  return COTT_OK;
+}
+
+// One scan-type pass over head-dim-128 tensors, cut into `nseg` segments per sequence when nseg > 1: the segments'
+// own states (STATE_ONLY launch), their exclusive prefix in scan order, then the pass itself.  `ws`: 2 x B*H*(dz/64)*nseg
+// fp32 [128 x 64] matrices (only touched when nseg > 1).
+template <typename T, bool REV, bool NORMS>
+int run_wide(const WideTensors& t, WideArgs a, int B, int H, int N, int dtype, int nseg_requested, float* ws, cudaStream_t stream) {
+  const SegPlan plan = plan_segments(N, nseg_requested);
+  a.chunks_per_seg = plan.cps;
+  a.init_state = nullptr;
+  a.state_out = nullptr;
+  if (plan.nseg > 1) {
+    const size_t units = (size_t)B * H * (t.dz / 64);
+    const size_t A = units * plan.nseg * (size_t)(kTcChunk * kTcD);
+    WideArgs sa = a;
+    sa.state_out = ws;
+    sa.eps = nullptr;
+    sa.rq_out = sa.rk_out = sa.w_out = nullptr;
+    WideTensors st = t;
+    st.x = nullptr, st.c = nullptr, st.out = nullptr;
+    int r = launch_wide_t<T, REV, NORMS, true>(st, sa, B, H, N, dtype, plan.nseg, stream);
+    if (r) return r;
+    seg_prefix_kernel<<<(unsigned)units, 256, 0, stream>>>(ws, ws + A, plan.nseg, kTcChunk * kTcD);
+    COTT_CUDA_TRY(cudaGetLastError());
+    a.init_state = ws + A;
+  }
+  return launch_wide_t<T, REV, NORMS, false>(t, a, B, H, N, dtype, plan.nseg, stream);
+}
+
+size_t wide_ws_floats(int B, int H, int N, int dz, int nseg) {
+  return 2 * (size_t)B * H * (dz / 64) * plan_segments(N, nseg).nseg * (size_t)(kTcChunk * kTcD);
+}
+
+int wide_seg_count(int B, int H, int N, int dz) {
+  const long units = (long)B * H * (dz / 64);
+  const int total = (N + kTcChunk - 1) / kTcChunk;
+  if (units <= 0 || total < 4) return 1;
+  int sm = 148, dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, dev);
+  long nseg = sm / units;
+  if (nseg > total / 2) nseg = total / 2;
+  return nseg < 2 ? 1 : (int)nseg;
+}
+
+// workspace of the fused head-dim-128 pair: six fp32 vectors [B*H*N] (1/|q|, 1/|k|, keep a/|k|, -q^.dq^/|q|^2, eps,
+// -eps/|k|^2), the running keep count [B*N], then the segment states
+struct WideWs {
+  float *rq, *rk, *w, *cq, *eps, *ck;
+  int* count;
+  float* seg;
+};
+WideWs wide_ws(void* workspace, int B, int H, int N) {
+  const size_t V = (size_t)B * H * N;
+  float* f = static_cast<float*>(workspace);
+  WideWs s{f, f + V, f + 2 * V, f + 3 * V, f + 4 * V, f + 5 * V, reinterpret_cast<int*>(f + 6 * V), nullptr};
+  const size_t cnt = ((size_t)B * N + 3) & ~(size_t)3;
+  s.seg = f + 6 * V + cnt;
+  return s;
+}
+
+template <typename T>
+int run_wide_fwd(const void* q, const void* k, const void* v, const unsigned char* keep, const float* nc, void* out, void* workspace,
+                 int B, int H, int N, int dtype, cudaStream_t stream) {
+  WideWs ws = wide_ws(workspace, B, H, N);
+  WideArgs a = {};
+  a.norm_const = nc;
+  a.rq_out = ws.rq, a.rk_out = ws.rk, a.w_out = ws.w;
+  if (keep) {
+    keep_count_kernel<<<(unsigned)B, 256, 0, stream>>>(keep, ws.count, N);
+    COTT_CUDA_TRY(cudaGetLastError());
+    a.keep = keep, a.count = ws.count;
+  }
+  WideTensors t{q, k, v, nullptr, out, 128};
+  return run_wide<T, false, true>(t, a, B, H, N, dtype, wide_seg_count(B, H, N, 128), ws.seg, stream);
+}
+
+template <typename T>
+int run_wide_bwd(const void* q, const void* k, const void* v, const unsigned char* keep, const float* nc, const void* out, const void* dout,
+                 void* workspace, void* dq, void* dk, void* dv, float* dnorm, int B, int H, int N, int dtype, cudaStream_t stream) {
+  WideWs ws = wide_ws(workspace, B, H, N);
+  const long rows = (long)B * H * N;
+  const int nseg = wide_seg_count(B, H, N, 128);
+  // -q^.dq^ / |q|^2 from q^_t . dq^_t = dO_t . O_t
+  rowdot_coef_kernel<T><<<(unsigned)((rows * 16 + 255) / 256), 256, 0, stream>>>(static_cast<const T*>(dout), static_cast<const T*>(out), ws.rq,
+                                                                                ws.cq, rows);
+  COTT_CUDA_TRY(cudaGetLastError());
+  int st;
+  {  // dq = rq scan(dO, V, diag(w) K) + cq q                      (Custom_Kernel.py:106 with the module math around it)
+    WideArgs a = {};
+    a.zscale = ws.w, a.oscale = ws.rq, a.ccoef = ws.cq;
+    WideTensors t{dout, v, k, q, dq, 128};
+    if ((st = run_wide<T, false, false>(t, a, B, H, N, dtype, nseg, ws.seg, stream))) return st;
+  }
+  COTT_CUDA_TRY(cudaMemsetAsync(ws.eps, 0, sizeof(float) * rows, stream));
+  COTT_CUDA_TRY(cudaMemsetAsync(dnorm, 0, sizeof(float) * H, stream));
+  {  // dv = w scan_rev(K, diag(rq) Q, dO);  eps = v' . dv'          (:108)
+    WideArgs a = {};
+    a.yscale = ws.rq, a.oscale = ws.w, a.eps = ws.eps;
+    WideTensors t{k, q, dout, v, dv, 128};
+    if ((st = run_wide<T, true, false>(t, a, B, H, N, dtype, nseg, ws.seg, stream))) return st;
+  }
+  eps_coef_kernel<<<dim3((unsigned)((long)B * H), (unsigned)((N + 1023) / 1024)), 256, 0, stream>>>(ws.eps, ws.rk, ws.ck, nc, dnorm,
+                                                                                                 keep ? ws.count : nullptr, H, N);
+  COTT_CUDA_TRY(cudaGetLastError());
+  {  // dk = w scan_rev(V, dO, diag(rq) Q) + ck k                    (:107)
+    WideArgs a = {};
+    a.zscale = ws.rq, a.oscale = ws.w, a.ccoef = ws.ck;
+    WideTensors t{v, dout, q, k, dk, 128};
+    if ((st = run_wide<T, true, false>(t, a, B, H, N, dtype, nseg, ws.seg, stream))) return st;
+  }
+  return COTT_OK;
+}
+
 template <typename T>
 int run_bwd_train(const void* q, const void* k, const void* v, const unsigned char* keep, const float* nc, const void* dout,
                   const void* saved, float* ws, int nseg, const cott_layout* layout, void* dq, void* dk, void* dv, float* dnorm,
@@ -426,9 +569,31 @@ cudaError_t scratch_pool(cudaMemPool_t* pool) {
   return cudaSuccess;
 }
 
+// Head dim 128 for Q and K: the native kernel (both halves of q, k go into the same score and state accumulators);
+// scratch only for the segment states of long sequences with few (batch, head) pairs.
+template <typename T>
+int launch_scan_tc_128(const void* q, const void* k, const void* v, void* out, int B, int H, int N, int Dv, int dtype,
+                       int reversed, cudaStream_t stream) {
+  const int nseg = wide_seg_count(B, H, N, Dv);
+  const size_t ws_bytes = nseg > 1 ? wide_ws_floats(B, H, N, Dv, nseg) * sizeof(float) : 0;
+  float* ws = nullptr;
+  if (ws_bytes) {
+    cudaMemPool_t pool;
+    COTT_CUDA_TRY(scratch_pool(&pool));
+    COTT_CUDA_TRY(cudaMallocFromPoolAsync(reinterpret_cast<void**>(&ws), ws_bytes, pool, stream));
+  }
+  WideTensors t{q, k, v, nullptr, out, Dv};
+  WideArgs a = {};
+  const int st = reversed ? run_wide<T, true, false>(t, a, B, H, N, dtype, nseg, ws, stream)
+                          : run_wide<T, false, false>(t, a, B, H, N, dtype, nseg, ws, stream);
+  if (ws) COTT_CUDA_TRY(cudaFreeAsync(ws, stream));
+  return st;
+}
+
 template <typename T>
 int launch_scan_tc_wide(const void* q, const void* k, const void* v, void* out, int B, int H, int N, int Dk, int Dv, int dtype,
                         int reversed, cudaStream_t stream) {
+  if (Dk == 128) return launch_scan_tc_128<T>(q, k, v, out, B, H, N, Dv, dtype, reversed, stream);
   const TileStrides sqk{(long long)H * N * Dk, (long long)N * Dk, Dk}, sv{(long long)H * N * Dv, (long long)N * Dv, Dv};
   const TileStrides dense = contiguous_bhnd(H, N);
   const long rows = (long)B * H * N;
@@ -655,6 +820,57 @@ int cott_cos_attn_bwd_train(const void* q, const void* k, const void* v, const u
                                                            dnorm_const, B, H, N, dtype, s)
                             : run_bwd_train<__half>(q, k, v, keep, norm_const, dout, saved, ws, nseg, layout, dq, dk, dv, dnorm_const,
                                                     B, H, N, dtype, s);
+}
+
+size_t cott_cos_attn_wide_workspace_bytes(int B, int H, int N) {
+  if (B <= 0 || H <= 0 || N <= 0) return 0;
+  const size_t V = (size_t)B * H * N, cnt = ((size_t)B * N + 3) & ~(size_t)3;
+  return (6 * V + cnt + wide_ws_floats(B, H, N, 128, wide_seg_count(B, H, N, 128))) * sizeof(float);
+}
+
+static int check_wide_args(int B, int H, int N, int Dk, int Dv, int dtype) {
+  if (dtype != COTT_BF16 && dtype != COTT_F16)
+    return fail(COTT_ERR_DTYPE, "the fused head-dim-128 path takes float16/bfloat16 (dtype code %d given)", dtype);
+  if (B < 0 || H < 0 || N < 0) return fail(COTT_ERR_SHAPE, "negative size B=%d H=%d N=%d", B, H, N);
+  if (Dk != 128 || Dv != 128) return fail(COTT_ERR_UNSUPPORTED, "this entry point is built for head dim 128 (got Dk=%d Dv=%d)", Dk, Dv);
+  if ((long)B * H > 0x7fffffffL) return fail(COTT_ERR_SHAPE, "B*H too large");
+  return COTT_OK;
+}
+
+int cott_cos_attn_wide_fwd(const void* q, const void* k, const void* v, const unsigned char* keep, const float* norm_const,
+                           void* out, void* workspace, int B, int H, int N, int Dk, int Dv, int dtype, void* stream) {
+  int st = check_wide_args(B, H, N, Dk, Dv, dtype);
+  if (st) return st;
+  if ((long)B * H * N == 0) return COTT_OK;
+  if ((st = check_ptrs16({{q, "q"}, {k, "k"}, {v, "v"}, {out, "out"}, {workspace, "workspace"}}))) return st;
+  if (!norm_const) return fail(COTT_ERR_NULL, "null pointer: norm_const");
+  DeviceScope scope(q);
+  COTT_CUDA_TRY(scope.status());
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return dtype == COTT_BF16 ? run_wide_fwd<__nv_bfloat16>(q, k, v, keep, norm_const, out, workspace, B, H, N, dtype, s)
+                            : run_wide_fwd<__half>(q, k, v, keep, norm_const, out, workspace, B, H, N, dtype, s);
+}
+
+int cott_cos_attn_wide_bwd(const void* q, const void* k, const void* v, const unsigned char* keep, const float* norm_const,
+                           const void* out, const void* dout, void* workspace, void* dq, void* dk, void* dv,
+                           float* dnorm_const, int B, int H, int N, int Dk, int Dv, int dtype, void* stream) {
+  int st = check_wide_args(B, H, N, Dk, Dv, dtype);
+  if (st) return st;
+  if (!dnorm_const && H > 0) return fail(COTT_ERR_NULL, "null pointer: dnorm_const");
+  if ((long)B * H * N == 0) {
+    if (H > 0) COTT_CUDA_TRY(cudaMemsetAsync(dnorm_const, 0, sizeof(float) * H, static_cast<cudaStream_t>(stream)));
+    return COTT_OK;
+  }
+  if ((st = check_ptrs16({{q, "q"}, {k, "k"}, {v, "v"}, {out, "out"}, {dout, "dout"}, {dq, "dq"}, {dk, "dk"}, {dv, "dv"},
+                          {workspace, "workspace"}})))
+    return st;
+  if (!norm_const) return fail(COTT_ERR_NULL, "null pointer: norm_const");
+  DeviceScope scope(q);
+  COTT_CUDA_TRY(scope.status());
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return dtype == COTT_BF16
+             ? run_wide_bwd<__nv_bfloat16>(q, k, v, keep, norm_const, out, dout, workspace, dq, dk, dv, dnorm_const, B, H, N, dtype, s)
+             : run_wide_bwd<__half>(q, k, v, keep, norm_const, out, dout, workspace, dq, dk, dv, dnorm_const, B, H, N, dtype, s);
 }
 
 int cott_cos_attn_prefill_state(const void* k, const void* v, const float* norm_const, float* state, void* workspace,

@@ -98,6 +98,28 @@ __device__ __forceinline__ void tma_load_tile(void* smem_dst, const CUtensorMap*
       "r"(b)
       : "memory");
 }
+// The same with a column offset x (a multiple of 8 elements, so that x * 2 bytes is a multiple of 16): tensors whose
+// rows are wider than one 64-column box.
+__device__ __forceinline__ void tma_load_tile_x(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int h,
+                                                int b) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(h),
+      "r"(b)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_tile_x(const CUtensorMap* map, const void* smem_src, int x, int y, int h, int b) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(h), "r"(b)
+               : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_tile_x(const CUtensorMap* map, int x, int y, int h, int b) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(x), "r"(y), "r"(h), "r"(b)
+               : "memory");
+}
 // The same box fetched into L2 only (no shared-memory destination, nothing to wait for): a later tma_load_tile of
 // it is served from L2.
 __device__ __forceinline__ void tma_prefetch_tile(const CUtensorMap* map, int y, int h, int b) {
@@ -278,11 +300,13 @@ inline TileStrides contiguous_bhnd(long H, long N) { return TileStrides{H * N * 
 
 // Tensor map of a [B, H, N, 64] 16-bit tensor with the given strides: dimensions (64, N, H, B), box
 // (64, box_rows, 1, 1), 128-byte swizzle.  Returns 0, 1 (driver entry point missing) or 100 + CUresult.
+// `row_elems`: elements per row of the tensor (64 by default; 128 / 192 / 256 for wider heads, whose rows are then
+// addressed as 64-column boxes at column offsets 0, 64, ...).
 inline int make_tmap_rows64(CUtensorMap* map, const void* base, int is_bf16, long B, long H, long N, TileStrides st,
-                            int box_rows) {
+                            int box_rows, int row_elems = 64) {
   PFN_encodeTiled enc = get_encode_tiled();
   if (!enc) return 1;
-  cuuint64_t dims[4] = {64, (cuuint64_t)N, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t dims[4] = {(cuuint64_t)row_elems, (cuuint64_t)N, (cuuint64_t)H, (cuuint64_t)B};
   cuuint64_t strides[3] = {(cuuint64_t)st.n * 2, (cuuint64_t)st.h * 2, (cuuint64_t)st.b * 2};
   cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};

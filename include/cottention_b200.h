@@ -173,6 +173,27 @@ int cott_cos_attn_bwd_train(const void* q, const void* k, const void* v, const u
                             float* dnorm_const, int B, int H, int N, int Dk, int Dv, int dtype, void* stream);
 
 /*
+ * Fused causal cosine attention for head dim 128 (Dk = Dv = 128, bf16 / fp16): the math of cott_cos_attn_fwd / _bwd,
+ * padding mask included (`keep`, see cott_cos_attn_fwd_seg).  In the reference this head dim runs kernel_mod_4<T, 32>
+ * (Cuda_Kernel/combined_kernel_general.cu:173-251, chosen at :281-284) inside the same module math
+ * (GPT_Trainer/GPTCosAttention.py:229-248,282) and the three scans of CustomAttention.backward (Custom_Kernel.py:106-108).
+ * Forward: one tensor-core pass (two CTAs per sequence, one per 64-column half of V; both halves of q and k go into the
+ * same score and state accumulators).  Backward: a row-dot pass over (dout, out), then three tensor-core passes (dq
+ * forward; dv and dk reversed) with the normalisation terms applied in their epilogues.  Few (batch, head) pairs with a
+ * long sequence are cut into segments inside the call.
+ * `workspace`: cott_cos_attn_wide_workspace_bytes(B, H, N) bytes of device memory, 16-byte aligned; the forward leaves
+ * its row factors there, so pass the same buffer, untouched, to the backward together with the forward's `out`.
+ */
+size_t cott_cos_attn_wide_workspace_bytes(int B, int H, int N);
+int cott_cos_attn_wide_fwd(const void* q, const void* k, const void* v, const unsigned char* keep,
+                           const float* norm_const, void* out, void* workspace, int B, int H, int N, int Dk, int Dv,
+                           int dtype, void* stream);
+int cott_cos_attn_wide_bwd(const void* q, const void* k, const void* v, const unsigned char* keep,
+                           const float* norm_const, const void* out, const void* dout, void* workspace, void* dq,
+                           void* dk, void* dv, float* dnorm_const, int B, int H, int N, int Dk, int Dv, int dtype,
+                           void* stream);
+
+/*
  * Prefill -> decode hand-off: the decode state (cott_decode_step layout, float32 [B,H,Dv,Dk]) that a prompt of N
  * tokens at positions 1..N leaves behind, state[b,h,j,i] = sum_s v'_s[j] k^_s[i], computed with the segment-state
  * kernels instead of N recurrent steps (the reference absorbs a prompt token by token, GPTCosAttention.py:253-272).
