@@ -22,8 +22,11 @@
 // REV walks the sequence backwards with the mask flipped (the reversed scans of Custom_Kernel.py:107-108).
 // STATE_ONLY keeps only the state chain and writes the segment's own S to global memory (segment-parallel launches).
 //
-// Shared memory (all dynamic): two stages of (X 32 KB, Y 32 KB, Z 16 KB, C 16 KB) and the double-buffered 16-bit
-// state operand 2 x 16 KB = 224 KB, then the row scalars and the barriers.  TMEM: P 2 x 128 | Acc 2 x 64 | S 64.
+// Shared memory (all dynamic): two stages of (X 32 KB, Y 32 KB, Z 16 KB), the double-buffered 16-bit state operand
+// 2 x 16 KB and a two-slot output staging ring 2 x 16 KB = 224 KB, then the row scalars and the barriers.  A stage is
+// refilled as soon as the MMAs of its chunk have completed: output rows are staged in the ring (C rows are copied
+// there straight from global memory by the thread that owns the row), so no store has to drain first.
+// TMEM: P 2 x 128 | Acc 2 x 64 | S 64.
 #pragma once
 
 #include "causal_tc.cuh"
@@ -32,7 +35,7 @@ namespace cott {
 
 constexpr int kWdThreads = 640;  // 3 issuing warps, 1 TMA warp, 4 groups of 4 warps
 constexpr int kWdStages = 2;
-constexpr int kWdStageBytes = 6 * kTileBytes;
+constexpr int kWdStageBytes = 5 * kTileBytes;
 constexpr int kWdStateBytes = kTcChunk * 128;  // one 16-bit [128 x 64] state operand
 
 struct WideArgs {
@@ -49,12 +52,15 @@ struct WideArgs {
   float* state_out;         // STATE_ONLY: [B*H][slices][nseg][128 x 64]
   const unsigned char* keep;  // NORMS only: padding ([B, N], with its inclusive running count) or both null
   const int* count;
+  const void* c;        // the C tensor [B,H,N,dz] (dense), or null
+  int dz;               // row length of Z / C / out in elements
   int chunks_per_seg;
   int H, N;
-  int has_c;
 };
 
-// a 128-column row of a two-panel tile: sum of squares / in-place scaling
+// a 128-column row of a two-panel tile.  (Rolled two-piece routines on purpose: versions with eight pieces in flight
+// are faster in isolation and slowed the whole kernel down -- every role runs on every scheduler and competes for
+// one instruction cache.)
 template <typename T>
 __device__ __forceinline__ float row_sumsq2(unsigned char* tile, int row) {
   return row_sumsq_rolled<T>(tile, row) + row_sumsq_rolled<T>(tile + kTileBytes, row);
@@ -63,21 +69,22 @@ __device__ __forceinline__ float row_sumsq2(unsigned char* tile, int row) {
 template <typename T, bool REV, bool NORMS, bool STATE_ONLY>
 __global__ void __launch_bounds__(kWdThreads, 1)
 wide_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapY,
-            const __grid_constant__ CUtensorMap mapZ, const __grid_constant__ CUtensorMap mapC,
-            const __grid_constant__ CUtensorMap mapOut, const WideArgs a) {
+            const __grid_constant__ CUtensorMap mapZ, const __grid_constant__ CUtensorMap mapOut, const WideArgs a) {
   using namespace ptx;
   constexpr int NS = kWdStages;
   constexpr bool BF = Pack2<T>::kBf16;
 
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* sS = smem + NS * kWdStageBytes;  // 2 x [128 x 64] 16-bit state operand (rows = columns of Y)
-  float* s_rq = reinterpret_cast<float*>(sS + 2 * kWdStateBytes);  // [NS][128] output row scale of a stage (NORMS)
+  unsigned char* sO = sS + 2 * kWdStateBytes;     // 2 x [128 x 64] output staging ring
+  float* s_rq = reinterpret_cast<float*>(sO + 2 * kTileBytes);  // [NS][128] output row scale of a stage (NORMS)
   uint64_t* bars = reinterpret_cast<uint64_t*>(s_rq + NS * kTcChunk);
   uint64_t *bar_full = bars, *bar_free_in = bars + 2, *bar_out = bars + 4, *bar_prep = bars + 6, *bar_p_full = bars + 8,
            *bar_p_ready = bars + 10, *bar_acc_full = bars + 12, *bar_acc_free = bars + 14, *bar_state = bars + 16;
   uint64_t &bar_s_full = bars[18], &bar_state2 = bars[19], &bar_init = bars[20];
-  uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 21);
-  int& abort_flag_s = *(reinterpret_cast<int*>(bars + 21) + 1);
+  uint64_t* bar_stg_free = bars + 21;  // [2]: the store of the chunk that used the slot has read it
+  uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 23);
+  int& abort_flag_s = *(reinterpret_cast<int*>(bars + 23) + 1);
   volatile int* abort_flag = &abort_flag_s;
 
   const int tid = threadIdx.x, lane = tid & 31;
@@ -98,9 +105,7 @@ wide_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CU
   auto st_x = [&](int c) { return smem + (c % NS) * kWdStageBytes; };
   auto st_y = [&](int c) { return smem + (c % NS) * kWdStageBytes + 2 * kTileBytes; };
   auto st_z = [&](int c) { return smem + (c % NS) * kWdStageBytes + 4 * kTileBytes; };
-  auto st_c = [&](int c) { return smem + (c % NS) * kWdStageBytes + 5 * kTileBytes; };
-  // the output rows of a chunk are staged over a tile of the chunk that has no reader left
-  auto st_o = [&](int c) { return a.has_c ? st_c(c) : st_x(c); };
+  auto st_o = [&](int c) { return sO + (c & 1) * kTileBytes; };
 
   if (smem_u32(smem) & 1023u) {  // the swizzle atoms need the 1024-byte alignment the declaration asks for
     if (tid == 0) atomicCAS(&g_cott_status, 0, (15 << 16));
@@ -109,7 +114,9 @@ wide_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CU
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
       mbar_init(&bar_full[s], 1);
-      mbar_init(&bar_free_in[s], STATE_ONLY ? 4 : 8);  // output group (accumulator MMAs done) + state group (state MMAs done)
+      // state group (state MMAs done) + in NORMS mode the output group (it reads the X tile for the row norm);
+      // the TMA thread itself waits for the accumulator MMAs
+      mbar_init(&bar_free_in[s], (NORMS && !STATE_ONLY) ? 8 : 4);
       mbar_init(&bar_out[s], 4);
       mbar_init(&bar_prep[s], 4);
       mbar_init(&bar_p_full[s], 1);
@@ -117,6 +124,7 @@ wide_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CU
       mbar_init(&bar_acc_full[s], 1);
       mbar_init(&bar_acc_free[s], 4);
       mbar_init(&bar_state[s], 4);
+      mbar_init(&bar_stg_free[s], 1);
     }
     mbar_init(&bar_s_full, 1);
     mbar_init(&bar_state2, 4);
@@ -155,7 +163,7 @@ wide_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CU
       const int xz = 64 * slice;  // column offset of the Z / C / output slice
       auto issue_loads = [&](int c) {
         const int s = c % NS, y = row0_of(c);
-        mbar_expect_tx(&bar_full[s], (STATE_ONLY ? 3 : (a.has_c ? 6 : 5)) * kTileBytes);
+        mbar_expect_tx(&bar_full[s], (STATE_ONLY ? 3 : 5) * kTileBytes);
         if (!STATE_ONLY) {
           tma_load_tile_x(st_x(c), &mapX, &bar_full[s], 0, y, h, bb);
           tma_load_tile_x(st_x(c) + kTileBytes, &mapX, &bar_full[s], 64, y, h, bb);
@@ -163,7 +171,6 @@ wide_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CU
         tma_load_tile_x(st_y(c), &mapY, &bar_full[s], 0, y, h, bb);
         tma_load_tile_x(st_y(c) + kTileBytes, &mapY, &bar_full[s], 64, y, h, bb);
         tma_load_tile_x(st_z(c), &mapZ, &bar_full[s], xz, y, h, bb);
-        if (!STATE_ONLY && a.has_c) tma_load_tile_x(st_c(c), &mapC, &bar_full[s], xz, y, h, bb);
       };
       auto prefetch = [&](int c) {  // pull a chunk further ahead into L2: with two stages a refill should be an L2 hit
         if (c >= nchunks) return;
@@ -175,30 +182,27 @@ wide_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CU
         tma_prefetch_tile_x(&mapY, 0, y, h, bb);
         tma_prefetch_tile_x(&mapY, 64, y, h, bb);
         tma_prefetch_tile_x(&mapZ, xz, y, h, bb);
-        if (!STATE_ONLY && a.has_c) tma_prefetch_tile_x(&mapC, xz, y, h, bb);
       };
       for (int c = 0; c < NS && c < nchunks; ++c) issue_loads(c);
       prefetch(NS);
       for (int c = 0; c < nchunks; ++c) {
         const int s = c % NS;
-        const bool refill = c + NS < nchunks;
-        if (STATE_ONLY) {
-          if (refill) {
-            if (!wait_bar(&bar_free_in[s], (c / NS) & 1, abort_flag, kWaitStageFree, c)) break;
-            issue_loads(c + NS);
-            prefetch(c + NS + 1);
-          }
-          continue;
+        if (c + NS < nchunks) {
+          // every MMA of chunk c has completed and nothing else reads its tiles: refill the stage.  (The output
+          // group may be running late -- its rows of the previous chunk, a C row still on its way from HBM -- so the
+          // accumulator MMAs are waited for here, not reported by it.)
+          if (!STATE_ONLY && !wait_bar(&bar_acc_full[c & 1], (c >> 1) & 1, abort_flag, kWaitAcc, c)) break;
+          if (!wait_bar(&bar_free_in[s], (c / NS) & 1, abort_flag, kWaitStageFree, c)) break;
+          issue_loads(c + NS);
+          prefetch(c + NS + 1);
         }
-        // every MMA of chunk c has completed
-        if (refill && !wait_bar(&bar_free_in[s], (c / NS) & 1, abort_flag, kWaitStageFree, c)) break;
+        if (STATE_ONLY) continue;
         if (!wait_bar(&bar_out[s], (c / NS) & 1, abort_flag, kWaitStageFree, c)) break;
         tma_store_tile_x(&mapOut, st_o(c), xz, row0_of(c), h, bb);
         tma_store_commit();
-        if (refill) {
-          tma_store_wait_read<0>();  // the staging tile is part of the stage
-          issue_loads(c + NS);
-          prefetch(c + NS + 1);
+        if (c >= 1) {  // the store of chunk c-1 has read its staging slot
+          tma_store_wait_read<1>();
+          mbar_arrive(&bar_stg_free[(c - 1) & 1]);
         }
       }
       tma_store_wait<0>();
@@ -215,15 +219,18 @@ wide_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CU
           mma_ss(tP, dX + (k >> 2) * kPanel + 2 * (k & 3), dY + (k >> 2) * kPanel + 2 * (k & 3), kIdescP, k > 0);
         mma_commit(&bar_p_full[c & 1]);
       };
-      bool ok = wait_bar1(&bar_prep[0], 0, abort_flag, kWaitPrepped, 0);
+      // The scores read X and Y only: they can go as soon as the TMA has landed, without waiting for the row pass
+      // of the operand group -- unless that pass rewrites Y (yscale).
+      uint64_t* gate = a.yscale ? bar_prep : bar_full;
+      bool ok = wait_bar1(&gate[0], 0, abort_flag, kWaitPrepped, 0);
       if (ok) {
         tc_fence_after_sync();
         issue_scores(0);
       }
       for (int c = 0; ok && c + 1 < nchunks; ++c) {
-        // scores of chunk c+1: its prepared tiles, and (buffer reuse) the accumulator MMAs of chunk c-1 done
+        // scores of chunk c+1: its tiles, and (buffer reuse) the accumulator MMAs of chunk c-1 done
         const int s1 = (c + 1) % NS;
-        ok = wait_bar2(&bar_prep[s1], ((c + 1) / NS) & 1, c >= 1 ? &bar_acc_full[(c + 1) & 1] : &bar_prep[s1],
+        ok = wait_bar2(&gate[s1], ((c + 1) / NS) & 1, c >= 1 ? &bar_acc_full[(c + 1) & 1] : &gate[s1],
                        c >= 1 ? (((c - 1) >> 1) & 1) : (((c + 1) / NS) & 1), abort_flag, kWaitTma, c);
         if (!ok) break;
         tc_fence_after_sync();
@@ -380,14 +387,9 @@ wide_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CU
         const float rk = m.kp ? inv_norm(row_sumsq2<T>(st_y(c), row)) : 0.f;
         const float w = rk * length_factor(m.n, sigma);
         scale_row_rolled<T>(st_z(c), row, w);
-        if (!STATE_ONLY) {
-          const float rq = m.kp ? inv_norm(row_sumsq2<T>(st_x(c), row)) : 0.f;
-          s_rq[s * kTcChunk + row] = rq;
-          if (slice == 0 && pos < N && a.rq_out) {
-            a.rq_out[row_base + pos] = rq;
-            a.rk_out[row_base + pos] = rk;
-            a.w_out[row_base + pos] = w;
-          }
+        if (!STATE_ONLY && slice == 0 && pos < N && a.rk_out) {
+          a.rk_out[row_base + pos] = rk;
+          a.w_out[row_base + pos] = w;
         }
       } else {
         if (a.yscale) {
@@ -405,29 +407,46 @@ wide_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CU
     if (!STATE_ONLY) {
       const int wq = warp & 3, row = 32 * wq + lane;
       const uint32_t lane_base = static_cast<uint32_t>(32 * wq) << 16;
+      const bool has_c = a.c != nullptr;
       for (int c = 0; c < nchunks; ++c) {
         const int s = c % NS, b = c & 1;
         const int pos = row0_of(c) + row;
-        // (also orders the read of s_rq after the operand group's write)
-        if (!wait_bar_warp(&bar_prep[s], (c / NS) & 1, abort_flag, kWaitPrepped, c)) break;
+        unsigned char* dst = st_o(c);
+        // (every phase of `full` is observed)
+        if (!wait_bar_warp(&bar_full[s], (c / NS) & 1, abort_flag, kWaitTma, c)) break;
         float beta = 1.f, alpha = 0.f;
-        if (NORMS) beta = s_rq[s * kTcChunk + row];
-        else {
+        if constexpr (NORMS) {
+          // the row norm of x only needs the TMA data: taken while the MMAs run (the stage cannot be refilled before
+          // this group reports the accumulator MMAs)
+          beta = row_mask(keep_b, count_b, pos, N).kp ? inv_norm(row_sumsq2<T>(st_x(c), row)) : 0.f;
+          if (slice == 0 && pos < N && a.rq_out) a.rq_out[row_base + pos] = beta;
+          if (lane == 0) mbar_arrive(&bar_free_in[s]);  // (warp-converged) this warp is done with the X tile
+        } else {
           if (a.oscale) beta = pos < N ? a.oscale[row_base + pos] : 0.f;
-          if (a.has_c && a.ccoef) alpha = pos < N ? a.ccoef[row_base + pos] : 0.f;
+          if (has_c && a.ccoef) alpha = pos < N ? a.ccoef[row_base + pos] : 0.f;
+        }
+        // this thread's C row, straight from global memory: issued now, so that the loads have the waits below to land
+        uint4 u[8];
+        if (has_c) {
+          const uint4* src = reinterpret_cast<const uint4*>(static_cast<const T*>(a.c) + (row_base + min(pos, N - 1)) * a.dz + 64 * slice);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) u[j] = pos < N ? src[j] : make_uint4(0, 0, 0, 0);
+        }
+        // the staging slot was last stored from two chunks ago
+        if (c >= 2 && !wait_bar_warp(&bar_stg_free[b], ((c - 2) >> 1) & 1, abort_flag, kWaitStageFree, c)) break;
+        if (has_c) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) *tile_piece(dst, row, j) = u[j];
         }
         if (!wait_bar_warp(&bar_acc_full[b], (c >> 1) & 1, abort_flag, kWaitAcc, c)) break;
         tc_fence_after_sync();
-        // the score and accumulator MMAs of this chunk have completed (the state group reports the state MMAs)
-        if (lane == 0) mbar_arrive(&bar_free_in[s]);
         const uint32_t tAcc = tAcc0 + 64 * b + lane_base;
-        unsigned char* dst = st_o(c);
-        if (a.has_c) {
+        if (has_c) {
           if (a.eps) {  // eps += beta (C_row . Acc_row), then the row itself
-            const float e = beta * row_from_acc_dot<T>(st_c(c), row, tAcc, beta);
+            const float e = beta * row_from_acc_dot<T>(dst, row, tAcc, beta);
             if (pos < N) atomicAdd(a.eps + row_base + pos, e);
           } else {
-            row_from_acc<T, true>(st_c(c), row, tAcc, beta, alpha);
+            row_from_acc<T, true>(dst, row, tAcc, beta, alpha);
           }
         } else {
           row_from_acc<T, false>(dst, row, tAcc, beta, 0.f);
@@ -452,7 +471,8 @@ wide_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CU
 }
 
 inline size_t wide_smem_bytes() {
-  return static_cast<size_t>(kWdStages * kWdStageBytes + 2 * kWdStateBytes + kWdStages * kTcChunk * sizeof(float) + 32 * sizeof(uint64_t));
+  return static_cast<size_t>(kWdStages * kWdStageBytes + 2 * kWdStateBytes + 2 * kTileBytes + kWdStages * kTcChunk * sizeof(float) +
+                             32 * sizeof(uint64_t));
 }
 
 // Exclusive prefix over the segments of each (b, h, slice), in scan order: prefix[u][seg] = sum_{s' < seg} state[u][s'].
@@ -465,6 +485,21 @@ __global__ void seg_prefix_kernel(const float* __restrict__ state, float* __rest
       prefix[base + static_cast<size_t>(s) * elems + e] = run;
       run += state[base + static_cast<size_t>(s) * elems + e];
     }
+  }
+}
+
+// The segment states of a pass whose roles of Y and Z are swapped are the transposes of these: with the full state
+// M[r][c] (128 x 128, r over the columns of Y, c over the columns of Z) stored as two [128 x 64] column slices,
+//   dst[u][I][seg][r][c] = src[u][r / 64][seg][64 I + c][r % 64]          (u = batch * heads + head, I = 0, 1)
+// (dq's prefix states from the forward's, dk's from dv's: two state-only launches less per backward).
+// grid = (B*H, nseg), any block size.
+__global__ void seg_transpose_kernel(const float* __restrict__ src, float* __restrict__ dst, int nseg) {
+  const int u = blockIdx.x, seg = blockIdx.y;
+  constexpr int E = kTcChunk * kTcD;  // 128 x 64
+  for (int e = threadIdx.x; e < 2 * E; e += blockDim.x) {
+    const int I = e / E, r = (e % E) / kTcD, c = e % kTcD;
+    dst[((static_cast<size_t>(u) * 2 + I) * nseg + seg) * E + r * kTcD + c] =
+        src[((static_cast<size_t>(u) * 2 + r / 64) * nseg + seg) * E + (64 * I + c) * kTcD + r % 64];
   }
 }
 

@@ -276,23 +276,23 @@ inline TileStrides dense_rows(long H, long N, long D) { return TileStrides{H * N
 
 template <typename T, bool REV, bool NORMS, bool STATE_ONLY>
 int launch_wide_t(const WideTensors& t, WideArgs a, int B, int H, int N, int dtype, int nseg, cudaStream_t stream) {
-  CUtensorMap mx, my, mz, mc, mo;
+  CUtensorMap mx, my, mz, mo;
   const int bf = dtype == COTT_BF16;
   int r;
   const void* xs = t.x ? t.x : t.y;  // STATE_ONLY launches have no X
   if ((r = make_tmap_rows64(&mx, xs, bf, B, H, N, dense_rows(H, N, 128), kTcChunk, 128)) ||
       (r = make_tmap_rows64(&my, t.y, bf, B, H, N, dense_rows(H, N, 128), kTcChunk, 128)) ||
       (r = make_tmap_rows64(&mz, t.z, bf, B, H, N, dense_rows(H, N, t.dz), kTcChunk, t.dz)) ||
-      (r = make_tmap_rows64(&mc, t.c ? t.c : t.z, bf, B, H, N, dense_rows(H, N, t.dz), kTcChunk, t.dz)) ||
       (r = make_tmap_rows64(&mo, t.out ? t.out : t.z, bf, B, H, N, dense_rows(H, N, t.dz), kTcChunk, t.dz)))
     return fail(COTT_ERR_CUDA, "cuTensorMapEncodeTiled failed for a head-dim-128 tensor: %d", r);
-  a.has_c = t.c != nullptr;
+  a.c = t.c;
+  a.dz = t.dz;
   a.H = H;
   a.N = N;
   auto kern = wide_kernel<T, REV, NORMS, STATE_ONLY>;
   const size_t smem = wide_smem_bytes();
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<dim3((unsigned)((long)B * H), t.dz / 64, nseg), kWdThreads, smem, stream>>>(mx, my, mz, mc, mo, a);
+  kern<<<dim3((unsigned)((long)B * H), t.dz / 64, nseg), kWdThreads, smem, stream>>>(mx, my, mz, mo, a);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
@@ -300,13 +300,18 @@ int launch_wide_t(const WideTensors& t, WideArgs a, int B, int H, int N, int dty
 // One scan-type pass over head-dim-128 tensors, cut into `nseg` segments per sequence when nseg > 1: the segments'
 // own states (STATE_ONLY launch), their exclusive prefix in scan order, then the pass itself.  `ws`: 2 x B*H*(dz/64)*nseg
 // fp32 [128 x 64] matrices (only touched when nseg > 1).
+// `given_prefix`: the prefix states are already there (a transposed copy of another pass's), skip the state-only launch.
+// After the call ws + A holds the prefix states this pass ran with (A = units * nseg matrices).
 template <typename T, bool REV, bool NORMS>
-int run_wide(const WideTensors& t, WideArgs a, int B, int H, int N, int dtype, int nseg_requested, float* ws, cudaStream_t stream) {
+int run_wide(const WideTensors& t, WideArgs a, int B, int H, int N, int dtype, int nseg_requested, float* ws, cudaStream_t stream,
+             const float* given_prefix = nullptr) {
   const SegPlan plan = plan_segments(N, nseg_requested);
   a.chunks_per_seg = plan.cps;
   a.init_state = nullptr;
   a.state_out = nullptr;
-  if (plan.nseg > 1) {
+  if (plan.nseg > 1 && given_prefix) {
+    a.init_state = given_prefix;
+  } else if (plan.nseg > 1) {
     const size_t units = (size_t)B * H * (t.dz / 64);
     const size_t A = units * plan.nseg * (size_t)(kTcChunk * kTcD);
     WideArgs sa = a;
@@ -344,14 +349,19 @@ int wide_seg_count(int B, int H, int N, int dz) {
 struct WideWs {
   float *rq, *rk, *w, *cq, *eps, *ck;
   int* count;
-  float* seg;
+  float* seg;      // 2 x A floats: the segments' own states and their prefix, of the pass that is running
+  float* seg_fwd;  // A floats: the forward's prefix states (the backward transposes them for dq)
+  float* seg_t;    // A floats: a transposed prefix for the pass that is running
 };
 WideWs wide_ws(void* workspace, int B, int H, int N) {
   const size_t V = (size_t)B * H * N;
   float* f = static_cast<float*>(workspace);
-  WideWs s{f, f + V, f + 2 * V, f + 3 * V, f + 4 * V, f + 5 * V, reinterpret_cast<int*>(f + 6 * V), nullptr};
+  WideWs s{f, f + V, f + 2 * V, f + 3 * V, f + 4 * V, f + 5 * V, reinterpret_cast<int*>(f + 6 * V), nullptr, nullptr, nullptr};
   const size_t cnt = ((size_t)B * N + 3) & ~(size_t)3;
+  const size_t A = wide_ws_floats(B, H, N, 128, wide_seg_count(B, H, N, 128)) / 2;
   s.seg = f + 6 * V + cnt;
+  s.seg_fwd = s.seg + 2 * A;
+  s.seg_t = s.seg_fwd + A;
   return s;
 }
 
@@ -368,7 +378,13 @@ int run_wide_fwd(const void* q, const void* k, const void* v, const unsigned cha
     a.keep = keep, a.count = ws.count;
   }
   WideTensors t{q, k, v, nullptr, out, 128};
-  return run_wide<T, false, true>(t, a, B, H, N, dtype, wide_seg_count(B, H, N, 128), ws.seg, stream);
+  const int nseg = plan_segments(N, wide_seg_count(B, H, N, 128)).nseg;
+  int st = run_wide<T, false, true>(t, a, B, H, N, dtype, nseg, ws.seg, stream);
+  if (st == COTT_OK && nseg > 1) {  // the backward's dq pass starts its segments from the transposes of these
+    const size_t A = wide_ws_floats(B, H, N, 128, nseg) / 2;
+    COTT_CUDA_TRY(cudaMemcpyAsync(ws.seg_fwd, ws.seg + A, A * sizeof(float), cudaMemcpyDeviceToDevice, stream));
+  }
+  return st;
 }
 
 template <typename T>
@@ -376,7 +392,9 @@ int run_wide_bwd(const void* q, const void* k, const void* v, const unsigned cha
                  void* workspace, void* dq, void* dk, void* dv, float* dnorm, int B, int H, int N, int dtype, cudaStream_t stream) {
   WideWs ws = wide_ws(workspace, B, H, N);
   const long rows = (long)B * H * N;
-  const int nseg = wide_seg_count(B, H, N, 128);
+  const int nseg = plan_segments(N, wide_seg_count(B, H, N, 128)).nseg;
+  const size_t A = wide_ws_floats(B, H, N, 128, nseg) / 2;
+  const dim3 tgrid((unsigned)((long)B * H), (unsigned)nseg);
   // -q^.dq^ / |q|^2 from q^_t . dq^_t = dO_t . O_t
   rowdot_coef_kernel<T><<<(unsigned)((rows * 16 + 255) / 256), 256, 0, stream>>>(static_cast<const T*>(dout), static_cast<const T*>(out), ws.rq,
                                                                                 ws.cq, rows);
@@ -386,7 +404,11 @@ int run_wide_bwd(const void* q, const void* k, const void* v, const unsigned cha
     WideArgs a = {};
     a.zscale = ws.w, a.oscale = ws.rq, a.ccoef = ws.cq;
     WideTensors t{dout, v, k, q, dq, 128};
-    if ((st = run_wide<T, false, false>(t, a, B, H, N, dtype, nseg, ws.seg, stream))) return st;
+    if (nseg > 1) {  // sum_s v_s (x) w_s k_s is the transpose of the forward's sum_s k_s (x) w_s v_s
+      seg_transpose_kernel<<<tgrid, 256, 0, stream>>>(ws.seg_fwd, ws.seg_t, nseg);
+      COTT_CUDA_TRY(cudaGetLastError());
+    }
+    if ((st = run_wide<T, false, false>(t, a, B, H, N, dtype, nseg, ws.seg, stream, nseg > 1 ? ws.seg_t : nullptr))) return st;
   }
   COTT_CUDA_TRY(cudaMemsetAsync(ws.eps, 0, sizeof(float) * rows, stream));
   COTT_CUDA_TRY(cudaMemsetAsync(dnorm, 0, sizeof(float) * H, stream));
@@ -403,7 +425,11 @@ int run_wide_bwd(const void* q, const void* k, const void* v, const unsigned cha
     WideArgs a = {};
     a.zscale = ws.rq, a.oscale = ws.w, a.ccoef = ws.ck;
     WideTensors t{v, dout, q, k, dk, 128};
-    if ((st = run_wide<T, true, false>(t, a, B, H, N, dtype, nseg, ws.seg, stream))) return st;
+    if (nseg > 1) {  // sum_t dO_t (x) q^_t is the transpose of the dv pass's sum_t q^_t (x) dO_t (its prefix is still in ws.seg + A)
+      seg_transpose_kernel<<<tgrid, 256, 0, stream>>>(ws.seg + A, ws.seg_t, nseg);
+      COTT_CUDA_TRY(cudaGetLastError());
+    }
+    if ((st = run_wide<T, true, false>(t, a, B, H, N, dtype, nseg, ws.seg, stream, nseg > 1 ? ws.seg_t : nullptr))) return st;
   }
   return COTT_OK;
 }
@@ -825,7 +851,7 @@ int cott_cos_attn_bwd_train(const void* q, const void* k, const void* v, const u
 size_t cott_cos_attn_wide_workspace_bytes(int B, int H, int N) {
   if (B <= 0 || H <= 0 || N <= 0) return 0;
   const size_t V = (size_t)B * H * N, cnt = ((size_t)B * N + 3) & ~(size_t)3;
-  return (6 * V + cnt + wide_ws_floats(B, H, N, 128, wide_seg_count(B, H, N, 128))) * sizeof(float);
+  return (6 * V + cnt + 2 * wide_ws_floats(B, H, N, 128, wide_seg_count(B, H, N, 128))) * sizeof(float);
 }
 
 static int check_wide_args(int B, int H, int N, int Dk, int Dv, int dtype) {

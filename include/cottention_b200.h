@@ -56,6 +56,17 @@ const char* cott_status_string(int status);
  * kept in fp32 (fp64 for COTT_F64).  Constraints: Dk % 16 == 0, 16 <= Dk <= 256
  * (the reference: D_attn % 16 == 0, D_attn >= 32, :372-374), Dv >= 1, N >= 0.
  * `out` may be the same buffer as `v` (the reference's inplace=true, :403-404).
+ *
+ * Kernels: 16-bit dtypes with D_attn = 64 or 128 and D_value a multiple of 64 run on the tensor cores (tcgen05; at 128
+ * both halves of q and k go into the same score and state accumulators, the counterpart of the reference's
+ * kernel_mod_4<T, 32>, :173-251); D_attn = 192 / 256 as 64-wide tensor-core launches on strided slices; everything else
+ * on the exact CUDA-core kernel.
+ * Memory: unlike the reference's kernel call, which needs no workspace, the tensor-core paths take stream-ordered
+ * scratch from a memory pool that the LIBRARY owns and keeps for the life of the process (cudaMallocFromPoolAsync /
+ * cudaFreeAsync on `stream`, release threshold = unlimited) in two cases: few (batch, head) pairs with a long sequence
+ * (fp32 segment states, 2 x B*H*ceil(Dv/64)*nseg*32 KB) and D_attn = 192 / 256 (one [B,H,N,64] partial result).  The
+ * allocation is visible under stream capture.  Callers that must control every byte use the fused entry points below,
+ * which take their workspace from the caller.
  */
 int cott_scan(const void* q, const void* k, const void* v, void* out, int B, int H, int N, int Dk,
               int Dv, int dtype, int reversed, void* stream);
