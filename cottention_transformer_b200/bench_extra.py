@@ -267,6 +267,34 @@ def bench_prefill_sharded(N, d, world=1, rank=0, iters=3, H=16):
     return t
 
 
+def bench_one_pass(B=8, H=16, N=4096, d=64, iters=20):
+    """The two backward routes at the headline shape, kernels only through the C ABI: forward / forward that also keeps
+    its chunk states, and the two-kernel backward / the one-pass backward that reads those states."""
+    L = _lib.lib()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev).manual_seed(1234)
+    q, k, v, do = (torch.randn(B, H, N, d, device=dev, generator=g).bfloat16() for _ in range(4))
+    out, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
+    nc, dnc = 0.5 * torch.ones(H, device=dev), torch.empty(H, device=dev)
+    saved = torch.empty(L.cott_cos_attn_saved_bytes(B, H, N), dtype=torch.uint8, device=dev)
+    st = _lib.stream_ptr(dev)
+    P = lambda t: t.data_ptr()  # noqa: E731
+    fns = {
+        "fwd_us": lambda: L.cott_cos_attn_fwd(P(q), P(k), P(v), P(nc), P(out), B, H, N, d, d, 3, st),
+        "fwd_keeping_states_us": lambda: L.cott_cos_attn_fwd_train(P(q), P(k), P(v), None, P(nc), P(out), P(saved), None, 1, None, B, H, N,
+                                                                   d, d, 3, st),
+        "bwd_two_kernels_us": lambda: L.cott_cos_attn_bwd(P(q), P(k), P(v), P(nc), P(do), P(dq), P(dk), P(dv), P(dnc), B, H, N, d, d, 3, st),
+        "bwd_one_pass_us": lambda: L.cott_cos_attn_bwd_train(P(q), P(k), P(v), None, P(nc), P(do), P(saved), None, 1, None, P(dq), P(dk),
+                                                             P(dv), P(dnc), B, H, N, d, d, 3, st),
+    }
+    res = {"what": f"causal backward routes, B={B} H={H} N={N} d={d} bf16, kernels only"}
+    for name, fn in fns.items():
+        res[name] = _time(lambda: _lib.check(fn(), name), iters, warmup=3) * 1e6
+    _lib.check_device_status()
+    res["hbm_passes"] = {"two_kernels": 11, "one_pass": 7.5, "forward_extra_for_one_pass": 0.5}
+    return res
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--decode-steps", type=int, default=256)
@@ -274,6 +302,8 @@ if __name__ == "__main__":
     ap.add_argument("--long-context", action="store_true", help="only the B=1 long-sequence prefill sweep")
     ap.add_argument("--scan", action="store_true", help="only the bare scan of the reference's kernel API, per dtype")
     ap.add_argument("--bidir-only", action="store_true", help="only the bidirectional benchmark")
+    ap.add_argument("--one-pass", action="store_true", help="only the two backward routes at the headline shape")
+    ap.add_argument("--prefill", nargs=2, type=int, metavar=("N", "D"), help="only one long-context prefill step (B=1, H=16)")
     a = ap.parse_args()
     if a.long_context:
         for n in (16384, 65536, 262144):
@@ -284,6 +314,15 @@ if __name__ == "__main__":
     if a.scan:
         print(json.dumps(bench_scan()))
         print(json.dumps(bench_scan_d128()))
+        raise SystemExit(0)
+    if a.one_pass:
+        print(json.dumps(bench_one_pass()))
+        raise SystemExit(0)
+    if a.prefill:
+        n, d = a.prefill
+        t = bench_prefill_sharded(n, d)
+        print(json.dumps({"what": f"causal fwd+bwd prefill, B=1 H=16 N={n} d={d} bf16", "us_per_step": t * 1e6,
+                          "frac": 11 * 16 * n * d * 2 / t / 1e9 / _peak_gbs()[0]}))
         raise SystemExit(0)
     if a.bidir_only:
         print(json.dumps(bench_bidir()))

@@ -476,10 +476,10 @@ inline size_t wide_smem_bytes() {
 }
 
 // Exclusive prefix over the segments of each (b, h, slice), in scan order: prefix[u][seg] = sum_{s' < seg} state[u][s'].
-// grid = B*H*slices, any block size; `elems` floats per matrix.
+// grid = (B*H*slices, any), any block size; `elems` floats per matrix (the elements are split over gridDim.y blocks).
 __global__ void seg_prefix_kernel(const float* __restrict__ state, float* __restrict__ prefix, int nseg, int elems) {
   const size_t base = static_cast<size_t>(blockIdx.x) * nseg * elems;
-  for (int e = threadIdx.x; e < elems; e += blockDim.x) {
+  for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < elems; e += gridDim.y * blockDim.x) {
     float run = 0.f;
     for (int s = 0; s < nseg; ++s) {
       prefix[base + static_cast<size_t>(s) * elems + e] = run;
@@ -492,11 +492,11 @@ __global__ void seg_prefix_kernel(const float* __restrict__ state, float* __rest
 // M[r][c] (128 x 128, r over the columns of Y, c over the columns of Z) stored as two [128 x 64] column slices,
 //   dst[u][I][seg][r][c] = src[u][r / 64][seg][64 I + c][r % 64]          (u = batch * heads + head, I = 0, 1)
 // (dq's prefix states from the forward's, dk's from dv's: two state-only launches less per backward).
-// grid = (B*H, nseg), any block size.
+// grid = (B*H, nseg, any), any block size.
 __global__ void seg_transpose_kernel(const float* __restrict__ src, float* __restrict__ dst, int nseg) {
   const int u = blockIdx.x, seg = blockIdx.y;
   constexpr int E = kTcChunk * kTcD;  // 128 x 64
-  for (int e = threadIdx.x; e < 2 * E; e += blockDim.x) {
+  for (int e = blockIdx.z * blockDim.x + threadIdx.x; e < 2 * E; e += gridDim.z * blockDim.x) {
     const int I = e / E, r = (e % E) / kTcD, c = e % kTcD;
     dst[((static_cast<size_t>(u) * 2 + I) * nseg + seg) * E + r * kTcD + c] =
         src[((static_cast<size_t>(u) * 2 + r / 64) * nseg + seg) * E + (64 * I + c) * kTcD + r % 64];

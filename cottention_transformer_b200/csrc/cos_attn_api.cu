@@ -322,7 +322,7 @@ int run_wide(const WideTensors& t, WideArgs a, int B, int H, int N, int dtype, i
     st.x = nullptr, st.c = nullptr, st.out = nullptr;
     int r = launch_wide_t<T, REV, NORMS, true>(st, sa, B, H, N, dtype, plan.nseg, stream);
     if (r) return r;
-    seg_prefix_kernel<<<(unsigned)units, 256, 0, stream>>>(ws, ws + A, plan.nseg, kTcChunk * kTcD);
+    seg_prefix_kernel<<<dim3((unsigned)units, 8), 256, 0, stream>>>(ws, ws + A, plan.nseg, kTcChunk * kTcD);
     COTT_CUDA_TRY(cudaGetLastError());
     a.init_state = ws + A;
   }
@@ -394,7 +394,7 @@ int run_wide_bwd(const void* q, const void* k, const void* v, const unsigned cha
   const long rows = (long)B * H * N;
   const int nseg = plan_segments(N, wide_seg_count(B, H, N, 128)).nseg;
   const size_t A = wide_ws_floats(B, H, N, 128, nseg) / 2;
-  const dim3 tgrid((unsigned)((long)B * H), (unsigned)nseg);
+  const dim3 tgrid((unsigned)((long)B * H), (unsigned)nseg, 8);
   // -q^.dq^ / |q|^2 from q^_t . dq^_t = dO_t . O_t
   rowdot_coef_kernel<T><<<(unsigned)((rows * 16 + 255) / 256), 256, 0, stream>>>(static_cast<const T*>(dout), static_cast<const T*>(out), ws.rq,
                                                                                 ws.cq, rows);
