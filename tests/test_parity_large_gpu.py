@@ -205,3 +205,34 @@ def test_a_wait_that_nothing_completes_is_reported_and_leaves_the_device_usable(
     _lib.check_device_status()
     ref = O.cos_attn_causal(q.double(), k.double(), v.double(), nc.double())
     assert _rel(out.cpu(), ref)[1] <= REL16
+
+
+def test_three_way_report_at_the_headline_shape(capsys):
+    """B=8, H=16, N=4096, d=64, bf16, the operator the reference exports (FastAttention2.kernel.bfloat16 and the three
+    scans of CustomAttention.backward): this library and the reference's own compiled kernel on the same rounded
+    inputs, each against the fp64 recurrence on four (batch, head) slices.  The reference keeps its running sums in
+    bf16 (combined_kernel_general.cu:121,143), so it is the less accurate of the two; this library must be within the
+    16-bit tolerance of the truth and no further from it than the reference is."""
+    from cottention_transformer_b200 import kernel as K
+    ref = load_reference_kernel()
+    if ref is None:
+        pytest.skip("oracle/_ref not built")
+    B, H, N, d = 8, 16, 4096, 64
+    q, k, v, do, _ = O.make_inputs(B, H, N, d, seed=1234, dtype=torch.bfloat16)
+    qc, kc, vc, dc = (t.cuda() for t in (q, k, v, do))
+    calls = {"out": (qc, kc, vc, False), "dq": (dc, vc, kc, False), "dk": (vc, dc, qc, True), "dv": (kc, qc, dc, True)}
+    slices = [(0, 0), (0, H - 1), (B - 1, 0), (B - 1, H - 1)]
+    lines = []
+    for name, (x, y, z, rev) in calls.items():
+        ours = K.bfloat16(x, y, z, 1, False, rev)
+        theirs = ref.bfloat16(x.clone(), y.clone(), z.clone(), 1, False, rev)
+        e_ours, e_ref = 0.0, 0.0
+        for b, h in slices:
+            truth = O.scan_recurrent(x[b:b + 1, h:h + 1].cpu(), y[b:b + 1, h:h + 1].cpu(), z[b:b + 1, h:h + 1].cpu(), rev, "f64")
+            e_ours = max(e_ours, _rel(ours[b:b + 1, h:h + 1], truth)[1])
+            e_ref = max(e_ref, _rel(theirs[b:b + 1, h:h + 1], truth)[1])
+        assert e_ours <= REL16 and e_ours <= e_ref + 1e-3, (name, e_ours, e_ref)
+        lines.append(f"{name}: this library {e_ours:.2e}, reference kernel {e_ref:.2e}")
+    with capsys.disabled():
+        print("\n[headline shape, bf16 scan and its three backward scans, worst Frobenius error vs the fp64 recurrence on 4 slices] "
+              + "; ".join(lines))
