@@ -46,12 +46,20 @@ _SIGNATURES = {
     "cott_bidir_bwd_strided": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "cott_bidir_fwd_static": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "cott_rotary": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, ctypes.c_longlong, _I, _I, _P],
+    "cott_cos_attn_fwd_rotary": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "cott_cos_attn_bwd_rotary": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "cott_check_status": [ctypes.POINTER(ctypes.c_int)],
     "cott_selftest_device_wait": [_I, _I, _I, _P],
 }
 _STR = {"cott_version": [], "cott_last_error": [], "cott_status_string": [_I]}
 _SIZE = {"cott_bidir_scratch_bytes": [_I, _I, _I, _I, _I, _I], "cott_cos_attn_saved_bytes": [_I, _I, _I],
          "cott_cos_attn_wide_workspace_bytes": [_I, _I, _I], "cott_cos_attn_seg_workspace_bytes": [_I, _I, _I, _I]}
+
+class CottRotaryTables(ctypes.Structure):
+    """``cott_rotary_tables``: fp32 sin / cos tables, the rotary dim and the element stride between batch entries."""
+    _fields_ = [("sin_table", ctypes.c_void_p), ("cos_table", ctypes.c_void_p), ("rot_dim", ctypes.c_int),
+                ("table_batch_stride", ctypes.c_longlong)]
+
 
 class CottLayout(ctypes.Structure):
     """``cott_layout``: element strides (batch, head, position) of q/k/v/dq/dk/dv and of out/dout."""

@@ -295,6 +295,45 @@ def bench_one_pass(B=8, H=16, N=4096, d=64, iters=20):
     return res
 
 
+def bench_rotary(B=8, H=16, N=1024, d=64, iters=20):
+    """The rotary embedding of q, k: inside the causal kernels against a pass of its own, on a packed [B, N, 3, H, 64]
+    tensor, kernels only through the C ABI (forward and backward timed separately)."""
+    import ctypes
+    L = _lib.lib()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev).manual_seed(1234)
+    qkv = torch.randn(B, N, 3, H, d, device=dev, generator=g).bfloat16()
+    dqkv = torch.empty_like(qkv)
+    do = torch.randn(B, N, H, d, device=dev, generator=g).bfloat16()
+    out = torch.empty_like(do)
+    nc, dnc = 0.5 * torch.ones(H, device=dev), torch.empty(H, device=dev)
+    ang = torch.arange(N, device=dev).float()[:, None] / (10000 ** (torch.arange(0, d, 2, device=dev).float() / d))
+    sin, cos = torch.sin(ang).contiguous(), torch.cos(ang).contiguous()
+    lay = _lib.CottLayout(N * 3 * H * d, d, 3 * H * d, N * H * d, d, H * d)
+    rlay = _lib.CottLayout(N * 3 * H * d, d, 3 * H * d, 0, 0, 0)
+    rot = _lib.CottRotaryTables(sin.data_ptr(), cos.data_ptr(), d, 0)
+    ws = torch.empty(L.cott_cos_attn_seg_workspace_bytes(B, H, N, 1), dtype=torch.uint8, device=dev)
+    st = _lib.stream_ptr(dev)
+    P = lambda t: t.data_ptr()  # noqa: E731
+    q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+    gq, gk, gv = dqkv[:, :, 0], dqkv[:, :, 1], dqkv[:, :, 2]
+    LB, RB = ctypes.byref(lay), ctypes.byref(rot)
+    fns = {
+        "fwd_us": lambda: L.cott_cos_attn_fwd_seg(P(q), P(k), P(v), None, P(nc), P(out), P(ws), 1, LB, B, H, N, d, d, 3, st),
+        "fwd_rotary_inside_us": lambda: L.cott_cos_attn_fwd_rotary(P(q), P(k), P(v), None, P(nc), P(out), P(ws), LB, RB, B, H, N, d, d, 3, st),
+        "bwd_us": lambda: L.cott_cos_attn_bwd_seg(P(q), P(k), P(v), None, P(nc), P(do), P(ws), 1, LB, P(gq), P(gk), P(gv), P(dnc), B, H,
+                                                  N, d, d, 3, st),
+        "bwd_rotary_inside_us": lambda: L.cott_cos_attn_bwd_rotary(P(q), P(k), P(v), None, P(nc), P(do), P(ws), LB, RB, P(gq), P(gk), P(gv),
+                                                                   P(dnc), B, H, N, d, d, 3, st),
+        "rotary_pass_us": lambda: L.cott_rotary(P(q), P(k), P(sin), P(cos), ctypes.byref(rlay), B, H, N, d, d, 0, 0, 3, st),
+    }
+    res = {"what": f"rotary embedding inside the causal kernels vs a pass of its own, packed QKV, B={B} H={H} N={N} d={d} bf16, kernels only"}
+    for name, fn in fns.items():
+        res[name] = _time(lambda: _lib.check(fn(), name), iters, warmup=3) * 1e6
+    _lib.check_device_status()
+    return res
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--decode-steps", type=int, default=256)
@@ -304,7 +343,11 @@ if __name__ == "__main__":
     ap.add_argument("--bidir-only", action="store_true", help="only the bidirectional benchmark")
     ap.add_argument("--one-pass", action="store_true", help="only the two backward routes at the headline shape")
     ap.add_argument("--prefill", nargs=2, type=int, metavar=("N", "D"), help="only one long-context prefill step (B=1, H=16)")
+    ap.add_argument("--rotary", nargs="?", type=int, const=1024, metavar="N", help="only the rotary routes, B=8 H=16 at sequence length N")
     a = ap.parse_args()
+    if a.rotary:
+        print(json.dumps(bench_rotary(N=a.rotary)))
+        raise SystemExit(0)
     if a.long_context:
         for n in (16384, 65536, 262144):
             print(json.dumps(bench_long_context(n)))

@@ -30,6 +30,7 @@ from .cos_attention import (cos_attn_bidirectional, cos_attn_bidirectional_packe
 class CosSelfAttention(nn.Module):
     permute = False  # True: the reference's layout handling (permute + contiguous copies around the op)
     rotary = None    # (sin, cos) fp32 [S, 32]: GPT-J rotary on q and k (GPTCosAttention.py:458-476), packed path only
+    rotary_separate = False  # True: a pass of its own over q, k (rotary_packed_) instead of inside the attention kernels
 
     def __init__(self, d_model, n_heads, causal):
         super().__init__()
@@ -41,12 +42,16 @@ class CosSelfAttention(nn.Module):
     def forward(self, x):
         B, S, D = x.shape
         qkv = self.qkv(x)
+        rot = None
         if self.rotary is not None and self.causal and not self.permute:
-            qkv = rotary_packed_(qkv, self.rotary[0][:S], self.rotary[1][:S], heads=self.h)
+            rot = (self.rotary[0][:S], self.rotary[1][:S])
+            if self.rotary_separate:
+                qkv, rot = rotary_packed_(qkv, rot[0], rot[1], heads=self.h), None
         qkv = qkv.view(B, S, 3, self.h, D // self.h)
         if not self.permute:  # strided tensor maps: no head split / merge copies
-            op = cos_attn_causal_packed if self.causal else cos_attn_bidirectional_packed
-            return self.proj(op(qkv, self.norm_const).reshape(B, S, D))
+            if self.causal:
+                return self.proj(cos_attn_causal_packed(qkv, self.norm_const, rotary=rot).reshape(B, S, D))
+            return self.proj(cos_attn_bidirectional_packed(qkv, self.norm_const).reshape(B, S, D))
         qkv = qkv.permute(2, 0, 3, 1, 4).contiguous()  # [3,B,H,S,d]
         op = cos_attn_causal if self.causal else cos_attn_bidirectional
         o = op(qkv[0], qkv[1], qkv[2], self.norm_const)
@@ -91,7 +96,7 @@ CONFIGS = {
 }
 
 
-def run_model(name, steps=10, warmup=3, layers=0, permute=False, rotary=False, ddp_bf16_grads=False):
+def run_model(name, steps=10, warmup=3, layers=0, permute=False, rotary=False, ddp_bf16_grads=False, rotary_separate=False):
     """One harness, on this rank's current CUDA device; under more than one rank the default process group must be
     initialised (NCCL).  Returns the result dict on rank 0, None elsewhere.
 
@@ -111,6 +116,7 @@ def run_model(name, steps=10, warmup=3, layers=0, permute=False, rotary=False, d
     if layers:
         cfg["n_layers"] = layers
     CosSelfAttention.rotary = None
+    CosSelfAttention.rotary_separate = rotary_separate
     if rotary:
         ang = torch.arange(cfg["seq"], device=dev).float()[:, None] / (10000 ** (torch.arange(0, 64, 2, device=dev).float() / 64))
         CosSelfAttention.rotary = (torch.sin(ang), torch.cos(ang))
@@ -174,14 +180,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (smoke runs)")
     ap.add_argument("--permute", action="store_true", help="permute + copy around the op instead of the packed layout")
-    ap.add_argument("--rotary", action="store_true", help="gpt: rotary embedding on q and k (in place on the packed projection)")
+    ap.add_argument("--rotary", action="store_true", help="gpt: rotary embedding on q and k, inside the attention kernels")
+    ap.add_argument("--rotary-separate", action="store_true", help="with --rotary: as a pass of its own, in place on the packed projection")
     ap.add_argument("--bf16-allreduce", action="store_true", help="DDP: all-reduce bf16 copies of the gradients")
     a = ap.parse_args()
     world, rank, local = (int(os.environ.get(k, d)) for k, d in (("WORLD_SIZE", 1), ("RANK", 0), ("LOCAL_RANK", 0)))
     torch.cuda.set_device(local)
     if world > 1:
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local))
-    res = run_model(a.model, a.steps, a.warmup, a.layers, a.permute, a.rotary, ddp_bf16_grads=a.bf16_allreduce)
+    res = run_model(a.model, a.steps, a.warmup, a.layers, a.permute, a.rotary, ddp_bf16_grads=a.bf16_allreduce,
+                    rotary_separate=a.rotary_separate)
     if rank == 0:
         print(json.dumps(res))
     if world > 1:

@@ -119,7 +119,7 @@ class _FusedCausalPacked(torch.autograd.Function):
     maps, so the head split / merge permutes (GPTCosAttention.py:447-449,478-479,500) cost no copy."""
 
     @staticmethod
-    def forward(ctx, qkv, norm_const, keep=None):
+    def forward(ctx, qkv, norm_const, keep=None, sin=None, cos=None):
         qkv = qkv.contiguous()
         B, N, three, H, D = qkv.shape
         nc = norm_const.detach().reshape(-1).to(device=qkv.device, dtype=torch.float32).contiguous()
@@ -128,44 +128,80 @@ class _FusedCausalPacked(torch.autograd.Function):
         L = _lib.lib()
         q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
         kp = None if keep is None else keep.to(device=qkv.device, dtype=torch.uint8).contiguous()
+        rot = None
+        if sin is not None:  # the rotary embedding of q, k inside the kernels (one segment per sequence)
+            per_batch = sin.dim() == 3 and sin.shape[0] > 1
+            rot = _lib.CottRotaryTables(_lib.ptr(sin), _lib.ptr(cos), 2 * sin.shape[-1], N * sin.shape[-1] if per_batch else 0)
         with torch.cuda.device(qkv.device):
-            nseg = L.cott_cos_attn_seg_count(B, H, N)
+            nseg = 1 if rot is not None else L.cott_cos_attn_seg_count(B, H, N)
             ws = torch.empty(L.cott_cos_attn_seg_workspace_bytes(B, H, N, nseg), dtype=torch.uint8, device=qkv.device)
-            st = L.cott_cos_attn_fwd_seg(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(kp), _lib.ptr(nc), _lib.ptr(out),
-                                         _lib.ptr(ws), nseg, ctypes.byref(lay), B, H, N, D, D, _lib.DTYPE_CODE[qkv.dtype],
-                                         _lib.stream_ptr(qkv.device))
-        _lib.check(st, "cott_cos_attn_fwd_seg")
-        ctx.save_for_backward(qkv, nc)
-        ctx.ws, ctx.nseg, ctx.kp, ctx.lay = ws, nseg, kp, lay
+            if rot is not None:
+                st = L.cott_cos_attn_fwd_rotary(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(kp), _lib.ptr(nc), _lib.ptr(out),
+                                                _lib.ptr(ws), ctypes.byref(lay), ctypes.byref(rot), B, H, N, D, D,
+                                                _lib.DTYPE_CODE[qkv.dtype], _lib.stream_ptr(qkv.device))
+            else:
+                st = L.cott_cos_attn_fwd_seg(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(kp), _lib.ptr(nc), _lib.ptr(out),
+                                             _lib.ptr(ws), nseg, ctypes.byref(lay), B, H, N, D, D, _lib.DTYPE_CODE[qkv.dtype],
+                                             _lib.stream_ptr(qkv.device))
+        _lib.check(st, "cott_cos_attn_fwd_rotary" if rot is not None else "cott_cos_attn_fwd_seg")
+        ctx.save_for_backward(qkv, nc, sin, cos)
+        ctx.ws, ctx.nseg, ctx.kp, ctx.lay, ctx.rot = ws, nseg, kp, lay, rot
         ctx.nc_shape, ctx.nc_dtype = norm_const.shape, norm_const.dtype
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        qkv, nc = ctx.saved_tensors
+        qkv, nc, sin, cos = ctx.saved_tensors
         B, N, three, H, D = qkv.shape
         dout = dout.contiguous().to(qkv.dtype)
         dqkv = torch.empty_like(qkv)
         dnc = torch.empty(H, dtype=torch.float32, device=qkv.device)
+        L = _lib.lib()
         with torch.cuda.device(qkv.device):
-            st = _lib.lib().cott_cos_attn_bwd_seg(
-                _lib.ptr(qkv[:, :, 0]), _lib.ptr(qkv[:, :, 1]), _lib.ptr(qkv[:, :, 2]), _lib.ptr(ctx.kp), _lib.ptr(nc),
-                _lib.ptr(dout), _lib.ptr(ctx.ws), ctx.nseg, ctypes.byref(ctx.lay), _lib.ptr(dqkv[:, :, 0]),
-                _lib.ptr(dqkv[:, :, 1]), _lib.ptr(dqkv[:, :, 2]), _lib.ptr(dnc), B, H, N, D, D, _lib.DTYPE_CODE[qkv.dtype],
-                _lib.stream_ptr(qkv.device))
-        _lib.check(st, "cott_cos_attn_bwd_seg")
-        return dqkv, dnc.reshape(ctx.nc_shape).to(ctx.nc_dtype), None
+            if ctx.rot is not None:
+                st = L.cott_cos_attn_bwd_rotary(
+                    _lib.ptr(qkv[:, :, 0]), _lib.ptr(qkv[:, :, 1]), _lib.ptr(qkv[:, :, 2]), _lib.ptr(ctx.kp), _lib.ptr(nc),
+                    _lib.ptr(dout), _lib.ptr(ctx.ws), ctypes.byref(ctx.lay), ctypes.byref(ctx.rot), _lib.ptr(dqkv[:, :, 0]),
+                    _lib.ptr(dqkv[:, :, 1]), _lib.ptr(dqkv[:, :, 2]), _lib.ptr(dnc), B, H, N, D, D, _lib.DTYPE_CODE[qkv.dtype],
+                    _lib.stream_ptr(qkv.device))
+            else:
+                st = L.cott_cos_attn_bwd_seg(
+                    _lib.ptr(qkv[:, :, 0]), _lib.ptr(qkv[:, :, 1]), _lib.ptr(qkv[:, :, 2]), _lib.ptr(ctx.kp), _lib.ptr(nc),
+                    _lib.ptr(dout), _lib.ptr(ctx.ws), ctx.nseg, ctypes.byref(ctx.lay), _lib.ptr(dqkv[:, :, 0]),
+                    _lib.ptr(dqkv[:, :, 1]), _lib.ptr(dqkv[:, :, 2]), _lib.ptr(dnc), B, H, N, D, D, _lib.DTYPE_CODE[qkv.dtype],
+                    _lib.stream_ptr(qkv.device))
+        _lib.check(st, "cott_cos_attn_bwd_rotary" if ctx.rot is not None else "cott_cos_attn_bwd_seg")
+        return dqkv, dnc.reshape(ctx.nc_shape).to(ctx.nc_dtype), None, None, None
 
 
-def cos_attn_causal_packed(qkv, norm_const, keep=None):
+def cos_attn_causal_packed(qkv, norm_const, keep=None, rotary=None):
     """Causal cosine attention on a packed ``[B, N, 3, H, 64]`` bf16 / fp16 tensor (the reshaped output of one QKV
     projection); returns ``[B, N, H, 64]`` (reshape to ``[B, N, H*64]`` for the output projection).  Same function
-    as ``cos_attn_causal`` on the permuted tensors, without the permute copies in either direction."""
+    as ``cos_attn_causal`` on the permuted tensors, without the permute copies in either direction.
+
+    ``rotary=(sin, cos)`` -- fp32 ``[N, rot/2]`` or ``[B, N, rot/2]``, the two halves of the module's
+    ``embed_positions`` gathered at ``position_ids`` (GPTCosAttention.py:458-476) -- applies the rotary embedding to
+    q and k **inside the kernels** (their tiles are rotated in shared memory, dq and dk are rotated back on the way
+    out): the same bits as ``rotary_packed_`` followed by this op, without that op's passes over q, k, dq, dk, and
+    ``qkv`` itself is left as the projection wrote it.  The rotary dim must be a multiple of 16; sequences that this
+    op would cut into segments (few heads, very long N) take the separate rotary pass instead."""
     if not qkv.is_cuda:
         raise RuntimeError("cos_attn_causal_packed needs a CUDA tensor (there is no CPU path)")
     if qkv.dim() != 5 or qkv.shape[2] != 3 or qkv.shape[-1] != 64 or qkv.dtype not in FUSED_DTYPES:
         raise RuntimeError("cos_attn_causal_packed takes a [B, N, 3, H, 64] bfloat16 / float16 tensor")
-    return _FusedCausalPacked.apply(qkv, norm_const, keep)
+    if rotary is None:
+        return _FusedCausalPacked.apply(qkv, norm_const, keep)
+    sin, cos = rotary
+    sin = sin.to(device=qkv.device, dtype=torch.float32).contiguous()
+    cos = cos.to(device=qkv.device, dtype=torch.float32).contiguous()
+    B, N, _, H, _ = qkv.shape
+    if sin.shape != cos.shape or sin.shape[-2] != N or (sin.dim() == 3 and sin.shape[0] not in (1, B)):
+        raise RuntimeError("sin / cos must be [N, rot/2] or [B, N, rot/2]")
+    with torch.cuda.device(qkv.device):
+        one_segment = _lib.lib().cott_cos_attn_seg_count(B, H, N) == 1
+    if (2 * sin.shape[-1]) % 16 or not one_segment:
+        return _FusedCausalPacked.apply(rotary_packed_(qkv.contiguous(), sin, cos), norm_const, keep)
+    return _FusedCausalPacked.apply(qkv, norm_const, keep, sin, cos)
 
 
 class _RotaryPacked(torch.autograd.Function):

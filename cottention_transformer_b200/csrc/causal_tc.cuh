@@ -365,6 +365,48 @@ __device__ __forceinline__ void scale_row_rolled(unsigned char* tile, int row, f
     *p1 = v;
   }
 }
+// Rotary position embedding inside the kernels (GPTCosAttention.py:458-476, "rotate every two"): the tables are
+// fp32 [N, 4 * pieces] (sin and cos of the `4 * pieces` rotated pairs of a position; one table per batch entry when
+// batch_stride != 0), `pieces` = rotary dim / 8 = the 16-byte pieces of a row that are rotated (a multiple of 2).
+struct RotArgs {
+  const float* sin;
+  const float* cos;
+  int pieces;
+  long long batch_stride;
+};
+// Rotates (INV: by the transposed rotation) the first 8 * pieces elements of row `row` of one or two tiles that hold
+// the same position, in place; `sin_row`, `cos_row` point at that position's table rows.
+template <typename T, bool INV, int NT>
+__device__ __forceinline__ void rotate_rows(unsigned char* t0, unsigned char* t1, int row, const float* __restrict__ sin_row,
+                                            const float* __restrict__ cos_row, int pieces) {
+#pragma unroll 1
+  for (int j = 0; j < pieces; j += 2) {
+    float4 sn[2], cs[2];
+    sn[0] = __ldg(reinterpret_cast<const float4*>(sin_row) + j);
+    cs[0] = __ldg(reinterpret_cast<const float4*>(cos_row) + j);
+    sn[1] = __ldg(reinterpret_cast<const float4*>(sin_row) + j + 1);
+    cs[1] = __ldg(reinterpret_cast<const float4*>(cos_row) + j + 1);
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      unsigned char* tile = t ? t1 : t0;
+#pragma unroll
+      for (int jj = 0; jj < 2; ++jj) {
+        uint4* p = tile_piece(tile, row, j + jj);
+        uint4 u = *p;
+        uint32_t* w = reinterpret_cast<uint32_t*>(&u);
+        const float s4[4] = {sn[jj].x, sn[jj].y, sn[jj].z, sn[jj].w}, c4[4] = {cs[jj].x, cs[jj].y, cs[jj].z, cs[jj].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = Pack2<T>::unpack(w[e]);
+          float xo, yo;
+          rot_pair(f.x, f.y, c4[e], INV ? -s4[e] : s4[e], xo, yo);
+          w[e] = Pack2<T>::pack(xo, yo);
+        }
+        *p = u;
+      }
+    }
+  }
+}
 // fp32 state (M=64 accumulator layout, see state_to_smem) -> 16-bit swizzled smem operand
 template <typename T>
 __device__ __forceinline__ void state_to_smem_rolled(uint32_t tS_lane, unsigned char* sS, int wq, int lane) {
@@ -444,15 +486,19 @@ constexpr int kTcStagesFwd = 4;  // the forward kernel has the shared memory for
 // sensitive to every instruction added to their loops, and the common case needs neither.
 // SAVE (forward only): the 16-bit state operand of every chunk -- the state BEFORE the chunk, [64 x 64], rows d_k --
 // is also written to `saved` ([B*H][chunks of the sequence][64][64], row-major), for the one-pass backward.
-template <typename T, int MODE, bool EXT, bool SAVE = false>
+// ROT (forward and dQ, EXT only, one segment): q and k are rotated by the rotary embedding inside the kernel -- the
+// Q and K tiles are rewritten in shared memory before any MMA reads them, and the dQ rows are rotated back before
+// they are stored -- so the tensors in HBM stay un-rotated and no separate pass over q, k, dq, dk is needed.
+template <typename T, int MODE, bool EXT, bool SAVE = false, bool ROT = false>
 __global__ void __launch_bounds__(kTcThreads, 1)
 causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapY,
                  const __grid_constant__ CUtensorMap mapZ, const __grid_constant__ CUtensorMap mapQ,
                  const __grid_constant__ CUtensorMap mapOut, const float* __restrict__ norm_const, int H, int N,
                  const float* __restrict__ init_state_arg, int chunks_per_seg_arg,
                  const unsigned char* __restrict__ keep_arg, const int* __restrict__ count_arg,
-                 uint4* __restrict__ saved = nullptr) {
+                 uint4* __restrict__ saved, const RotArgs rot) {
   using namespace ptx;
+  static_assert(!ROT || (EXT && !SAVE && (MODE == kModeFwd || MODE == kModeDq)), "rotary: forward / dQ, EXT, no saved states");
   // Shared memory: NS stages of the tiles that are only read (forward: Y, Z; dQ: X, Y, Z), a ring of
   // NS + 1 tiles for the tile that doubles as the output staging buffer (forward: X; dQ: q), the 16-bit
   // state operand (2 x 8 KB).  The ring is one slot longer than the stage count, so the tile of chunk c+NS
@@ -499,6 +545,10 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   const int* count_b = (EXT && count_arg) ? count_arg + static_cast<size_t>(bh / H) * N : nullptr;
   // first row of local chunk c (the reversed scan numbers chunks and segments from the end of the sequence)
   auto row0_of = [&](int c) { return (kRev ? total_chunks - 1 - (chunk0 + c) : chunk0 + c) * kTcChunk; };
+  // table rows of position `pos` of this CTA's batch entry
+  const long long rot_base = ROT ? static_cast<long long>(bb) * rot.batch_stride : 0;
+  auto rot_sin = [&](int pos) { return rot.sin + rot_base + static_cast<long long>(pos) * (4 * rot.pieces); };
+  auto rot_cos = [&](int pos) { return rot.cos + rot_base + static_cast<long long>(pos) * (4 * rot.pieces); };
 
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
@@ -562,7 +612,10 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         for (int k = 0; k < 4; ++k) mma_ss(tP, dX + 2 * k, dY + 2 * k, kIdescP, k > 0);
         mma_commit(&bar_p_full[c & 1]);
       };
-      bool ok = wait_bar1(&bar_full[0], 0, abort_flag, kWaitTma, 0);
+      // (with the rotary embedding in the kernel the scores read the rotated Q and K tiles: wait for the operand group)
+      constexpr bool kRotScores = ROT && MODE == kModeFwd;
+      bool ok = kRotScores ? wait_bar2(&bar_full[0], 0, &bar_prep[0], 0, abort_flag, kWaitTma, 0)
+                           : wait_bar1(&bar_full[0], 0, abort_flag, kWaitTma, 0);
       if (ok) {
         tc_fence_after_sync();
         issue_scores(0);
@@ -572,7 +625,8 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
           // scores of chunk c+1: its TMA, and (buffer reuse) the accumulator MMAs of chunk c-1 done
           const int s1 = (c + 1) % NS;
           ok = wait_bar4(&bar_full[s1], ((c + 1) / NS) & 1, c >= 1 ? &bar_acc_full[(c + 1) & 1] : nullptr,
-                         ((c - 1) >> 1) & 1, nullptr, 0, nullptr, 0, abort_flag, kWaitTma, c);
+                         ((c - 1) >> 1) & 1, kRotScores ? &bar_prep[s1] : nullptr, ((c + 1) / NS) & 1, nullptr, 0, abort_flag,
+                         kWaitTma, c);
           if (!ok) break;
           tc_fence_after_sync();
           issue_scores(c + 1);
@@ -740,6 +794,13 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       if ((c & 1) != mine) continue;
       unsigned char* sZ = stage_of(c) + kIdxZ * kTileBytes;
       unsigned char* sK = (MODE == kModeDq) ? sZ : stage_of(c) + kIdxY * kTileBytes;
+      if constexpr (ROT) {  // forward: the Q and K rows of this position; dQ: the K row (its Z operand)
+        const int pos = row0_of(c) + row;
+        if (pos < N) {
+          if (MODE == kModeFwd) rotate_rows<T, false, 2>(ring_of(c), sK, row, rot_sin(pos), rot_cos(pos), rot.pieces);
+          else rotate_rows<T, false, 1>(sK, sK, row, rot_sin(pos), rot_cos(pos), rot.pieces);
+        }
+      }
       if constexpr (!kScan) {
         const RowMask m = row_mask(keep_b, count_b, row0_of(c) + row, N);
         const float rk = m.kp ? inv_norm(row_sumsq_rolled<T>(sK, row)) : 0.f;
@@ -760,9 +821,17 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       // (every phase of `full` is observed, also for the other group's chunks: see the operand groups)
       if (!wait_bar_warp(&bar_full[s], (c / NS) & 1, abort_flag, kWaitTma, c)) break;
       if ((c & 1) != mine) continue;
-      const float rq = kScan ? 1.f : row_mask(keep_b, count_b, row0_of(c) + row, N).kp ? inv_norm(row_sumsq_rolled<T>(sQ, row)) : 0.f;
+      // (rotary in the kernel: the dQ pass rotates its own q row first -- nothing else touches the q tile; the
+      // forward's X tile is rotated by the operand group, so its norm is taken once the MMAs, which wait for that
+      // group, have completed: the value read never depends on which of the two groups was faster)
+      const int pos = row0_of(c) + row;
+      if (ROT && MODE == kModeDq && pos < N) rotate_rows<T, false, 1>(sQ, sQ, row, rot_sin(pos), rot_cos(pos), rot.pieces);
+      float rq = 1.f;
+      if (!kScan && !(ROT && MODE == kModeFwd))
+        rq = row_mask(keep_b, count_b, pos, N).kp ? inv_norm(row_sumsq_rolled<T>(sQ, row)) : 0.f;
       if (!wait_bar_warp(&bar_acc_full[b], (c >> 1) & 1, abort_flag, kWaitAcc, c)) break;
       tc_fence_after_sync();
+      if (ROT && MODE == kModeFwd) rq = row_mask(keep_b, count_b, pos, N).kp ? inv_norm(row_sumsq_rolled<T>(sQ, row)) : 0.f;
       // The score and accumulator MMAs of this chunk have completed (the operand group reports the state
       // MMAs): the stage can be refilled.
       if (lane == 0) mbar_arrive(&bar_free_in[s]);
@@ -776,6 +845,8 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         // dq = (dq^ - q^ (q^ . dq^)) / |q| with dq^ = acc and q^ = rq q
         const float delta = row_dot_acc<T>(sQ, row, tAcc) * (rq * rq * rq);
         row_from_acc<T, true>(sQ, row, tAcc, rq, -delta);
+        // the row is the gradient of the rotated q: back through the rotation
+        if (ROT && pos < N) rotate_rows<T, true, 1>(sQ, sQ, row, rot_sin(pos), rot_cos(pos), rot.pieces);
       }
       tc_fence_before_sync();
       warp_arrive(&bar_acc_free[b], lane);
@@ -809,15 +880,18 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
 //   d norm_const[h] += -sigma (1 - sigma) sum_s ln(n_s) eps_s         (GPTCosAttention.py:241 by the chain rule)
 // Same warp roles as causal_tc_kernel; the two score tiles fill TMEM, so they are single-buffered:
 // the score MMAs of chunk c+1 are queued right behind the accumulator MMAs of chunk c.
-template <typename T, bool EXT>
+// ROT: as in causal_tc_kernel -- the Q and K tiles are rotated in shared memory (by the score group, before it
+// builds Qw), and the dK rows are rotated back before they are stored.
+template <typename T, bool EXT, bool ROT = false>
 __global__ void __launch_bounds__(kKvThreads, 1)
 causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                      const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
                      const __grid_constant__ CUtensorMap mapDK, const __grid_constant__ CUtensorMap mapDV, float* __restrict__ dnorm,
                      const float* __restrict__ norm_const, int H, int N, const float* __restrict__ init_state_arg,
                      int chunks_per_seg_arg, const unsigned char* __restrict__ keep_arg,
-                     const int* __restrict__ count_arg) {
+                     const int* __restrict__ count_arg, const RotArgs rot) {
   using namespace ptx;
+  static_assert(!ROT || EXT, "rotary: EXT only");
   constexpr int STAGE = 4 * kTileBytes;
   constexpr int NS = kTcStages;
   constexpr bool BF = Pack2<T>::kBf16;
@@ -850,6 +924,9 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   const bool has_init = EXT && init_state != nullptr && seg + 1 < static_cast<int>(gridDim.y);
   const unsigned char* keep_b = (EXT && keep_arg) ? keep_arg + static_cast<size_t>(bh / H) * N : nullptr;
   const int* count_b = (EXT && count_arg) ? count_arg + static_cast<size_t>(bh / H) * N : nullptr;
+  const long long rot_base = ROT ? static_cast<long long>(bb) * rot.batch_stride : 0;
+  auto rot_sin = [&](int pos) { return rot.sin + rot_base + static_cast<long long>(pos) * (4 * rot.pieces); };
+  auto rot_cos = [&](int pos) { return rot.cos + rot_base + static_cast<long long>(pos) * (4 * rot.pieces); };
 
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
@@ -987,7 +1064,9 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
         if (ci > 0 || has_init) {
           // the state terms need the 16-bit state after chunk ci-1 and the accumulators read out, not the
           // masked scores: they are issued while the score tiles are still being masked
-          if (ci > 0 ? !wait_bar2(&bar_state, (ci - 1) & 1, &bar_acc_free, (ci - 1) & 1, abort_flag, kWaitState, ci)
+          // (rotary in the kernel: they read the rotated K tile, which the score group reports with Qw)
+          if (ci > 0 ? !wait_bar4(&bar_state, (ci - 1) & 1, &bar_acc_free, (ci - 1) & 1, ROT ? &bar_prep[s] : nullptr,
+                                  (ci / NS) & 1, nullptr, 0, abort_flag, kWaitState, ci)
                      : !wait_bar1(&bar_init, 0, abort_flag, kWaitState, ci))
             break;
           tc_fence_after_sync();
@@ -1020,6 +1099,10 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       const int s = ci % NS;
       if (!wait_bar_warp(&bar_full[s], (ci / NS) & 1, abort_flag, kWaitTma, ci)) return false;
       unsigned char* sQ = smem + s * STAGE;
+      if constexpr (ROT) {
+        const int pos = (last_chunk - ci) * kTcChunk + row;
+        if (pos < N) rotate_rows<T, false, 2>(sQ, sQ + kTileBytes, row, rot_sin(pos), rot_cos(pos), rot.pieces);
+      }
       scale_row_rolled<T>(sQ, row, row_mask(keep_b, count_b, (last_chunk - ci) * kTcChunk + row, N).kp
                                        ? inv_norm(row_sumsq_rolled<T>(sQ, row))
                                        : 0.f);
@@ -1078,10 +1161,14 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       const int pos = (last_chunk - ci) * kTcChunk + row;
       if (!wait_bar_warp(&bar_full[s], (ci / NS) & 1, abort_flag, kWaitTma, ci)) break;
       const RowMask m = row_mask(keep_b, count_b, pos, N);
-      const float rk = m.kp ? inv_norm(row_sumsq_rolled<T>(sK, row)) : 0.f;
+      // (rotary in the kernel: the K tile is rotated by the score group, so the norm is taken once the MMAs, which
+      // wait for that group, have completed -- the value never depends on which group was faster)
+      float rk = 0.f;
+      if (!ROT) rk = m.kp ? inv_norm(row_sumsq_rolled<T>(sK, row)) : 0.f;
       const float a = length_factor(m.n, sigma);
       if (!wait_bar_warp(&bar_acc_full, ci & 1, abort_flag, kWaitAcc, ci)) break;
       tc_fence_after_sync();
+      if (ROT) rk = m.kp ? inv_norm(row_sumsq_rolled<T>(sK, row)) : 0.f;
       // dV first (its row product with v gives eps), then dK; each is staged as soon as it is ready, in
       // the V / K tile of this stage: every MMA that reads them completed before acc_full and this thread
       // is done with its own rows, so they have no reader left.  The TMA thread stores and refills them.
@@ -1093,6 +1180,8 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       row_from_acc<T, true>(sK, row, tK + lane_base, c1, -rk * rk * eps);
       tc_fence_before_sync();
       warp_arrive(&bar_acc_free, lane);
+      // the row is the gradient of the rotated k: back through the rotation
+      if (ROT && pos < N) rotate_rows<T, true, 1>(sK, sK, row, rot_sin(pos), rot_cos(pos), rot.pieces);
       ptx::fence_proxy_async_smem();
       warp_arrive(&bar_out[s], lane);
       if (m.n > 1.0f && pos < N) gsum += logf(m.n) * eps;

@@ -90,6 +90,14 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_acc<__nv_bfloat16>(flo
   return __float2bfloat16_rn(x);
 }
 
+// One pair of the rotary embedding ("rotate every two"): (x, y) -> (x c - y s, y c + x s).  Spelled with explicit
+// roundings so that every kernel that rotates -- the stand-alone pass and the causal kernels that rotate their tiles
+// in shared memory -- produces the same bits.
+__device__ __forceinline__ void rot_pair(float x, float y, float c, float s, float& xo, float& yo) {
+  xo = __fmaf_rn(x, c, -__fmul_rn(y, s));
+  yo = __fmaf_rn(y, c, __fmul_rn(x, s));
+}
+
 // Tensor-core path of the bidirectional form (defined next to the other tcgen05 kernels, which share the
 // device status word): head dim 64, 16-bit dtypes, 16-byte aligned tensors.  `*_usable` says whether a
 // problem qualifies; the launchers assume it does.

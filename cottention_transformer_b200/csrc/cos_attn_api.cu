@@ -48,6 +48,7 @@ struct SegPlan {
   const unsigned char* keep = nullptr;  // padding: [B, N] keep flags and their inclusive running count, or both null
   const int* count = nullptr;
   TileStrides in{0, 0, 0}, out{0, 0, 0};  // strides of q, k, v, dq, dk, dv / of out, dout; all zero = contiguous [B,H,N,64]
+  RotArgs rot{nullptr, nullptr, 0, 0};    // rotary embedding of q, k inside the kernels (one segment only), or sin = null
 };
 TileStrides in_strides(const SegPlan& p, long H, long N) { return p.in.n ? p.in : contiguous_bhnd(H, N); }
 TileStrides out_strides(const SegPlan& p, long H, long N) { return p.out.n ? p.out : contiguous_bhnd(H, N); }
@@ -70,13 +71,14 @@ int launch_fwd(const void* q, const void* k, const void* v, const float* nc, voi
       (st = tmap(&mo, out, dtype, B, H, N, out_strides(plan, H, N))))
     return st;
   const bool ext = plan.nseg > 1 || init || plan.keep;
-  auto kern = saved ? (ext ? causal_tc_kernel<T, kModeFwd, true, true> : causal_tc_kernel<T, kModeFwd, false, true>)
-                    : (ext ? causal_tc_kernel<T, kModeFwd, true, false> : causal_tc_kernel<T, kModeFwd, false, false>);
+  auto kern = plan.rot.sin ? causal_tc_kernel<T, kModeFwd, true, false, true>
+              : saved      ? (ext ? causal_tc_kernel<T, kModeFwd, true, true> : causal_tc_kernel<T, kModeFwd, false, true>)
+                           : (ext ? causal_tc_kernel<T, kModeFwd, true, false> : causal_tc_kernel<T, kModeFwd, false, false>);
   const size_t smem = causal_tc_smem_bytes(kModeFwd);
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   if (plan.cps == 0) plan.cps = plan_segments(N, 1).cps;
   kern<<<dim3((unsigned)BH, plan.nseg), kTcThreads, smem, stream>>>(mq, mk, mv, mq, mo, nc, H, N, init, plan.cps, plan.keep, plan.count,
-                                                                   static_cast<uint4*>(saved));
+                                                                   static_cast<uint4*>(saved), plan.rot);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
@@ -92,11 +94,12 @@ int launch_bwd_dq(const void* q, const void* k, const void* v, const float* nc, 
       (st = tmap(&mo, dq, dtype, B, H, N, in_strides(plan, H, N))))
     return st;
   const bool ext = plan.nseg > 1 || init || plan.keep;
-  auto kern = ext ? causal_tc_kernel<T, kModeDq, true> : causal_tc_kernel<T, kModeDq, false>;
+  auto kern = plan.rot.sin ? causal_tc_kernel<T, kModeDq, true, false, true>
+                           : (ext ? causal_tc_kernel<T, kModeDq, true> : causal_tc_kernel<T, kModeDq, false>);
   const size_t smem = causal_tc_smem_bytes(kModeDq);
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   if (plan.cps == 0) plan.cps = plan_segments(N, 1).cps;
-  kern<<<dim3((unsigned)BH, plan.nseg), kTcThreads, smem, stream>>>(md, mv, mk, mq, mo, nc, H, N, init, plan.cps, plan.keep, plan.count, nullptr);
+  kern<<<dim3((unsigned)BH, plan.nseg), kTcThreads, smem, stream>>>(md, mv, mk, mq, mo, nc, H, N, init, plan.cps, plan.keep, plan.count, nullptr, plan.rot);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
@@ -114,11 +117,12 @@ int launch_bwd_dkdv(const void* q, const void* k, const void* v, const float* nc
     return st;
   COTT_CUDA_TRY(cudaMemsetAsync(dnorm, 0, sizeof(float) * H, stream));
   const bool ext = plan.nseg > 1 || init || plan.keep;
-  auto kern = ext ? causal_bwd_kv_kernel<T, true> : causal_bwd_kv_kernel<T, false>;
+  auto kern = plan.rot.sin ? causal_bwd_kv_kernel<T, true, true>
+                           : (ext ? causal_bwd_kv_kernel<T, true> : causal_bwd_kv_kernel<T, false>);
   const size_t smem = causal_bwd_kv_smem_bytes();
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   if (plan.cps == 0) plan.cps = plan_segments(N, 1).cps;
-  kern<<<dim3((unsigned)BH, plan.nseg), kKvThreads, smem, stream>>>(mq, mk, mv, md, mdk, mdv, dnorm, nc, H, N, init, plan.cps, plan.keep, plan.count);
+  kern<<<dim3((unsigned)BH, plan.nseg), kKvThreads, smem, stream>>>(mq, mk, mv, md, mdk, mdv, dnorm, nc, H, N, init, plan.cps, plan.keep, plan.count, plan.rot);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
@@ -181,9 +185,10 @@ void apply_layout(SegPlan& plan, const cott_layout* l) {
 template <typename T>
 int run_fwd_seg(const void* q, const void* k, const void* v, const unsigned char* keep, const float* nc, void* out,
                 float* ws, int nseg, const cott_layout* layout, int B, int H, int N, int dtype, cudaStream_t stream,
-                void* saved = nullptr) {
+                void* saved = nullptr, RotArgs rot = RotArgs{nullptr, nullptr, 0, 0}) {
   SegPlan plan = plan_segments(N, nseg);
   apply_layout(plan, layout);
+  plan.rot = rot;
   const size_t A = seg_array_floats(B, H, plan.nseg);
   if (keep) {  // running count of the kept positions, behind the five state arrays
     int* count = reinterpret_cast<int*>(ws + 5 * A);
@@ -203,9 +208,10 @@ int run_fwd_seg(const void* q, const void* k, const void* v, const unsigned char
 template <typename T>
 int run_bwd_seg(const void* q, const void* k, const void* v, const unsigned char* keep, const float* nc, const void* dout,
                 float* ws, int nseg, const cott_layout* layout, void* dq, void* dk, void* dv, float* dnorm, int B, int H,
-                int N, int dtype, cudaStream_t stream) {
+                int N, int dtype, cudaStream_t stream, RotArgs rot = RotArgs{nullptr, nullptr, 0, 0}) {
   SegPlan plan = plan_segments(N, nseg);
   apply_layout(plan, layout);
+  plan.rot = rot;
   const size_t A = seg_array_floats(B, H, plan.nseg);
   if (keep) {  // the forward call left the running count in the workspace
     plan.keep = keep;
@@ -543,7 +549,7 @@ int launch_scan_tc_t(const void* q, const void* k, const void* v, void* out, int
   const size_t smem = causal_tc_smem_bytes(kModeScan);
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   kern<<<dim3((unsigned)((long)B * H), plan.nseg), kTcThreads, smem, stream>>>(mq, mk, mv, mq, mo, nullptr, H, N, init, plan.cps, nullptr,
-                                                                              nullptr, nullptr);
+                                                                              nullptr, nullptr, RotArgs{nullptr, nullptr, 0, 0});
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
@@ -799,6 +805,64 @@ int cott_cos_attn_bwd_seg(const void* q, const void* k, const void* v, const uns
   return dtype == COTT_BF16
              ? run_bwd_seg<__nv_bfloat16>(q, k, v, keep, norm_const, dout, ws, nseg, layout, dq, dk, dv, dnorm_const, B, H, N, dtype, s)
              : run_bwd_seg<__half>(q, k, v, keep, norm_const, dout, ws, nseg, layout, dq, dk, dv, dnorm_const, B, H, N, dtype, s);
+}
+
+namespace {
+// checks of the rotary argument shared by the two calls below
+int check_rotary(const cott_rotary_tables* r, RotArgs* out) {
+  if (!r || !r->sin_table || !r->cos_table) return fail(COTT_ERR_NULL, "null pointer: rotary tables");
+  if (r->rot_dim < 16 || r->rot_dim % 16 || r->rot_dim > kTcD)
+    return fail(COTT_ERR_SHAPE, "rotary dim must be a multiple of 16 between 16 and 64 (got %d)", r->rot_dim);
+  if (r->table_batch_stride & 3 || r->table_batch_stride < 0) return fail(COTT_ERR_ALIGN, "table_batch_stride must be a non-negative multiple of 4");
+  if ((reinterpret_cast<uintptr_t>(r->sin_table) | reinterpret_cast<uintptr_t>(r->cos_table)) & 15)
+    return fail(COTT_ERR_ALIGN, "rotary tables must be 16-byte aligned");
+  *out = RotArgs{r->sin_table, r->cos_table, r->rot_dim / 8, r->table_batch_stride};
+  return COTT_OK;
+}
+}  // namespace
+
+int cott_cos_attn_fwd_rotary(const void* q, const void* k, const void* v, const unsigned char* keep,
+                             const float* norm_const, void* out, void* workspace, const cott_layout* layout,
+                             const cott_rotary_tables* rotary, int B, int H, int N, int Dk, int Dv, int dtype, void* stream) {
+  int st = check_fused_args(B, H, N, Dk, Dv, dtype);
+  if (st) return st;
+  RotArgs rot;
+  if ((st = check_rotary(rotary, &rot))) return st;
+  if ((long)B * H * N == 0) return COTT_OK;
+  if ((st = check_ptrs16({{q, "q"}, {k, "k"}, {v, "v"}, {out, "out"}, {workspace, "workspace"}}))) return st;
+  if (!norm_const) return fail(COTT_ERR_NULL, "null pointer: norm_const");
+  DeviceScope scope(q);
+  COTT_CUDA_TRY(scope.status());
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  float* ws = static_cast<float*>(workspace);
+  return dtype == COTT_BF16 ? run_fwd_seg<__nv_bfloat16>(q, k, v, keep, norm_const, out, ws, 1, layout, B, H, N, dtype, s, nullptr, rot)
+                            : run_fwd_seg<__half>(q, k, v, keep, norm_const, out, ws, 1, layout, B, H, N, dtype, s, nullptr, rot);
+}
+
+int cott_cos_attn_bwd_rotary(const void* q, const void* k, const void* v, const unsigned char* keep,
+                             const float* norm_const, const void* dout, void* workspace, const cott_layout* layout,
+                             const cott_rotary_tables* rotary, void* dq, void* dk, void* dv, float* dnorm_const, int B,
+                             int H, int N, int Dk, int Dv, int dtype, void* stream) {
+  int st = check_fused_args(B, H, N, Dk, Dv, dtype);
+  if (st) return st;
+  RotArgs rot;
+  if ((st = check_rotary(rotary, &rot))) return st;
+  if (!dnorm_const && H > 0) return fail(COTT_ERR_NULL, "null pointer: dnorm_const");
+  if ((long)B * H * N == 0) {
+    if (H > 0) COTT_CUDA_TRY(cudaMemsetAsync(dnorm_const, 0, sizeof(float) * H, static_cast<cudaStream_t>(stream)));
+    return COTT_OK;
+  }
+  if ((st = check_ptrs16({{q, "q"}, {k, "k"}, {v, "v"}, {dout, "dout"}, {dq, "dq"}, {dk, "dk"}, {dv, "dv"},
+                          {workspace, "workspace"}})))
+    return st;
+  if (!norm_const) return fail(COTT_ERR_NULL, "null pointer: norm_const");
+  DeviceScope scope(q);
+  COTT_CUDA_TRY(scope.status());
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  float* ws = static_cast<float*>(workspace);
+  return dtype == COTT_BF16
+             ? run_bwd_seg<__nv_bfloat16>(q, k, v, keep, norm_const, dout, ws, 1, layout, dq, dk, dv, dnorm_const, B, H, N, dtype, s, rot)
+             : run_bwd_seg<__half>(q, k, v, keep, norm_const, dout, ws, 1, layout, dq, dk, dv, dnorm_const, B, H, N, dtype, s, rot);
 }
 
 size_t cott_cos_attn_saved_bytes(int B, int H, int N) {

@@ -55,7 +55,9 @@ __global__ void rotary_kernel(T* __restrict__ q, T* __restrict__ k, const float*
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const float2 f = Pair16<T>::unpack(w[e]);
-      w[e] = Pair16<T>::pack(f.x * c[e] - f.y * s[e], f.y * c[e] + f.x * s[e]);
+      float xo, yo;
+      rot_pair(f.x, f.y, c[e], s[e], xo, yo);
+      w[e] = Pair16<T>::pack(xo, yo);
     }
   }
   *reinterpret_cast<uint4*>(q + off) = u[0];

@@ -346,6 +346,32 @@ int cott_selftest_device_wait(int polls, int code, int chunk, void* stream);
 int cott_rotary(void* q, void* k, const float* sin_table, const float* cos_table, const cott_layout* layout, int B,
                 int H, int N, int D, int rot_dim, long long table_batch_stride, int inverse, int dtype, void* stream);
 
+/*
+ * The fused causal forward / backward with the rotary position embedding of the reference's GPT module folded in
+ * (GPT_Trainer/GPTCosAttention.py:458-476 followed by :229-248,282): q and k are rotated inside the kernels -- their
+ * tiles are rewritten in shared memory before any product reads them, and the dq and dk rows are rotated back before
+ * they are stored -- so q, k in device memory stay as the projection wrote them and the separate passes over q, k
+ * (forward) and dq, dk (backward) of cott_rotary are not needed.  Results are those of cott_rotary followed by
+ * cott_cos_attn_fwd_seg / _bwd_seg with nseg = 1 (bit for bit: the same fp32 arithmetic and the same roundings).
+ * Arguments as for those calls (keep, layout and workspace included; workspace of
+ * cott_cos_attn_seg_workspace_bytes(B, H, N, 1) bytes, passed untouched from the forward to the backward call),
+ * one segment per sequence; `rotary` as for cott_rotary, with rot_dim a multiple of 16, 16 <= rot_dim <= 64.
+ */
+typedef struct cott_rotary_tables {
+  const float* sin_table;         /* fp32 [N, rot_dim/2], or [B, N, rot_dim/2] with table_batch_stride = N * rot_dim/2 */
+  const float* cos_table;
+  int rot_dim;                    /* the first rot_dim elements of every head are rotated */
+  long long table_batch_stride;   /* 0 = one table for every batch entry */
+} cott_rotary_tables;
+int cott_cos_attn_fwd_rotary(const void* q, const void* k, const void* v, const unsigned char* keep,
+                             const float* norm_const, void* out, void* workspace, const cott_layout* layout,
+                             const cott_rotary_tables* rotary, int B, int H, int N, int Dk, int Dv, int dtype,
+                             void* stream);
+int cott_cos_attn_bwd_rotary(const void* q, const void* k, const void* v, const unsigned char* keep,
+                             const float* norm_const, const void* dout, void* workspace, const cott_layout* layout,
+                             const cott_rotary_tables* rotary, void* dq, void* dk, void* dv, float* dnorm_const,
+                             int B, int H, int N, int Dk, int Dv, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -374,6 +374,45 @@ def test_rotary_packed_matches_rotate_every_two(dt, d, rot, per_batch):
     assert (x.grad.float() - xr.grad).abs().max().item() <= 8 * tol * w.abs().max().item()
 
 
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("N,rot,per_batch,masked", [(1, 64, False, False), (100, 64, False, True), (128, 32, True, False),
+                                                    (129, 16, False, False), (640, 64, True, True), (1000, 48, False, False),
+                                                    (4096, 64, False, False)])
+def test_rotary_inside_the_kernels_is_bit_identical_to_the_separate_pass(dt, N, rot, per_batch, masked):
+    """``cos_attn_causal_packed(qkv, ..., rotary=(sin, cos))`` rotates the Q and K tiles in shared memory and the dq, dk
+    rows on their way out; it must give the bits of ``rotary_packed_`` followed by ``cos_attn_causal_packed`` -- output,
+    all of dqkv and the norm_const gradient -- and leave ``qkv`` itself un-rotated.  (A rotary dim that is not a
+    multiple of 16 takes the separate pass inside the op; that route is covered by the same comparison.)"""
+    from cottention_transformer_b200 import cos_attn_causal_packed, rotary_packed_, _lib
+    B, H, d = 2, 40, 64          # 80 sequences: one segment per sequence on a 148-SM part, so the kernels rotate
+    g = torch.Generator(device="cuda").manual_seed(N + rot)
+    base = torch.randn(B, N, 3, H, d, device="cuda", generator=g).to(dt)
+    pos = torch.arange(N, device="cuda").float()[None, :, None] + (torch.arange(B, device="cuda").float()[:, None, None] * 5 if per_batch else 0)
+    ang = pos / (10000 ** (torch.arange(0, rot, 2, device="cuda").float() / rot))
+    sin, cos = (torch.sin(ang), torch.cos(ang)) if per_batch else (torch.sin(ang)[0], torch.cos(ang)[0])
+    keep = None
+    if masked:
+        keep = torch.rand(B, N, device="cuda", generator=g) > 0.2
+        keep[:, -1] = True
+    do = torch.randn(B, N, H, d, device="cuda", generator=g).to(dt)
+    res = []
+    for in_kernel in (False, True):
+        x = base.clone().requires_grad_()
+        nc = torch.linspace(-1.0, 1.5, H, device="cuda").view(1, H, 1, 1).requires_grad_()
+        if in_kernel:
+            out = cos_attn_causal_packed(x, nc, keep, rotary=(sin, cos))
+        else:
+            y = rotary_packed_((x * 1).view(B, N, 3 * H * d), sin, cos, heads=H).view(B, N, 3, H, d)
+            out = cos_attn_causal_packed(y, nc, keep)
+        out.backward(do)
+        _lib.check_device_status()
+        res.append((out.detach(), x.grad, nc.grad))
+    assert torch.equal(res[0][0], res[1][0])
+    assert torch.equal(res[0][1], res[1][1])
+    # (the norm_const gradient is summed by atomics, whose order is not fixed from launch to launch)
+    assert torch.allclose(res[0][2], res[1][2], rtol=1e-4, atol=1e-5 * res[0][2].abs().max().item())
+
+
 def test_rotary_backward_leaves_a_shared_gradient_alone():
     """The rotated tensor and another tensor are summed: autograd hands the SAME gradient tensor to both branches.
     The rotary backward works in place, so it must do so on a private copy -- the other branch has to receive the

@@ -59,14 +59,17 @@ def test_unmodified_reference_module_runs_on_this_library(reference_gpt_module, 
         assert err <= tol, (name, err)
 
 
+@pytest.mark.parametrize("rotary_in_kernel", [False, True])
 @pytest.mark.parametrize("name", ["rot32", "rot64"])
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
-def test_packed_pipeline_matches_the_reference_module_forward(name, dt):
+def test_packed_pipeline_matches_the_reference_module_forward(name, dt, rotary_in_kernel):
     """``GPTCosAttention.forward`` (:427-511) recorded from the reference in float64 -- projections, rotary embedding by
     ``transformers``' ``apply_rotary_pos_emb`` with per-batch positions, head split / merge permutes, ``_cos_attn`` with a
     padding mask, output projection -- against this library's pipeline for the same module: ONE QKV projection,
     ``rotary_packed_`` in place on it, ``cos_attn_causal_packed`` on the packed tensor (strided tensor maps, no
-    permute copies), output projection.  16-bit tolerance on the output and on the gradients."""
+    permute copies), output projection.  16-bit tolerance on the output and on the gradients.
+    ``rotary_in_kernel``: the rotary embedding is applied by the attention kernels themselves
+    (``cos_attn_causal_packed(..., rotary=(sin, cos))``) instead of by a pass of its own."""
     from cottention_transformer_b200 import cos_attn_causal_packed, rotary_packed_
     g = np.load(os.path.join(GOLDEN, f"gpt_module_forward_{name}.npz"))
     H = int(g["num_heads"])
@@ -80,8 +83,11 @@ def test_packed_pipeline_matches_the_reference_module_forward(name, dt):
     sin, cos = torch.from_numpy(g["sin"]).float().cuda(), torch.from_numpy(g["cos"]).float().cuda()   # [B, S, rot/2]
     # (the projections stay in fp32 so that the 16-bit error measured below is the attention path's, not the GEMMs')
     qkv = torch.nn.functional.linear(hidden, wqkv).to(dt)                    # [B, S, 3*H*d], q | k | v blocks of H*d
-    qkv = rotary_packed_(qkv, sin, cos, heads=H)
-    ctx = cos_attn_causal_packed(qkv.view(B, S, 3, H, d), nc, keep)          # [B, S, H, d]
+    if rotary_in_kernel:
+        ctx = cos_attn_causal_packed(qkv.view(B, S, 3, H, d), nc, keep, rotary=(sin, cos))
+    else:
+        qkv = rotary_packed_(qkv, sin, cos, heads=H)
+        ctx = cos_attn_causal_packed(qkv.view(B, S, 3, H, d), nc, keep)      # [B, S, H, d]
     out = torch.nn.functional.linear(ctx.reshape(B, S, E).float(), wo)
     do = torch.from_numpy(g["dout"]).cuda()
     (out.float() * do).sum().backward()
