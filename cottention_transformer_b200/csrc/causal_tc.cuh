@@ -374,38 +374,61 @@ struct RotArgs {
   int pieces;
   long long batch_stride;
 };
-// Rotates (INV: by the transposed rotation) the first 8 * pieces elements of row `row` of one or two tiles that hold
-// the same position, in place; `sin_row`, `cos_row` point at that position's table rows.
+// A warp rotates its own 32 rows of a tile (rows 32 (warp % 4) ..): lane l takes piece l % 8 of the rows 4 i + l / 8,
+// i = 0 .. 7, so that one load instruction of the warp covers four whole table rows (row-per-thread loads touch 32
+// different lines per instruction and are bound by the load pipe).  A round = the table values of four of a lane's
+// eight rows, in registers; the loads of round 0 are issued before the wait that precedes the rotation (the position
+// is known in advance), so their latency -- an L2 round trip -- hides behind it.
+struct RotRegs {
+  float4 sn[4], cs[4];
+};
+// `sin_tab`, `cos_tab`: the table rows of the warp's first row; `nrows`: how many of the warp's rows exist (<= 32)
+__device__ __forceinline__ void rot_load(RotRegs& t, const float* __restrict__ sin_tab, const float* __restrict__ cos_tab, int lane,
+                                         int round, int pieces, int nrows) {
+  const int pj = lane & 7;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = 16 * round + 4 * i + (lane >> 3);
+    if (pj < pieces && r < nrows) {
+      t.sn[i] = __ldg(reinterpret_cast<const float4*>(sin_tab + static_cast<size_t>(r) * (4 * pieces)) + pj);
+      t.cs[i] = __ldg(reinterpret_cast<const float4*>(cos_tab + static_cast<size_t>(r) * (4 * pieces)) + pj);
+    }
+  }
+}
+// Rotates (INV: by the transposed rotation) the first 8 * pieces elements of the warp's rows `row_base` .. of one or
+// two tiles that hold the same positions, in place; `t` holds round 0.  Ends with a __syncwarp: the rows are then
+// read row-per-thread.
 template <typename T, bool INV, int NT>
-__device__ __forceinline__ void rotate_rows(unsigned char* t0, unsigned char* t1, int row, const float* __restrict__ sin_row,
-                                            const float* __restrict__ cos_row, int pieces) {
+__device__ __forceinline__ void rotate_rows(RotRegs& t, unsigned char* t0, unsigned char* t1, int row_base, int lane,
+                                            const float* __restrict__ sin_tab, const float* __restrict__ cos_tab, int pieces,
+                                            int nrows) {
+  const int pj = lane & 7;
 #pragma unroll 1
-  for (int j = 0; j < pieces; j += 2) {
-    float4 sn[2], cs[2];
-    sn[0] = __ldg(reinterpret_cast<const float4*>(sin_row) + j);
-    cs[0] = __ldg(reinterpret_cast<const float4*>(cos_row) + j);
-    sn[1] = __ldg(reinterpret_cast<const float4*>(sin_row) + j + 1);
-    cs[1] = __ldg(reinterpret_cast<const float4*>(cos_row) + j + 1);
+  for (int round = 0; round < 2; ++round) {
+    if (round) rot_load(t, sin_tab, cos_tab, lane, 1, pieces, nrows);
 #pragma unroll
-    for (int t = 0; t < NT; ++t) {
-      unsigned char* tile = t ? t1 : t0;
+    for (int i = 0; i < 4; ++i) {
+      const int r = 16 * round + 4 * i + (lane >> 3);
+      if (pj < pieces && r < nrows) {
+        const float s4[4] = {t.sn[i].x, t.sn[i].y, t.sn[i].z, t.sn[i].w}, c4[4] = {t.cs[i].x, t.cs[i].y, t.cs[i].z, t.cs[i].w};
 #pragma unroll
-      for (int jj = 0; jj < 2; ++jj) {
-        uint4* p = tile_piece(tile, row, j + jj);
-        uint4 u = *p;
-        uint32_t* w = reinterpret_cast<uint32_t*>(&u);
-        const float s4[4] = {sn[jj].x, sn[jj].y, sn[jj].z, sn[jj].w}, c4[4] = {cs[jj].x, cs[jj].y, cs[jj].z, cs[jj].w};
+        for (int tt = 0; tt < NT; ++tt) {
+          uint4* p = tile_piece(tt ? t1 : t0, row_base + r, pj);
+          uint4 u = *p;
+          uint32_t* w = reinterpret_cast<uint32_t*>(&u);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f = Pack2<T>::unpack(w[e]);
-          float xo, yo;
-          rot_pair(f.x, f.y, c4[e], INV ? -s4[e] : s4[e], xo, yo);
-          w[e] = Pack2<T>::pack(xo, yo);
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = Pack2<T>::unpack(w[e]);
+            float xo, yo;
+            rot_pair(f.x, f.y, c4[e], INV ? -s4[e] : s4[e], xo, yo);
+            w[e] = Pack2<T>::pack(xo, yo);
+          }
+          *p = u;
         }
-        *p = u;
       }
     }
   }
+  __syncwarp();
 }
 // fp32 state (M=64 accumulator layout, see state_to_smem) -> 16-bit swizzled smem operand
 template <typename T>
@@ -479,6 +502,7 @@ enum {
 
 constexpr int kTcThreads = 896;  // forward / dQ: 3 issuing warps, 6 groups of 4 warps, 1 TMA warp
 constexpr int kKvThreads = 480;  // dK/dV: 2 issuing warps, 3 groups of 4 warps, 1 TMA warp
+constexpr int kKvThreadsRot = 608;  // + a group that rotates the Q and K tiles (rotary embedding inside the kernel)
 constexpr int kTcStages = 3;
 constexpr int kTcStagesFwd = 4;  // the forward kernel has the shared memory for a deeper ring (2 tiles per stage)
 
@@ -790,17 +814,17 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       // Every phase of a barrier has to be observed, also for the chunks of the other group: a parity
       // wait cannot tell phase n from phase n+2, and with 3 stages a group that only looked at its own
       // chunks would skip every other phase of each `full` barrier.
+      RotRegs rt;
+      const int wrow0 = row0_of(c) + 32 * (warp & 3);  // position of the warp's first row
+      if (ROT && (c & 1) == mine) rot_load(rt, rot_sin(wrow0), rot_cos(wrow0), lane, 0, rot.pieces, N - wrow0);
       if (!wait_bar_warp(&bar_full[s], (c / NS) & 1, abort_flag, kWaitTma, c)) break;
       if ((c & 1) != mine) continue;
       unsigned char* sZ = stage_of(c) + kIdxZ * kTileBytes;
       unsigned char* sK = (MODE == kModeDq) ? sZ : stage_of(c) + kIdxY * kTileBytes;
-      if constexpr (ROT) {  // forward: the Q and K rows of this position; dQ: the K row (its Z operand)
-        const int pos = row0_of(c) + row;
-        if (pos < N) {
-          if (MODE == kModeFwd) rotate_rows<T, false, 2>(ring_of(c), sK, row, rot_sin(pos), rot_cos(pos), rot.pieces);
-          else rotate_rows<T, false, 1>(sK, sK, row, rot_sin(pos), rot_cos(pos), rot.pieces);
-        }
-      }
+      // (rotary: the K rows and the Q / q rows of these positions, with the same table values.  This group runs ahead
+      // of the MMAs -- it waits for nothing but the loads -- so the rotation is off the chain that sets the chunk period.)
+      if constexpr (ROT)
+        rotate_rows<T, false, 2>(rt, ring_of(c), sK, 32 * (warp & 3), lane, rot_sin(wrow0), rot_cos(wrow0), rot.pieces, N - wrow0);
       if constexpr (!kScan) {
         const RowMask m = row_mask(keep_b, count_b, row0_of(c) + row, N);
         const float rk = m.kp ? inv_norm(row_sumsq_rolled<T>(sK, row)) : 0.f;
@@ -819,19 +843,16 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       unsigned char* sQ = ring_of(c);  // forward: X; dQ: q
       // the row norm of q only needs the TMA data: do it while the MMAs run
       // (every phase of `full` is observed, also for the other group's chunks: see the operand groups)
+      const int wrow0 = row0_of(c) + 32 * wq;  // position of the warp's first row
       if (!wait_bar_warp(&bar_full[s], (c / NS) & 1, abort_flag, kWaitTma, c)) break;
       if ((c & 1) != mine) continue;
-      // (rotary in the kernel: the dQ pass rotates its own q row first -- nothing else touches the q tile; the
-      // forward's X tile is rotated by the operand group, so its norm is taken once the MMAs, which wait for that
-      // group, have completed: the value read never depends on which of the two groups was faster)
-      const int pos = row0_of(c) + row;
-      if (ROT && MODE == kModeDq && pos < N) rotate_rows<T, false, 1>(sQ, sQ, row, rot_sin(pos), rot_cos(pos), rot.pieces);
+      // (rotary in the kernel: the tile is rotated by the operand group, so its norm is taken once the MMAs, which
+      // wait for that group, have completed -- the value read never depends on which of the two groups was faster)
       float rq = 1.f;
-      if (!kScan && !(ROT && MODE == kModeFwd))
-        rq = row_mask(keep_b, count_b, pos, N).kp ? inv_norm(row_sumsq_rolled<T>(sQ, row)) : 0.f;
+      if (!kScan && !ROT) rq = row_mask(keep_b, count_b, row0_of(c) + row, N).kp ? inv_norm(row_sumsq_rolled<T>(sQ, row)) : 0.f;
       if (!wait_bar_warp(&bar_acc_full[b], (c >> 1) & 1, abort_flag, kWaitAcc, c)) break;
       tc_fence_after_sync();
-      if (ROT && MODE == kModeFwd) rq = row_mask(keep_b, count_b, pos, N).kp ? inv_norm(row_sumsq_rolled<T>(sQ, row)) : 0.f;
+      if (ROT) rq = row_mask(keep_b, count_b, row0_of(c) + row, N).kp ? inv_norm(row_sumsq_rolled<T>(sQ, row)) : 0.f;
       // The score and accumulator MMAs of this chunk have completed (the operand group reports the state
       // MMAs): the stage can be refilled.
       if (lane == 0) mbar_arrive(&bar_free_in[s]);
@@ -845,11 +866,15 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         // dq = (dq^ - q^ (q^ . dq^)) / |q| with dq^ = acc and q^ = rq q
         const float delta = row_dot_acc<T>(sQ, row, tAcc) * (rq * rq * rq);
         row_from_acc<T, true>(sQ, row, tAcc, rq, -delta);
-        // the row is the gradient of the rotated q: back through the rotation
-        if (ROT && pos < N) rotate_rows<T, true, 1>(sQ, sQ, row, rot_sin(pos), rot_cos(pos), rot.pieces);
       }
       tc_fence_before_sync();
       warp_arrive(&bar_acc_free[b], lane);
+      if (ROT && MODE == kModeDq) {  // the rows are the gradient of the rotated q: back through the rotation
+        RotRegs rt;
+        __syncwarp();  // the rows are now rotated piece-per-lane
+        rot_load(rt, rot_sin(wrow0), rot_cos(wrow0), lane, 0, rot.pieces, N - wrow0);
+        rotate_rows<T, true, 1>(rt, sQ, sQ, 32 * wq, lane, rot_sin(wrow0), rot_cos(wrow0), rot.pieces, N - wrow0);
+      }
       fence_proxy_async_smem();
       warp_arrive(&bar_out[s], lane);
     }
@@ -880,10 +905,11 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
 //   d norm_const[h] += -sigma (1 - sigma) sum_s ln(n_s) eps_s         (GPTCosAttention.py:241 by the chain rule)
 // Same warp roles as causal_tc_kernel; the two score tiles fill TMEM, so they are single-buffered:
 // the score MMAs of chunk c+1 are queued right behind the accumulator MMAs of chunk c.
-// ROT: as in causal_tc_kernel -- the Q and K tiles are rotated in shared memory (by the score group, before it
-// builds Qw), and the dK rows are rotated back before they are stored.
+// ROT: as in causal_tc_kernel -- the Q and K tiles are rotated in shared memory, by a warp group of their own that
+// works as soon as a stage has arrived (two chunks ahead of its use: the rotation is off the chain that sets the chunk
+// period), and the dK rows are rotated back before they are stored.
 template <typename T, bool EXT, bool ROT = false>
-__global__ void __launch_bounds__(kKvThreads, 1)
+__global__ void __launch_bounds__(ROT ? kKvThreadsRot : kKvThreads, 1)
 causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                      const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
                      const __grid_constant__ CUtensorMap mapDK, const __grid_constant__ CUtensorMap mapDV, float* __restrict__ dnorm,
@@ -901,8 +927,8 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   // compiler, so tile accesses compile to LDS/STS rather than generic loads and stores)
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char* sR = smem + NS * STAGE;  // 2 x [64 x 64] 16-bit state operand (rows = d_k, cols = d_v), double-buffered
-  __shared__ uint64_t bar_full[NS], bar_free_in[NS], bar_out[NS], bar_prep[NS], bar_p_full, bar_p_ready, bar_acc_full, bar_acc_free,
-      bar_state, bar_state2, bar_r_full, bar_init;
+  __shared__ uint64_t bar_full[NS], bar_free_in[NS], bar_out[NS], bar_prep[NS], bar_rot[NS], bar_p_full, bar_p_ready, bar_acc_full,
+      bar_acc_free, bar_state, bar_state2, bar_r_full, bar_init;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag_s;
   volatile int* abort_flag = &abort_flag_s;
@@ -934,6 +960,7 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       mbar_init(&bar_free_in[s], 8);  // output group (accumulator MMAs done) + operand group (state MMAs done)
       mbar_init(&bar_out[s], 4);
       mbar_init(&bar_prep[s], 4);
+      mbar_init(&bar_rot[s], 4);
     }
     mbar_init(&bar_p_full, 1);
     mbar_init(&bar_p_ready, 8);  // score group (E) + operand group (F)
@@ -1098,11 +1125,9 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
     auto prepare = [&](int ci) -> bool {
       const int s = ci % NS;
       if (!wait_bar_warp(&bar_full[s], (ci / NS) & 1, abort_flag, kWaitTma, ci)) return false;
+      // (rotary in the kernel: the rotated Q tile)
+      if (ROT && !wait_bar_warp(&bar_rot[s], (ci / NS) & 1, abort_flag, kWaitTma, ci)) return false;
       unsigned char* sQ = smem + s * STAGE;
-      if constexpr (ROT) {
-        const int pos = (last_chunk - ci) * kTcChunk + row;
-        if (pos < N) rotate_rows<T, false, 2>(sQ, sQ + kTileBytes, row, rot_sin(pos), rot_cos(pos), rot.pieces);
-      }
       scale_row_rolled<T>(sQ, row, row_mask(keep_b, count_b, (last_chunk - ci) * kTcChunk + row, N).kp
                                        ? inv_norm(row_sumsq_rolled<T>(sQ, row))
                                        : 0.f);
@@ -1119,6 +1144,20 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       warp_arrive(&bar_p_ready, lane);
       // Qw of the next chunk, while the accumulator MMAs of this one run
       if (ci + 1 < nchunks && !(ok = prepare(ci + 1))) break;
+    }
+  } else if (ROT && warp >= 15) {
+    // rotary group: the Q and K tiles of every stage, as soon as it has arrived
+    const int wq = warp & 3;
+    for (int ci = 0; ci < nchunks; ++ci) {
+      const int s = ci % NS;
+      const int wrow0 = (last_chunk - ci) * kTcChunk + 32 * wq;
+      RotRegs rt;
+      rot_load(rt, rot_sin(wrow0), rot_cos(wrow0), lane, 0, rot.pieces, N - wrow0);
+      if (!wait_bar_warp(&bar_full[s], (ci / NS) & 1, abort_flag, kWaitTma, ci)) break;
+      unsigned char* sQ = smem + s * STAGE;
+      rotate_rows<T, false, 2>(rt, sQ, sQ + kTileBytes, 32 * wq, lane, rot_sin(wrow0), rot_cos(wrow0), rot.pieces, N - wrow0);
+      fence_proxy_async_smem();
+      warp_arrive(&bar_rot[s], lane);
     }
   } else if (warp >= 10) {
     // operand group: mask + convert F, then the fp32 state after this chunk -> 16-bit operand
@@ -1169,6 +1208,8 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       if (!wait_bar_warp(&bar_acc_full, ci & 1, abort_flag, kWaitAcc, ci)) break;
       tc_fence_after_sync();
       if (ROT) rk = m.kp ? inv_norm(row_sumsq_rolled<T>(sK, row)) : 0.f;
+      RotRegs rt;  // (rotary: the table values for the way back, loaded while the accumulator rows are written)
+      if (ROT) rot_load(rt, rot_sin(pos - lane), rot_cos(pos - lane), lane, 0, rot.pieces, N - (pos - lane));
       // dV first (its row product with v gives eps), then dK; each is staged as soon as it is ready, in
       // the V / K tile of this stage: every MMA that reads them completed before acc_full and this thread
       // is done with its own rows, so they have no reader left.  The TMA thread stores and refills them.
@@ -1181,7 +1222,11 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
       tc_fence_before_sync();
       warp_arrive(&bar_acc_free, lane);
       // the row is the gradient of the rotated k: back through the rotation
-      if (ROT && pos < N) rotate_rows<T, true, 1>(sK, sK, row, rot_sin(pos), rot_cos(pos), rot.pieces);
+      if (ROT) {
+        const int wrow0 = pos - lane;  // position of the warp's first row
+        __syncwarp();  // the rows are now rotated piece-per-lane
+        rotate_rows<T, true, 1>(rt, sK, sK, 32 * wq, lane, rot_sin(wrow0), rot_cos(wrow0), rot.pieces, N - wrow0);
+      }
       ptx::fence_proxy_async_smem();
       warp_arrive(&bar_out[s], lane);
       if (m.n > 1.0f && pos < N) gsum += logf(m.n) * eps;

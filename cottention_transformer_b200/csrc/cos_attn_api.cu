@@ -122,7 +122,7 @@ int launch_bwd_dkdv(const void* q, const void* k, const void* v, const float* nc
   const size_t smem = causal_bwd_kv_smem_bytes();
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   if (plan.cps == 0) plan.cps = plan_segments(N, 1).cps;
-  kern<<<dim3((unsigned)BH, plan.nseg), kKvThreads, smem, stream>>>(mq, mk, mv, md, mdk, mdv, dnorm, nc, H, N, init, plan.cps, plan.keep, plan.count, plan.rot);
+  kern<<<dim3((unsigned)BH, plan.nseg), plan.rot.sin ? kKvThreadsRot : kKvThreads, smem, stream>>>(mq, mk, mv, md, mdk, mdv, dnorm, nc, H, N, init, plan.cps, plan.keep, plan.count, plan.rot);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }

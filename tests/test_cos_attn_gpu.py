@@ -375,16 +375,17 @@ def test_rotary_packed_matches_rotate_every_two(dt, d, rot, per_batch):
 
 
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("N,rot,per_batch,masked", [(1, 64, False, False), (100, 64, False, True), (128, 32, True, False),
-                                                    (129, 16, False, False), (640, 64, True, True), (1000, 48, False, False),
-                                                    (4096, 64, False, False)])
-def test_rotary_inside_the_kernels_is_bit_identical_to_the_separate_pass(dt, N, rot, per_batch, masked):
+@pytest.mark.parametrize("N,rot,per_batch,masked,B,H", [(1, 64, False, False, 2, 40), (100, 64, False, True, 2, 40),
+                                                        (128, 32, True, False, 2, 40), (129, 16, False, False, 2, 40),
+                                                        (640, 64, True, True, 2, 40), (1000, 48, False, False, 2, 40),
+                                                        (4096, 64, False, False, 2, 40), (1024, 64, False, False, 8, 16)])
+def test_rotary_inside_the_kernels_is_bit_identical_to_the_separate_pass(dt, N, rot, per_batch, masked, B, H):
     """``cos_attn_causal_packed(qkv, ..., rotary=(sin, cos))`` rotates the Q and K tiles in shared memory and the dq, dk
     rows on their way out; it must give the bits of ``rotary_packed_`` followed by ``cos_attn_causal_packed`` -- output,
     all of dqkv and the norm_const gradient -- and leave ``qkv`` itself un-rotated.  (A rotary dim that is not a
     multiple of 16 takes the separate pass inside the op; that route is covered by the same comparison.)"""
     from cottention_transformer_b200 import cos_attn_causal_packed, rotary_packed_, _lib
-    B, H, d = 2, 40, 64          # 80 sequences: one segment per sequence on a 148-SM part, so the kernels rotate
+    d = 64                       # (80 or 128 sequences: one segment per sequence on a 148-SM part, so the kernels rotate)
     g = torch.Generator(device="cuda").manual_seed(N + rot)
     base = torch.randn(B, N, 3, H, d, device="cuda", generator=g).to(dt)
     pos = torch.arange(N, device="cuda").float()[None, :, None] + (torch.arange(B, device="cuda").float()[:, None, None] * 5 if per_batch else 0)
