@@ -213,13 +213,28 @@ bidir_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
 
 // -------------------------------------------------------------------------------------------------
 // backward
-// The sequence is walked twice over one ring of two stages (q, K, V, dO tiles): items 0 .. n-1 build the two
-// states, items n .. 2n-1 apply them.  dq, dk, dv rows are staged in place over the q, K, V tiles.
+// A persistent kernel: CTA x takes the sequences x, x + gridDim.x, ... (one CTA per SM), and the items of all its
+// sequences go through ONE ring of three stages (q, K, V, dO tiles).  A sequence is walked twice: items 0 .. n-1
+// build the two states, items n .. 2n-1 apply them; dq, dk, dv rows are staged in place over the q, K, V tiles.
+// Why persistent: at BERT sizes (n = 4) a sequence costs 9 us of fixed latency (launch wave, TMEM allocation, first
+// load, final stores) on top of 3.2 us per chunk, and 384 sequences on 148 SMs ran as three waves of one-sequence
+// CTAs; here the ring carries on across sequences, so the loads of the next sequence are in flight while the last
+// rows of this one are written and stored, and a CTA's share is 2.6 sequences, not 3.
+// (An item lives ~4 us -- load, row factors, MMAs, output rows, store -- so the ring depth sets the item rate.)
+// Barrier phases: `full` completes once per item, so its parity follows the item number; the other per-stage barriers
+// complete for one kind of item only, and each of their waiters waits for every completion, so each waiter keeps a
+// phase bit per stage.
 // TMEM (512 columns allocated): S 64 | D 64 | AccQ 64 | AccK 64 | AccV 64
 // Warps: 0 = TMA (lane 0), 1 = MMA issue (lane 0), three groups of four (each warp works on the tile rows /
-// TMEM lanes 32 (w % 4) ..): group 0 (warps 2-5) scales operands and, in the second pass, publishes the row
-// factors; group 1 (6-9) and group 2 (10-13) share the other per-row work.
+// TMEM lanes 32 (w % 4) ..).  First pass: group 0 (warps 2-5) builds Qw, group 1 (6-9) Zw, in place.  Second pass:
+// no operand is rewritten -- the row factor of Zw = diag(w) V is applied to the dk rows instead (AccK = V D^T,
+// dk^ = w AccK), so the MMAs of an item start as soon as it has arrived; group 0 publishes the row factors
+// meanwhile and writes the dv rows, group 1 the dq rows, group 2 (10-13) the dk rows.
+// (Timeline of one CTA at BERT sizes: an item lives ~12,000 cycles -- load 3,500-5,500, MMAs 1,200, output rows
+// 2,000-2,700, the TMA store reading the stage 2,400 -- and three stages are all that fit, so the item rate is the
+// ring's; everything that shortens an item's life in its stage shows directly.)
 constexpr int kBtcBwdThreads = 448;
+constexpr int kBtcBwdStages = 3;
 
 template <typename T>
 __global__ void __launch_bounds__(kBtcBwdThreads, 1)
@@ -227,39 +242,42 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
                     const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
                     const __grid_constant__ CUtensorMap mapDQ, const __grid_constant__ CUtensorMap mapDK,
                     const __grid_constant__ CUtensorMap mapDV, const unsigned char* __restrict__ keep,
-                    const float* __restrict__ norm_const, float* __restrict__ dnorm, int H, int N) {
+                    const float* __restrict__ norm_const, float* __restrict__ dnorm, int H, int N, int BH) {
   using namespace ptx;
   constexpr bool BF = Pack2<T>::kBf16;
   constexpr int STAGE = 4 * kTileBytes;
+  constexpr int NS = kBtcBwdStages;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  unsigned char* sS = smem + 2 * STAGE;      // [64 x 64] 16-bit, rows d_k
+  unsigned char* sS = smem + NS * STAGE;     // [64 x 64] 16-bit, rows d_k
   unsigned char* sD = sS + kTcD * 128;       // [64 x 64] 16-bit, rows d_k
-  __shared__ uint64_t bar_full[2], bar_prep1[2], bar_prep2[2], bar_free1[2], bar_out[2], bar_st_full, bar_state, bar_acc_full,
+  __shared__ uint64_t bar_full[NS], bar_prep1[NS], bar_prep2[NS], bar_free1[NS], bar_out[NS], bar_st_full, bar_state, bar_acc_full,
       bar_acc_free;
-  __shared__ float s_rq[2][kTcChunk], s_rk[2][kTcChunk], s_w[2][kTcChunk];  // row factors of the second pass
+  __shared__ float s_rq[NS][kTcChunk], s_rk[NS][kTcChunk], s_w[NS][kTcChunk];  // row factors of the second pass
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag_s;
   volatile int* abort_flag = &abort_flag_s;
 
   const int tid = threadIdx.x, lane = tid & 31;
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
-  const int bh = blockIdx.x, h = bh % H, b = bh / H, bb = b;
-  const int n = (N + kTcChunk - 1) / kTcChunk;  // chunks; the ring carries 2n items
-  const unsigned char* keep_b = keep ? keep + static_cast<size_t>(b) * N : nullptr;
+  const int n = (N + kTcChunk - 1) / kTcChunk;  // chunks; a sequence is 2n items
+  const int items = 2 * n;
+  const int nseq = (BH - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+  const int total = nseq * items;               // items of this CTA; item g = t * items + j of its t-th sequence
+  auto seq_of = [&](int t) { return static_cast<int>(blockIdx.x) + t * static_cast<int>(gridDim.x); };
 
   if (tid == 0) {
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < NS; ++s) {
       mbar_init(&bar_full[s], 1);
       mbar_init(&bar_prep1[s], 8);  // groups 0 and 1
       mbar_init(&bar_prep2[s], 4);  // group 0
       mbar_init(&bar_free1[s], 1);
-      mbar_init(&bar_out[s], 8);    // groups 1 and 2
+      mbar_init(&bar_out[s], 12);   // all three groups
     }
     mbar_init(&bar_st_full, 1);
     mbar_init(&bar_state, 8);       // groups 1 and 2
     mbar_init(&bar_acc_full, 1);
-    mbar_init(&bar_acc_free, 8);    // groups 1 and 2
+    mbar_init(&bar_acc_free, 12);   // all three groups
     mbar_fence_init();
     abort_flag_s = 0;
     tma_prefetch_desc(&mapQ);
@@ -283,12 +301,19 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
   if (warp == 0) {
     if (lane == 0) {
       bool ok = true;
-      // hand back the stage of item i: state items are released by their MMAs, apply items once their three
+      uint32_t ph_free1 = 0, ph_out = 0;  // phase bit per stage
+      // hand back the stage of item g: state items are released by their MMAs, apply items once their three
       // output tiles have been stored from it
-      auto retire = [&](int i) -> bool {
-        const int s = i & 1;
-        if (i < n) return wait_bar(&bar_free1[s], (i >> 1) & 1, abort_flag, kWaitStageFree, i);
-        if (!wait_bar(&bar_out[s], ((i - n) >> 1) & 1, abort_flag, kWaitStageFree, i)) return false;
+      auto retire = [&](int g) -> bool {
+        const int t = g / items, i = g - t * items, s = g % NS;
+        if (i < n) {
+          const bool r = wait_bar(&bar_free1[s], (ph_free1 >> s) & 1, abort_flag, kWaitStageFree, g);
+          ph_free1 ^= 1u << s;
+          return r;
+        }
+        if (!wait_bar(&bar_out[s], (ph_out >> s) & 1, abort_flag, kWaitStageFree, g)) return false;
+        ph_out ^= 1u << s;
+        const int bh = seq_of(t), h = bh % H, bb = bh / H;
         unsigned char* st = smem + s * STAGE;
         const int y = (i - n) * kTcChunk;
         tma_store_tile(&mapDQ, st, y, h, bb);
@@ -298,9 +323,11 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
         tma_store_wait_read<0>();
         return true;
       };
-      for (int j = 0; ok && j < 2 * n; ++j) {
-        const int s = j & 1, y = (j < n ? j : j - n) * kTcChunk;
-        if (j >= 2 && !(ok = retire(j - 2))) break;
+      for (int g = 0; ok && g < total; ++g) {
+        const int t = g / items, j = g - t * items, s = g % NS;
+        const int bh = seq_of(t), h = bh % H, bb = bh / H;
+        const int y = (j < n ? j : j - n) * kTcChunk;
+        if (g >= NS && !(ok = retire(g - NS))) break;
         unsigned char* st = smem + s * STAGE;
         mbar_expect_tx(&bar_full[s], STAGE);
         tma_load_tile(st, &mapQ, &bar_full[s], y, h, bb);
@@ -308,125 +335,143 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
         tma_load_tile(st + 2 * kTileBytes, &mapV, &bar_full[s], y, h, bb);
         tma_load_tile(st + 3 * kTileBytes, &mapDO, &bar_full[s], y, h, bb);
       }
-      for (int i = (2 * n >= 2 ? 2 * n - 2 : 0); ok && i < 2 * n; ++i) ok = retire(i);
+      for (int g = (total >= NS ? total - NS : 0); ok && g < total; ++g) ok = retire(g);
       tma_store_wait<0>();
     }
   } else if (warp == 1) {
     if (lane == 0) {
       bool ok = true;
-      for (int j = 0; ok && j < n; ++j) {  // S += K^T Zw,  D += Qw^T dO
-        const int s = j & 1;
-        if (!(ok = wait_bar1(&bar_prep1[s], (j >> 1) & 1, abort_flag, kWaitPrepped, j))) break;
-        tc_fence_after_sync();
-        const uint32_t q0 = smem_u32(smem + s * STAGE);
-        const uint64_t dQm = mdesc(q0), dKm = mdesc(q0 + kTileBytes), dZm = mdesc(q0 + 2 * kTileBytes),
-                       dDm = mdesc(q0 + 3 * kTileBytes);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) mma_ss(tS, dKm + 128 * k, dZm + 128 * k, kIdescS, (j > 0 || k > 0) ? 1u : 0u);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) mma_ss(tD, dQm + 128 * k, dDm + 128 * k, kIdescS, (j > 0 || k > 0) ? 1u : 0u);
-        mma_commit(&bar_free1[s]);
-      }
-      if (ok) mma_commit(&bar_st_full);
-      ok = ok && wait_bar1(&bar_state, 0, abort_flag, kWaitState, 0);
+      uint32_t ph_prep1 = 0;
+      int p2 = 0;  // apply items issued so far (the accumulators are single-buffered across sequences too)
       const uint64_t dSk = kdesc(smem_u32(sS)), dDk = kdesc(smem_u32(sD)), dDmn = mdesc(smem_u32(sD));
-      for (int c = 0; ok && c < n; ++c) {
-        const int j = n + c, s = j & 1;
-        if (!(ok = wait_bar4(&bar_prep2[s], (c >> 1) & 1, c > 0 ? &bar_acc_free : nullptr, (c - 1) & 1, nullptr, 0, nullptr, 0,
-                             abort_flag, kWaitPrepped, j)))
-          break;
-        tc_fence_after_sync();
-        const uint32_t q0 = smem_u32(smem + s * STAGE);
-        const uint64_t dK = kdesc(q0 + kTileBytes), dZ = kdesc(q0 + 2 * kTileBytes), dDO = kdesc(q0 + 3 * kTileBytes);
+      for (int t = 0; ok && t < nseq; ++t) {
+        const int g0 = t * items;
+        for (int j = 0; ok && j < n; ++j) {  // S += K^T Zw,  D += Qw^T dO
+          const int s = (g0 + j) % NS;
+          if (!(ok = wait_bar1(&bar_prep1[s], (ph_prep1 >> s) & 1, abort_flag, kWaitPrepped, g0 + j))) break;
+          ph_prep1 ^= 1u << s;
+          tc_fence_after_sync();
+          const uint32_t q0 = smem_u32(smem + s * STAGE);
+          const uint64_t dQm = mdesc(q0), dKm = mdesc(q0 + kTileBytes), dZm = mdesc(q0 + 2 * kTileBytes),
+                         dDm = mdesc(q0 + 3 * kTileBytes);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) mma_ss(tAQ, dDO + 2 * k, dSk + 2 * k, kIdescKK, k > 0);   // AccQ = dO S^T
+          for (int k = 0; k < 8; ++k) mma_ss(tS, dKm + 128 * k, dZm + 128 * k, kIdescS, (j > 0 || k > 0) ? 1u : 0u);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) mma_ss(tAK, dZ + 2 * k, dDk + 2 * k, kIdescKK, k > 0);    // AccK = Zw D^T
+          for (int k = 0; k < 8; ++k) mma_ss(tD, dQm + 128 * k, dDm + 128 * k, kIdescS, (j > 0 || k > 0) ? 1u : 0u);
+          mma_commit(&bar_free1[s]);
+        }
+        if (!ok) break;
+        // (the commit also covers the apply MMAs of the previous sequence, which read the 16-bit states that the
+        // conversion triggered by this barrier overwrites)
+        mma_commit(&bar_st_full);
+        if (!(ok = wait_bar1(&bar_state, t & 1, abort_flag, kWaitState, t))) break;
+        for (int c = 0; ok && c < n; ++c, ++p2) {
+          const int g = g0 + n + c, s = g % NS;
+          // the item's tiles as they arrived (nothing is rewritten in this pass) and the accumulators read out
+          if (!(ok = wait_bar4(&bar_full[s], (g / NS) & 1, p2 > 0 ? &bar_acc_free : nullptr, (p2 - 1) & 1, nullptr, 0,
+                               nullptr, 0, abort_flag, kWaitPrepped, g)))
+            break;
+          tc_fence_after_sync();
+          const uint32_t q0 = smem_u32(smem + s * STAGE);
+          const uint64_t dK = kdesc(q0 + kTileBytes), dZ = kdesc(q0 + 2 * kTileBytes), dDO = kdesc(q0 + 3 * kTileBytes);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) mma_ss(tAV, dK + 2 * k, dDmn + 128 * k, kIdescMN, k > 0);  // AccV = K D
-        mma_commit(&bar_acc_full);
+          for (int k = 0; k < 4; ++k) mma_ss(tAQ, dDO + 2 * k, dSk + 2 * k, kIdescKK, k > 0);   // AccQ = dO S^T
+#pragma unroll
+          for (int k = 0; k < 4; ++k) mma_ss(tAK, dZ + 2 * k, dDk + 2 * k, kIdescKK, k > 0);    // AccK = V D^T
+#pragma unroll
+          for (int k = 0; k < 4; ++k) mma_ss(tAV, dK + 2 * k, dDmn + 128 * k, kIdescMN, k > 0);  // AccV = K D
+          mma_commit(&bar_acc_full);
+        }
       }
     }
   } else {
     const int group = (warp - 2) >> 2;  // 0, 1, 2
     const int wq = warp & 3, row = 32 * wq + lane;
     const uint32_t lane_base = static_cast<uint32_t>(32 * wq) << 16;
-    const float L = btc_count_keep(keep_b, N, lane);
-    const float sigma = 1.0f / (1.0f + __expf(-norm_const[h]));
-    const float a = length_factor(fmaxf(L, 1.0f), sigma);
-    float gsum = 0.f;
+    uint32_t ph_prep2 = 0;
+    int p2 = 0;  // apply items seen so far
     bool ok = true;
-    // ---- first pass: Qw = diag(keep / |q|) q (group 0),  Zw = diag(keep a / |k|) V (group 1), in place
-    if (group < 2) {
-      for (int j = 0; ok && j < n; ++j) {
-        const int s = j & 1, pos = j * kTcChunk + row;
-        if (!(ok = wait_bar_warp(&bar_full[s], (j >> 1) & 1, abort_flag, kWaitTma, j))) break;
-        unsigned char* st = smem + s * STAGE;
-        const bool kp = pos < N && (!keep_b || keep_b[pos]);
-        if (group == 0)
-          scale_row_rolled<T>(st, row, kp ? inv_norm(row_sumsq_rolled<T>(st, row)) : 0.f);
+    for (int t = 0; ok && t < nseq; ++t) {
+      const int g0 = t * items;
+      const int bh = seq_of(t), h = bh % H, b = bh / H;
+      const unsigned char* keep_b = keep ? keep + static_cast<size_t>(b) * N : nullptr;
+      const float L = btc_count_keep(keep_b, N, lane);
+      const float sigma = 1.0f / (1.0f + __expf(-norm_const[h]));
+      const float a = length_factor(fmaxf(L, 1.0f), sigma);
+      float gsum = 0.f;
+      // ---- first pass: Qw = diag(keep / |q|) q (group 0),  Zw = diag(keep a / |k|) V (group 1), in place
+      if (group < 2) {
+        for (int j = 0; ok && j < n; ++j) {
+          const int g = g0 + j, s = g % NS, pos = j * kTcChunk + row;
+          if (!(ok = wait_bar_warp(&bar_full[s], (g / NS) & 1, abort_flag, kWaitTma, g))) break;
+          unsigned char* st = smem + s * STAGE;
+          const bool kp = pos < N && (!keep_b || keep_b[pos]);
+          if (group == 0)
+            scale_row_rolled<T>(st, row, kp ? inv_norm(row_sumsq_rolled<T>(st, row)) : 0.f);
+          else
+            scale_row_rolled<T>(st + 2 * kTileBytes, row, kp ? inv_norm(row_sumsq_rolled<T>(st + kTileBytes, row)) * a : 0.f);
+          fence_proxy_async_smem();
+          warp_arrive(&bar_prep1[s], lane);
+        }
+      }
+      // ---- the two states -> 16-bit operands (group 1: S, group 2: D)
+      if (group >= 1 && ok && (ok = wait_bar_warp(&bar_st_full, t & 1, abort_flag, kWaitState, t))) {
+        tc_fence_after_sync();
+        if (group == 1)
+          state_to_smem_rolled<T>(tS + lane_base, sS, wq, lane);
         else
-          scale_row_rolled<T>(st + 2 * kTileBytes, row, kp ? inv_norm(row_sumsq_rolled<T>(st + kTileBytes, row)) * a : 0.f);
+          state_to_smem_rolled<T>(tD + lane_base, sD, wq, lane);
         fence_proxy_async_smem();
-        warp_arrive(&bar_prep1[s], lane);
+        tc_fence_before_sync();
+        warp_arrive(&bar_state, lane);
       }
-    }
-    // ---- the two states -> 16-bit operands (group 1: S, group 2: D)
-    if (group >= 1 && ok && (ok = wait_bar_warp(&bar_st_full, 0, abort_flag, kWaitState, 0))) {
-      tc_fence_after_sync();
-      if (group == 1)
-        state_to_smem_rolled<T>(tS + lane_base, sS, wq, lane);
-      else
-        state_to_smem_rolled<T>(tD + lane_base, sD, wq, lane);
-      fence_proxy_async_smem();
-      tc_fence_before_sync();
-      warp_arrive(&bar_state, lane);
-    }
-    // ---- second pass
-    for (int c = 0; ok && c < n; ++c) {
-      const int j = n + c, s = j & 1, pos = c * kTcChunk + row;
-      unsigned char* sQ = smem + s * STAGE;
-      unsigned char* sK = sQ + kTileBytes;
-      unsigned char* sV = sQ + 2 * kTileBytes;
-      if (group == 0) {  // row factors, Zw again (q and K stay raw for the output rows)
-        if (!(ok = wait_bar_warp(&bar_full[s], (j >> 1) & 1, abort_flag, kWaitTma, j))) break;
-        const bool kp = pos < N && (!keep_b || keep_b[pos]);
-        const float rq = kp ? inv_norm(row_sumsq_rolled<T>(sQ, row)) : 0.f;
-        const float rk = kp ? inv_norm(row_sumsq_rolled<T>(sK, row)) : 0.f;
-        s_rq[s][row] = rq;
-        s_rk[s][row] = rk;
-        s_w[s][row] = rk * a;
-        scale_row_rolled<T>(sV, row, rk * a);
+      // ---- second pass
+      for (int c = 0; ok && c < n; ++c, ++p2) {
+        const int g = g0 + n + c, s = g % NS, pos = c * kTcChunk + row;
+        unsigned char* sQ = smem + s * STAGE;
+        unsigned char* sK = sQ + kTileBytes;
+        unsigned char* sV = sQ + 2 * kTileBytes;
+        if (group == 0) {  // the row factors, for the other two groups
+          if (!(ok = wait_bar_warp(&bar_full[s], (g / NS) & 1, abort_flag, kWaitTma, g))) break;
+          const bool kp = pos < N && (!keep_b || keep_b[pos]);
+          const float rk = kp ? inv_norm(row_sumsq_rolled<T>(sK, row)) : 0.f;
+          s_rq[s][row] = kp ? inv_norm(row_sumsq_rolled<T>(sQ, row)) : 0.f;
+          s_rk[s][row] = rk;
+          s_w[s][row] = rk * a;
+          warp_arrive(&bar_prep2[s], lane);
+          if (!(ok = wait_bar_warp(&bar_acc_full, p2 & 1, abort_flag, kWaitAcc, g))) break;
+          tc_fence_after_sync();
+          // dv = w AccV;  v' . dv' = w (v . AccV)
+          const float w = rk * a;
+          gsum += w * row_from_acc_dot<T>(sV, row, tAV + lane_base, w);
+        } else {
+          // groups 1 and 2: the row factors (prep2) and the accumulators
+          if (!(ok = wait_bar_warp(&bar_prep2[s], (ph_prep2 >> s) & 1, abort_flag, kWaitPrepped, g))) break;
+          ph_prep2 ^= 1u << s;
+          if (!(ok = wait_bar_warp(&bar_acc_full, p2 & 1, abort_flag, kWaitAcc, g))) break;
+          tc_fence_after_sync();
+          if (group == 1) {
+            // dq = keep/|q| (dq^ - q^ (q^ . dq^)),  dq^ = AccQ,  q^ = rq q
+            const float rq = s_rq[s][row];
+            const float dotq = row_dot_acc<T>(sQ, row, tAQ + lane_base);
+            row_from_acc<T, true>(sQ, row, tAQ + lane_base, rq, -rq * rq * rq * dotq);
+          } else {
+            // dk = dk^' - k^ (k^ . dk^') with dk^' = w AccK  (= dk^ / |k|; the row factor of Zw, applied here)
+            const float rk = s_rk[s][row], w = s_w[s][row];
+            const float dotk = row_dot_acc<T>(sK, row, tAK + lane_base);
+            row_from_acc<T, true>(sK, row, tAK + lane_base, w, -rk * rk * w * dotk);
+          }
+        }
+        tc_fence_before_sync();
+        warp_arrive(&bar_acc_free, lane);
         fence_proxy_async_smem();
-        warp_arrive(&bar_prep2[s], lane);
-        continue;
+        warp_arrive(&bar_out[s], lane);
       }
-      // groups 1 and 2: the row factors (prep2) and the accumulators
-      if (!(ok = wait_bar_warp(&bar_prep2[s], (c >> 1) & 1, abort_flag, kWaitPrepped, j))) break;
-      if (!(ok = wait_bar_warp(&bar_acc_full, c & 1, abort_flag, kWaitAcc, c))) break;
-      tc_fence_after_sync();
-      if (group == 1) {
-        // dq = keep/|q| (dq^ - q^ (q^ . dq^)),  dq^ = AccQ,  q^ = rq q
-        const float rq = s_rq[s][row];
-        const float dotq = row_dot_acc<T>(sQ, row, tAQ + lane_base);
-        row_from_acc<T, true>(sQ, row, tAQ + lane_base, rq, -rq * rq * rq * dotq);
-        // dv = w AccV;  v' . dv' = (w v) . AccV with w v = the Zw row
-        gsum += row_from_acc_dot<T>(sV, row, tAV + lane_base, s_w[s][row]);
-      } else {
-        // dk = AccK - k^ (k^ . AccK)   (AccK = dk^ / |k|)
-        const float rk = s_rk[s][row];
-        const float dotk = row_dot_acc<T>(sK, row, tAK + lane_base);
-        row_from_acc<T, true>(sK, row, tAK + lane_base, 1.0f, -rk * rk * dotk);
-      }
-      tc_fence_before_sync();
-      warp_arrive(&bar_acc_free, lane);
-      fence_proxy_async_smem();
-      warp_arrive(&bar_out[s], lane);
-    }
-    if (group == 1) {
+      if (group == 0 && ok) {
 #pragma unroll
-      for (int off = 16; off > 0; off >>= 1) gsum += __shfl_down_sync(0xffffffffu, gsum, off);
-      if (lane == 0 && L > 1.0f) atomicAdd(dnorm + h, -sigma * (1.0f - sigma) * __logf(L) * gsum);
+        for (int off = 16; off > 0; off >>= 1) gsum += __shfl_down_sync(0xffffffffu, gsum, off);
+        if (lane == 0 && L > 1.0f) atomicAdd(dnorm + h, -sigma * (1.0f - sigma) * __logf(L) * gsum);
+      }
     }
   }
 
@@ -434,14 +479,13 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
   tc_fence_before_sync();
   __syncthreads();
   if (tid == 0 && *abort_flag) {
-    mbar_wait(&bar_full[0], 0, 64);
-    mbar_wait(&bar_full[1], 0, 64);
+    for (int s = 0; s < NS; ++s) mbar_wait(&bar_full[s], 0, 64);
   }
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
-inline size_t bidir_bwd_tc_smem_bytes() { return static_cast<size_t>(8 * kTileBytes + 2 * kTcD * 128 + 1024); }
+inline size_t bidir_bwd_tc_smem_bytes() { return static_cast<size_t>(kBtcBwdStages * 4 * kTileBytes + 2 * kTcD * 128 + 1024); }
 
 inline size_t bidir_fwd_tc_smem_bytes() { return static_cast<size_t>((2 * kBtcKv + 2) * kTileBytes + kTcD * 128 + 1024); }
 

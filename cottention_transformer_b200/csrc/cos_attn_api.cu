@@ -502,7 +502,11 @@ int launch_bidir_bwd_tc_t(const void* q, const void* k, const void* v, const uns
   auto kern = bidir_bwd_tc_kernel<T>;
   const size_t smem = bidir_bwd_tc_smem_bytes();
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<(unsigned)BH, kBtcBwdThreads, smem, stream>>>(mq, mk, mv, md, mdq, mdk, mdv, keep, nc, dnorm, H, N);
+  // persistent: one CTA per SM, each takes every gridDim.x-th sequence
+  int dev = 0, sm = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, dev);
+  const unsigned grid = (unsigned)(BH < sm ? BH : sm);
+  kern<<<grid, kBtcBwdThreads, smem, stream>>>(mq, mk, mv, md, mdq, mdk, mdv, keep, nc, dnorm, H, N, (int)BH);
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
