@@ -213,26 +213,32 @@ bidir_fwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
 
 // -------------------------------------------------------------------------------------------------
 // backward
-// A persistent kernel: CTA x takes the sequences x, x + gridDim.x, ... (one CTA per SM), and the items of all its
-// sequences go through ONE ring of three stages (q, K, V, dO tiles).  A sequence is walked twice: items 0 .. n-1
-// build the two states, items n .. 2n-1 apply them; dq, dk, dv rows are staged in place over the q, K, V tiles.
-// Why persistent: at BERT sizes (n = 4) a sequence costs 9 us of fixed latency (launch wave, TMEM allocation, first
-// load, final stores) on top of 3.2 us per chunk, and 384 sequences on 148 SMs ran as three waves of one-sequence
-// CTAs; here the ring carries on across sequences, so the loads of the next sequence are in flight while the last
-// rows of this one are written and stored, and a CTA's share is 2.6 sequences, not 3.
-// (An item lives ~4 us -- load, row factors, MMAs, output rows, store -- so the ring depth sets the item rate.)
-// Barrier phases: `full` completes once per item, so its parity follows the item number; the other per-stage barriers
-// complete for one kind of item only, and each of their waiters waits for every completion, so each waiter keeps a
-// phase bit per stage.
-// TMEM (512 columns allocated): S 64 | D 64 | AccQ 64 | AccK 64 | AccV 64
+// A persistent kernel: CTA x takes the sequences x, x + gridDim.x, ... (one CTA per SM), and the tiles of all its
+// sequences go through ONE ring of three stages (q, K, V, dO tiles of a chunk).  A sequence is walked twice: the
+// first pass builds the two states, the second applies them; dq, dk, dv rows are staged in place over the q, K, V
+// tiles and leave by TMA.
+// The kernel is bound by the bytes an SM can move (a traced CTA sustains ~40 GB/s: 64 KB loads that take 2-3 us,
+// 48 KB stores), so the second pass does not load again what is still in shared memory: the last three chunks of
+// the first pass stay in their stages ("resident") and are the first three chunks of the second pass; only the
+// chunks before them are loaded a second time.  At BERT sizes (four chunks) a sequence is 5 loads instead of 8.
+//   slots of a sequence (a slot = one load into the next stage of the ring):  first pass chunks 0 .. n-1, then the
+//   reloads of chunks 0 .. n-R-1 (R = min(n, stages) resident chunks);
+//   second pass order: the resident chunks n-R .. n-1, then the reloaded ones -- the order in which their stages
+//   are needed again, so stages retire in slot order.
+// A resident chunk arrives in the second pass as the first pass left it: the q tile holds Qw = q^, the V tile
+// Zw = w v, and its row factors are in shared memory; a reloaded chunk is raw (its factors are computed again and
+// the factor of Zw is applied to the dk rows instead, so nothing is rewritten before its MMAs).
+// Why persistent: a sequence of four chunks cost 9 us of fixed latency (launch wave, TMEM allocation, first load,
+// final stores), and 384 sequences on 148 SMs ran as three waves; here the ring carries on across sequences.
+// Barrier phases: `full` completes once per slot, so its parity follows the slot number; the other per-stage barriers
+// complete for some slots only, and each of their waiters waits for every completion, so each waiter keeps a phase
+// bit per stage.
+// TMEM (512 columns): S 64 | D 64 | 2 x (AccQ 64 | AccK 64 | AccV 64) -- the accumulators are double-buffered, so the
+// MMAs of the next chunk run while the rows of this one are written (the second pass is a chain MMAs -> rows otherwise)
 // Warps: 0 = TMA (lane 0), 1 = MMA issue (lane 0), three groups of four (each warp works on the tile rows /
-// TMEM lanes 32 (w % 4) ..).  First pass: group 0 (warps 2-5) builds Qw, group 1 (6-9) Zw, in place.  Second pass:
-// no operand is rewritten -- the row factor of Zw = diag(w) V is applied to the dk rows instead (AccK = V D^T,
-// dk^ = w AccK), so the MMAs of an item start as soon as it has arrived; group 0 publishes the row factors
-// meanwhile and writes the dv rows, group 1 the dq rows, group 2 (10-13) the dk rows.
-// (Timeline of one CTA at BERT sizes: an item lives ~12,000 cycles -- load 3,500-5,500, MMAs 1,200, output rows
-// 2,000-2,700, the TMA store reading the stage 2,400 -- and three stages are all that fit, so the item rate is the
-// ring's; everything that shortens an item's life in its stage shows directly.)
+// TMEM lanes 32 (w % 4) ..).  First pass: group 0 (warps 2-5) builds Qw, group 1 (6-9) Zw, in place, and both leave
+// their row factors.  Second pass: group 0 writes the dv rows (and, for a reloaded chunk, the row factors first),
+// group 1 the dq rows, group 2 (10-13) the dk rows.
 constexpr int kBtcBwdThreads = 448;
 constexpr int kBtcBwdStages = 3;
 
@@ -251,8 +257,8 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char* sS = smem + NS * STAGE;     // [64 x 64] 16-bit, rows d_k
   unsigned char* sD = sS + kTcD * 128;       // [64 x 64] 16-bit, rows d_k
-  __shared__ uint64_t bar_full[NS], bar_prep1[NS], bar_prep2[NS], bar_free1[NS], bar_out[NS], bar_st_full, bar_state, bar_acc_full,
-      bar_acc_free;
+  __shared__ uint64_t bar_full[NS], bar_prep1[NS], bar_prep2[NS], bar_free1[NS], bar_out[NS], bar_st_full, bar_state, bar_acc_full[2],
+      bar_acc_free[2];
   __shared__ float s_rq[NS][kTcChunk], s_rk[NS][kTcChunk], s_w[NS][kTcChunk];  // row factors of the second pass
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag_s;
@@ -260,10 +266,14 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
 
   const int tid = threadIdx.x, lane = tid & 31;
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
-  const int n = (N + kTcChunk - 1) / kTcChunk;  // chunks; a sequence is 2n items
-  const int items = 2 * n;
+  const int n = (N + kTcChunk - 1) / kTcChunk;  // chunks of a sequence
+  const int R = n < NS ? n : NS;                // chunks that stay in their stages between the two passes
+  const int SL = 2 * n - R;                     // slots (loads) of a sequence: n first-pass chunks + n - R reloads
   const int nseq = (BH - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
-  const int total = nseq * items;               // items of this CTA; item g = t * items + j of its t-th sequence
+  const int total = nseq * SL;                  // slots of this CTA; slot t * SL + i of its t-th sequence, stage = slot % NS
+  // second-pass item m of a sequence: its chunk and the slot that holds it
+  auto p2_chunk = [&](int m) { return m < R ? n - R + m : m - R; };
+  auto p2_slot = [&](int m) { return m < R ? n - R + m : n + (m - R); };
   auto seq_of = [&](int t) { return static_cast<int>(blockIdx.x) + t * static_cast<int>(gridDim.x); };
 
   if (tid == 0) {
@@ -276,8 +286,10 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
     }
     mbar_init(&bar_st_full, 1);
     mbar_init(&bar_state, 8);       // groups 1 and 2
-    mbar_init(&bar_acc_full, 1);
-    mbar_init(&bar_acc_free, 12);   // all three groups
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bar_acc_full[i], 1);
+      mbar_init(&bar_acc_free[i], 12);  // all three groups
+    }
     mbar_fence_init();
     abort_flag_s = 0;
     tma_prefetch_desc(&mapQ);
@@ -293,7 +305,7 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = tmem_slot;
-  const uint32_t tS = tmem, tD = tmem + 64, tAQ = tmem + 128, tAK = tmem + 192, tAV = tmem + 256;
+  const uint32_t tS = tmem, tD = tmem + 64, tAcc = tmem + 128;  // accumulator set i: AccQ, AccK, AccV at tAcc + 192 i + 0 / 64 / 128
   constexpr uint32_t kIdescS = make_idesc(64, 64, BF, true, true);
   constexpr uint32_t kIdescKK = make_idesc(128, 64, BF, false, false);  // B K-major
   constexpr uint32_t kIdescMN = make_idesc(128, 64, BF, false, true);   // B MN-major
@@ -302,11 +314,11 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
     if (lane == 0) {
       bool ok = true;
       uint32_t ph_free1 = 0, ph_out = 0;  // phase bit per stage
-      // hand back the stage of item g: state items are released by their MMAs, apply items once their three
-      // output tiles have been stored from it
+      // hand back the stage of slot g: a first-pass chunk that does not stay is released by its MMAs, every other
+      // slot once the three output tiles of its chunk have been stored from it
       auto retire = [&](int g) -> bool {
-        const int t = g / items, i = g - t * items, s = g % NS;
-        if (i < n) {
+        const int t = g / SL, i = g - t * SL, s = g % NS;
+        if (i < n - R) {
           const bool r = wait_bar(&bar_free1[s], (ph_free1 >> s) & 1, abort_flag, kWaitStageFree, g);
           ph_free1 ^= 1u << s;
           return r;
@@ -315,7 +327,7 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
         ph_out ^= 1u << s;
         const int bh = seq_of(t), h = bh % H, bb = bh / H;
         unsigned char* st = smem + s * STAGE;
-        const int y = (i - n) * kTcChunk;
+        const int y = (i < n ? i : i - n) * kTcChunk;
         tma_store_tile(&mapDQ, st, y, h, bb);
         tma_store_tile(&mapDK, st + kTileBytes, y, h, bb);
         tma_store_tile(&mapDV, st + 2 * kTileBytes, y, h, bb);
@@ -324,9 +336,9 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
         return true;
       };
       for (int g = 0; ok && g < total; ++g) {
-        const int t = g / items, j = g - t * items, s = g % NS;
+        const int t = g / SL, i = g - t * SL, s = g % NS;
         const int bh = seq_of(t), h = bh % H, bb = bh / H;
-        const int y = (j < n ? j : j - n) * kTcChunk;
+        const int y = (i < n ? i : i - n) * kTcChunk;
         if (g >= NS && !(ok = retire(g - NS))) break;
         unsigned char* st = smem + s * STAGE;
         mbar_expect_tx(&bar_full[s], STAGE);
@@ -342,10 +354,10 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
     if (lane == 0) {
       bool ok = true;
       uint32_t ph_prep1 = 0;
-      int p2 = 0;  // apply items issued so far (the accumulators are single-buffered across sequences too)
+      int p2 = 0;  // second-pass items issued so far (they take the two accumulator sets in turn, across sequences too)
       const uint64_t dSk = kdesc(smem_u32(sS)), dDk = kdesc(smem_u32(sD)), dDmn = mdesc(smem_u32(sD));
       for (int t = 0; ok && t < nseq; ++t) {
-        const int g0 = t * items;
+        const int g0 = t * SL;
         for (int j = 0; ok && j < n; ++j) {  // S += K^T Zw,  D += Qw^T dO
           const int s = (g0 + j) % NS;
           if (!(ok = wait_bar1(&bar_prep1[s], (ph_prep1 >> s) & 1, abort_flag, kWaitPrepped, g0 + j))) break;
@@ -358,18 +370,21 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
           for (int k = 0; k < 8; ++k) mma_ss(tS, dKm + 128 * k, dZm + 128 * k, kIdescS, (j > 0 || k > 0) ? 1u : 0u);
 #pragma unroll
           for (int k = 0; k < 8; ++k) mma_ss(tD, dQm + 128 * k, dDm + 128 * k, kIdescS, (j > 0 || k > 0) ? 1u : 0u);
-          mma_commit(&bar_free1[s]);
+          if (j < n - R) mma_commit(&bar_free1[s]);  // (a chunk that stays is not handed back here)
         }
         if (!ok) break;
-        // (the commit also covers the apply MMAs of the previous sequence, which read the 16-bit states that the
-        // conversion triggered by this barrier overwrites)
+        // (the commit also covers the second-pass MMAs of the previous sequence, which read the 16-bit states that
+        // the conversion triggered by this barrier overwrites)
         mma_commit(&bar_st_full);
         if (!(ok = wait_bar1(&bar_state, t & 1, abort_flag, kWaitState, t))) break;
-        for (int c = 0; ok && c < n; ++c, ++p2) {
-          const int g = g0 + n + c, s = g % NS;
-          // the item's tiles as they arrived (nothing is rewritten in this pass) and the accumulators read out
-          if (!(ok = wait_bar4(&bar_full[s], (g / NS) & 1, p2 > 0 ? &bar_acc_free : nullptr, (p2 - 1) & 1, nullptr, 0,
-                               nullptr, 0, abort_flag, kWaitPrepped, g)))
+        for (int m = 0; ok && m < n; ++m, ++p2) {
+          const int g = g0 + p2_slot(m), s = g % NS;
+          // a reloaded chunk: its tiles as they arrive (nothing is rewritten before the MMAs); a resident one is
+          // there already.  And the accumulators read out.
+          const int ab = p2 & 1;
+          const uint32_t tAQ = tAcc + 192 * ab, tAK = tAQ + 64, tAV = tAQ + 128;
+          if (!(ok = wait_bar4(m >= R ? &bar_full[s] : nullptr, (g / NS) & 1, p2 >= 2 ? &bar_acc_free[ab] : nullptr,
+                               ((p2 >> 1) - 1) & 1, nullptr, 0, nullptr, 0, abort_flag, kWaitPrepped, g)))
             break;
           tc_fence_after_sync();
           const uint32_t q0 = smem_u32(smem + s * STAGE);
@@ -377,10 +392,10 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
 #pragma unroll
           for (int k = 0; k < 4; ++k) mma_ss(tAQ, dDO + 2 * k, dSk + 2 * k, kIdescKK, k > 0);   // AccQ = dO S^T
 #pragma unroll
-          for (int k = 0; k < 4; ++k) mma_ss(tAK, dZ + 2 * k, dDk + 2 * k, kIdescKK, k > 0);    // AccK = V D^T
+          for (int k = 0; k < 4; ++k) mma_ss(tAK, dZ + 2 * k, dDk + 2 * k, kIdescKK, k > 0);    // AccK = (Zw or V) D^T
 #pragma unroll
           for (int k = 0; k < 4; ++k) mma_ss(tAV, dK + 2 * k, dDmn + 128 * k, kIdescMN, k > 0);  // AccV = K D
-          mma_commit(&bar_acc_full);
+          mma_commit(&bar_acc_full[ab]);
         }
       }
     }
@@ -389,27 +404,34 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
     const int wq = warp & 3, row = 32 * wq + lane;
     const uint32_t lane_base = static_cast<uint32_t>(32 * wq) << 16;
     uint32_t ph_prep2 = 0;
-    int p2 = 0;  // apply items seen so far
+    int p2 = 0;  // second-pass items seen so far
     bool ok = true;
     for (int t = 0; ok && t < nseq; ++t) {
-      const int g0 = t * items;
+      const int g0 = t * SL;
       const int bh = seq_of(t), h = bh % H, b = bh / H;
       const unsigned char* keep_b = keep ? keep + static_cast<size_t>(b) * N : nullptr;
       const float L = btc_count_keep(keep_b, N, lane);
       const float sigma = 1.0f / (1.0f + __expf(-norm_const[h]));
       const float a = length_factor(fmaxf(L, 1.0f), sigma);
       float gsum = 0.f;
-      // ---- first pass: Qw = diag(keep / |q|) q (group 0),  Zw = diag(keep a / |k|) V (group 1), in place
+      // ---- first pass: Qw = diag(keep / |q|) q (group 0),  Zw = diag(keep a / |k|) V (group 1), in place; the row
+      // factors stay in shared memory for the chunks that stay
       if (group < 2) {
         for (int j = 0; ok && j < n; ++j) {
           const int g = g0 + j, s = g % NS, pos = j * kTcChunk + row;
           if (!(ok = wait_bar_warp(&bar_full[s], (g / NS) & 1, abort_flag, kWaitTma, g))) break;
           unsigned char* st = smem + s * STAGE;
           const bool kp = pos < N && (!keep_b || keep_b[pos]);
-          if (group == 0)
-            scale_row_rolled<T>(st, row, kp ? inv_norm(row_sumsq_rolled<T>(st, row)) : 0.f);
-          else
-            scale_row_rolled<T>(st + 2 * kTileBytes, row, kp ? inv_norm(row_sumsq_rolled<T>(st + kTileBytes, row)) * a : 0.f);
+          if (group == 0) {
+            const float rq = kp ? inv_norm(row_sumsq_rolled<T>(st, row)) : 0.f;
+            s_rq[s][row] = rq;
+            scale_row_rolled<T>(st, row, rq);
+          } else {
+            const float rk = kp ? inv_norm(row_sumsq_rolled<T>(st + kTileBytes, row)) : 0.f;
+            s_rk[s][row] = rk;
+            s_w[s][row] = rk * a;
+            scale_row_rolled<T>(st + 2 * kTileBytes, row, rk * a);
+          }
           fence_proxy_async_smem();
           warp_arrive(&bar_prep1[s], lane);
         }
@@ -426,44 +448,52 @@ bidir_bwd_tc_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_const
         warp_arrive(&bar_state, lane);
       }
       // ---- second pass
-      for (int c = 0; ok && c < n; ++c, ++p2) {
-        const int g = g0 + n + c, s = g % NS, pos = c * kTcChunk + row;
+      for (int m = 0; ok && m < n; ++m, ++p2) {
+        const int g = g0 + p2_slot(m), s = g % NS, pos = p2_chunk(m) * kTcChunk + row;
+        const bool resident = m < R;  // the q tile holds Qw and the V tile Zw; the row factors are in shared memory
+        const int ab = p2 & 1;
+        const uint32_t tAQ = tAcc + 192 * ab, tAK = tAQ + 64, tAV = tAQ + 128;
         unsigned char* sQ = smem + s * STAGE;
         unsigned char* sK = sQ + kTileBytes;
         unsigned char* sV = sQ + 2 * kTileBytes;
-        if (group == 0) {  // the row factors, for the other two groups
-          if (!(ok = wait_bar_warp(&bar_full[s], (g / NS) & 1, abort_flag, kWaitTma, g))) break;
-          const bool kp = pos < N && (!keep_b || keep_b[pos]);
-          const float rk = kp ? inv_norm(row_sumsq_rolled<T>(sK, row)) : 0.f;
-          s_rq[s][row] = kp ? inv_norm(row_sumsq_rolled<T>(sQ, row)) : 0.f;
-          s_rk[s][row] = rk;
-          s_w[s][row] = rk * a;
-          warp_arrive(&bar_prep2[s], lane);
-          if (!(ok = wait_bar_warp(&bar_acc_full, p2 & 1, abort_flag, kWaitAcc, g))) break;
+        if (group == 0) {
+          if (!resident) {  // the row factors of a reloaded chunk, for the other two groups
+            if (!(ok = wait_bar_warp(&bar_full[s], (g / NS) & 1, abort_flag, kWaitTma, g))) break;
+            const bool kp = pos < N && (!keep_b || keep_b[pos]);
+            const float rk = kp ? inv_norm(row_sumsq_rolled<T>(sK, row)) : 0.f;
+            s_rq[s][row] = kp ? inv_norm(row_sumsq_rolled<T>(sQ, row)) : 0.f;
+            s_rk[s][row] = rk;
+            s_w[s][row] = rk * a;
+            warp_arrive(&bar_prep2[s], lane);
+          }
+          if (!(ok = wait_bar_warp(&bar_acc_full[ab], (p2 >> 1) & 1, abort_flag, kWaitAcc, g))) break;
           tc_fence_after_sync();
-          // dv = w AccV;  v' . dv' = w (v . AccV)
-          const float w = rk * a;
-          gsum += w * row_from_acc_dot<T>(sV, row, tAV + lane_base, w);
+          // dv = w AccV;  v' . dv' = (w v) . AccV: the tile holds w v (resident) or v (reloaded)
+          const float w = s_w[s][row];
+          const float d = row_from_acc_dot<T>(sV, row, tAV + lane_base, w);
+          gsum += resident ? d : w * d;
         } else {
-          // groups 1 and 2: the row factors (prep2) and the accumulators
-          if (!(ok = wait_bar_warp(&bar_prep2[s], (ph_prep2 >> s) & 1, abort_flag, kWaitPrepped, g))) break;
-          ph_prep2 ^= 1u << s;
-          if (!(ok = wait_bar_warp(&bar_acc_full, p2 & 1, abort_flag, kWaitAcc, g))) break;
+          // groups 1 and 2: the row factors (prep2, for a reloaded chunk) and the accumulators
+          if (!resident) {
+            if (!(ok = wait_bar_warp(&bar_prep2[s], (ph_prep2 >> s) & 1, abort_flag, kWaitPrepped, g))) break;
+            ph_prep2 ^= 1u << s;
+          }
+          if (!(ok = wait_bar_warp(&bar_acc_full[ab], (p2 >> 1) & 1, abort_flag, kWaitAcc, g))) break;
           tc_fence_after_sync();
           if (group == 1) {
-            // dq = keep/|q| (dq^ - q^ (q^ . dq^)),  dq^ = AccQ,  q^ = rq q
+            // dq = keep/|q| (dq^ - q^ (q^ . dq^)),  dq^ = AccQ; the tile holds q^ (resident) or q (reloaded: q^ = rq q)
             const float rq = s_rq[s][row];
             const float dotq = row_dot_acc<T>(sQ, row, tAQ + lane_base);
-            row_from_acc<T, true>(sQ, row, tAQ + lane_base, rq, -rq * rq * rq * dotq);
+            row_from_acc<T, true>(sQ, row, tAQ + lane_base, rq, resident ? -rq * dotq : -rq * rq * rq * dotq);
           } else {
-            // dk = dk^' - k^ (k^ . dk^') with dk^' = w AccK  (= dk^ / |k|; the row factor of Zw, applied here)
-            const float rk = s_rk[s][row], w = s_w[s][row];
+            // dk = dk^' - k^ (k^ . dk^') with dk^' = dk^ / |k| = AccK (resident: Zw D^T) or w AccK (reloaded: V D^T)
+            const float rk = s_rk[s][row], w = resident ? 1.0f : s_w[s][row];
             const float dotk = row_dot_acc<T>(sK, row, tAK + lane_base);
             row_from_acc<T, true>(sK, row, tAK + lane_base, w, -rk * rk * w * dotk);
           }
         }
         tc_fence_before_sync();
-        warp_arrive(&bar_acc_free, lane);
+        warp_arrive(&bar_acc_free[ab], lane);
         fence_proxy_async_smem();
         warp_arrive(&bar_out[s], lane);
       }
