@@ -228,6 +228,10 @@ def run_extras(world, rank, dev, with_cpu):
                "achieved_gbs_per_gpu": r["algorithmic_bytes_per_step"] / t / 1e9,
                "frac": r["algorithmic_bytes_per_step"] / t / 1e9 / peak, "cuda_graph": r["cuda_graph"],
                "us_per_step_python_launch": r["us_per_step_python_launch"]}
+        if r.get("two_groups"):  # the batch as two independent chains of launches on two streams
+            t2 = max_over_ranks(r["two_groups"]["us_per_step"] * 1e-6)
+            row["two_groups"] = {"what": r["two_groups"]["what"], "us_per_step": t2 * 1e6, "tokens_per_s": world * 64 / t2,
+                                 "frac": r["algorithmic_bytes_per_step"] / t2 / 1e9 / peak}
         if with_cpu and rank == 0:
             threads = os.cpu_count() or 1
             row["cpu_baseline"] = {"value": cpu_decode_sample(d, threads), "unit": "tokens/s", "cores": threads, "kind": "port",

@@ -81,6 +81,7 @@ def bench_decode(d, steps, B=64, H=16):
     except Exception as e:  # report the eager figure and say why
         graphed = f"graph capture failed: {type(e).__name__}: {str(e)[:80]}"
     bytes_step = B * H * (2 * d * d * 4 + 4 * d * 2)
+    t2 = _decode_groups(L, dev, d, B, H, nstates, groups=2) if graphed is True else None
     # multi-token launch: state resident in registers
     T = 512
     qs = torch.randn(B, H, T, d, device=dev, generator=g).bfloat16()
@@ -100,7 +101,47 @@ def bench_decode(d, steps, B=64, H=16):
         "tokens_per_s": B / t, "algorithmic_bytes_per_step": bytes_step,
         "achieved_gbs": bytes_step / t / 1e9, "peak_gbs": peak, "peak_source": kind, "frac": bytes_step / t / 1e9 / peak,
         "multi_token_launch": {"T": T, "us_per_token": tm / T * 1e6, "tokens_per_s": B * T / tm},
+        "two_groups": None if t2 is None else {
+            "what": "the batch as two independent half-batches, each its own chain of per-token launches on its own stream",
+            "us_per_step": t2 * 1e6, "tokens_per_s": B / t2, "frac": bytes_step / t2 / 1e9 / peak},
     }
+
+
+def _decode_groups(L, dev, d, B, H, nstates, groups=2, steps=64, reps=16):
+    """The same decode work as ``groups`` independent chains (different batch entries never depend on each other): one
+    CUDA graph of per-token launches per group, replayed on a stream of its own, so that one chain's launch gap and
+    first-byte latency fall into the other's streaming.  Seconds per step of the whole batch."""
+    Bc = B // groups
+    g = torch.Generator(device=dev).manual_seed(4321)
+    nc = 0.5 * torch.ones(H, device=dev)
+    cur = torch.cuda.current_stream()
+    streams, graphs, keep = [torch.cuda.Stream() for _ in range(groups)], [], []
+    for c in range(groups):
+        states = [torch.zeros(Bc, H, d, d, device=dev) for _ in range(nstates)]
+        q, k, v = (torch.randn(Bc, H, 1, d, device=dev, generator=g).bfloat16() for _ in range(3))
+        out = torch.empty_like(v)
+        keep.append((states, q, k, v, out))
+        s = streams[c]
+        s.wait_stream(cur)
+        with torch.cuda.stream(s):
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=s):
+                for i in range(steps):
+                    _lib.check(L.cott_decode_step(states[i % nstates].data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                                  nc.data_ptr(), out.data_ptr(), Bc, H, d, d, 3, i + 1, None,
+                                                  _lib.stream_ptr(dev)), "cott_decode_step")
+        graphs.append(gr)
+    torch.cuda.synchronize()
+
+    def once():
+        for c in range(groups):
+            streams[c].wait_stream(cur)
+            with torch.cuda.stream(streams[c]):
+                graphs[c].replay()
+        for c in range(groups):
+            cur.wait_stream(streams[c])
+
+    return _time(once, reps, warmup=3) / steps
 
 
 def bench_bidir(B=32, H=12, N=512, d=64):
