@@ -59,8 +59,10 @@ const char* cott_status_string(int status);
  *
  * Kernels: 16-bit dtypes with D_attn = 64 or 128 and D_value a multiple of 64 run on the tensor cores (tcgen05; at 128
  * both halves of q and k go into the same score and state accumulators, the counterpart of the reference's
- * kernel_mod_4<T, 32>, :173-251); D_attn = 192 / 256 as 64-wide tensor-core launches on strided slices; everything else
- * on the exact CUDA-core kernel.
+ * kernel_mod_4<T, 32>, :173-251); D_attn = 192 / 256 as 64-wide tensor-core launches on strided slices, whose partial
+ * results (one per 64-wide slice of D_attn, each an fp32 sum rounded once to the storage type) are added in the storage
+ * type -- up to four roundings per output at D_attn = 256, 1e-2 relative against the exact kernel; everything else on the
+ * exact CUDA-core kernel.
  * Memory: unlike the reference's kernel call, which needs no workspace, the tensor-core paths take stream-ordered
  * scratch from a memory pool that the LIBRARY owns and keeps for the life of the process (cudaMallocFromPoolAsync /
  * cudaFreeAsync on `stream`, release threshold = unlimited) in two cases: few (batch, head) pairs with a long sequence
