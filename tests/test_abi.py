@@ -60,6 +60,28 @@ def test_argument_validation_needs_no_gpu(lib):
     assert lib.cott_scan(None, None, None, None, 0, 1, 8, 32, 16, 0, 0, None) == 0  # empty: nothing to do
 
 
+def test_rotary_arguments_are_checked_without_a_gpu():
+    """``cott_cos_attn_fwd_rotary``: the rotary descriptor is validated before any pointer is touched."""
+    from cottention_transformer_b200 import _lib
+    L = _lib.lib()
+    buf = (ctypes.c_float * 64)()
+    addr = ctypes.addressof(buf)
+    addr += (-addr) % 16  # 16-byte aligned inside the buffer
+
+    def call(rot):
+        return L.cott_cos_attn_fwd_rotary(None, None, None, None, None, None, None, None, None if rot is None else ctypes.byref(rot),
+                                          1, 2, 128, 64, 64, 3, None)
+
+    assert call(None) == 1                                                     # no descriptor
+    assert call(_lib.CottRotaryTables(None, None, 64, 0)) == 1                 # null tables
+    assert call(_lib.CottRotaryTables(addr, addr, 24, 0)) == 2                 # rotary dim not a multiple of 16
+    assert b"multiple of 16" in L.cott_last_error()
+    assert call(_lib.CottRotaryTables(addr, addr, 128, 0)) == 2                # wider than the head
+    assert call(_lib.CottRotaryTables(addr + 4, addr, 64, 0)) == 5             # misaligned table
+    assert call(_lib.CottRotaryTables(addr, addr, 64, 6)) == 5                 # batch stride not a multiple of 4
+    assert L.cott_cos_attn_fwd_rotary(None, None, None, None, None, None, None, None, None, 1, 2, 128, 128, 128, 3, None) == 7  # head dim 128
+
+
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     from cottention_transformer_b200 import _lib
     monkeypatch.setattr(_lib, "_lib", None)
