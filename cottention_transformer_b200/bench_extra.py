@@ -273,7 +273,7 @@ def bench_long_context_d128(N, B=1, H=16, d=128, iters=5):
     _lib.check_device_status()
     nbytes = 11 * B * H * N * d * 2
     peak, kind = _peak_gbs()
-    return {"what": f"causal fwd+bwd prefill, B={B} H={H} N={N} d={d} bf16, row factors around tensor-core scans",
+    return {"what": f"causal fwd+bwd prefill, B={B} H={H} N={N} d={d} bf16, the fused 128-wide tensor-core kernels",
             "us_per_step": t * 1e6, "tokens_per_s": B * N / t, "algorithmic_bytes": nbytes, "frac": nbytes / t / 1e9 / peak,
             "peak_source": kind}
 
@@ -282,7 +282,7 @@ def bench_prefill_sharded(N, d, world=1, rank=0, iters=3, H=16):
     """Long-context prefill, forward + backward, B = 1, the H heads split over `world` GPUs (no tensor crosses GPUs:
     every head is an independent sequence).  The full tensors are generated from one seed and sliced, so every GPU
     count works on the same data.  Through the public op ``cos_attn_causal`` (head dim 64: fused tensor-core kernels,
-    segment-parallel; head dim 128: row factors around tensor-core scans).  Returns this rank's seconds per step."""
+    segment-parallel; head dim 128: the fused 128-wide kernels, one scan per output).  Returns this rank's seconds per step."""
     from .cos_attention import cos_attn_causal
     from .sharding import shard_range
     dev = torch.device("cuda", torch.cuda.current_device())

@@ -376,19 +376,19 @@ struct RotArgs {
 };
 // A warp rotates its own 32 rows of a tile (rows 32 (warp % 4) ..): lane l takes piece l % 8 of the rows 4 i + l / 8,
 // i = 0 .. 7, so that one load instruction of the warp covers four whole table rows (row-per-thread loads touch 32
-// different lines per instruction and are bound by the load pipe).  A round = the table values of four of a lane's
-// eight rows, in registers; the loads of round 0 are issued before the wait that precedes the rotation (the position
+// different lines per instruction and are bound by the load pipe).  A batch = the table values of four of a lane's
+// eight rows, in registers; the loads of the first batch are issued before the wait that precedes the rotation (the position
 // is known in advance), so their latency -- an L2 round trip -- hides behind it.
 struct RotRegs {
   float4 sn[4], cs[4];
 };
 // `sin_tab`, `cos_tab`: the table rows of the warp's first row; `nrows`: how many of the warp's rows exist (<= 32)
 __device__ __forceinline__ void rot_load(RotRegs& t, const float* __restrict__ sin_tab, const float* __restrict__ cos_tab, int lane,
-                                         int round, int pieces, int nrows) {
+                                         int batch, int pieces, int nrows) {
   const int pj = lane & 7;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const int r = 16 * round + 4 * i + (lane >> 3);
+    const int r = 16 * batch + 4 * i + (lane >> 3);
     if (pj < pieces && r < nrows) {
       t.sn[i] = __ldg(reinterpret_cast<const float4*>(sin_tab + static_cast<size_t>(r) * (4 * pieces)) + pj);
       t.cs[i] = __ldg(reinterpret_cast<const float4*>(cos_tab + static_cast<size_t>(r) * (4 * pieces)) + pj);
@@ -396,7 +396,7 @@ __device__ __forceinline__ void rot_load(RotRegs& t, const float* __restrict__ s
   }
 }
 // Rotates (INV: by the transposed rotation) the first 8 * pieces elements of the warp's rows `row_base` .. of one or
-// two tiles that hold the same positions, in place; `t` holds round 0.  Ends with a __syncwarp: the rows are then
+// two tiles that hold the same positions, in place; `t` holds the first batch.  Ends with a __syncwarp: the rows are then
 // read row-per-thread.
 template <typename T, bool INV, int NT>
 __device__ __forceinline__ void rotate_rows(RotRegs& t, unsigned char* t0, unsigned char* t1, int row_base, int lane,
@@ -404,11 +404,11 @@ __device__ __forceinline__ void rotate_rows(RotRegs& t, unsigned char* t0, unsig
                                             int nrows) {
   const int pj = lane & 7;
 #pragma unroll 1
-  for (int round = 0; round < 2; ++round) {
-    if (round) rot_load(t, sin_tab, cos_tab, lane, 1, pieces, nrows);
+  for (int batch = 0; batch < 2; ++batch) {
+    if (batch) rot_load(t, sin_tab, cos_tab, lane, 1, pieces, nrows);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const int r = 16 * round + 4 * i + (lane >> 3);
+      const int r = 16 * batch + 4 * i + (lane >> 3);
       if (pj < pieces && r < nrows) {
         const float s4[4] = {t.sn[i].x, t.sn[i].y, t.sn[i].z, t.sn[i].w}, c4[4] = {t.cs[i].x, t.cs[i].y, t.cs[i].z, t.cs[i].w};
 #pragma unroll

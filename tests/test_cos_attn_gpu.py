@@ -169,7 +169,7 @@ def test_exact_mode_matches_reference_fixture_with_padding(dt):
 
 
 def test_full_size_config_properties():
-    """BASELINE shape (B=8,H=16,N=4096,d=64,bf16): checked on a slice against the oracle and by
+    """The headline benchmark shape (B=8,H=16,N=4096,d=64,bf16): checked on a slice against the oracle and by
     linearity in V (out(q,k,v1+v2) = out(q,k,v1) + out(q,k,v2) up to rounding)."""
     from cottention_transformer_b200 import cos_attn_causal, _lib
     B, H, N = 8, 16, 4096
