@@ -555,6 +555,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // broadcast: provably warp-uniform
   const int bh = blockIdx.x;
   const int h = bh % H, bb = bh / H;
+  pdl_allow_next();  // the next kernel of the stream may set itself up on the SMs this one leaves free
   // Segment-parallel launches (gridDim.y > 1) give each CTA `chunks_per_seg` consecutive chunks of the
   // sequence and the state before its first chunk (`init_state[bh][seg]`, fp32 [64 x 64] in this kernel's
   // own state layout, rows = columns of Y); chunk numbers below are local, `chunk0 + c` is the position.
@@ -606,6 +607,7 @@ causal_tc_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  pdl_wait_prior();  // nothing another kernel may have written has been read so far
   const uint32_t tmem = tmem_slot;
   // TMEM columns: scores 2 x 128 | accumulators 2 x 64 | state 64
   const uint32_t tP0 = tmem, tAcc0 = tmem + 256, tS = tmem + 384;
@@ -937,6 +939,7 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);  // broadcast: provably warp-uniform
   const int bh = blockIdx.x;
   const int h = bh % H, bb = bh / H;
+  pdl_allow_next();
   // Segment-parallel launches (gridDim.y > 1): this CTA owns `chunks_per_seg` consecutive chunks, walks them
   // backwards, and starts from the state of everything after them (`init_state[bh][seg]`, fp32 [64 x 64],
   // rows d_k).  `ci` is local; the position of item ci is chunk `last_chunk - ci`.
@@ -984,6 +987,7 @@ causal_bwd_kv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_cons
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  pdl_wait_prior();
   const uint32_t tmem = tmem_slot;
   const uint32_t tE = tmem, tF = tmem + 128, tK = tmem + 256, tV = tmem + 320, tR = tmem + 384;
 

@@ -49,6 +49,10 @@ struct SegPlan {
   const int* count = nullptr;
   TileStrides in{0, 0, 0}, out{0, 0, 0};  // strides of q, k, v, dq, dk, dv / of out, dout; all zero = contiguous [B,H,N,64]
   RotArgs rot{nullptr, nullptr, 0, 0};    // rotary embedding of q, k inside the kernels (one segment only), or sin = null
+  // The caller has already zeroed the norm_const gradient on the stream, before the dQ launch: a memset between the dQ
+  // and the dK/dV launch would end the chain of programmatic dependent launches (the dK/dV kernel could not set itself
+  // up while the dQ kernel drains).
+  bool dnorm_zeroed = false;
 };
 TileStrides in_strides(const SegPlan& p, long H, long N) { return p.in.n ? p.in : contiguous_bhnd(H, N); }
 TileStrides out_strides(const SegPlan& p, long H, long N) { return p.out.n ? p.out : contiguous_bhnd(H, N); }
@@ -77,8 +81,8 @@ int launch_fwd(const void* q, const void* k, const void* v, const float* nc, voi
   const size_t smem = causal_tc_smem_bytes(kModeFwd);
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   if (plan.cps == 0) plan.cps = plan_segments(N, 1).cps;
-  kern<<<dim3((unsigned)BH, plan.nseg), kTcThreads, smem, stream>>>(mq, mk, mv, mq, mo, nc, H, N, init, plan.cps, plan.keep, plan.count,
-                                                                   static_cast<uint4*>(saved), plan.rot);
+  COTT_CUDA_TRY(launch_pdl(kern, dim3((unsigned)BH, plan.nseg), kTcThreads, smem, stream, mq, mk, mv, mq, mo, nc, H, N, init, plan.cps,
+                           plan.keep, plan.count, static_cast<uint4*>(saved), plan.rot));
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
@@ -99,7 +103,8 @@ int launch_bwd_dq(const void* q, const void* k, const void* v, const float* nc, 
   const size_t smem = causal_tc_smem_bytes(kModeDq);
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   if (plan.cps == 0) plan.cps = plan_segments(N, 1).cps;
-  kern<<<dim3((unsigned)BH, plan.nseg), kTcThreads, smem, stream>>>(md, mv, mk, mq, mo, nc, H, N, init, plan.cps, plan.keep, plan.count, nullptr, plan.rot);
+  COTT_CUDA_TRY(launch_pdl(kern, dim3((unsigned)BH, plan.nseg), kTcThreads, smem, stream, md, mv, mk, mq, mo, nc, H, N, init, plan.cps,
+                           plan.keep, plan.count, static_cast<uint4*>(nullptr), plan.rot));
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
@@ -115,14 +120,15 @@ int launch_bwd_dkdv(const void* q, const void* k, const void* v, const float* nc
       (st = tmap(&mv, v, dtype, B, H, N, in_strides(plan, H, N))) || (st = tmap(&md, dout, dtype, B, H, N, out_strides(plan, H, N))) ||
       (st = tmap(&mdk, dk, dtype, B, H, N, in_strides(plan, H, N))) || (st = tmap(&mdv, dv, dtype, B, H, N, in_strides(plan, H, N))))
     return st;
-  COTT_CUDA_TRY(cudaMemsetAsync(dnorm, 0, sizeof(float) * H, stream));
+  if (!plan.dnorm_zeroed) COTT_CUDA_TRY(cudaMemsetAsync(dnorm, 0, sizeof(float) * H, stream));
   const bool ext = plan.nseg > 1 || init || plan.keep;
   auto kern = plan.rot.sin ? causal_bwd_kv_kernel<T, true, true>
                            : (ext ? causal_bwd_kv_kernel<T, true> : causal_bwd_kv_kernel<T, false>);
   const size_t smem = causal_bwd_kv_smem_bytes();
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   if (plan.cps == 0) plan.cps = plan_segments(N, 1).cps;
-  kern<<<dim3((unsigned)BH, plan.nseg), plan.rot.sin ? kKvThreadsRot : kKvThreads, smem, stream>>>(mq, mk, mv, md, mdk, mdv, dnorm, nc, H, N, init, plan.cps, plan.keep, plan.count, plan.rot);
+  COTT_CUDA_TRY(launch_pdl(kern, dim3((unsigned)BH, plan.nseg), plan.rot.sin ? kKvThreadsRot : kKvThreads, smem, stream, mq, mk, mv, md, mdk,
+                           mdv, dnorm, nc, H, N, init, plan.cps, plan.keep, plan.count, plan.rot));
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
@@ -218,6 +224,8 @@ int run_bwd_seg(const void* q, const void* k, const void* v, const unsigned char
     plan.count = reinterpret_cast<const int*>(ws + 5 * A);
   }
   if (plan.nseg == 1) {
+    COTT_CUDA_TRY(cudaMemsetAsync(dnorm, 0, sizeof(float) * H, stream));
+    plan.dnorm_zeroed = true;
     int st = launch_bwd_dq<T>(q, k, v, nc, dout, dq, B, H, N, dtype, stream, nullptr, plan);
     return st ? st : launch_bwd_dkdv<T>(q, k, v, nc, dout, dk, dv, dnorm, B, H, N, dtype, stream, nullptr, plan);
   }
@@ -552,8 +560,9 @@ int launch_scan_tc_t(const void* q, const void* k, const void* v, void* out, int
                             : (reversed ? causal_tc_kernel<T, kModeScanRev, false> : causal_tc_kernel<T, kModeScan, false>);
   const size_t smem = causal_tc_smem_bytes(kModeScan);
   COTT_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<dim3((unsigned)((long)B * H), plan.nseg), kTcThreads, smem, stream>>>(mq, mk, mv, mq, mo, nullptr, H, N, init, plan.cps, nullptr,
-                                                                              nullptr, nullptr, RotArgs{nullptr, nullptr, 0, 0});
+  COTT_CUDA_TRY(launch_pdl(kern, dim3((unsigned)((long)B * H), plan.nseg), kTcThreads, smem, stream, mq, mk, mv, mq, mo,
+                           static_cast<const float*>(nullptr), H, N, init, plan.cps, static_cast<const unsigned char*>(nullptr),
+                           static_cast<const int*>(nullptr), static_cast<uint4*>(nullptr), RotArgs{nullptr, nullptr, 0, 0}));
   COTT_CUDA_TRY(cudaGetLastError());
   return COTT_OK;
 }
@@ -749,9 +758,27 @@ int cott_cos_attn_bwd_dkdv(const void* q, const void* k, const void* v, const fl
 int cott_cos_attn_bwd(const void* q, const void* k, const void* v, const float* norm_const, const void* dout,
                       void* dq, void* dk, void* dv, float* dnorm_const, int B, int H, int N, int Dk, int Dv,
                       int dtype, void* stream) {
-  int st = cott_cos_attn_bwd_dq(q, k, v, norm_const, dout, dq, B, H, N, Dk, Dv, dtype, stream);
+  int st = check_fused_args(B, H, N, Dk, Dv, dtype);
   if (st) return st;
-  return cott_cos_attn_bwd_dkdv(q, k, v, norm_const, dout, dk, dv, dnorm_const, B, H, N, Dk, Dv, dtype, stream);
+  if (!dnorm_const && H > 0) return fail(COTT_ERR_NULL, "null pointer: dnorm_const");
+  if ((long)B * H * N == 0 || !norm_const) {  // nothing to launch, or an argument error: the two calls report it
+    st = cott_cos_attn_bwd_dq(q, k, v, norm_const, dout, dq, B, H, N, Dk, Dv, dtype, stream);
+    return st ? st : cott_cos_attn_bwd_dkdv(q, k, v, norm_const, dout, dk, dv, dnorm_const, B, H, N, Dk, Dv, dtype, stream);
+  }
+  if ((st = check_ptrs16({{q, "q"}, {k, "k"}, {v, "v"}, {dout, "dout"}, {dq, "dq"}, {dk, "dk"}, {dv, "dv"}}))) return st;
+  DeviceScope scope(q);
+  COTT_CUDA_TRY(scope.status());
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // the gradient of norm_const is zeroed before the dQ launch, so that the two kernels follow each other directly
+  COTT_CUDA_TRY(cudaMemsetAsync(dnorm_const, 0, sizeof(float) * H, s));
+  SegPlan plan;
+  plan.dnorm_zeroed = true;
+  if (dtype == COTT_BF16) {
+    st = launch_bwd_dq<__nv_bfloat16>(q, k, v, norm_const, dout, dq, B, H, N, dtype, s, nullptr, plan);
+    return st ? st : launch_bwd_dkdv<__nv_bfloat16>(q, k, v, norm_const, dout, dk, dv, dnorm_const, B, H, N, dtype, s, nullptr, plan);
+  }
+  st = launch_bwd_dq<__half>(q, k, v, norm_const, dout, dq, B, H, N, dtype, s, nullptr, plan);
+  return st ? st : launch_bwd_dkdv<__half>(q, k, v, norm_const, dout, dk, dv, dnorm_const, B, H, N, dtype, s, nullptr, plan);
 }
 
 int cott_cos_attn_seg_count(int B, int H, int N) {

@@ -48,8 +48,8 @@ decode_kernel(float* __restrict__ state, const T* __restrict__ q, const T* __res
   // one before wrote.  The launch is allowed to begin while its predecessor in the stream is still draining (its CTAs
   // are placed as slots free up, instead of after the whole grid has retired and a launch gap has passed); nothing
   // that another kernel may have produced -- state, q, k, v, norm_const -- is read before the wait below.
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  pdl_allow_next();
+  pdl_wait_prior();
   const float sigma = 1.0f / (1.0f + __expf(-norm_const[h]));
   const long long p0 = positions ? positions[b] : pos0;
   const int piece = tid % LPR;        // which float4 of the row
@@ -124,22 +124,6 @@ decode_kernel(float* __restrict__ state, const T* __restrict__ q, const T* __res
   }
 }
 
-// <<<grid, threads, 0, stream>>> with the programmatic-stream-serialization attribute (see decode_kernel)
-template <typename K, typename... Args>
-cudaError_t launch_pdl(K kernel, unsigned grid, unsigned threads, cudaStream_t stream, Args... args) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(threads);
-  cfg.dynamicSmemBytes = 0;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kernel, args...);
-}
-
 template <typename T>
 int launch_decode(float* state, const void* q, const void* k, const void* v, const float* nc, void* out, int B, int H,
                   int Dk, int Dv, int T_steps, long long pos0, const long long* positions, cudaStream_t stream) {
@@ -147,11 +131,11 @@ int launch_decode(float* state, const void* q, const void* k, const void* v, con
 #define COTT_DECODE_CASE(DK)                                                                                     \
   case DK:                                                                                                       \
     if (Dv <= 64)                                                                                                \
-      COTT_CUDA_TRY(launch_pdl(decode_kernel<T, DK, 64>, grid, DecodeCfg<DK>::kThreads, stream, state,           \
+      COTT_CUDA_TRY(launch_pdl(decode_kernel<T, DK, 64>, dim3(grid), DecodeCfg<DK>::kThreads, 0, stream, state,           \
                                static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v), nc, \
                                static_cast<T*>(out), H, Dv, T_steps, pos0, positions));                          \
     else                                                                                                         \
-      COTT_CUDA_TRY(launch_pdl(decode_kernel<T, DK, 128>, grid, DecodeCfg<DK>::kThreads, stream, state,          \
+      COTT_CUDA_TRY(launch_pdl(decode_kernel<T, DK, 128>, dim3(grid), DecodeCfg<DK>::kThreads, 0, stream, state,          \
                                static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v), nc, \
                                static_cast<T*>(out), H, Dv, T_steps, pos0, positions));                          \
     break;
