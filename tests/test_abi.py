@@ -94,11 +94,13 @@ def test_dropin_names_import():
     import sys
     sys.path.insert(0, os.path.join(REPO, "cottention_transformer_b200", "dropin"))
     try:
+        import FastAttention   # the extension's older name
         import FastAttention2
         from FastAttention2 import kernel
         from Custom_Kernel import CustomAttention
         assert all(hasattr(kernel, n) for n in ("float32", "float64", "float16", "bfloat16"))
         assert hasattr(FastAttention2, "kernel") and hasattr(CustomAttention, "apply")
+        assert FastAttention.kernel is FastAttention2.kernel
     finally:
         sys.path.pop(0)
 
