@@ -495,7 +495,9 @@ def main():
                 "sample": f"{slices} of {B_PER_GPU * H} (batch,head) slices at N={N}, d={D}, fp32, PyTorch cumsum "
                           f"formulation + autograd, {secs:.1f} s (after one untimed warm-up slice)",
                 "config1_forward_s": cpu_config1_forward(threads),
+                "config1_forward_s_one_thread": cpu_config1_forward(1),
                 "config1": "forward only, fp32, B=2 H=8 N=1024 d=64, the same formulation, whole"}
+            torch.set_num_threads(threads)
         if extra is not None:
             line["extra"] = extra
         print(json.dumps(line), flush=True)
