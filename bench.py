@@ -20,7 +20,8 @@ Keys beyond the basic contract:
   extra      secondary workloads, each with its own algorithmic bytes, device time and fraction of the HBM peak:
              ``prefill_long`` (B=1, H=16 heads split over the ranks, N in {16k, 64k, 256k}, d in {64, 128}, fwd+bwd)
              and ``decode`` (batch 64 per GPU, 4096 single-token steps, fp32 state, d in {64, 128}) with the
-             reference's CPU recurrent loop timed beside it, and ``train`` (whole-model bf16 training steps of a
+             reference's CPU recurrent loop timed beside it, ``bidirectional`` (fwd+bwd at BERT-base attention
+             shapes) and ``train`` (whole-model bf16 training steps of a
              GPT-style decoder and a BERT-base encoder with the op inside, DDP when there are several ranks);
              ``--no-extra`` skips them
 
@@ -237,6 +238,14 @@ def run_extras(world, rank, dev, with_cpu):
             row["cpu_baseline"] = {"value": cpu_decode_sample(d, threads), "unit": "tokens/s", "cores": threads, "kind": "port",
                                    "sample": "200 tokens at batch 1, float64 state, the reference's per-token torch loop"}
         decode.append(row)
+    # the bidirectional form at BERT-base attention shapes (B=32 per GPU, H=12, N=512, d=64): every rank its own batch
+    rb = X.bench_bidir()
+    tb = max_over_ranks((rb["fwd_kernel_us"] + rb["bwd_kernel_us"]) * 1e-6)
+    ts = max_over_ranks(rb["us_per_step"] * 1e-6)
+    bidir = {"what": "bidirectional cosine attention fwd+bwd, B=32 per GPU, H=12, N=512, d=64, bf16 (BERT-base attention shapes)",
+             "scaling": "weak", "kernels_us": tb * 1e6, "fwd_kernel_us": rb["fwd_kernel_us"], "bwd_kernel_us": rb["bwd_kernel_us"],
+             "kernels_frac": rb["algorithmic_bytes"] / tb / 1e9 / peak, "us_per_step_through_the_op": ts * 1e6,
+             "tokens_per_s": world * 32 * 512 / ts, "algorithmic_bytes_per_gpu": rb["algorithmic_bytes"]}
     # whole-model training steps around the op (synthetic token ids, random weights; DDP over NCCL when world > 1)
     from cottention_transformer_b200 import bench_train as T
     train = [T.run_model(name, steps=4, warmup=2) for name in ("gpt", "bert")]
@@ -249,7 +258,8 @@ def run_extras(world, rank, dev, with_cpu):
                              "rows": prefill},
             "decode": {"what": "recurrent decode, one launch per token replayed from a CUDA graph, batch 64 per GPU, "
                                "bf16 tokens, fp32 state in HBM (8 state buffers in rotation: larger than L2 at d=128)",
-                       "scaling": "weak", "rows": decode}}
+                       "scaling": "weak", "rows": decode},
+            "bidirectional": bidir}
 
 
 def reference_cuda_kernel_sample(iters=3):
