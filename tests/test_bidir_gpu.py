@@ -44,10 +44,12 @@ def test_matches_reference_module_fixture(name, dt):
 # head dim 64 in a 16-bit dtype takes the tensor-core kernels (chunks of 128: 1, 129 and 640 cover one short
 # chunk, a one-row tail and an odd chunk count; 4 x 100 and 3 x 111 sequences are more than the SMs of the GPU, so
 # the CTAs of the persistent backward kernel walk two or three sequences each, of different heads and batch entries,
-# through one ring); everything else takes the CUDA-core kernels
+# through one ring; 2 x 100 sequences of 600 positions add chunks that are loaded a second time -- five chunks, three of
+# which stay in shared memory between the passes -- to a ring that carries on across sequences); everything else takes
+# the CUDA-core kernels
 @pytest.mark.parametrize("shape", [(2, 3, 512, 64, 64), (1, 2, 77, 32, 48), (2, 2, 1, 16, 16), (1, 1, 300, 128, 128),
                                    (2, 2, 1, 64, 64), (1, 2, 129, 64, 64), (1, 3, 640, 64, 64), (4, 100, 200, 64, 64),
-                                   (3, 111, 384, 64, 64)])
+                                   (3, 111, 384, 64, 64), (2, 100, 600, 64, 64)])
 @pytest.mark.parametrize("masked", [False, True])
 def test_matches_oracle(dt, shape, masked):
     from cottention_transformer_b200 import cos_attn_bidirectional
