@@ -6,6 +6,8 @@
 * config 5 (B=1, N in {65536, 262144}, d in {64, 128}): forward and gradients against the reference's own
   compiled kernel in float64 (sequential in N, so long sequences cost it no memory) with the module math
   and the backward of Custom_Kernel.py:106-108 around it; one head is cross-checked by the C fp64 recurrence;
+* config 4's attention shape (B=32, H=12, N=512, d=64, bf16, bidirectional, with and without padding): forward and
+  gradients of every sequence against the fp64 oracle (evaluated on the GPU);
 * decode: 4096 single-token steps at batch 64 against the fp64 restatement of the reference's loop;
 * the time-out path of the tensor-core kernels (a wait that nothing completes) without any fault.
 
@@ -59,6 +61,40 @@ def test_config2_full_size_forward_and_gradients_match_the_fp64_oracle(capsys):
     with capsys.disabled():
         print(f"\n[config 2 full size, bf16 vs fp64 oracle, worst Frobenius error over the 128 slices] "
               + ", ".join(f"{n} {x:.2e}" for n, x in worst.items()) + f", dnorm {e / dnc_t.abs().max().item():.2e}")
+
+
+@pytest.mark.parametrize("masked", [False, True])
+def test_config4_bidirectional_forward_and_gradients_match_the_fp64_oracle(masked, capsys):
+    """BERT-base attention shapes: 384 sequences of four chunks, i.e. the persistent backward kernel with two or three
+    sequences per CTA and a chunk that is loaded a second time."""
+    from cottention_transformer_b200 import cos_attn_bidirectional, _lib
+    B, H, N, d = 32, 12, 512, 64
+    q, k, v, do, _ = O.make_inputs(B, H, N, d, seed=44, normalize=False, dtype=torch.bfloat16)
+    nc = torch.linspace(-0.5, 1.0, H)
+    keep = None
+    if masked:
+        g = torch.Generator().manual_seed(5)
+        lengths = torch.randint(N // 4, N + 1, (B,), generator=g)
+        keep = (torch.arange(N)[None, :] < lengths[:, None])
+    qd, kd, vd = (t.double().cuda().requires_grad_() for t in (q, k, v))
+    ncd = nc.double().cuda().requires_grad_()
+    ref = O.cos_attn_bidirectional(qd, kd, vd, ncd, None if keep is None else keep.cuda())
+    (ref * do.double().cuda()).sum().backward()
+    qc, kc, vc = (t.cuda().requires_grad_() for t in (q, k, v))
+    ncc = nc.cuda().requires_grad_()
+    out = cos_attn_bidirectional(qc, kc, vc, ncc, None if keep is None else keep.cuda())
+    out.backward(do.cuda())
+    _lib.check_device_status()
+    errs = {}
+    for name, a, b in (("out", out, ref.detach()), ("dq", qc.grad, qd.grad), ("dk", kc.grad, kd.grad), ("dv", vc.grad, vd.grad)):
+        e_max, e_fro = _rel(a.detach(), b)
+        errs[name] = e_fro
+        assert e_max <= REL16 and e_fro <= REL16, (name, e_max, e_fro)
+    e = (ncc.grad.double() - ncd.grad).abs().max().item() / ncd.grad.abs().max().item()
+    assert e <= REL16, e
+    with capsys.disabled():
+        print(f"\n[config 4 attention shape, bidirectional, bf16 vs fp64 oracle, masked={masked}] Frobenius errors "
+              + ", ".join(f"{n} {x:.2e}" for n, x in errs.items()) + f", dnorm {e:.2e}")
 
 
 class _RefScan(torch.autograd.Function):
