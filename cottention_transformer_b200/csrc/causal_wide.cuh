@@ -470,6 +470,22 @@ wide_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CU
   if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
+// Decode state of a whole prompt from the segment states of a head-dim-128 state pass:
+// state[bh][j][i] (+)= sum_seg seg_state[bh][j / 64][seg][i][j % 64]   (the decode kernel keeps the value index first,
+// GPTCosAttention.py:264).  grid = (B*H, 2 slices), any block size.
+__global__ void wide_seg_to_decode_state_kernel(const float* __restrict__ seg_state, float* __restrict__ state, int nseg,
+                                                int accumulate) {
+  const int slice = blockIdx.y;
+  const size_t base = (static_cast<size_t>(blockIdx.x) * gridDim.y + slice) * nseg * (kTcChunk * kTcD);
+  float* dst = state + static_cast<size_t>(blockIdx.x) * (128 * 128);
+  for (int e = threadIdx.x; e < 64 * 128; e += blockDim.x) {
+    const int jj = e / 128, i = e % 128;  // output element [64 slice + jj][i] = input element [i][jj]
+    float sum = accumulate ? dst[(64 * slice + jj) * 128 + i] : 0.f;
+    for (int s = 0; s < nseg; ++s) sum += seg_state[base + static_cast<size_t>(s) * (kTcChunk * kTcD) + i * kTcD + jj];
+    dst[(64 * slice + jj) * 128 + i] = sum;
+  }
+}
+
 inline size_t wide_smem_bytes() {
   return static_cast<size_t>(kWdStages * kWdStageBytes + 2 * kWdStateBytes + 2 * kTileBytes + kWdStages * kTcChunk * sizeof(float) +
                              32 * sizeof(uint64_t));

@@ -994,8 +994,43 @@ int cott_cos_attn_wide_bwd(const void* q, const void* k, const void* v, const un
              : run_wide_bwd<__half>(q, k, v, keep, norm_const, out, dout, workspace, dq, dk, dv, dnorm_const, B, H, N, dtype, s);
 }
 
+}  // extern "C"
+
+namespace {
+// head dim 128: a state-only pass of the wide kernel (row norms and the length factor from the tiles), then the sum
+// over the segments, transposed into the decode layout.  `workspace`: cott_cos_attn_wide_workspace_bytes(B, H, N).
+template <typename T>
+int run_wide_prefill_state(const void* k, const void* v, const float* nc, float* state, void* workspace, int accumulate, int B,
+                           int H, int N, int dtype, cudaStream_t stream) {
+  WideWs ws = wide_ws(workspace, B, H, N);
+  const SegPlan plan = plan_segments(N, wide_seg_count(B, H, N, 128));
+  WideArgs a = {};
+  a.norm_const = nc;
+  a.chunks_per_seg = plan.cps;
+  a.state_out = ws.seg;
+  WideTensors t{nullptr, k, v, nullptr, nullptr, 128};
+  int st = launch_wide_t<T, false, true, true>(t, a, B, H, N, dtype, plan.nseg, stream);
+  if (st) return st;
+  wide_seg_to_decode_state_kernel<<<dim3((unsigned)((long)B * H), 2), 256, 0, stream>>>(ws.seg, state, plan.nseg, accumulate != 0);
+  COTT_CUDA_TRY(cudaGetLastError());
+  return COTT_OK;
+}
+}  // namespace
+
+extern "C" {
+
 int cott_cos_attn_prefill_state(const void* k, const void* v, const float* norm_const, float* state, void* workspace,
                                 int nseg, int accumulate, int B, int H, int N, int Dk, int Dv, int dtype, void* stream) {
+  if (Dk == 128 && Dv == 128 && (dtype == COTT_BF16 || dtype == COTT_F16) && B > 0 && H > 0 && N > 0) {
+    int stw = check_ptrs16({{k, "k"}, {v, "v"}, {workspace, "workspace"}, {state, "state"}});
+    if (stw) return stw;
+    if (!norm_const) return fail(COTT_ERR_NULL, "null pointer: norm_const");
+    DeviceScope scope(state);
+    COTT_CUDA_TRY(scope.status());
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return dtype == COTT_BF16 ? run_wide_prefill_state<__nv_bfloat16>(k, v, norm_const, state, workspace, accumulate, B, H, N, dtype, s)
+                              : run_wide_prefill_state<__half>(k, v, norm_const, state, workspace, accumulate, B, H, N, dtype, s);
+  }
   int st = check_fused_args(B, H, N, Dk, Dv, dtype);
   if (st) return st;
   if ((long)B * H == 0) return COTT_OK;

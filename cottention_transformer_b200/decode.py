@@ -25,10 +25,11 @@ class CosAttnDecodeState:
 
     def prefill(self, q, k, v, norm_const):
         """Absorb a whole prompt at once (fresh state only): the outputs come from the fused causal kernels and the
-        state from the segment-state kernels, instead of T recurrent steps.  bf16 / fp16, head dim 64; anything
+        state from the segment-state kernels, instead of T recurrent steps.  bf16 / fp16, head dim 64 or 128; anything
         else falls back to ``step``.  Returns ``[B, H, T, d_v]``."""
-        from .cos_attention import cos_attn_causal, fused_supported
-        if self.cur_s != 1 or not fused_supported(q, k, v):
+        from .cos_attention import cos_attn_causal, fused_supported, wide_supported
+        wide = wide_supported(q, k, v) and q.shape[-1] == 128
+        if self.cur_s != 1 or not (wide or fused_supported(q, k, v)):
             return self.step(q, k, v, norm_const)
         B, H, T, D = q.shape
         k, v = k.contiguous(), v.contiguous()
@@ -37,8 +38,9 @@ class CosAttnDecodeState:
         L = _lib.lib()
         nc = norm_const.detach().reshape(-1).to(device=q.device, dtype=torch.float32).contiguous()
         with torch.cuda.device(q.device):
-            nseg = L.cott_cos_attn_seg_count(B, H, T)
-            ws = torch.empty(max(L.cott_cos_attn_seg_workspace_bytes(B, H, T, nseg), 16), dtype=torch.uint8, device=q.device)
+            nseg = 1 if wide else L.cott_cos_attn_seg_count(B, H, T)
+            nbytes = L.cott_cos_attn_wide_workspace_bytes(B, H, T) if wide else L.cott_cos_attn_seg_workspace_bytes(B, H, T, nseg)
+            ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
             st = L.cott_cos_attn_prefill_state(_lib.ptr(k), _lib.ptr(v), _lib.ptr(nc), _lib.ptr(self.state), _lib.ptr(ws), nseg,
                                                0, B, H, T, D, D, _lib.DTYPE_CODE[q.dtype], _lib.stream_ptr(q.device))
         _lib.check(st, "cott_cos_attn_prefill_state")

@@ -212,7 +212,9 @@ int cott_cos_attn_wide_bwd(const void* q, const void* k, const void* v, const un
  * kernels instead of N recurrent steps (the reference absorbs a prompt token by token, GPTCosAttention.py:253-272).
  * `accumulate` != 0 adds to `state` instead of overwriting it -- only meaningful for a state that is still at
  * position 0, since the length factor uses positions 1..N.  `workspace`: cott_cos_attn_seg_workspace_bytes(B, H, N,
- * nseg) bytes.  bf16 / fp16 prompts, head dim 64.  The prompt's outputs come from cott_cos_attn_fwd(_seg).
+ * nseg) bytes.  bf16 / fp16 prompts, head dim 64 (the prompt's outputs come from cott_cos_attn_fwd(_seg)) or head dim
+ * 128 (a state-only pass of the 128-wide kernel; `nseg` is ignored, `workspace` is
+ * cott_cos_attn_wide_workspace_bytes(B, H, N) bytes, the outputs come from cott_cos_attn_wide_fwd).
  */
 int cott_cos_attn_prefill_state(const void* k, const void* v, const float* norm_const, float* state,
                                 void* workspace, int nseg, int accumulate, int B, int H, int N, int Dk, int Dv,

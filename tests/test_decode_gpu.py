@@ -81,19 +81,21 @@ def test_decode_rejects_bad_arguments():
 
 
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("d", [64, 128])
 @pytest.mark.parametrize("shape", [(2, 3, 300), (1, 16, 4096)])
-def test_prefill_hands_the_state_to_decode(dt, shape):
-    """A prompt absorbed by ``prefill`` (fused causal kernels + segment-state kernels) followed by single-token
-    steps gives what the recurrent kernel gives for the whole stream (state and outputs)."""
+def test_prefill_hands_the_state_to_decode(dt, shape, d):
+    """A prompt absorbed by ``prefill`` (fused causal kernels + segment-state kernels; head dim 128: the 128-wide
+    kernels and a state-only pass of them) followed by single-token steps gives what the recurrent kernel gives for the
+    whole stream (state and outputs)."""
     from cottention_transformer_b200 import CosAttnDecodeState
     B, H, N = shape
     T = 5
-    q, k, v, _, _ = O.make_inputs(B, H, N + T, 64, 64, seed=N, normalize=False, dtype=dt)
+    q, k, v, _, _ = O.make_inputs(B, H, N + T, d, d, seed=N, normalize=False, dtype=dt)
     q, k, v = q.cuda(), k.cuda(), v.cuda()
     nc = torch.linspace(-0.5, 1.0, H).cuda()
-    ref = CosAttnDecodeState(B, H, 64)
+    ref = CosAttnDecodeState(B, H, d)
     out_ref = ref.step(q, k, v, nc)                      # every token through the recurrent kernel (fp32 state)
-    fast = CosAttnDecodeState(B, H, 64)
+    fast = CosAttnDecodeState(B, H, d)
     out_p = fast.prefill(q[:, :, :N], k[:, :, :N], v[:, :, :N], nc)
     assert fast.cur_s == N + 1
     outs = [fast.step(q[:, :, N + t:N + t + 1], k[:, :, N + t:N + t + 1], v[:, :, N + t:N + t + 1], nc) for t in range(T)]
